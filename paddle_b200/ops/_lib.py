@@ -1,0 +1,116 @@
+"""ctypes loader for the native libraries plus the device-side status word.
+
+The kernels are exported with a C ABI (``pd_*`` symbols).  Python passes raw device pointers, sizes
+and the current CUDA stream.  On a machine with a GPU a missing library is a hard error: the ops in
+this package never fall back silently to another implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_LIB_DIR = os.path.join(_PKG, "lib")
+_lock = threading.Lock()
+_kernels = None
+_runtime = None
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel gave up on a bounded wait (or rejected its arguments) and wrote a status word."""
+
+
+def _load(name: str, builder: str):
+    path = os.path.join(_LIB_DIR, name)
+    if not os.path.exists(path):
+        try:
+            from . import build as _build
+            getattr(_build, builder)()
+        except Exception as e:  # noqa: BLE001
+            raise NativeLibraryError(
+                f"{name} is not built and building it failed: {e}. "
+                f"Run `python -m paddle_b200.ops.build`.") from e
+    try:
+        return ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+    except OSError as e:
+        raise NativeLibraryError(f"cannot load {path}: {e}") from e
+
+
+def kernels() -> ctypes.CDLL:
+    """The CUDA kernel library (``libpd_kernels.so``)."""
+    global _kernels
+    if _kernels is None:
+        with _lock:
+            if _kernels is None:
+                _kernels = _load("libpd_kernels.so", "build_kernels")
+    return _kernels
+
+
+def runtime() -> ctypes.CDLL:
+    """The host runtime library (``libpd_runtime.so``)."""
+    global _runtime
+    if _runtime is None:
+        with _lock:
+            if _runtime is None:
+                _runtime = _load("libpd_runtime.so", "build_runtime")
+    return _runtime
+
+
+def have_gpu() -> bool:
+    return torch.cuda.is_available()
+
+
+# ---------------------------------------------------------------------------------------- helpers
+c_void_p, c_int, c_int64, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
+
+
+def ptr(t) -> ctypes.c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream() -> ctypes.c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_LAUNCH_ERRORS = {
+    -1: "bad shape", -2: "pointer/stride alignment", -3: "TMA tensor-map encoding failed",
+    -4: "CUDA launch error", -5: "size beyond the supported maximum",
+}
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what}: native launcher returned {rc} ({_LAUNCH_ERRORS.get(rc, 'unknown')})")
+
+
+# One 4-int status word per device: {code, block, site, detail}; written by kernels whose bounded
+# waits expire.  Checked by `check_status()` (tests, step boundaries), never on the hot path.
+_status = {}
+
+
+def status_buffer(device=None) -> torch.Tensor:
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = dev.index
+    buf = _status.get(key)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=dev)
+        _status[key] = buf
+    return buf
+
+
+def check_status(device=None, reset: bool = True):
+    buf = status_buffer(device)
+    vals = buf.tolist()  # synchronises
+    if vals[0] != 0:
+        if reset:
+            buf.zero_()
+        names = {1: "mbarrier wait timed out", 2: "flag wait timed out", 3: "bad argument"}
+        raise KernelStatusError(
+            f"kernel status {vals[0]} ({names.get(vals[0], '?')}): block={vals[1]} site={vals[2]} detail={vals[3]}")

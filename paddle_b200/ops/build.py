@@ -1,0 +1,127 @@
+"""In-tree build of the native libraries.
+
+Two artefacts are produced next to this package (both git-ignored, both loaded at import time):
+
+* ``paddle_b200/lib/libpd_kernels.so`` — every CUDA kernel of the framework, compiled by ``nvcc`` for
+  ``sm_100a`` only, exported through a plain C ABI and loaded with ``ctypes``.
+* ``paddle_b200/lib/libpd_runtime.so`` — the host runtime in C++ (flags registry, TCP store, comm
+  watchdog, reshard planner, gradient bucketing), also a C ABI.
+
+``nvcc`` cross-compiles without a GPU, so the build can run on a CPU-only machine.  Sources are
+recompiled only when they (or a header) are newer than their object file.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+
+PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CSRC = os.path.join(PKG_DIR, "csrc")
+LIB_DIR = os.path.join(PKG_DIR, "lib")
+OBJ_DIR = os.path.join(LIB_DIR, "obj")
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+    "--expt-relaxed-constexpr", "-Xptxas", "-v",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wall"]
+
+
+def _nvcc() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found; set NVCC or add it to PATH")
+    return cand
+
+
+def _newest_header(d: str) -> float:
+    t = 0.0
+    for f in os.listdir(d):
+        if f.endswith((".h", ".cuh", ".hpp")):
+            t = max(t, os.path.getmtime(os.path.join(d, f)))
+    return t
+
+
+def _compile_one(cmd, src, obj, log_path):
+    p = subprocess.run(cmd, capture_output=True, text=True)
+    with open(log_path, "w") as f:
+        f.write(" ".join(cmd) + "\n" + p.stdout + p.stderr)
+    if p.returncode != 0:
+        raise RuntimeError(f"compile failed for {src}:\n{p.stdout}\n{p.stderr}")
+    return obj
+
+
+def build_kernels(verbose: bool = False, force: bool = False) -> str:
+    """Compile every ``csrc/kernels/*.cu`` for sm_100a and link ``libpd_kernels.so``."""
+    kdir = os.path.join(CSRC, "kernels")
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    out = os.path.join(LIB_DIR, "libpd_kernels.so")
+    srcs = sorted(f for f in os.listdir(kdir) if f.endswith(".cu"))
+    hdr_t = _newest_header(kdir)
+    nvcc = _nvcc()
+    jobs, objs = [], []
+    for s in srcs:
+        src = os.path.join(kdir, s)
+        obj = os.path.join(OBJ_DIR, s[:-3] + ".o")
+        objs.append(obj)
+        if (not force and os.path.exists(obj)
+                and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_t)):
+            continue
+        cmd = [nvcc, *NVCC_FLAGS, "-I", kdir, "-c", src, "-o", obj]
+        jobs.append((cmd, src, obj, obj + ".log"))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for fut in [ex.submit(_compile_one, *j) for j in jobs]:
+                o = fut.result()
+                if verbose:
+                    print("compiled", os.path.basename(o), file=sys.stderr)
+    if jobs or not os.path.exists(out):
+        cmd = [nvcc, "-shared", "-o", out, *objs, "-lcudart", "-gencode", "arch=compute_100a,code=sm_100a"]
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode != 0:
+            raise RuntimeError("link failed:\n" + p.stdout + p.stderr)
+    return out
+
+
+def build_runtime(verbose: bool = False, force: bool = False) -> str:
+    """Compile ``csrc/runtime/*.cc`` into ``libpd_runtime.so`` (host-only C++)."""
+    rdir = os.path.join(CSRC, "runtime")
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    out = os.path.join(LIB_DIR, "libpd_runtime.so")
+    srcs = sorted(f for f in os.listdir(rdir) if f.endswith(".cc"))
+    if not srcs:
+        return ""
+    hdr_t = _newest_header(rdir)
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    jobs, objs = [], []
+    for s in srcs:
+        src = os.path.join(rdir, s)
+        obj = os.path.join(OBJ_DIR, "rt_" + s[:-3] + ".o")
+        objs.append(obj)
+        if (not force and os.path.exists(obj)
+                and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_t)):
+            continue
+        jobs.append(([cxx, *CXX_FLAGS, "-I", rdir, "-c", src, "-o", obj], src, obj, obj + ".log"))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for fut in [ex.submit(_compile_one, *j) for j in jobs]:
+                fut.result()
+    if jobs or not os.path.exists(out):
+        p = subprocess.run([cxx, "-shared", "-o", out, *objs, "-pthread"], capture_output=True, text=True)
+        if p.returncode != 0:
+            raise RuntimeError("link failed:\n" + p.stdout + p.stderr)
+    return out
+
+
+def build_all(verbose: bool = False, force: bool = False):
+    return build_kernels(verbose, force), build_runtime(verbose, force)
+
+
+if __name__ == "__main__":
+    k, r = build_all(verbose=True, force="--force" in sys.argv)
+    print(k)
+    print(r)
