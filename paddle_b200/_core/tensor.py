@@ -111,6 +111,15 @@ class Tensor(torch.Tensor):
         return torch.Tensor.element_size(self)
 
     # ---- autograd
+    @property
+    def grad(self):
+        g = torch.Tensor.grad.__get__(self)
+        return None if g is None else (g if isinstance(g, Tensor) else g.as_subclass(Tensor))
+
+    @grad.setter
+    def grad(self, v):
+        torch.Tensor.grad.__set__(self, v)
+
     def backward(self, grad_tensor=None, retain_graph=False):
         torch.Tensor.backward(self, gradient=grad_tensor, retain_graph=retain_graph)
 
