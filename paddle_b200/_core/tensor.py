@@ -358,6 +358,12 @@ class Tensor(torch.Tensor):
 
     __str__ = __repr__
 
+    def __float__(self):
+        return float(torch.Tensor.item(self.detach()))
+
+    def __int__(self):
+        return int(torch.Tensor.item(self.detach()))
+
     def __hash__(self):
         return id(self)
 
