@@ -1,0 +1,453 @@
+// Flash-attention backward for sm_100a, head_dim 128, bf16, causal or full, GQA.
+// (Reference: the external FA2 library behind paddle/phi/kernels/gpu/flash_attn_grad_kernel.cu:317.)
+//
+// One CTA owns a 128-row K/V tile of one kv head and walks over the query heads of its group and the
+// 64-row query sub-tiles that can see it.  Every GEMM has M = 128 = the kv rows of the tile, so the
+// per-row softmax threads coincide with TMEM lanes and P^T / dS^T feed the next GEMMs straight from
+// TMEM (no shared-memory round trip):
+//   (1) S^T  = K  Q_t^T          SS   N = 64      (2) dP^T = V dO_t^T          SS   N = 64
+//   softmax warps: P^T = exp2(S^T*c - LSE), dS^T = P^T o (dP^T - Delta) * scale  -> TMEM (bf16) + smem
+//   (3) dV  += P^T  dO_t         TS   N = 128     (4) dK  += dS^T Q_t           TS   N = 128
+//   (5) dQ_t^T = K^T dS_t^T      SS   N = 64  -> drained by 4 extra warps, transposed in shared memory
+//       and added to an fp32 dQ accumulator with a TMA reduce (cp.reduce.async.bulk.tensor .add).
+// dK / dV stay in TMEM for the whole walk and are written once.  TMEM columns:
+//   dK 0-127 | dV 128-255 | S^T 256-319 | dP^T 320-383 | P^T 384-415 | dS^T 416-447 | dQ^T 448-511
+// Warps: 0-3 softmax (+ final dK/dV store), 4-7 dQ drain, 8 TMA producer, 9 MMA issuer.
+#include <math.h>
+
+#include "host_utils.h"
+#include "sm100_prims.cuh"
+
+namespace pd {
+namespace fab {
+
+constexpr int BKV = 128, BQ = 64, D = 128;
+constexpr int KV_TILE = BKV * D * 2;          // 32 KB (two 16 KB boxes)
+constexpr int KV_HALF = KV_TILE / 2;
+constexpr int Q_TILE = BQ * D * 2;            // 16 KB (two 8 KB boxes)
+constexpr int Q_HALF = Q_TILE / 2;
+constexpr int STAGES = 3;
+constexpr int DS_BYTES = BKV * BQ * 2;        // 16 KB
+constexpr int DQ_STAGE_BYTES = BQ * D * 4;    // 32 KB fp32 [64 q][128 d]
+constexpr int NUM_THREADS = 320;
+constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + DS_BYTES + DQ_STAGE_BYTES + 1024 + 256;
+constexpr uint32_t COL_DK = 0, COL_DV = 128, COL_ST = 256, COL_DPT = 320, COL_PT = 384, COL_DST = 416,
+                   COL_DQT = 448;
+
+struct Barriers {
+  uint64_t kv_full;
+  uint64_t qdo_full[STAGES], qdo_empty[STAGES];
+  uint64_t st_full, pds_full, dq_full, dq_empty, dkv_full, drain;
+  uint32_t tmem_base;
+  int abort_flag;
+  int drain_decision;
+};
+
+struct Params {
+  int B, Sq, Sk, Hq, Hkv, causal;
+  float scale, scale_log2;
+  const float* lse;     // [B, Hq, Sq] natural log
+  const float* delta;   // [B, Hq, Sq]
+  int* status;
+};
+
+__device__ __forceinline__ bool warp_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int site) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, site) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) {
+#pragma unroll 1
+    for (int i = 0; i < 1024 && !mbar_try_wait(bar, parity); ++i) {
+    }
+  }
+  return ok != 0;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
+                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                 const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
+                 const __grid_constant__ CUtensorMap tmDV, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + KV_TILE;
+  uint8_t* sQ = sV + KV_TILE;                       // STAGES x [Q tile | dO tile]
+  uint8_t* sDS = sQ + STAGES * 2 * Q_TILE;
+  uint8_t* sDQ = sDS + DS_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(sDQ + DQ_STAGE_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x, kv_head = blockIdx.y, batch = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int kv0 = jb * BKV;
+  const int causal_off = p.Sk - p.Sq;
+  const int n_sub = (p.Sq + BQ - 1) / BQ;
+  int t0 = 0;
+  if (p.causal) {
+    const int first_q = kv0 - causal_off;            // first query row that sees kv row kv0
+    t0 = first_q > 0 ? first_q / BQ : 0;
+  }
+  const int per_head = n_sub > t0 ? n_sub - t0 : 0;
+  const int n_it = per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->kv_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&bars->qdo_full[s], 1);
+      mbar_init(&bars->qdo_empty[s], 1);
+    }
+    mbar_init(&bars->st_full, 1);
+    mbar_init(&bars->pds_full, 128);
+    mbar_init(&bars->dq_full, 1);
+    mbar_init(&bars->dq_empty, 128);
+    mbar_init(&bars->dkv_full, 1);
+    mbar_init(&bars->drain, 1);
+    bars->abort_flag = 0;
+    bars->drain_decision = 0;
+    fence_mbar_init();
+  }
+  if (warp == 9) tmem_alloc(&bars->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 8) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tmQ);
+      prefetch_tmap(&tmDO);
+      mbar_expect_tx(&bars->kv_full, 2 * KV_TILE);
+      tma_load_4d(sK, &tmK, &bars->kv_full, 0, kv_head, kv0, batch);
+      tma_load_4d(sK + KV_HALF, &tmK, &bars->kv_full, 64, kv_head, kv0, batch);
+      tma_load_4d(sV, &tmV, &bars->kv_full, 0, kv_head, kv0, batch);
+      tma_load_4d(sV + KV_HALF, &tmV, &bars->kv_full, 64, kv_head, kv0, batch);
+      bool ok = true;
+      int issued = 0;
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait(&bars->qdo_empty[s], ph ^ 1, abort_flag, p.status, 100 + s)) { ok = false; break; }
+        const int qh = kv_head * group + it / per_head;
+        const int q0 = (t0 + it % per_head) * BQ;
+        uint8_t* dst = sQ + s * 2 * Q_TILE;
+        mbar_expect_tx(&bars->qdo_full[s], 2 * Q_TILE);
+        tma_load_4d(dst, &tmQ, &bars->qdo_full[s], 0, qh, q0, batch);
+        tma_load_4d(dst + Q_HALF, &tmQ, &bars->qdo_full[s], 64, qh, q0, batch);
+        tma_load_4d(dst + Q_TILE, &tmDO, &bars->qdo_full[s], 0, qh, q0, batch);
+        tma_load_4d(dst + Q_TILE + Q_HALF, &tmDO, &bars->qdo_full[s], 64, qh, q0, batch);
+        issued = it + 1;
+      }
+      if (!ok || *abort_flag || n_it == 0) {
+        mbar_drain(&bars->kv_full, 0);
+        for (int it = max(0, issued - STAGES); it < issued; ++it)
+          mbar_drain(&bars->qdo_full[it % STAGES], (it / STAGES) & 1);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 9) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_s = make_idesc(BKV, BQ, false, false);   // (1),(2)
+      constexpr uint32_t idesc_kv = make_idesc(BKV, D, false, true);    // (3),(4)  A from TMEM
+      constexpr uint32_t idesc_dq = make_idesc(D, BQ, true, true);      // (5)
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), ds_addr = smem_u32(sDS);
+      bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, p.status, 200);
+      auto issue_s = [&](int it) -> bool {
+        const int s = it % STAGES;
+        if (!mbar_wait(&bars->qdo_full[s], (it / STAGES) & 1, abort_flag, p.status, 210 + s)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + s * 2 * Q_TILE), do_addr = q_addr + Q_TILE;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t offa = (ks >> 2) * KV_HALF + (ks & 3) * 32;
+          const uint32_t offb = (ks >> 2) * Q_HALF + (ks & 3) * 32;
+          umma_bf16_ss(tmem + COL_ST, make_smem_desc_sw128(k_addr + offa, 16, 1024),
+                       make_smem_desc_sw128(q_addr + offb, 16, 1024), idesc_s, ks != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t offa = (ks >> 2) * KV_HALF + (ks & 3) * 32;
+          const uint32_t offb = (ks >> 2) * Q_HALF + (ks & 3) * 32;
+          umma_bf16_ss(tmem + COL_DPT, make_smem_desc_sw128(v_addr + offa, 16, 1024),
+                       make_smem_desc_sw128(do_addr + offb, 16, 1024), idesc_s, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(&bars->st_full);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it % STAGES;
+        const uint32_t q_addr = smem_u32(sQ + s * 2 * Q_TILE), do_addr = q_addr + Q_TILE;
+        if (!mbar_wait(&bars->pds_full, it & 1, abort_flag, p.status, 220)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks)   // (3) dV += P^T dO
+          umma_bf16_ts(tmem + COL_DV, tmem + COL_PT + ks * 8,
+                       make_smem_desc_sw128(do_addr + ks * 2048, Q_HALF, 1024), idesc_kv, (it | ks) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks)   // (4) dK += dS^T Q
+          umma_bf16_ts(tmem + COL_DK, tmem + COL_DST + ks * 8,
+                       make_smem_desc_sw128(q_addr + ks * 2048, Q_HALF, 1024), idesc_kv, (it | ks) != 0 ? 1u : 0u);
+        if (!mbar_wait(&bars->dq_empty, (it & 1) ^ 1, abort_flag, p.status, 230)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < BKV / 16; ++ks)  // (5) dQ^T = K^T dS^T
+          umma_bf16_ss(tmem + COL_DQT, make_smem_desc_sw128(k_addr + ks * 2048, KV_HALF, 1024),
+                       make_smem_desc_sw128(ds_addr + ks * 2048, 16, 1024), idesc_dq, ks != 0 ? 1u : 0u);
+        umma_commit(&bars->dq_full);
+        umma_commit(&bars->qdo_empty[s]);
+        if (it + 1 < n_it) {
+          if (!issue_s(it + 1)) { ok = false; break; }
+        }
+      }
+      if (ok) umma_commit(&bars->dkv_full);
+      else {
+        umma_commit(&bars->drain);
+        mbar_drain(&bars->drain, 0);
+      }
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // ---------------------------------------------------------------- softmax warps: thread = kv row
+    const int row = threadIdx.x;
+    const int kvi = kv0 + row;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int sw = row & 7;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int qh = kv_head * group + it / per_head;
+      const int q0 = (t0 + it % per_head) * BQ;
+      // per-column statistics: lane l keeps columns l and l + 32
+      const float* lse_row = p.lse + (static_cast<size_t>(batch) * p.Hq + qh) * p.Sq;
+      const float* dl_row = p.delta + (static_cast<size_t>(batch) * p.Hq + qh) * p.Sq;
+      float lse2[2], dlt[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int qi = q0 + h * 32 + lane;
+        const bool in = qi < p.Sq;
+        lse2[h] = in ? lse_row[qi] * 1.4426950408889634f : INFINITY;   // +inf -> p = 0 for padded rows
+        dlt[h] = in ? dl_row[qi] : 0.f;
+      }
+      if (!warp_mbar_wait(&bars->st_full, it & 1, abort_flag, p.status, 300)) { ok = false; break; }
+      tc_fence_after();
+      // visible iff kv <= q + off  <=>  q_local >= kvi - off - q0
+      const int first_visible = p.causal ? (kvi - causal_off - q0) : 0;
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        uint32_t s_r[32], dp_r[32];
+        tmem_ld_32x32(tmem + lane_base + COL_ST + h * 32, s_r);
+        tmem_ld_32x32(tmem + lane_base + COL_DPT + h * 32, dp_r);
+        tmem_ld_wait();
+        uint32_t pk_p[16], pk_ds[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float l2 = __shfl_sync(0xffffffffu, lse2[h], c + e);
+            const float dl = __shfl_sync(0xffffffffu, dlt[h], c + e);
+            float pe = fast_exp2(fmaf(__uint_as_float(s_r[c + e]), p.scale_log2, -l2));
+            if (h * 32 + c + e < first_visible) pe = 0.f;
+            pv[e] = pe;
+            dsv[e] = pe * (__uint_as_float(dp_r[c + e]) - dl) * p.scale;
+          }
+          pk_p[c >> 1] = pack_bf16x2(pv[0], pv[1]);
+          pk_ds[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+        }
+        tmem_st_32x16(tmem + lane_base + COL_PT + h * 16, pk_p);
+        tmem_st_32x16(tmem + lane_base + COL_DST + h * 16, pk_ds);
+        uint8_t* row_ptr = sDS + row * 128;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          *reinterpret_cast<uint4*>(row_ptr + (((h * 4 + jj) ^ sw) << 4)) =
+              make_uint4(pk_ds[4 * jj], pk_ds[4 * jj + 1], pk_ds[4 * jj + 2], pk_ds[4 * jj + 3]);
+      }
+      tmem_st_wait();
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&bars->pds_full);
+    }
+    // ---- final: dK, dV (fp32 in TMEM) -> bf16 -> swizzled staging (Q/dO ring is idle now) -> TMA store
+    if (ok && n_it > 0) ok = warp_mbar_wait(&bars->dkv_full, 0, abort_flag, p.status, 310);
+    named_bar_sync(1, 128);
+    if (ok) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        uint8_t* stage = sQ + which * KV_TILE;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          if (n_it > 0) {
+            tmem_ld_32x32(tmem + lane_base + (which == 0 ? COL_DK : COL_DV) + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          uint8_t* row_ptr = stage + (c >> 1) * KV_HALF + row * 128;
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * jj + 0]), __uint_as_float(r[8 * jj + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * jj + 2]), __uint_as_float(r[8 * jj + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * jj + 4]), __uint_as_float(r[8 * jj + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * jj + 6]), __uint_as_float(r[8 * jj + 7]));
+            *reinterpret_cast<uint4*>(row_ptr + ((((c & 1) * 4 + jj) ^ sw) << 4)) = v;
+          }
+        }
+      }
+      fence_proxy_async_smem();
+    }
+    named_bar_sync(1, 128);
+    if (ok && threadIdx.x == 0) {
+      tma_store_4d(&tmDK, sQ, 0, kv_head, kv0, batch);
+      tma_store_4d(&tmDK, sQ + KV_HALF, 64, kv_head, kv0, batch);
+      tma_store_4d(&tmDV, sQ + KV_TILE, 0, kv_head, kv0, batch);
+      tma_store_4d(&tmDV, sQ + KV_TILE + KV_HALF, 64, kv_head, kv0, batch);
+      tma_commit_group();
+      tma_wait_group<0>();
+    }
+  } else {
+    // ---------------------------------------------------------------- dQ drain warps (4..7): thread = d
+    const int dr = threadIdx.x - 128;                 // 0..127 = head-dim index = TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float* stage = reinterpret_cast<float*>(sDQ);
+    for (int it = 0; it < n_it; ++it) {
+      if (dr == 0) {
+        const bool ok = mbar_wait(&bars->dq_full, it & 1, abort_flag, p.status, 400);
+        if (ok) tma_wait_group_read<0>();             // previous reduce has read the staging tile
+        bars->drain_decision = ok ? 1 : 0;
+      }
+      named_bar_sync(2, 128);
+      if (bars->drain_decision == 0) break;
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(tmem + lane_base + COL_DQT, r0);
+      tmem_ld_32x32(tmem + lane_base + COL_DQT + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->dq_empty);
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        stage[c * D + dr] = __uint_as_float(r0[c]);
+        stage[(c + 32) * D + dr] = __uint_as_float(r1[c]);
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(2, 128);
+      if (dr == 0) {
+        const int qh = kv_head * group + it / per_head;
+        const int q0 = (t0 + it % per_head) * BQ;
+        tma_reduce_add_4d(&tmDQ, sDQ, 0, qh, q0, batch);
+        tma_commit_group();
+      }
+    }
+    if (dr == 0) tma_wait_group<0>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) tmem_dealloc(tmem, 512);
+}
+
+// delta[b, h, s] = sum_d dO * O     (one warp per row)
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                             float* __restrict__ delta, int B, int S, int H, int64_t o_tok, int64_t o_batch,
+                             int64_t do_tok, int64_t do_batch) {
+  const int64_t w = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t total = static_cast<int64_t>(B) * S * H;
+  if (w >= total) return;
+  const int h = static_cast<int>(w % H);
+  const int64_t bs = w / H;
+  const int s = static_cast<int>(bs % S), b = static_cast<int>(bs / S);
+  const uint2 a = *reinterpret_cast<const uint2*>(o + b * o_batch + s * o_tok + h * D + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(d_o + b * do_batch + s * do_tok + h * D + lane * 4);
+  const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+  const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+  const float2 g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.x));
+  const float2 g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.y));
+  float acc = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[(static_cast<size_t>(b) * H + h) * S + s] = acc;
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n) {
+  const int64_t nvec = n >> 2;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(src)[i];
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    reinterpret_cast<uint2*>(dst)[i] = o;
+  }
+}
+
+static bool make_map_bf16(CUtensorMap* m, const void* ptr, int B, int S, int H, int64_t tok, int64_t batch,
+                          uint32_t rows) {
+  uint64_t dims[4] = {D, static_cast<uint64_t>(H), static_cast<uint64_t>(S), static_cast<uint64_t>(B)};
+  uint64_t strides[3] = {D * 2, static_cast<uint64_t>(tok) * 2, static_cast<uint64_t>(batch) * 2};
+  uint32_t box[4] = {64, 1, rows, 1};
+  return encode_tmap(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace fab
+}  // namespace pd
+
+// dq_acc: zero-initialised fp32 [B, Sq, Hq, 128] (contiguous); delta: fp32 [B, Hq, Sq] scratch;
+// dq/dk/dv: contiguous bf16 outputs.  `unused` keeps the argument list stable.
+PD_EXPORT int pd_flash_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
+                                const float* lse, float* delta, float* dq_acc, void* unused, void* dq, void* dk,
+                                void* dv, int B, int Sq, int Sk, int Hq, int Hkv, int64_t q_tok, int64_t q_batch,
+                                int64_t k_tok, int64_t k_batch, int64_t v_tok, int64_t v_batch, int64_t o_tok,
+                                int64_t o_batch, int64_t do_tok, int64_t do_batch, float scale, int causal,
+                                int* status, cudaStream_t stream) {
+  using namespace pd;
+  using namespace pd::fab;
+  (void)unused;
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return kErrBadShape;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(d_o)) return kErrAlignment;
+  if ((q_tok % 8) || (k_tok % 8) || (v_tok % 8) || (o_tok % 8) || (do_tok % 8)) return kErrAlignment;
+  CUtensorMap tmQ, tmDO, tmK, tmV, tmDQ, tmDK, tmDV;
+  bool ok = make_map_bf16(&tmQ, q, B, Sq, Hq, q_tok, q_batch, BQ) &&
+            make_map_bf16(&tmDO, d_o, B, Sq, Hq, do_tok, do_batch, BQ) &&
+            make_map_bf16(&tmK, k, B, Sk, Hkv, k_tok, k_batch, BKV) &&
+            make_map_bf16(&tmV, v, B, Sk, Hkv, v_tok, v_batch, BKV) &&
+            make_map_bf16(&tmDK, dk, B, Sk, Hkv, int64_t(Hkv) * D, int64_t(Sk) * Hkv * D, BKV) &&
+            make_map_bf16(&tmDV, dv, B, Sk, Hkv, int64_t(Hkv) * D, int64_t(Sk) * Hkv * D, BKV);
+  {
+    uint64_t dims[4] = {D, static_cast<uint64_t>(Hq), static_cast<uint64_t>(Sq), static_cast<uint64_t>(B)};
+    uint64_t strides[3] = {D * 4, static_cast<uint64_t>(Hq) * D * 4, static_cast<uint64_t>(Sq) * Hq * D * 4};
+    uint32_t box[4] = {D, 1, BQ, 1};
+    ok = ok && encode_tmap(&tmDQ, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dq_acc, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_NONE);
+  }
+  if (!ok) return kErrTensorMap;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return kErrCuda;
+    configured = true;
+  }
+  const int64_t rows = static_cast<int64_t>(B) * Sq * Hq;
+  delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
+      (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, Sq, Hq, o_tok, o_batch, do_tok, do_batch);
+  Params p{B, Sq, Sk, Hq, Hkv, causal, scale, scale * 1.4426950408889634f, lse, delta, status};
+  dim3 grid((Sk + BKV - 1) / BKV, Hkv, B);
+  flash_bwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmQ, tmDO, tmK, tmV, tmDQ, tmDK, tmDV, p);
+  const int64_t n = rows * D;
+  int64_t blocks = ((n >> 2) + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  f32_to_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
+  return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
+}

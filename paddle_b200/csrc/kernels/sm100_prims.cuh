@@ -194,6 +194,14 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, const
       "r"(smem_u32(smem_src)), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* tmap, const void* smem_src,
+                                                  int x, int y, int z, int w) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::
+          "l"(reinterpret_cast<uint64_t>(tmap)),
+      "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 __device__ __forceinline__ void tma_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
