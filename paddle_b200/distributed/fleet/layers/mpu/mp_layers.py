@@ -1,0 +1,124 @@
+"""Tensor-parallel layers (python/paddle/distributed/fleet/layers/mpu/mp_layers.py):
+``VocabParallelEmbedding`` (:49), ``ColumnParallelLinear`` (:336, weight ``[in, out/n]``),
+``RowParallelLinear`` (:543, weight ``[in/n, out]``, bias added after the reduce), ``ParallelCrossEntropy``
+(:744).  Parameters carry ``is_distributed`` and ``split_axis`` so checkpoints and mp sync can tell shards
+from replicated tensors (mp_layers.py:157-159,435-450,673-675)."""
+from __future__ import annotations
+
+import torch
+
+from ....._core.tensor import as_tensor
+from .....nn import functional as F
+from .....nn.initializer import Constant
+from .....nn.layer.layers import Layer
+from .... import collective as C
+from . import mp_ops
+from .random import get_rng_state_tracker
+
+
+def _hcg():
+    from ... import fleet
+    return fleet.get_hybrid_communicate_group()
+
+
+def _mark(param, axis):
+    param.is_distributed = True
+    param.split_axis = axis
+
+
+class VocabParallelEmbedding(Layer):
+    def __init__(self, num_embeddings, embedding_dim, weight_attr=None, mp_group=None, name=None):
+        super().__init__()
+        hcg = _hcg()
+        self.model_parallel_group = mp_group or hcg.get_model_parallel_group()
+        self.world_size = self.model_parallel_group.nranks if self.model_parallel_group else 1
+        self.rank = self.model_parallel_group.rank if self.model_parallel_group else 0
+        assert num_embeddings % self.world_size == 0, "vocabulary must divide evenly over the mp group"
+        self.origin_num_embeddings = num_embeddings
+        per = num_embeddings // self.world_size
+        self.vocab_start_index = self.rank * per
+        self.is_mp = self.world_size > 1
+        if self.is_mp:
+            with get_rng_state_tracker().rng_state():
+                self.weight = self.create_parameter([per, embedding_dim], weight_attr)
+            _mark(self.weight, 0)
+        else:
+            self.weight = self.create_parameter([per, embedding_dim], weight_attr)
+
+    def forward(self, x):
+        if not self.is_mp:
+            return F.embedding(x, self.weight)
+        out = mp_ops._c_lookup_table(self.weight, x, start_index=self.vocab_start_index,
+                                     vocab_size=self.origin_num_embeddings)
+        return mp_ops._mp_allreduce(out, group=self.model_parallel_group)
+
+
+class ColumnParallelLinear(Layer):
+    def __init__(self, in_features, out_features, weight_attr=None, has_bias=None, gather_output=True,
+                 fuse_matmul_bias=False, mp_group=None, name=None):
+        super().__init__()
+        hcg = _hcg()
+        self.model_parallel_group = mp_group or hcg.get_model_parallel_group()
+        self.world_size = self.model_parallel_group.nranks if self.model_parallel_group else 1
+        self.is_mp = self.world_size > 1
+        self.gather_output = gather_output
+        assert out_features % self.world_size == 0
+        self.output_size_per_partition = out_features // self.world_size
+        if self.is_mp:
+            with get_rng_state_tracker().rng_state():
+                self.weight = self.create_parameter([in_features, self.output_size_per_partition], weight_attr)
+            _mark(self.weight, 1)
+        else:
+            self.weight = self.create_parameter([in_features, self.output_size_per_partition], weight_attr)
+        if has_bias:
+            self.bias = self.create_parameter([self.output_size_per_partition], None, is_bias=True)
+            if self.is_mp:
+                _mark(self.bias, 0)
+        else:
+            self.bias = None
+
+    def forward(self, x):
+        x_par = mp_ops._c_identity(x, group=self.model_parallel_group) if self.is_mp else x
+        out = F.linear(x_par, self.weight, self.bias)
+        if self.gather_output and self.is_mp:
+            out = mp_ops._c_concat(out, group=self.model_parallel_group)
+        return out
+
+
+class RowParallelLinear(Layer):
+    def __init__(self, in_features, out_features, weight_attr=None, has_bias=True, input_is_parallel=False,
+                 fuse_matmul_bias=False, mp_group=None, name=None):
+        super().__init__()
+        hcg = _hcg()
+        self.model_parallel_group = mp_group or hcg.get_model_parallel_group()
+        self.world_size = self.model_parallel_group.nranks if self.model_parallel_group else 1
+        self.is_mp = self.world_size > 1
+        self.input_is_parallel = input_is_parallel
+        assert in_features % self.world_size == 0
+        self.input_size_per_partition = in_features // self.world_size
+        if self.is_mp:
+            with get_rng_state_tracker().rng_state():
+                self.weight = self.create_parameter([self.input_size_per_partition, out_features], weight_attr)
+            _mark(self.weight, 0)
+        else:
+            self.weight = self.create_parameter([self.input_size_per_partition, out_features], weight_attr)
+        self.bias = self.create_parameter([out_features], None, is_bias=True) if has_bias else None
+
+    def forward(self, x):
+        if not self.input_is_parallel and self.is_mp:
+            x = mp_ops._c_split(x, group=self.model_parallel_group)
+        out = F.linear(x, self.weight)
+        if self.is_mp:
+            out = mp_ops._mp_allreduce(out, group=self.model_parallel_group)
+        return out + self.bias if self.bias is not None else out
+
+
+class ParallelCrossEntropy(Layer):
+    def __init__(self, mp_group=None, name=None, ignore_index=-100):
+        super().__init__()
+        self.model_parallel_group = mp_group or _hcg().get_model_parallel_group()
+        self.ignore_index = ignore_index
+
+    def forward(self, input, label):
+        return mp_ops._c_softmax_with_cross_entropy(input, label, group=self.model_parallel_group,
+                                                    ignore_index=self.ignore_index)

@@ -1,0 +1,188 @@
+"""Tensor-parallel glue operators (python/paddle/distributed/fleet/layers/mpu/mp_ops.py):
+``_c_identity`` (identity fwd / all-reduce bwd, :41), ``_c_split`` (:57), ``_c_concat`` (all-gather on the
+last axis), ``_mp_allreduce`` (all-reduce fwd / identity bwd, :226), ``_c_lookup_table`` (:310),
+``_c_softmax_with_cross_entropy`` (:385), ``split`` (:773)."""
+from __future__ import annotations
+
+import torch
+
+from ....._core.tensor import as_tensor
+from .... import collective as C
+
+
+def _mp_group(group):
+    if group is not None:
+        return group
+    from ... import fleet
+    return fleet.get_hybrid_communicate_group().get_model_parallel_group()
+
+
+class _CIdentity(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy):
+        dy = dy.contiguous()
+        C.all_reduce(dy, group=ctx.group)
+        return dy, None
+
+
+class _MpAllReduce(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        out = x.contiguous().clone()
+        C.all_reduce(out, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        return dy, None
+
+
+class _CSplit(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n, r = group.nranks, group.rank
+        return x.chunk(n, -1)[r].contiguous()
+
+    @staticmethod
+    def backward(ctx, dy):
+        g = ctx.group
+        outs = []
+        C.all_gather(outs, dy.contiguous(), g)
+        return torch.cat(outs, -1), None
+
+
+class _CConcat(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        outs = []
+        C.all_gather(outs, x.contiguous(), group)
+        return torch.cat(outs, -1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        g = ctx.group
+        return dy.chunk(g.nranks, -1)[g.rank].contiguous(), None
+
+
+def _c_identity(tensor, group=None, skip_c_identity_dynamic=False):
+    g = _mp_group(group)
+    if g is None or g.nranks == 1 or skip_c_identity_dynamic:
+        return tensor
+    return as_tensor(_CIdentity.apply(tensor, g))
+
+
+def _mp_allreduce(tensor, op=C.ReduceOp.SUM, group=None, use_calc_stream=True, use_model_parallel=True,
+                  skip_c_identity_dynamic=False):
+    g = _mp_group(group)
+    if g is None or g.nranks == 1:
+        return tensor
+    return as_tensor(_MpAllReduce.apply(tensor, g))
+
+
+def _c_split(tensor, group=None):
+    g = _mp_group(group)
+    if g is None or g.nranks == 1:
+        return tensor
+    return as_tensor(_CSplit.apply(tensor, g))
+
+
+def _c_concat(tensor, group=None):
+    g = _mp_group(group)
+    if g is None or g.nranks == 1:
+        return tensor
+    return as_tensor(_CConcat.apply(tensor, g))
+
+
+def _c_lookup_table(table, index, start_index=0, vocab_size=-1, name=None):
+    """Rows outside ``[start_index, start_index + rows)`` give zeros (c_embedding,
+    paddle/phi/kernels/gpu/c_embedding_kernel.cu:31)."""
+    from .....ops import functional as K
+    return K.embedding(index, table, None, vocab_start=start_index)
+
+
+class _ParallelCE(torch.autograd.Function):
+    """Vocab-parallel softmax cross entropy.  Each rank computes (max, sum-exp, target logit) of its
+    logits shard in one kernel pass; the three per-token fp32 vectors are combined across the group with
+    one packed all-reduce pair (MAX then SUM) instead of the reference's three
+    (c_softmax_with_cross_entropy_kernel.cu:229,309,322); backward writes (softmax - onehot) * dloss."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, group, ignore_index):
+        from .....ops import native
+        V = logits.shape[-1]
+        l2 = logits.reshape(-1, V)
+        if not l2.is_contiguous():
+            l2 = l2.contiguous()
+        lab = labels.reshape(-1)
+        vstart = group.rank * V
+        use_native = l2.is_cuda and l2.dtype in (torch.bfloat16, torch.float32) and V % 8 == 0
+        if use_native:
+            mx, sm, tg, _ = native.ce_stats(l2, lab, vstart, ignore_index, want_loss=False)
+        else:
+            lf = l2.float()
+            mx = lf.max(-1).values
+            sm = torch.exp(lf - mx[:, None]).sum(-1)
+            local = lab - vstart
+            ok = (local >= 0) & (local < V) & (lab != ignore_index)
+            tg = torch.where(ok, lf.gather(1, local.clamp(0, V - 1)[:, None]).squeeze(1), torch.zeros_like(mx))
+        gmx = mx.clone()
+        C.all_reduce(gmx, C.ReduceOp.MAX, group)
+        packed = torch.stack([sm * torch.exp(mx - gmx), tg])
+        C.all_reduce(packed, C.ReduceOp.SUM, group)
+        lse = gmx + packed[0].log()
+        loss = torch.where(lab == ignore_index, torch.zeros_like(lse), lse - packed[1])
+        ctx.save_for_backward(l2, lab, lse)
+        ctx.vstart, ctx.ignore_index, ctx.use_native, ctx.shape = vstart, ignore_index, use_native, logits.shape
+        return loss.view(labels.shape)
+
+    @staticmethod
+    def backward(ctx, dloss):
+        from .....ops import native
+        l2, lab, lse = ctx.saved_tensors
+        dl = dloss.reshape(-1).contiguous().float()
+        if ctx.use_native:
+            d = native.ce_bwd(l2, lab, lse, dl, ctx.vstart, ctx.ignore_index)
+        else:
+            V = l2.shape[-1]
+            p = torch.exp(l2.float() - lse[:, None])
+            local = lab - ctx.vstart
+            ok = (local >= 0) & (local < V)
+            onehot = torch.zeros_like(p)
+            onehot[ok, local[ok]] = 1.0
+            d = ((p - onehot) * torch.where(lab == ctx.ignore_index, torch.zeros_like(dl), dl)[:, None]).to(l2.dtype)
+        return d.view(ctx.shape), None, None, None
+
+
+def _c_softmax_with_cross_entropy(logits, label, group=None, return_softmax=False, ignore_index=-100):
+    g = _mp_group(group)
+    lab = label.squeeze(-1) if label.dim() == logits.dim() else label
+    if g is None or g.nranks == 1:
+        from .....ops import functional as K
+        loss = K.softmax_cross_entropy(logits, lab, ignore_index)
+    else:
+        loss = as_tensor(_ParallelCE.apply(logits, lab, g, ignore_index))
+    loss = loss.unsqueeze(-1) if label.dim() == logits.dim() else loss
+    if return_softmax:
+        raise NotImplementedError("return_softmax is not supported for the vocab-parallel loss")
+    return loss
+
+
+def split(x, size, operation, axis=0, num_partitions=1, gather_out=True, weight_attr=None, bias_attr=None, name=None):
+    """Build a parallel linear / embedding on the fly (mp_ops.py:773)."""
+    from .mp_layers import ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedding
+    if operation == "embedding":
+        return VocabParallelEmbedding(size[0], size[1], weight_attr=weight_attr)(x)
+    if operation == "linear":
+        if axis == 0:
+            return RowParallelLinear(size[0], size[1], weight_attr=weight_attr, has_bias=bias_attr is not False,
+                                     input_is_parallel=False)(x)
+        return ColumnParallelLinear(size[0], size[1], weight_attr=weight_attr, has_bias=bias_attr is not False,
+                                    gather_output=gather_out)(x)
+    raise ValueError(f"unknown operation {operation}")

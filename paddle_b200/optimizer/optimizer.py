@@ -134,7 +134,7 @@ class Optimizer:
         grad_scale = self._aux_grad_scale
         clip = self._grad_clip
         if clip is not None:
-            if isinstance(clip, ClipGradByGlobalNorm) and pgs[0][1].is_cuda:
+            if isinstance(clip, ClipGradByGlobalNorm):
                 # fold the clip coefficient into the update kernel: no extra pass over the gradients
                 sel = [g for p, g, _ in pgs if getattr(p, "need_clip", True)]
                 coef = clip.clip_coef(self._global_norm_sq(clip, [(p, g) for p, g, _ in pgs])) if sel else None

@@ -1,0 +1,53 @@
+"""Spawn N rank processes on this host (the reference's substitute for a cluster:
+test/legacy_test/test_parallel_dygraph_dataparallel.py:100 ``start_local_trainers``), wait with a
+timeout, and collect what each rank pickled."""
+import os
+import pickle
+import socket
+import subprocess
+import sys
+import tempfile
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def run_workers(script, nranks, backend="gloo", extra_env=None, timeout=240, args=(), gpus=False):
+    port = free_port()
+    eps = ",".join(f"127.0.0.1:{port + i}" for i in range(nranks))
+    out = os.path.join(tempfile.mkdtemp(prefix="pdtest_"), "out")
+    procs = []
+    for r in range(nranks):
+        env = dict(os.environ)
+        env.update({"PADDLE_TRAINER_ID": str(r), "PADDLE_TRAINERS_NUM": str(nranks), "PADDLE_TRAINER_ENDPOINTS": eps,
+                    "PADDLE_CURRENT_ENDPOINT": f"127.0.0.1:{port + r}", "PADDLE_MASTER": f"127.0.0.1:{port}",
+                    "PADDLE_DISTRI_BACKEND": backend, "PD_TEST_OUT": out, "PYTHONPATH": ROOT,
+                    "FLAGS_selected_gpus": str(r if gpus else 0), "OMP_NUM_THREADS": "2"})
+        if not gpus:
+            env["CUDA_VISIBLE_DEVICES"] = ""
+        env.pop("RANK", None), env.pop("WORLD_SIZE", None)
+        env.update(extra_env or {})
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "dist_workers", script), *args],
+                                      env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    logs, rcs = [], []
+    for p in procs:
+        try:
+            o, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            o, _ = p.communicate()
+            o += "\n[timeout]"
+        logs.append(o)
+        rcs.append(p.returncode)
+    if any(rc != 0 for rc in rcs):
+        raise AssertionError("worker failed:\n" + "\n-----\n".join(l[-3000:] for l in logs))
+    res = []
+    for r in range(nranks):
+        with open(f"{out}.{r}", "rb") as f:
+            res.append(pickle.load(f))
+    return res

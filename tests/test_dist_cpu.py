@@ -1,0 +1,42 @@
+"""Multi-process CPU (gloo) tests: collective API vs NumPy expectations; DP / sharding parity with a
+single-rank twin (the pattern of test/collective/fleet/hybrid_parallel_sharding_model.py)."""
+import numpy as np
+import pytest
+
+from dist_utils import run_workers
+
+
+def test_collective_api_gloo():
+    res = run_workers("collective_api.py", 2)
+    x = [np.arange(8, dtype=np.float32) + 10 * r for r in range(2)]
+    for r in range(2):
+        o = res[r]
+        assert np.allclose(o["all_reduce_sum"], x[0] + x[1])
+        assert np.allclose(o["all_reduce_max"], np.maximum(x[0], x[1]))
+        assert np.allclose(o["all_reduce_avg"], (x[0] + x[1]) / 2)
+        assert np.allclose(o["broadcast"], x[1])
+        assert np.allclose(o["all_gather"], np.stack(x))
+        assert np.allclose(o["all_gather_into"], np.concatenate(x))
+        assert np.allclose(o["reduce_scatter"], (x[0] + x[1])[r * 4:(r + 1) * 4])
+        assert np.allclose(o["alltoall"], np.stack([np.full(3, j * 10 + r, np.float32) for j in range(2)]))
+        assert np.allclose(o["alltoall_single"], np.concatenate([x[j][r * 4:(r + 1) * 4] for j in range(2)]))
+        assert np.allclose(o["scatter"], np.full(4, r + 1))
+        assert o["async_ok"] and o["objects"] == [{"rank": 0}, {"rank": 1}]
+        assert np.allclose(o["group_all_reduce"], x[0] + x[1])
+        assert np.allclose(o["batch_p2p"], x[(r - 1) % 2])
+    assert np.allclose(res[0]["reduce"], x[0] + x[1])
+    assert np.allclose(res[1]["recv"], x[0])
+
+
+@pytest.mark.parametrize("mode", ["dp", "sharding", "sharding_v2"])
+def test_gpt_parity_with_single_rank(mode):
+    single = run_workers("gpt_dp_sharding.py", 1, args=("single", "2"))[0]
+    par = run_workers("gpt_dp_sharding.py", 2, args=(mode, "2"))
+    assert par[0]["reload_ok"]
+    mean_loss = np.mean([par[0]["losses"], par[1]["losses"]], axis=0)
+    assert np.allclose(mean_loss, single["losses"], rtol=2e-4, atol=2e-4), (mean_loss, single["losses"])
+    assert all(np.isfinite(single["losses"]))
+    for k, v in single["params"].items():
+        for r in range(2):
+            assert np.allclose(par[r]["params"][k], v, rtol=2e-3, atol=2e-4), k
+    assert par[0]["names"] == single["names"]
