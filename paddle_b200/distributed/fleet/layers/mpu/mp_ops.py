@@ -104,7 +104,7 @@ def _c_lookup_table(table, index, start_index=0, vocab_size=-1, name=None):
     """Rows outside ``[start_index, start_index + rows)`` give zeros (c_embedding,
     paddle/phi/kernels/gpu/c_embedding_kernel.cu:31)."""
     from .....ops import functional as K
-    return K.embedding(index, table, None, vocab_start=start_index)
+    return K.embedding(index, table, None, vocab_start=start_index, sharded=True)
 
 
 class _ParallelCE(torch.autograd.Function):
@@ -127,7 +127,7 @@ class _ParallelCE(torch.autograd.Function):
             mx, sm, tg, _ = native.ce_stats(l2, lab, vstart, ignore_index, want_loss=False)
         else:
             lf = l2.float()
-            mx = lf.max(-1).values
+            mx = torch.amax(lf, -1)
             sm = torch.exp(lf - mx[:, None]).sum(-1)
             local = lab - vstart
             ok = (local >= 0) & (local < V) & (lab != ignore_index)

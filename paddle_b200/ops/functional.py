@@ -329,10 +329,10 @@ class _EmbeddingFn(torch.autograd.Function):
         return None, dt.to(table.dtype), None, None
 
 
-def embedding(ids, table, padding_idx=None, vocab_start=0):
+def embedding(ids, table, padding_idx=None, vocab_start=0, sharded=False):
     if _native(table) and table.shape[1] % 8 == 0:
         return as_tensor(_EmbeddingFn.apply(ids, table, vocab_start, -1 if padding_idx is None else padding_idx))
-    if vocab_start == 0:
+    if vocab_start == 0 and not sharded:
         return torch.nn.functional.embedding(ids, table, padding_idx=padding_idx)
     local = ids - vocab_start
     ok = (local >= 0) & (local < table.shape[0])

@@ -40,3 +40,10 @@ def test_gpt_parity_with_single_rank(mode):
         for r in range(2):
             assert np.allclose(par[r]["params"][k], v, rtol=2e-3, atol=2e-4), k
     assert par[0]["names"] == single["names"]
+
+
+def test_llama_tp_sp_parity_cpu():
+    res = run_workers("llama_tp.py", 2, args=("float32",))
+    for r in res:
+        assert np.allclose(r["tp"], r["twin"], rtol=1e-4, atol=1e-4), (r["tp"], r["twin"])
+        assert r["maxdiff"] < 1e-3, r["maxdiff"]  # Adam turns tiny gradient noise into O(lr) steps

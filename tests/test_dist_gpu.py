@@ -1,0 +1,30 @@
+"""Multi-GPU tests (child processes, one per GPU, NCCL)."""
+import numpy as np
+import pytest
+
+from dist_utils import run_workers
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ENV = {"NCCL_NVLS_ENABLE": "0"}
+
+
+def test_collective_api_nccl():
+    res = run_workers("collective_api.py", 2, backend="nccl", gpus=True, extra_env=ENV)
+    x = [np.arange(8, dtype=np.float32) + 10 * r for r in range(2)]
+    for r in range(2):
+        o = res[r]
+        assert np.allclose(o["all_reduce_sum"], x[0] + x[1])
+        assert np.allclose(o["all_gather_into"], np.concatenate(x))
+        assert np.allclose(o["reduce_scatter"], (x[0] + x[1])[r * 4:(r + 1) * 4])
+        assert np.allclose(o["alltoall_single"], np.concatenate([x[j][r * 4:(r + 1) * 4] for j in range(2)]))
+        assert np.allclose(o["batch_p2p"], x[(r - 1) % 2])
+
+
+@pytest.mark.parametrize("policy", ["baseline", "fused"])
+def test_llama_tp_sp_parity_gpu(policy):
+    res = run_workers("llama_tp.py", 2, backend="nccl", gpus=True, args=("bfloat16", policy), extra_env=ENV)
+    for r in res:
+        assert np.allclose(r["tp"], r["twin"], rtol=3e-2, atol=3e-2), (r["tp"], r["twin"])
+        assert r["maxdiff"] < 2e-2, r["maxdiff"]
+        if policy == "fused":
+            assert r["launches"] > 0
