@@ -1,0 +1,651 @@
+// Fused compute + collective GEMMs over NVLink peer memory (one kernel launch each, one process per GPU):
+//
+//   ag_gemm : all-gather -> GEMM.  A few "comm" CTAs push this rank's activation shard into every peer's
+//             staging buffer with plain 16-byte peer stores, one flag per sub-chunk (st.release.sys); the
+//             remaining CTAs run the persistent tcgen05 GEMM, consuming chunks in arrival order (local
+//             shard first) — the TMA producer waits on the chunk flag (ld.acquire.sys, bounded) before it
+//             loads tiles of that chunk from LOCAL memory.  Nothing is read twice over NVLink.
+//   gemm_rs : GEMM -> reduce-scatter.  Tiles are computed destination by destination (remote first, own
+//             shard last); the epilogue TMA-stores each bf16 partial tile straight into the destination
+//             rank's receive buffer and bumps that tile's arrival counter (red.release.sys); every CTA then
+//             reduces tiles of its own shard as soon as all ranks' partials have landed.
+// These implement ColumnSequenceParallelLinear / RowSequenceParallelLinear forward and backward
+// (python/paddle/distributed/fleet/utils/sequence_parallel_utils.py:429,564), where the reference issues
+// a synchronous NCCL all-gather before / reduce-scatter after a cuBLAS GEMM (:58-82,543-549,669-678).
+// No TMA multicast is used anywhere.  Every cross-rank wait is bounded and reports through the status word.
+#include "host_utils.h"
+#include "sm100_prims.cuh"
+
+namespace pd {
+namespace gc {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+constexpr int B_STAGE_BYTES = BN * BK * 2;
+constexpr int C_CHUNK_BYTES = BM * 128;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * C_CHUNK_BYTES + 1024 + 256;
+constexpr int MAX_RANKS = 8;
+
+struct Barriers {
+  uint64_t full[STAGES], empty[STAGES], tfull[2], tempty[2], drain;
+  uint32_t tmem_base;
+  int abort_flag;
+  int epi_decision;
+};
+
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__device__ __forceinline__ void raster(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int G = 16;
+  const int per_group = G * tiles_n;
+  const int g = t / per_group;
+  const int first_m = g * G;
+  const int gsz = min(G, tiles_m - first_m);
+  const int r = t - g * per_group;
+  tm = first_m + r % gsz;
+  tn = r / gsz;
+}
+
+__device__ __forceinline__ void init_barriers(Barriers* bars) {
+  for (int s = 0; s < STAGES; ++s) {
+    mbar_init(&bars->full[s], 1);
+    mbar_init(&bars->empty[s], 1);
+  }
+  for (int a = 0; a < 2; ++a) {
+    mbar_init(&bars->tfull[a], 1);
+    mbar_init(&bars->tempty[a], 1);
+  }
+  mbar_init(&bars->drain, 1);
+  bars->abort_flag = 0;
+  bars->epi_decision = 0;
+  fence_mbar_init();
+}
+
+// MMA issuer loop shared by both kernels (identical to the plain GEMM).
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void mma_loop(Barriers* bars, uint8_t* sA, uint8_t* sB, uint32_t tmem_base, int my_tiles,
+                                         int KB, int* status) {
+  volatile int* abort_flag = &bars->abort_flag;
+  constexpr uint32_t idesc = make_idesc(BM, BN, A_MN, B_MN);
+  constexpr uint32_t a_kstep = A_MN ? 2048u : 32u, b_kstep = B_MN ? 2048u : 32u;
+  constexpr uint32_t a_lbo = A_MN ? 8192u : 16u, b_lbo = B_MN ? 8192u : 16u;
+  int s = 0;
+  uint32_t ph = 0;
+  bool ok = true;
+  for (int it = 0; it < my_tiles && ok; ++it) {
+    const int acc = it & 1;
+    const uint32_t acc_ph = (it >> 1) & 1;
+    if (!mbar_wait(&bars->tempty[acc], acc_ph ^ 1, abort_flag, status, 200 + acc)) { ok = false; break; }
+    tc_fence_after();
+    const uint32_t d_tmem = tmem_base + acc * BN;
+    for (int kb = 0; kb < KB; ++kb) {
+      if (!mbar_wait(&bars->full[s], ph, abort_flag, status, 300 + s)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES), b_addr = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+      for (int k = 0; k < BK / 16; ++k)
+        umma_bf16_ss(d_tmem, make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024),
+                     make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
+      umma_commit(&bars->empty[s]);
+      if (++s == STAGES) { s = 0; ph ^= 1; }
+    }
+    if (ok) umma_commit(&bars->tfull[acc]);
+  }
+  if (!ok) {
+    umma_commit(&bars->drain);
+    mbar_drain(&bars->drain, 0);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void load_stage(const CUtensorMap* tmA, const CUtensorMap* tmB, uint8_t* a_dst,
+                                           uint8_t* b_dst, uint64_t* bar, int m0, int n0, int k0) {
+  if (!A_MN) {
+    tma_load_2d(a_dst, tmA, bar, k0, m0);
+  } else {
+#pragma unroll
+    for (int c = 0; c < BM / 64; ++c) tma_load_2d(a_dst + c * 8192, tmA, bar, m0 + c * 64, k0);
+  }
+  if (!B_MN) {
+    tma_load_2d(b_dst, tmB, bar, k0, n0);
+  } else {
+#pragma unroll
+    for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * 8192, tmB, bar, n0 + c * 64, k0);
+  }
+}
+
+// ============================================================================================ ag_gemm
+struct AGParams {
+  int M, N, K;
+  int rank, nranks;
+  int rows_per_rank;   // token rows contributed by each rank
+  int sub_rows;        // token rows per arrival flag (multiple of 128, divides rows_per_rank)
+  int row_elems;       // elements per token row of the gathered matrix
+  int n_comm;          // CTAs that push the local shard; the rest run the GEMM
+  int epoch;           // call number on this slot (flags / acks hold the last completed epoch)
+  int wait_mode;       // 0: tokens are the M dimension (wait per M tile); 1: tokens are the reduction dim
+  int skip_push;       // 1: the gathered matrix of this epoch is already staged (second GEMM on the same data)
+  int do_ack;          // 1: this launch is the last reader of the epoch's staged data -> acknowledge to all ranks
+  int done_target;     // value of *local_done after every GEMM CTA of every acknowledging launch so far
+  const void* x_shard; // [rows_per_rank, row_elems] bf16, local
+  unsigned long long peer_stage[MAX_RANKS];  // staging buffer [nranks*rows_per_rank, row_elems] of every rank
+  unsigned long long peer_flags[MAX_RANKS];  // int32 [nranks][n_sub] of every rank
+  unsigned long long peer_ack[MAX_RANKS];    // int32 [nranks] of every rank
+  int* local_done;
+  int* status;
+  unsigned long long wait_ns;
+};
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ AGParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint8_t* sC = sB + STAGES * B_STAGE_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(sC + 2 * C_CHUNK_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_sub = p.rows_per_rank / p.sub_rows;
+  const int* flags_local = reinterpret_cast<const int*>(p.peer_flags[p.rank]);
+
+  if (static_cast<int>(blockIdx.x) < p.n_comm) {
+    // ------------------------------------------------------------------ comm CTA: push the local shard
+    __shared__ int comm_ok;
+    if (p.skip_push) return;
+    const int* ack_local = reinterpret_cast<const int*>(p.peer_ack[p.rank]);
+    const int jobs = p.nranks * n_sub;
+    const size_t chunk_bytes = static_cast<size_t>(p.sub_rows) * p.row_elems * 2;
+    unsigned checked = 0;
+    for (int j = blockIdx.x; j < jobs; j += p.n_comm) {
+      const int c = j / p.nranks, pi = j % p.nranks;
+      const int peer = (p.rank + pi) % p.nranks;
+      if (!(checked & (1u << peer))) {
+        // the peer must have finished reading what the previous epoch put into this slot
+        if (threadIdx.x == 0)
+          comm_ok = flag_wait_ge(ack_local + peer, p.epoch - 1, p.wait_ns, p.status, 500 + peer) ? 1 : 0;
+        __syncthreads();
+        const int ok = comm_ok;
+        __syncthreads();
+        if (!ok) return;
+        checked |= 1u << peer;
+      }
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.x_shard) + c * chunk_bytes);
+      uint4* dst = reinterpret_cast<uint4*>(p.peer_stage[peer] +
+                                            (static_cast<size_t>(p.rank) * n_sub + c) * chunk_bytes);
+      const int nvec = static_cast<int>(chunk_bytes >> 4);
+      int i = threadIdx.x;
+      for (; i + 3 * NUM_THREADS < nvec; i += 4 * NUM_THREADS) {
+        const uint4 v0 = src[i], v1 = src[i + NUM_THREADS], v2 = src[i + 2 * NUM_THREADS], v3 = src[i + 3 * NUM_THREADS];
+        dst[i] = v0; dst[i + NUM_THREADS] = v1; dst[i + 2 * NUM_THREADS] = v2; dst[i + 3 * NUM_THREADS] = v3;
+      }
+      for (; i < nvec; i += NUM_THREADS) dst[i] = src[i];
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<int*>(p.peer_flags[peer]) + p.rank * n_sub + c, p.epoch);
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- GEMM CTA
+  const int cta = blockIdx.x - p.n_comm, nct = gridDim.x - p.n_comm;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int KB = (p.K + BK - 1) / BK;
+  const int my_tiles = cta < num_tiles ? (num_tiles - cta + nct - 1) / nct : 0;
+  const int tiles_per_src = p.rows_per_rank / BM;           // wait_mode 0
+  const int kb_per_src = p.rows_per_rank / BK;              // wait_mode 1
+
+  if (threadIdx.x == 0) init_barriers(bars);
+  if (warp == 5) tmem_alloc(&bars->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+      int s = 0;
+      uint32_t ph = 0, armed = 0, armed_parity = 0;
+      bool ok = true;
+      int last_chunk = -1;
+      for (int t = cta; t < num_tiles && ok; t += nct) {
+        int tm, tn;
+        raster(t, tiles_m, tiles_n, tm, tn);
+        if (p.wait_mode == 0) tm = (tm + p.rank * tiles_per_src) % tiles_m;   // local shard first
+        const int m0 = tm * BM, n0 = tn * BN;
+        if (p.wait_mode == 0) {
+          const int chunk = m0 / p.sub_rows;      // == src * n_sub + sub-chunk
+          if (chunk != last_chunk) {
+            if (!flag_wait_ge(flags_local + chunk, p.epoch, p.wait_ns, p.status, 600)) { ok = false; *abort_flag = 1; break; }
+            fence_proxy_async_all();
+            last_chunk = chunk;
+          }
+        }
+        for (int kbi = 0; kbi < KB; ++kbi) {
+          int kb = kbi;
+          if (p.wait_mode == 1) {
+            kb = (kbi + p.rank * kb_per_src) % KB;
+            const int chunk = (kb * BK) / p.sub_rows;
+            if (chunk != last_chunk) {
+              if (!flag_wait_ge(flags_local + chunk, p.epoch, p.wait_ns, p.status, 610)) { ok = false; *abort_flag = 1; break; }
+              fence_proxy_async_all();
+              last_chunk = chunk;
+            }
+          }
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, p.status, 100 + s)) { ok = false; break; }
+          mbar_expect_tx(&bars->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+          armed |= 1u << s;
+          armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+          load_stage<A_MN, B_MN>(&tmA, &tmB, sA + s * A_STAGE_BYTES, sB + s * B_STAGE_BYTES, &bars->full[s], m0, n0,
+                                 kb * BK);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < STAGES; ++i)
+          if (armed & (1u << i)) mbar_drain(&bars->full[i], (armed_parity >> i) & 1u);
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    if (lane == 0) mma_loop<A_MN, B_MN>(bars, sA, sB, tmem_base, my_tiles, KB, p.status);
+    __syncwarp();
+  } else {
+    const int epi_tid = threadIdx.x;
+    constexpr int CW = (EPI == 0) ? 64 : 32;
+    constexpr int NCHUNK = BN / CW;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    int it = 0, chunk_counter = 0;
+    bool alive = true;
+    for (int t = cta; t < num_tiles; t += nct, ++it) {
+      int tm, tn;
+      raster(t, tiles_m, tiles_n, tm, tn);
+      if (p.wait_mode == 0) tm = (tm + p.rank * tiles_per_src) % tiles_m;
+      const int m0 = tm * BM, n0 = tn * BN;
+      const int acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      if (epi_tid == 0) bars->epi_decision = mbar_wait(&bars->tfull[acc], acc_ph, abort_flag, p.status, 400 + acc) ? 1 : 0;
+      named_bar_sync(1, 128);
+      if (bars->epi_decision == 0) { alive = false; break; }
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + lane_base + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < NCHUNK; ++c, ++chunk_counter) {
+        uint8_t* stage = sC + (chunk_counter & 1) * C_CHUNK_BYTES;
+        if (epi_tid == 0) tma_wait_group_read<1>();
+        named_bar_sync(1, 128);
+        uint8_t* row_ptr = stage + epi_tid * 128;
+        const int sw = epi_tid & 7;
+        if (EPI == 0) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_acc + c * CW + h * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(row_ptr + (((h * 4 + j) ^ sw) << 4)) = v;
+            }
+          }
+        } else {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c * CW, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(row_ptr + ((j ^ sw) << 4)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+        if (c == NCHUNK - 1) tc_fence_before();
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (epi_tid == 0) {
+          if (c == NCHUNK - 1) mbar_arrive(&bars->tempty[acc]);
+          if (EPI == 2) tma_reduce_add_2d(&tmC, stage, n0 + c * CW, m0);
+          else tma_store_2d(&tmC, stage, n0 + c * CW, m0);
+          tma_commit_group();
+        }
+      }
+    }
+    if (epi_tid == 0) {
+      tma_wait_group<0>();
+      if (alive && p.do_ack) {
+        // all staged data of this epoch has been consumed by this CTA: the last CTA acknowledges to every rank
+        __threadfence();
+        const int done = atomicAdd(p.local_done, 1) + 1;
+        if (done == p.done_target)
+          for (int r = 0; r < p.nranks; ++r)
+            st_release_sys(reinterpret_cast<int*>(p.peer_ack[r]) + p.rank, p.epoch);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+// ============================================================================================ gemm_rs
+struct RSParams {
+  int M, N, K;
+  int rank, nranks;
+  int rows_per_rank;
+  int epoch;
+  unsigned long long peer_counters[MAX_RANKS];  // int32 [tiles_per_dst * tiles_n] on every rank
+  unsigned long long peer_ack[MAX_RANKS];       // int32 [nranks] on every rank
+  const void* recv_local;                       // bf16 [nranks][rows_per_rank][N]
+  void* out;                                    // bf16 [rows_per_rank][N]
+  int* local_done;
+  int* status;
+  unsigned long long wait_ns;
+};
+struct RSMaps {
+  CUtensorMap dst[MAX_RANKS];   // partial-tile destination on rank d: [rows_per_rank, N] slab of this source
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ RSMaps maps, const __grid_constant__ RSParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint8_t* sC = sB + STAGES * B_STAGE_BYTES;
+  Barriers* bars = reinterpret_cast<Barriers*>(sC + 2 * C_CHUNK_BYTES);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, nct = gridDim.x;
+  const int tiles_per_dst = (p.rows_per_rank + BM - 1) / BM;
+  const int tiles_m = tiles_per_dst * p.nranks, tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int KB = (p.K + BK - 1) / BK;
+  const int my_tiles = cta < num_tiles ? (num_tiles - cta + nct - 1) / nct : 0;
+  const int tiles_dst_all = tiles_per_dst * tiles_n;     // tiles per destination
+
+  if (threadIdx.x == 0) init_barriers(bars);
+  if (warp == 5) tmem_alloc(&bars->tmem_base, 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  // tile t -> destination-major order: remote destinations first (rank+1, rank+2, ...), own shard last
+  auto decode = [&](int t, int& d, int& tml, int& tn) {
+    const int di = t / tiles_dst_all, r = t % tiles_dst_all;
+    d = (p.rank + 1 + di) % p.nranks;
+    tml = r % tiles_per_dst;
+    tn = r / tiles_per_dst;
+  };
+
+  if (warp == 4) {
+    if (lane == 0) {
+      prefetch_tmap(&tmA);
+      prefetch_tmap(&tmB);
+      int s = 0;
+      uint32_t ph = 0, armed = 0, armed_parity = 0;
+      bool ok = true;
+      for (int t = cta; t < num_tiles && ok; t += nct) {
+        int d, tml, tn;
+        decode(t, d, tml, tn);
+        const int m0 = d * p.rows_per_rank + tml * BM, n0 = tn * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, p.status, 100 + s)) { ok = false; break; }
+          mbar_expect_tx(&bars->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
+          armed |= 1u << s;
+          armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
+          load_stage<A_MN, B_MN>(&tmA, &tmB, sA + s * A_STAGE_BYTES, sB + s * B_STAGE_BYTES, &bars->full[s], m0, n0,
+                                 kb * BK);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok)
+        for (int i = 0; i < STAGES; ++i)
+          if (armed & (1u << i)) mbar_drain(&bars->full[i], (armed_parity >> i) & 1u);
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    if (lane == 0) mma_loop<A_MN, B_MN>(bars, sA, sB, tmem_base, my_tiles, KB, p.status);
+    __syncwarp();
+  } else {
+    const int epi_tid = threadIdx.x;
+    constexpr int CW = 64, NCHUNK = BN / CW;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int* ack_local = reinterpret_cast<const int*>(p.peer_ack[p.rank]);
+    int it = 0, chunk_counter = 0;
+    unsigned checked = 0;
+    bool alive = true;
+    for (int t = cta; t < num_tiles; t += nct, ++it) {
+      int d, tml, tn;
+      decode(t, d, tml, tn);
+      const int n0 = tn * BN;
+      const int acc = it & 1;
+      const uint32_t acc_ph = (it >> 1) & 1;
+      if (epi_tid == 0) {
+        bool ok = mbar_wait(&bars->tfull[acc], acc_ph, abort_flag, p.status, 400 + acc);
+        if (ok && !(checked & (1u << d))) {
+          // destination d must have finished reducing the previous epoch out of this slot
+          ok = flag_wait_ge(ack_local + d, p.epoch - 1, p.wait_ns, p.status, 700 + d);
+          if (!ok) *abort_flag = 1;
+          checked |= 1u << d;
+        }
+        bars->epi_decision = ok ? 1 : 0;
+      }
+      named_bar_sync(1, 128);
+      if (bars->epi_decision == 0) { alive = false; break; }
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + lane_base + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < NCHUNK; ++c, ++chunk_counter) {
+        uint8_t* stage = sC + (chunk_counter & 1) * C_CHUNK_BYTES;
+        if (epi_tid == 0) tma_wait_group_read<1>();
+        named_bar_sync(1, 128);
+        uint8_t* row_ptr = stage + epi_tid * 128;
+        const int sw = epi_tid & 7;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c * CW + h * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            *reinterpret_cast<uint4*>(row_ptr + (((h * 4 + j) ^ sw) << 4)) = v;
+          }
+        }
+        if (c == NCHUNK - 1) tc_fence_before();
+        fence_proxy_async_smem();
+        named_bar_sync(1, 128);
+        if (epi_tid == 0) {
+          if (c == NCHUNK - 1) mbar_arrive(&bars->tempty[acc]);
+          tma_store_2d(&maps.dst[d], stage, n0 + c * CW, tml * BM);
+          tma_commit_group();
+          if (c == NCHUNK - 1) {
+            tma_wait_group<0>();                 // the partial tile has fully landed in rank d's memory
+            __threadfence_system();
+            red_release_sys_add(reinterpret_cast<int*>(p.peer_counters[d]) + tml * tiles_n + tn, 1);
+          }
+        }
+      }
+    }
+    // ---- reduce phase: out[tile] = sum over sources of the partial tiles received for my shard
+    const int* counters = reinterpret_cast<const int*>(p.peer_counters[p.rank]);
+    const __nv_bfloat16* recv = static_cast<const __nv_bfloat16*>(p.recv_local);
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+    const size_t slab = static_cast<size_t>(p.rows_per_rank) * p.N;
+    for (int u = cta; u < tiles_dst_all && alive; u += nct) {
+      const int tml = u % tiles_per_dst, tn = u / tiles_per_dst;
+      if (epi_tid == 0)
+        bars->epi_decision = flag_wait_ge(counters + tml * tiles_n + tn, p.nranks * p.epoch, p.wait_ns, p.status, 800) ? 1 : 0;
+      named_bar_sync(1, 128);
+      const int okd = bars->epi_decision;
+      named_bar_sync(1, 128);
+      if (!okd) { alive = false; break; }
+      const int col = tn * BN + (epi_tid & 31) * 8;
+      if (col < p.N) {
+        for (int rr = epi_tid >> 5; rr < BM; rr += 4) {
+          const int row = tml * BM + rr;
+          if (row >= p.rows_per_rank) break;
+          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int s = 0; s < p.nranks; ++s) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(recv + s * slab + static_cast<size_t>(row) * p.N + col));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(h[e]);
+              acc8[2 * e] += f.x;
+              acc8[2 * e + 1] += f.y;
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc8[0], acc8[1]);
+          o.y = pack_bf16x2(acc8[2], acc8[3]);
+          o.z = pack_bf16x2(acc8[4], acc8[5]);
+          o.w = pack_bf16x2(acc8[6], acc8[7]);
+          *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * p.N + col) = o;
+        }
+      }
+    }
+    named_bar_sync(1, 128);
+    if (epi_tid == 0 && alive) {
+      __threadfence();
+      const int done = atomicAdd(p.local_done, 1) + 1;
+      if (done == nct * p.epoch)
+        for (int r = 0; r < p.nranks; ++r) st_release_sys(reinterpret_cast<int*>(p.peer_ack[r]) + p.rank, p.epoch);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem_base, 512);
+}
+
+template <typename KFn>
+static int set_smem(KFn k) {
+  return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) == cudaSuccess ? 0 : -1;
+}
+
+static bool make_ab_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, int M, int N, int K, int lda,
+                         int ldb, int a_mn, int b_mn) {
+  bool ok = true;
+  if (!a_mn) ok &= encode_tmap_2d(tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, K, M, uint64_t(lda) * 2, BK, BM);
+  else ok &= encode_tmap_2d(tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, M, K, uint64_t(lda) * 2, 64, BK);
+  if (!b_mn) ok &= encode_tmap_2d(tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, K, N, uint64_t(ldb) * 2, BK, BN);
+  else ok &= encode_tmap_2d(tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, N, K, uint64_t(ldb) * 2, 64, BK);
+  return ok;
+}
+
+}  // namespace gc
+}  // namespace pd
+
+// All-gather -> GEMM.  A / B are the operand pointers the GEMM reads (the gathered one points into the LOCAL
+// staging buffer peer_stage[rank]); see AGParams for the rest.  epi: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate.
+PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                         int a_mn, int b_mn, int epi, const void* x_shard, int rows_per_rank, int sub_rows,
+                         int row_elems, int rank, int nranks, int n_comm, int epoch, int wait_mode, int skip_push, int do_ack,
+                         const unsigned long long* peer_stage, const unsigned long long* peer_flags,
+                         const unsigned long long* peer_ack, int* local_done, int done_base, int wait_ms, int* status,
+                         cudaStream_t stream) {
+  using namespace pd;
+  using namespace pd::gc;
+  if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > MAX_RANKS) return kErrBadShape;
+  if (rows_per_rank % sub_rows || sub_rows % BM || (wait_mode == 0 && rows_per_rank % BM)) return kErrBadShape;
+  if ((lda % 8) || (ldb % 8) || (epi == 0 ? (ldc % 8) : (ldc % 4)) || (row_elems % 8)) return kErrAlignment;
+  CUtensorMap tmA, tmB, tmC;
+  bool ok = make_ab_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn, b_mn);
+  if (epi == 0) ok &= encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, C, N, M, uint64_t(ldc) * 2, 64, BM);
+  else ok &= encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, C, N, M, uint64_t(ldc) * 4, 32, BM);
+  if (!ok) return kErrTensorMap;
+  AGParams p;
+  p.M = M; p.N = N; p.K = K; p.rank = rank; p.nranks = nranks; p.rows_per_rank = rows_per_rank;
+  p.sub_rows = sub_rows; p.row_elems = row_elems; p.n_comm = n_comm; p.epoch = epoch; p.wait_mode = wait_mode;
+  p.skip_push = skip_push; p.do_ack = do_ack; p.x_shard = x_shard; p.local_done = local_done; p.status = status;
+  p.wait_ns = static_cast<unsigned long long>(wait_ms) * 1000000ull;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.peer_stage[i] = i < nranks ? peer_stage[i] : 0;
+    p.peer_flags[i] = i < nranks ? peer_flags[i] : 0;
+    p.peer_ack[i] = i < nranks ? peer_ack[i] : 0;
+  }
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int gemm_ctas = sm_count() - n_comm;
+  if (gemm_ctas > tiles) gemm_ctas = tiles;
+  if (gemm_ctas < 1) return kErrBadShape;
+  const int grid = gemm_ctas + n_comm;
+  p.done_target = 0;
+  if (do_ack) {   // cumulative count of acknowledging GEMM CTAs on this slot, kept next to the counter on the host side
+    p.done_target = done_base + gemm_ctas;
+  }
+#define PD_AG_CASE(AM, BM_, E)                                                                      \
+  if (a_mn == AM && b_mn == BM_ && epi == E) {                                                      \
+    static bool cfg = false;                                                                        \
+    auto kfn = ag_gemm_kernel<AM, BM_, E>;                                                          \
+    if (!cfg) { if (set_smem(kfn)) return kErrCuda; cfg = true; }                                   \
+    kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);                               \
+    return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;                                \
+  }
+  PD_AG_CASE(0, 1, 0)   // forward:  Y = AG(X) W            (tokens = M)
+  PD_AG_CASE(0, 0, 0)   // backward: dX = AG(dY) W^T        (tokens = M)
+  PD_AG_CASE(1, 1, 2)   // wgrad:    dW += AG(X)^T dY / X^T AG(dY)   (tokens = reduction dim)
+  PD_AG_CASE(1, 1, 0)
+#undef PD_AG_CASE
+  return kErrBadShape;
+}
+
+// GEMM -> reduce-scatter.  A: [M, K] (or [K, M] if a_mn), B as in pd_gemm_bf16, M = nranks * rows_per_rank.
+// peer_recv[d]: receive buffer of rank d, bf16 [nranks][rows_per_rank][N]; out: [rows_per_rank, N] bf16.
+PD_EXPORT int pd_gemm_rs(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int a_mn,
+                         int b_mn, int rows_per_rank, int rank, int nranks, int epoch,
+                         const unsigned long long* peer_recv, const unsigned long long* peer_counters,
+                         const unsigned long long* peer_ack, int* local_done, int wait_ms, int* status,
+                         cudaStream_t stream) {
+  using namespace pd;
+  using namespace pd::gc;
+  if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > MAX_RANKS || M != rows_per_rank * nranks) return kErrBadShape;
+  if ((lda % 8) || (ldb % 8) || (N % 8)) return kErrAlignment;
+  CUtensorMap tmA, tmB;
+  if (!make_ab_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn, b_mn)) return kErrTensorMap;
+  RSMaps maps;
+  const size_t slab_bytes = static_cast<size_t>(rows_per_rank) * N * 2;
+  for (int d = 0; d < MAX_RANKS; ++d) {
+    const int dd = d < nranks ? d : 0;
+    void* base = reinterpret_cast<void*>(peer_recv[dd] + static_cast<size_t>(rank) * slab_bytes);
+    if (!encode_tmap_2d(&maps.dst[d], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, N, rows_per_rank, uint64_t(N) * 2, 64, BM))
+      return kErrTensorMap;
+  }
+  RSParams p;
+  p.M = M; p.N = N; p.K = K; p.rank = rank; p.nranks = nranks; p.rows_per_rank = rows_per_rank; p.epoch = epoch;
+  p.recv_local = reinterpret_cast<const void*>(peer_recv[rank]);
+  p.out = out; p.local_done = local_done; p.status = status;
+  p.wait_ns = static_cast<unsigned long long>(wait_ms) * 1000000ull;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.peer_counters[i] = i < nranks ? peer_counters[i] : 0;
+    p.peer_ack[i] = i < nranks ? peer_ack[i] : 0;
+  }
+  const int tiles = ((rows_per_rank + BM - 1) / BM) * nranks * ((N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+#define PD_RS_CASE(AM, BM_)                                                                         \
+  if (a_mn == AM && b_mn == BM_) {                                                                  \
+    static bool cfg = false;                                                                        \
+    auto kfn = gemm_rs_kernel<AM, BM_>;                                                             \
+    if (!cfg) { if (set_smem(kfn)) return kErrCuda; cfg = true; }                                   \
+    kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, maps, p);                              \
+    return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;                                \
+  }
+  PD_RS_CASE(0, 1)   // forward:  Y = X W  -> reduce-scatter
+  PD_RS_CASE(0, 0)   // backward: dX = dY W^T -> reduce-scatter
+#undef PD_RS_CASE
+  return kErrBadShape;
+}

@@ -159,11 +159,11 @@ def register_sequence_parallel_allreduce_hooks(model, accumulation_steps=1, fuse
 
 
 # ------------------------------------------------------------------ layers
-def _use_fused(x, weight):
+def _use_fused(x, weight, group, tokens_per_rank):
     from ....ops import functional as K
     from ....parallel import fused_linear
     return (x.is_cuda and x.dtype == torch.bfloat16 and K.get_kernel_policy() == "fused"
-            and fused_linear.available(x, weight))
+            and tokens_per_rank % 128 == 0 and fused_linear.available(x, weight, group))
 
 
 class ColumnSequenceParallelLinear(Layer):
@@ -191,7 +191,7 @@ class ColumnSequenceParallelLinear(Layer):
     def forward(self, x):
         if not self.is_mp:
             return F.linear(x, self.weight, self.bias)
-        if _use_fused(x, self.weight):
+        if _use_fused(x, self.weight, self.model_parallel_group, x.shape[0]):
             from ....parallel import fused_linear
             out = fused_linear.allgather_linear(x, self.weight, self.model_parallel_group)
             return out if self.bias is None else out + self.bias
@@ -227,7 +227,7 @@ class RowSequenceParallelLinear(Layer):
     def forward(self, x):
         if not self.is_mp:
             return F.linear(x, self.weight, self.bias)
-        if _use_fused(x, self.weight):
+        if _use_fused(x, self.weight, self.model_parallel_group, x.shape[0] // self.world_size):
             from ....parallel import fused_linear
             out = fused_linear.linear_reduce_scatter(x, self.weight, self.model_parallel_group)
         else:

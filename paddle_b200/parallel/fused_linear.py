@@ -16,9 +16,9 @@ def _load():
     return _impl
 
 
-def available(x, weight) -> bool:
+def available(x, weight, group=None) -> bool:
     impl = _load()
-    return bool(impl) and impl.available(x, weight)
+    return bool(impl) and impl.available(x, weight, group)
 
 
 def allgather_linear(x, weight, group):

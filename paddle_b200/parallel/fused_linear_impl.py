@@ -1,0 +1,229 @@
+"""Host side of the fused all-gather->GEMM / GEMM->reduce-scatter kernels: symmetric staging slots,
+epoch bookkeeping and the autograd functions behind the sequence-parallel linears."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from .._core.tensor import as_tensor
+from ..ops import _lib, native
+from ..ops._lib import c_int, check, ptr, stream
+from . import symm
+
+BM, BN = 128, 256
+SUB_ROWS = 128
+N_COMM = int(os.environ.get("PD_AG_COMM_CTAS", "8"))
+WAIT_MS = int(os.environ.get("FLAGS_pd_wait_limit_ms", "2000"))
+_slots = {}
+_sm_count = None
+U64x8 = ctypes.c_ulonglong * 8
+
+
+def _sms():
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sm_count
+
+
+def _arr(vals):
+    return U64x8(*(list(vals) + [0] * (8 - len(vals))))
+
+
+class _AGSlot:
+    """Staging for one gathered matrix [nranks * rows, row_elems] bf16 + arrival flags + acks."""
+
+    def __init__(self, group, rows, row_elems):
+        n = group.nranks
+        self.n, self.rows, self.row_elems = n, rows, row_elems
+        self.n_sub = rows // SUB_ROWS
+        stage_bytes = n * rows * row_elems * 2
+        self.off_flags = (stage_bytes + 255) // 256 * 256
+        self.off_ack = self.off_flags + ((n * self.n_sub * 4 + 255) // 256 * 256)
+        self.block = symm.SymmBlock(self.off_ack + 256, group)
+        self.stage = self.block.view(0, (n * rows, row_elems), torch.bfloat16)
+        self.p_stage = _arr(self.block.peer_ptrs(0))
+        self.p_flags = _arr(self.block.peer_ptrs(self.off_flags))
+        self.p_ack = _arr(self.block.peer_ptrs(self.off_ack))
+        self.done = torch.zeros(1, dtype=torch.int32, device=self.stage.device)
+        self.epoch = 0
+        self.done_base = 0
+
+
+class _RSSlot:
+    """Receive buffer [nranks][rows][N] bf16 + per-tile arrival counters + acks."""
+
+    def __init__(self, group, rows, N):
+        n = group.nranks
+        self.n, self.rows, self.N = n, rows, N
+        tiles = ((rows + BM - 1) // BM) * ((N + BN - 1) // BN)
+        recv_bytes = n * rows * N * 2
+        self.off_cnt = (recv_bytes + 255) // 256 * 256
+        self.off_ack = self.off_cnt + ((tiles * 4 + 255) // 256 * 256)
+        self.block = symm.SymmBlock(self.off_ack + 256, group)
+        self.p_recv = _arr(self.block.peer_ptrs(0))
+        self.p_cnt = _arr(self.block.peer_ptrs(self.off_cnt))
+        self.p_ack = _arr(self.block.peer_ptrs(self.off_ack))
+        self.done = torch.zeros(1, dtype=torch.int32, device=self.block.local.device)
+        self.epoch = 0
+
+
+def _slot(kind, group, rows, width):
+    """Two alternating slots per (group, kind, shape) so consecutive calls rarely wait for an ack."""
+    key = (group.id, kind, rows, width)
+    pair = _slots.get(key)
+    if pair is None:
+        cls = _AGSlot if kind == "ag" else _RSSlot
+        pair = {"slots": [cls(group, rows, width), cls(group, rows, width)], "next": 0}
+        _slots[key] = pair
+    s = pair["slots"][pair["next"]]
+    pair["next"] ^= 1
+    return s
+
+
+def available(x, weight, group=None) -> bool:
+    if not symm.supported() or group is None or group.nranks not in (2, 4, 8):
+        return False
+    if os.environ.get("PD_DISABLE_FUSED_COMM") == "1":
+        return False
+    return x.dim() == 2 and x.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0
+
+
+def _ag_ok(rows):
+    return rows % SUB_ROWS == 0
+
+
+# ------------------------------------------------------------------------------------------ raw launches
+def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode, push=True, ack=True):
+    """out (=|+=) op(A) op(B) where one operand is the gathered matrix staged in ``slot``."""
+    if push:
+        slot.epoch += 1
+    tiles = ((M + BM - 1) // BM) * ((N + BN - 1) // BN)
+    gemm_ctas = min(_sms() - N_COMM, tiles)
+    rc = _lib.kernels().pd_ag_gemm(
+        ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
+        c_int(out.stride(0)), c_int(a_mn), c_int(b_mn), c_int(epi), ptr(x_shard), c_int(slot.rows), c_int(SUB_ROWS),
+        c_int(slot.row_elems), c_int(group.rank), c_int(group.nranks), c_int(N_COMM), c_int(slot.epoch),
+        c_int(wait_mode), c_int(0 if push else 1), c_int(1 if ack else 0), slot.p_stage, slot.p_flags, slot.p_ack,
+        ptr(slot.done), c_int(slot.done_base), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
+    check(rc, "pd_ag_gemm")
+    if ack:
+        slot.done_base += gemm_ctas
+    native._count()
+    return out
+
+
+def gemm_rs(slot, group, a, b, out, M, N, K, a_mn, b_mn):
+    slot.epoch += 1
+    rc = _lib.kernels().pd_gemm_rs(
+        ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)), c_int(a_mn),
+        c_int(b_mn), c_int(slot.rows), c_int(group.rank), c_int(group.nranks), c_int(slot.epoch), slot.p_recv,
+        slot.p_cnt, slot.p_ack, ptr(slot.done), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
+    check(rc, "pd_gemm_rs")
+    native._count()
+    return out
+
+
+def _wgrad(weight, a, b, M, N, K, slot, group, x_shard, push, ack):
+    """dW (+)= A^T B with tokens as the reduction dimension; straight into main_grad when present."""
+    mg = getattr(weight, "main_grad", None)
+    if mg is not None:
+        ag_gemm(slot, group, x_shard, a, b, mg, M, N, K, 1, 1, 2, 1, push, ack)
+        hook = getattr(weight, "_main_grad_ready_hook", None)
+        if hook is not None:
+            hook(weight)
+        return None
+    dw = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    ag_gemm(slot, group, x_shard, a, b, dw, M, N, K, 1, 1, 0, 1, push, ack)
+    return dw
+
+
+# ------------------------------------------------------------------------------------------ autograd
+class _AllGatherLinear(torch.autograd.Function):
+    """y[T, out/n] = all_gather(x[T/n, in]) @ W[in, out/n]"""
+
+    @staticmethod
+    def forward(ctx, x, weight, group):
+        x = x.contiguous()
+        rows, K = x.shape
+        n = group.nranks
+        T, N = rows * n, weight.shape[1]
+        slot = _slot("ag", group, rows, K)
+        y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+        ag_gemm(slot, group, x, slot.stage, weight, y, T, N, K, 0, 1, 0, 0)
+        ctx.save_for_backward(x, weight)
+        ctx.group, ctx.weight_ref = group, weight
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        group = ctx.group
+        dy = dy.contiguous()
+        rows, K = x.shape
+        n = group.nranks
+        T, N = rows * n, weight.shape[1]
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            rs = _slot("rs", group, rows, K)
+            dx = torch.empty((rows, K), dtype=torch.bfloat16, device=x.device)
+            gemm_rs(rs, group, dy, weight, dx, T, K, N, 0, 0)          # dX = dY W^T -> reduce-scatter
+        if ctx.needs_input_grad[1]:
+            slot = _slot("ag", group, rows, K)                          # re-gather x, overlapped with the dW GEMM
+            dw = _wgrad(ctx.weight_ref, slot.stage, dy, K, N, T, slot, group, x, True, True)
+        return dx, dw, None
+
+
+class _LinearReduceScatter(torch.autograd.Function):
+    """y[T/n, out] = reduce_scatter(x[T, in/n] @ W[in/n, out])"""
+
+    @staticmethod
+    def forward(ctx, x, weight, group):
+        x = x.contiguous()
+        T, K = x.shape
+        n = group.nranks
+        rows, N = T // n, weight.shape[1]
+        slot = _slot("rs", group, rows, N)
+        y = torch.empty((rows, N), dtype=torch.bfloat16, device=x.device)
+        gemm_rs(slot, group, x, weight, y, T, N, K, 0, 1)
+        ctx.save_for_backward(x, weight)
+        ctx.group, ctx.weight_ref = group, weight
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        group = ctx.group
+        dy = dy.contiguous()
+        T, K = x.shape
+        rows, N = dy.shape
+        slot = _slot("ag", group, rows, N)
+        dx = dw = None
+        need_dw = ctx.needs_input_grad[1]
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty((T, K), dtype=torch.bfloat16, device=x.device)
+            # dX = all_gather(dY) W^T ; the gathered dY stays staged for the weight gradient
+            ag_gemm(slot, group, dy, slot.stage, weight, dx, T, K, N, 0, 0, 0, 0, push=True, ack=not need_dw)
+            if need_dw:
+                dw = _wgrad(ctx.weight_ref, x, slot.stage, K, N, T, slot, group, dy, False, True)
+        elif need_dw:
+            dw = _wgrad(ctx.weight_ref, x, slot.stage, K, N, T, slot, group, dy, True, True)
+        return dx, dw, None
+
+
+def _shapes_ok(tokens_local_rows):
+    return _ag_ok(tokens_local_rows)
+
+
+def allgather_linear(x, weight, group):
+    if x.shape[0] % SUB_ROWS != 0:
+        raise ValueError(f"fused all-gather GEMM needs a multiple of {SUB_ROWS} tokens per rank, got {x.shape[0]}")
+    return as_tensor(_AllGatherLinear.apply(x, weight, group))
+
+
+def linear_reduce_scatter(x, weight, group):
+    if (x.shape[0] // group.nranks) % SUB_ROWS != 0:
+        raise ValueError(f"fused GEMM reduce-scatter needs a multiple of {SUB_ROWS} tokens per rank")
+    return as_tensor(_LinearReduceScatter.apply(x, weight, group))

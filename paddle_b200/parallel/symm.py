@@ -1,0 +1,59 @@
+"""Symmetric (peer-mapped) device memory for the fused compute+collective kernels.
+
+Every rank of a group allocates a block of the same size; after the rendezvous each rank knows the
+device address at which every peer's block is mapped into its own address space, so kernels can load
+and store peer memory directly over NVLink.  The allocation and the handle exchange use PyTorch's
+symmetric-memory allocator (CUDA VMM + fabric/fd handle exchange over the group's store); the reference
+has no counterpart (it only ever calls NCCL: paddle/phi/core/distributed/nccl_comm_context.cc:91-249).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as tdist
+
+_enabled_groups = set()
+
+
+class SymmBlock:
+    """One symmetric allocation: ``local`` is this rank's uint8 tensor, ``ptrs[r]`` the address of rank
+    r's block as seen from this process."""
+
+    def __init__(self, nbytes: int, group):
+        import torch.distributed._symmetric_memory as symm_mem
+        pg = group.process_group
+        name = pg.group_name
+        if name not in _enabled_groups:
+            try:
+                symm_mem.enable_symm_mem_for_group(name)
+            except Exception:  # noqa: BLE001 - newer torch enables groups lazily
+                pass
+            _enabled_groups.add(name)
+        nbytes = (nbytes + 255) // 256 * 256
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.local = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
+        self.local.zero_()
+        self.handle = symm_mem.rendezvous(self.local, pg)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.rank = self.handle.rank
+        self.world_size = self.handle.world_size
+        self.nbytes = nbytes
+        torch.cuda.synchronize()
+        tdist.barrier(group=pg, device_ids=[dev.index])
+
+    def view(self, offset: int, shape, dtype):
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nb = n * torch.empty(0, dtype=dtype).element_size()
+        return self.local[offset:offset + nb].view(dtype).view(*shape)
+
+    def peer_ptrs(self, offset: int):
+        return [p + offset for p in self.ptrs]
+
+
+def supported() -> bool:
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+    except ImportError:
+        return False
+    return torch.cuda.is_available()

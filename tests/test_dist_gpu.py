@@ -28,3 +28,10 @@ def test_llama_tp_sp_parity_gpu(policy):
         assert r["maxdiff"] < 2e-2, r["maxdiff"]
         if policy == "fused":
             assert r["launches"] > 0
+
+
+def test_fused_ag_gemm_and_gemm_rs():
+    res = run_workers("fused_comm.py", 2, backend="nccl", gpus=True, extra_env=ENV)
+    for r in res:
+        for k, v in r["errs"].items():
+            assert v < 3e-2, (k, v)
