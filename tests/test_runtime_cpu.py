@@ -1,0 +1,90 @@
+"""Native host runtime: TCP store commands, bucket assignment, watchdog verdicts, reshard planner."""
+import ctypes
+import threading
+import time
+
+import pytest
+
+
+def test_tcp_store_commands():
+    from paddle_b200.distributed.store import StoreTimeoutError, TCPStore
+    master = TCPStore("127.0.0.1", 0, is_master=True, world_size=2, timeout=5)
+    client = TCPStore("127.0.0.1", master.port, is_master=False, world_size=2, timeout=5)
+    client.set("k", b"hello")
+    assert master.get("k") == b"hello"
+    assert master.add("cnt", 3) == 3 and client.add("cnt", 4) == 7
+    assert client.check("k") and not client.check("nope")
+    got = {}
+    t = threading.Thread(target=lambda: got.setdefault("v", client.get("late")))
+    t.start()
+    time.sleep(0.2)
+    master.set("late", b"x" * 100000)
+    t.join(5)
+    assert got["v"] == b"x" * 100000
+    assert master.delete_key("k") and not master.check("k")
+    th = threading.Thread(target=lambda: client.barrier("b0", 2, 5))
+    th.start()
+    master.barrier("b0", 2, 5)
+    th.join(5)
+    assert not th.is_alive()
+    short = TCPStore("127.0.0.1", master.port, timeout=0.3)
+    with pytest.raises(StoreTimeoutError):
+        short.get("never-set")
+    client.close(), master.close()
+
+
+def test_assign_group_by_size_native_matches_python():
+    import torch
+    from paddle_b200.distributed import reducer
+    params = [torch.zeros(n, dtype=dt) for n, dt in [(1000, torch.float32), (300000, torch.float32),
+                                                       (50, torch.bfloat16), (700000, torch.float32),
+                                                       (90000, torch.bfloat16), (10, torch.float32)]]
+    groups = reducer.assign_group_by_size(params, [1 << 20, 2 << 20])
+    flat = sorted(i for g in groups for i in g)
+    assert flat == list(range(len(params)))
+    for g in groups:
+        assert len({params[i].dtype for i in g}) == 1
+    assert groups[0][0] == len(params) - 1          # walk starts from the last parameter
+
+
+def test_watchdog_reports_hung_collective():
+    from paddle_b200.distributed import watchdog
+    watchdog.start(timeout_s=0.2, poll_ms=20)
+    try:
+        ok = watchdog.task_create(0, "all_reduce", 1024)
+        watchdog.task_started(ok), watchdog.task_finished(ok)
+        hung = watchdog.task_create(0, "all_gather", 4096)
+        watchdog.task_started(hung)
+        never = watchdog.task_create(1, "broadcast", 16)
+        time.sleep(0.6)
+        reports = []
+        while True:
+            r = watchdog.poll()
+            if r is None:
+                break
+            reports.append(r)
+        assert any("started-but-not-finished" in r and "all_gather" in r and "last_done=all_reduce" in r for r in reports)
+        assert any("timeout-not-started" in r and "broadcast" in r for r in reports)
+        with pytest.raises(watchdog.CommTimeoutError):
+            h2 = watchdog.task_create(2, "reduce", 8)
+            time.sleep(0.5)
+            watchdog.check()
+    finally:
+        watchdog.stop()
+
+
+def test_reshard_planner():
+    from paddle_b200.ops import _lib
+    rt = _lib.runtime()
+    out = (ctypes.c_int * 30)()
+
+    def plan(src, dst):
+        n = rt.pd_plan_reshard((ctypes.c_int * len(src))(*src), (ctypes.c_int * len(dst))(*dst), len(src), out, 10)
+        return [(out[3 * i], out[3 * i + 1], out[3 * i + 2]) for i in range(n)]
+    assert plan([0], [-1]) == [(1, 0, 0)]                 # s -> r : all_gather
+    assert plan([-2], [-1]) == [(2, 0, -1)]               # p -> r : all_reduce
+    assert plan([-2], [1]) == [(3, 0, 1)]                 # p -> s : reduce_scatter
+    assert plan([-1], [0]) == [(4, 0, 0)]                 # r -> s : slice
+    assert plan([0], [1]) == [(5, 0, 1)]                  # s -> s : all_to_all
+    assert plan([0, -2], [-1, -1]) == [(2, 1, -1), (1, 0, 0)]
+    assert rt.pd_comm_static_check(1, 8, 16, 0, 2, 0) == 0 and rt.pd_comm_static_check(1, 8, 8, 0, 2, 0) == 3
