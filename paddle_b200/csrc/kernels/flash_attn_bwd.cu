@@ -381,15 +381,21 @@ __global__ void delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfl
   if (lane == 0) delta[(static_cast<size_t>(b) * H + h) * S + s] = acc;
 }
 
-__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n) {
-  const int64_t nvec = n >> 2;
-  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < nvec;
+// dq (bf16, [B, S, H, 128] with token / batch strides) = dq_acc (fp32, contiguous); 32 threads per row
+__global__ void dq_convert_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t rows,
+                                  int S, int H, int64_t tok, int64_t batch) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < rows * 32;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const float4 v = reinterpret_cast<const float4*>(src)[i];
+    const int64_t row = i >> 5;
+    const int c = static_cast<int>(i & 31) * 4;
+    const int h = static_cast<int>(row % H);
+    const int64_t bs = row / H;
+    const int64_t s = bs % S, b = bs / S;
+    const float4 v = *reinterpret_cast<const float4*>(src + row * D + c);
     uint2 o;
     o.x = pack_bf16x2(v.x, v.y);
     o.y = pack_bf16x2(v.z, v.w);
-    reinterpret_cast<uint2*>(dst)[i] = o;
+    *reinterpret_cast<uint2*>(dst + b * batch + s * tok + static_cast<int64_t>(h) * D + c) = o;
   }
 }
 
@@ -405,12 +411,13 @@ static bool make_map_bf16(CUtensorMap* m, const void* ptr, int B, int S, int H, 
 }  // namespace pd
 
 // dq_acc: zero-initialised fp32 [B, Sq, Hq, 128] (contiguous); delta: fp32 [B, Hq, Sq] scratch;
-// dq/dk/dv: contiguous bf16 outputs.  `unused` keeps the argument list stable.
+// dq/dk/dv: bf16 outputs [B, S, H, 128] with their own token / batch strides (e.g. views of a packed dqkv).  `unused` keeps the argument list stable.
 PD_EXPORT int pd_flash_attn_bwd(const void* d_o, const void* q, const void* k, const void* v, const void* o,
                                 const float* lse, float* delta, float* dq_acc, void* unused, void* dq, void* dk,
                                 void* dv, int B, int Sq, int Sk, int Hq, int Hkv, int64_t q_tok, int64_t q_batch,
                                 int64_t k_tok, int64_t k_batch, int64_t v_tok, int64_t v_batch, int64_t o_tok,
-                                int64_t o_batch, int64_t do_tok, int64_t do_batch, float scale, int causal,
+                                int64_t o_batch, int64_t do_tok, int64_t do_batch, int64_t dq_tok, int64_t dq_batch,
+                                int64_t dk_tok, int64_t dk_batch, int64_t dv_tok, int64_t dv_batch, float scale, int causal,
                                 int* status, cudaStream_t stream) {
   using namespace pd;
   using namespace pd::fab;
@@ -423,8 +430,8 @@ PD_EXPORT int pd_flash_attn_bwd(const void* d_o, const void* q, const void* k, c
             make_map_bf16(&tmDO, d_o, B, Sq, Hq, do_tok, do_batch, BQ) &&
             make_map_bf16(&tmK, k, B, Sk, Hkv, k_tok, k_batch, BKV) &&
             make_map_bf16(&tmV, v, B, Sk, Hkv, v_tok, v_batch, BKV) &&
-            make_map_bf16(&tmDK, dk, B, Sk, Hkv, int64_t(Hkv) * D, int64_t(Sk) * Hkv * D, BKV) &&
-            make_map_bf16(&tmDV, dv, B, Sk, Hkv, int64_t(Hkv) * D, int64_t(Sk) * Hkv * D, BKV);
+            make_map_bf16(&tmDK, dk, B, Sk, Hkv, dk_tok, dk_batch, BKV) &&
+            make_map_bf16(&tmDV, dv, B, Sk, Hkv, dv_tok, dv_batch, BKV);
   {
     uint64_t dims[4] = {D, static_cast<uint64_t>(Hq), static_cast<uint64_t>(Sq), static_cast<uint64_t>(B)};
     uint64_t strides[3] = {D * 4, static_cast<uint64_t>(Hq) * D * 4, static_cast<uint64_t>(Sq) * Hq * D * 4};
@@ -445,9 +452,9 @@ PD_EXPORT int pd_flash_attn_bwd(const void* d_o, const void* q, const void* k, c
   Params p{B, Sq, Sk, Hq, Hkv, causal, scale, scale * 1.4426950408889634f, lse, delta, status};
   dim3 grid((Sk + BKV - 1) / BKV, Hkv, B);
   flash_bwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmQ, tmDO, tmK, tmV, tmDQ, tmDK, tmDV, p);
-  const int64_t n = rows * D;
-  int64_t blocks = ((n >> 2) + 255) / 256;
+  int64_t blocks = (rows * 32 + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  f32_to_bf16_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
+  dq_convert_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, rows, Sq, Hq, dq_tok,
+                                                                       dq_batch);
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }

@@ -154,39 +154,74 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (static_cast<int>(blockIdx.x) < p.n_comm) {
     // ------------------------------------------------------------------ comm CTA: push the local shard
-    __shared__ int comm_ok;
-    if (p.skip_push) return;
+    // One thread drives a ring of bulk copies: local HBM -> shared memory (cp.async.bulk + mbarrier), shared
+    // memory -> the peer's staging buffer (cp.async.bulk store over NVLink).  Many KB stay in flight per CTA
+    // without occupying load/store units, so a handful of CTAs saturate the link.
+    if (p.skip_push || threadIdx.x != 0) return;
+    constexpr int RING = 8, LOOKAHEAD = 4, PIECE_MAX = 16384;
+    uint64_t* ring_bar = reinterpret_cast<uint64_t*>(smem + RING * PIECE_MAX);
+    for (int i = 0; i < RING; ++i) mbar_init(&ring_bar[i], 1);
+    fence_mbar_init();
+    int dummy_abort = 0;
     const int* ack_local = reinterpret_cast<const int*>(p.peer_ack[p.rank]);
     const int jobs = p.nranks * n_sub;
-    const size_t chunk_bytes = static_cast<size_t>(p.sub_rows) * p.row_elems * 2;
+    const int my_jobs = static_cast<int>(blockIdx.x) < jobs ? (jobs - static_cast<int>(blockIdx.x) + p.n_comm - 1) / p.n_comm : 0;
+    const uint32_t row_bytes = static_cast<uint32_t>(p.row_elems) * 2;
+    const int rows_per_piece = row_bytes >= PIECE_MAX ? 1 : PIECE_MAX / row_bytes;
+    const int ppj = (p.sub_rows + rows_per_piece - 1) / rows_per_piece;     // pieces per job
+    const int total = my_jobs * ppj;
+    auto piece_info = [&](int q, int& peer, int& c, int& row0, uint32_t& bytes) {
+      const int j = static_cast<int>(blockIdx.x) + (q / ppj) * p.n_comm;
+      c = j / p.nranks;
+      peer = (p.rank + j % p.nranks) % p.nranks;
+      row0 = (q % ppj) * rows_per_piece;
+      const int nrows = min(rows_per_piece, p.sub_rows - row0);
+      bytes = static_cast<uint32_t>(nrows) * row_bytes;
+    };
+    auto issue_load = [&](int q) {
+      int peer, c, row0;
+      uint32_t bytes;
+      piece_info(q, peer, c, row0, bytes);
+      const int slot = q % RING;
+      const uint8_t* src = static_cast<const uint8_t*>(p.x_shard) +
+                           (static_cast<size_t>(c) * p.sub_rows + row0) * row_bytes;
+      mbar_expect_tx(&ring_bar[slot], bytes);
+      bulk_load(smem + slot * PIECE_MAX, src, bytes, &ring_bar[slot]);
+    };
+    for (int q = 0; q < total && q < LOOKAHEAD; ++q) issue_load(q);
     unsigned checked = 0;
-    for (int j = blockIdx.x; j < jobs; j += p.n_comm) {
-      const int c = j / p.nranks, pi = j % p.nranks;
-      const int peer = (p.rank + pi) % p.nranks;
+    bool ok = true;
+    for (int q = 0; q < total && ok; ++q) {
+      if (q + LOOKAHEAD < total) {
+        tma_wait_group_read<LOOKAHEAD - 1>();      // the store that last read this slot has drained it
+        issue_load(q + LOOKAHEAD);
+      }
+      int peer, c, row0;
+      uint32_t bytes;
+      piece_info(q, peer, c, row0, bytes);
       if (!(checked & (1u << peer))) {
         // the peer must have finished reading what the previous epoch put into this slot
-        if (threadIdx.x == 0)
-          comm_ok = flag_wait_ge(ack_local + peer, p.epoch - 1, p.wait_ns, p.status, 500 + peer) ? 1 : 0;
-        __syncthreads();
-        const int ok = comm_ok;
-        __syncthreads();
-        if (!ok) return;
+        if (!flag_wait_ge(ack_local + peer, p.epoch - 1, p.wait_ns, p.status, 500 + peer)) { ok = false; break; }
         checked |= 1u << peer;
       }
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.x_shard) + c * chunk_bytes);
-      uint4* dst = reinterpret_cast<uint4*>(p.peer_stage[peer] +
-                                            (static_cast<size_t>(p.rank) * n_sub + c) * chunk_bytes);
-      const int nvec = static_cast<int>(chunk_bytes >> 4);
-      int i = threadIdx.x;
-      for (; i + 3 * NUM_THREADS < nvec; i += 4 * NUM_THREADS) {
-        const uint4 v0 = src[i], v1 = src[i + NUM_THREADS], v2 = src[i + 2 * NUM_THREADS], v3 = src[i + 3 * NUM_THREADS];
-        dst[i] = v0; dst[i + NUM_THREADS] = v1; dst[i + 2 * NUM_THREADS] = v2; dst[i + 3 * NUM_THREADS] = v3;
-      }
-      for (; i < nvec; i += NUM_THREADS) dst[i] = src[i];
-      __syncthreads();
-      if (threadIdx.x == 0) {
+      const int slot = q % RING;
+      if (!mbar_wait(&ring_bar[slot], (q / RING) & 1, &dummy_abort, p.status, 510)) { ok = false; break; }
+      uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_stage[peer]) +
+                     ((static_cast<size_t>(p.rank) * n_sub + c) * p.sub_rows + row0) * row_bytes;
+      bulk_store(dst, smem + slot * PIECE_MAX, bytes);
+      tma_commit_group();
+      if (q % ppj == ppj - 1) {                     // chunk complete: make it visible, then raise its flag
+        tma_wait_group<0>();
         __threadfence_system();
         st_release_sys(reinterpret_cast<int*>(p.peer_flags[peer]) + p.rank * n_sub + c, p.epoch);
+      }
+    }
+    if (!ok) {                                       // drain what is still in flight before leaving
+      tma_wait_group<0>();
+      for (int q = 0; q < total; ++q) {
+        const int slot = q % RING;
+        mbar_drain(&ring_bar[slot], (q / RING) & 1);
+        if (q >= RING) break;
       }
     }
     return;

@@ -122,6 +122,14 @@ class LlamaAttention(nn.Layer):
     def forward(self, x, batch, seq):
         qkv = self.qkv_proj(x)                                   # [tokens, (hq + 2 hkv) * d] local heads
         d, hq, hkv = self.head_dim, self.num_heads, self.num_kv_heads
+        if d == 128 and qkv.is_cuda and qkv.dtype == torch.bfloat16 and K.get_kernel_policy() == "fused" \
+                and qkv.is_contiguous():
+            # rope + attention directly on the packed projection (no slicing, one rope launch)
+            from ..ops import attention
+            cos, sin = K.rope_tables(seq, d, self.config.rope_theta, x.device, True)
+            o = as_tensor(attention.rope_attention_packed(qkv, cos, sin, batch, seq, hq, hkv, True,
+                                                          1.0 / math.sqrt(d)))
+            return self.o_proj(o.reshape([-1, hq * d]))
         qkv = qkv.reshape([batch, seq, hq + 2 * hkv, d])
         q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
         cos, sin = K.rope_tables(seq, d, self.config.rope_theta, x.device, True)

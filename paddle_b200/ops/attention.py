@@ -1,11 +1,11 @@
-"""Flash attention on the sm_100a kernels: autograd wrapper and shape gate."""
+"""Flash attention on the sm_100a kernels: raw launches, autograd wrappers and the fused
+rotary-embedding + attention operator that works in place on a packed qkv projection."""
 from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _lib, native
 from ._lib import c_float, c_int, c_int64, check, ptr, stream
-from . import native
 
 
 def supported(q, k, v) -> bool:
@@ -36,27 +36,27 @@ def fwd(q, k, v, causal, scale):
     return o, lse
 
 
-def bwd(do, q, k, v, o, lse, causal, scale):
-    k_ = _lib.kernels()
-    if not hasattr(k_, "pd_flash_attn_bwd"):
-        raise _lib.NativeLibraryError("pd_flash_attn_bwd is missing from libpd_kernels.so")
+def bwd(do, q, k, v, o, lse, causal, scale, dq=None, dk=None, dv=None):
+    """Gradients of :func:`fwd`.  ``dq/dk/dv`` may be pre-allocated views (e.g. slices of one packed dqkv
+    buffer); they only need dense 128-element heads."""
     q, k, v, o, do = (t if _view_ok(t) else t.contiguous() for t in (q, k, v, o, do))
     B, Sq, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
-    dq = torch.empty((B, Sq, Hq, D), dtype=torch.bfloat16, device=q.device)
-    dk = torch.empty((B, Sk, Hkv, D), dtype=torch.bfloat16, device=q.device)
-    dv = torch.empty((B, Sk, Hkv, D), dtype=torch.bfloat16, device=q.device)
-    dq_acc = torch.zeros((B, Sq, Hq, D), dtype=torch.float32, device=q.device)
-    delta = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
-    g = Hq // Hkv
-    dkv_acc = torch.zeros((2, B, Sk, Hkv, D), dtype=torch.float32, device=q.device) if g > 1 else None
-    rc = k_.pd_flash_attn_bwd(
-        ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(dq_acc), ptr(dkv_acc), ptr(dq), ptr(dk),
+    dev = q.device
+    dq = torch.empty((B, Sq, Hq, D), dtype=torch.bfloat16, device=dev) if dq is None else dq
+    dk = torch.empty((B, Sk, Hkv, D), dtype=torch.bfloat16, device=dev) if dk is None else dk
+    dv = torch.empty((B, Sk, Hkv, D), dtype=torch.bfloat16, device=dev) if dv is None else dv
+    assert _view_ok(dq) and _view_ok(dk) and _view_ok(dv)
+    dq_acc = torch.zeros((B, Sq, Hq, D), dtype=torch.float32, device=dev)
+    delta = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev)
+    rc = _lib.kernels().pd_flash_attn_bwd(
+        ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(dq_acc), ptr(None), ptr(dq), ptr(dk),
         ptr(dv), c_int(B), c_int(Sq), c_int(Sk), c_int(Hq), c_int(Hkv),
         c_int64(q.stride(1)), c_int64(q.stride(0)), c_int64(k.stride(1)), c_int64(k.stride(0)),
         c_int64(v.stride(1)), c_int64(v.stride(0)), c_int64(o.stride(1)), c_int64(o.stride(0)),
-        c_int64(do.stride(1)), c_int64(do.stride(0)),
-        c_float(scale), c_int(1 if causal else 0), ptr(_lib.status_buffer(q.device)), stream())
+        c_int64(do.stride(1)), c_int64(do.stride(0)), c_int64(dq.stride(1)), c_int64(dq.stride(0)),
+        c_int64(dk.stride(1)), c_int64(dk.stride(0)), c_int64(dv.stride(1)), c_int64(dv.stride(0)),
+        c_float(scale), c_int(1 if causal else 0), ptr(_lib.status_buffer(dev)), stream())
     check(rc, "pd_flash_attn_bwd")
     native._count(3)
     return dq, dk, dv
@@ -79,3 +79,42 @@ class _FlashAttnFn(torch.autograd.Function):
 
 def flash_attn_func(q, k, v, causal, scale):
     return _FlashAttnFn.apply(q, k, v, bool(causal), float(scale))
+
+
+class _RopeAttnPackedFn(torch.autograd.Function):
+    """Rotary embedding + attention on a packed projection ``qkv[B*S, (Hq + 2 Hkv) * 128]``.
+
+    Forward rotates the q and k heads inside the projection buffer itself (one launch: q and k heads are
+    adjacent) and runs flash attention on views of that buffer; the un-rotated values are consumed — the
+    producing linear layer never needs its own output again.  Backward lets the attention kernels write
+    dq / dk / dv straight into one packed gradient buffer and un-rotates its q,k heads in place, so no slice,
+    concat, zero-fill or gradient-accumulation kernel is launched for the projection."""
+
+    @staticmethod
+    def forward(ctx, qkv2d, cos, sin, B, S, hq, hkv, causal, scale):
+        qkv = qkv2d.detach().view(B, S, hq + 2 * hkv, 128)
+        rot = qkv[:, :, :hq + hkv]
+        native.rope(rot, cos, sin, None, seq_len=S, half_style=True, out=rot)
+        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
+        o, lse = fwd(q, k, v, causal, scale)
+        ctx.save_for_backward(qkv, o, lse, cos, sin)
+        ctx.meta = (B, S, hq, hkv, causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse, cos, sin = ctx.saved_tensors
+        B, S, hq, hkv, causal, scale = ctx.meta
+        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
+        dqkv = torch.empty_like(qkv)
+        bwd(do, q, k, v, o, lse, causal, scale, dq=dqkv[:, :, :hq], dk=dqkv[:, :, hq:hq + hkv],
+            dv=dqkv[:, :, hq + hkv:])
+        rot = dqkv[:, :, :hq + hkv]
+        native.rope(rot, cos, sin, None, seq_len=S, half_style=True, backward=True, out=rot)
+        return dqkv.view(B * S, -1), None, None, None, None, None, None, None, None
+
+
+def rope_attention_packed(qkv2d, cos, sin, B, S, hq, hkv, causal, scale):
+    """``qkv2d``: contiguous bf16 ``[B*S, (hq + 2*hkv) * 128]`` produced by the qkv projection (its q,k heads are
+    overwritten with the rotated values).  Returns the attention output ``[B, S, hq, 128]``."""
+    return _RopeAttnPackedFn.apply(qkv2d, cos, sin, int(B), int(S), int(hq), int(hkv), bool(causal), float(scale))
