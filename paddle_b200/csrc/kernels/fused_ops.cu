@@ -787,3 +787,45 @@ PD_EXPORT int pd_add_bf16(const void* a, const void* b, void* out, int64_t n, cu
   add_bf16_kernel<<<grid_for((n + 7) >> 3, 256), 256, 0, stream>>>((const bf16*)a, (const bf16*)b, (bf16*)out, n);
   return PD_CHECK_LAUNCH();
 }
+
+// ------------------------------------------------------------------------------------------ allocation-free entry
+// RMSNorm backward for callers that must not allocate device memory (see pd_no_alloc.h).  The per-CTA
+// partial sums of the weight gradient, which pd_rms_norm_bwd takes from the caller, live in a fixed array
+// inside this library instead.
+namespace pd {
+namespace ew {
+constexpr int NA_MAX_PARTS = 128;
+constexpr int NA_MAX_H = 8192;
+static __device__ __align__(256) float g_rms_bwd_scratch[NA_MAX_PARTS * NA_MAX_H];   // 4 MiB per GPU
+}  // namespace ew
+}  // namespace pd
+
+PD_EXPORT int pd_rms_norm_bwd_static(const void* dy, const void* x, const void* w, int w_is_f32,
+                                     const float* inv_rms, void* dx, const void* dx_add, float* dw,
+                                     int dw_accumulate, int64_t rows, int H, cudaStream_t stream) {
+  if (H % 8 != 0 || rows <= 0) return kErrBadShape;
+  if (H > NA_MAX_H || H > 8 * RN_THREADS * RN_MAXIT) return kErrTooLarge;
+  // The array's name is only a host-side handle: the device address is looked up once per device, with that
+  // device current, and passed to the kernels.
+  static float* scratch_of_device[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kErrCuda;
+  if (scratch_of_device[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rms_bwd_scratch) != cudaSuccess || p == nullptr)
+      return kErrCuda;
+    scratch_of_device[dev] = p;
+  }
+  float* partial = scratch_of_device[dev];
+  const int parts = rows < NA_MAX_PARTS ? static_cast<int>(rows) : NA_MAX_PARTS;
+  if (w_is_f32)
+    rms_norm_bwd_kernel<float><<<parts, RN_THREADS, 0, stream>>>(
+        (const bf16*)dy, (const bf16*)x, (const float*)w, inv_rms, (bf16*)dx, (const bf16*)dx_add, partial,
+        static_cast<int>(rows), H);
+  else
+    rms_norm_bwd_kernel<bf16><<<parts, RN_THREADS, 0, stream>>>(
+        (const bf16*)dy, (const bf16*)x, (const bf16*)w, inv_rms, (bf16*)dx, (const bf16*)dx_add, partial,
+        static_cast<int>(rows), H);
+  column_sum_kernel<<<(H + 255) / 256, 256, 0, stream>>>(partial, dw, parts, H, dw_accumulate);
+  return PD_CHECK_LAUNCH();
+}
