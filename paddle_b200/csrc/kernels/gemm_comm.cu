@@ -115,8 +115,35 @@ __device__ __forceinline__ void load_stage(const CUtensorMap* tmA, const CUtenso
   }
 }
 
+template <bool A_MN>
+__device__ __forceinline__ void load_a(const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int m0, int k0,
+                                       bool use3d = false) {
+  if (!A_MN) {
+    tma_load_2d(dst, tm, bar, k0, m0);
+  } else if (use3d) {
+    tma_load_3d(dst, tm, bar, 0, k0, m0 >> 6);
+  } else {
+#pragma unroll
+    for (int c = 0; c < BM / 64; ++c) tma_load_2d(dst + c * 8192, tm, bar, m0 + c * 64, k0);
+  }
+}
+template <bool B_MN>
+__device__ __forceinline__ void load_b(const CUtensorMap* tm, uint8_t* dst, uint64_t* bar, int n0, int k0,
+                                       bool use3d = false) {
+  if (!B_MN) {
+    tma_load_2d(dst, tm, bar, k0, n0);
+  } else if (use3d) {
+    tma_load_3d(dst, tm, bar, 0, k0, n0 >> 6);
+  } else {
+#pragma unroll
+    for (int c = 0; c < BN / 64; ++c) tma_load_2d(dst + c * 8192, tm, bar, n0 + c * 64, k0);
+  }
+}
+
 // ============================================================================================ ag_gemm
 struct AGParams {
+  int gathered_b;      // wait_mode 1 only: the gathered (token-major) operand is B instead of A
+  int mn3d;            // bit0/1/2: the A / B / local map is the 3-D (one box per operand) form
   int M, N, K;
   int rank, nranks;
   int rows_per_rank;   // token rows contributed by each rank
@@ -140,7 +167,8 @@ struct AGParams {
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ AGParams p) {
+               const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmL,
+               const __grid_constant__ AGParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -158,13 +186,14 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // memory -> the peer's staging buffer (cp.async.bulk store over NVLink).  Many KB stay in flight per CTA
     // without occupying load/store units, so a handful of CTAs saturate the link.
     if (p.skip_push || threadIdx.x != 0) return;
-    constexpr int RING = 8, LOOKAHEAD = 4, PIECE_MAX = 16384;
+    constexpr int RING = 12, LOOKAHEAD = 8, PIECE_MAX = 16384, FLAG_LAG = 3;
     uint64_t* ring_bar = reinterpret_cast<uint64_t*>(smem + RING * PIECE_MAX);
     for (int i = 0; i < RING; ++i) mbar_init(&ring_bar[i], 1);
     fence_mbar_init();
     int dummy_abort = 0;
     const int* ack_local = reinterpret_cast<const int*>(p.peer_ack[p.rank]);
-    const int jobs = p.nranks * n_sub;
+    const int npeers = p.nranks - 1;
+    const int jobs = npeers * n_sub;                 // the local shard is read in place by the GEMM
     const int my_jobs = static_cast<int>(blockIdx.x) < jobs ? (jobs - static_cast<int>(blockIdx.x) + p.n_comm - 1) / p.n_comm : 0;
     const uint32_t row_bytes = static_cast<uint32_t>(p.row_elems) * 2;
     const int rows_per_piece = row_bytes >= PIECE_MAX ? 1 : PIECE_MAX / row_bytes;
@@ -172,8 +201,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int total = my_jobs * ppj;
     auto piece_info = [&](int q, int& peer, int& c, int& row0, uint32_t& bytes) {
       const int j = static_cast<int>(blockIdx.x) + (q / ppj) * p.n_comm;
-      c = j / p.nranks;
-      peer = (p.rank + j % p.nranks) % p.nranks;
+      c = j / npeers;
+      peer = (p.rank + 1 + j % npeers) % p.nranks;
       row0 = (q % ppj) * rows_per_piece;
       const int nrows = min(rows_per_piece, p.sub_rows - row0);
       bytes = static_cast<uint32_t>(nrows) * row_bytes;
@@ -191,6 +220,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int q = 0; q < total && q < LOOKAHEAD; ++q) issue_load(q);
     unsigned checked = 0;
     bool ok = true;
+    int* pend_flag = nullptr;
+    int pend_q = 0;
     for (int q = 0; q < total && ok; ++q) {
       if (q + LOOKAHEAD < total) {
         tma_wait_group_read<LOOKAHEAD - 1>();      // the store that last read this slot has drained it
@@ -210,11 +241,28 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                      ((static_cast<size_t>(p.rank) * n_sub + c) * p.sub_rows + row0) * row_bytes;
       bulk_store(dst, smem + slot * PIECE_MAX, bytes);
       tma_commit_group();
-      if (q % ppj == ppj - 1) {                     // chunk complete: make it visible, then raise its flag
-        tma_wait_group<0>();
+      // A chunk's flag is raised FLAG_LAG pieces after its last store was issued: by then waiting for "all but
+      // the newest FLAG_LAG groups" costs nothing and guarantees the chunk has fully landed.
+      if (pend_flag != nullptr && q - pend_q >= FLAG_LAG) {
+        tma_wait_group<FLAG_LAG>();
         __threadfence_system();
-        st_release_sys(reinterpret_cast<int*>(p.peer_flags[peer]) + p.rank * n_sub + c, p.epoch);
+        st_release_sys(pend_flag, p.epoch);
+        pend_flag = nullptr;
       }
+      if (q % ppj == ppj - 1) {
+        if (pend_flag != nullptr) {                 // (only when a chunk has fewer than FLAG_LAG pieces)
+          tma_wait_group<1>();
+          __threadfence_system();
+          st_release_sys(pend_flag, p.epoch);
+        }
+        pend_flag = reinterpret_cast<int*>(p.peer_flags[peer]) + p.rank * n_sub + c;
+        pend_q = q;
+      }
+    }
+    if (ok && pend_flag != nullptr) {
+      tma_wait_group<0>();
+      __threadfence_system();
+      st_release_sys(pend_flag, p.epoch);
     }
     if (!ok) {                                       // drain what is still in flight before leaving
       tma_wait_group<0>();
@@ -247,6 +295,14 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       prefetch_tmap(&tmA);
       prefetch_tmap(&tmB);
+      prefetch_tmap(&tmL);
+      // everything the loop needs is copied out of the parameter block once: a single thread issues every TMA
+      // of this CTA, and re-reading parameters after each asm statement would put it on the critical path
+      const int wait_mode = p.wait_mode, rank = p.rank, rows_per_rank = p.rows_per_rank, sub_rows = p.sub_rows;
+      const int epoch = p.epoch, gathered_b = p.gathered_b, local_row0 = p.rank * p.rows_per_rank;
+      const bool a3d = (p.mn3d & 1) != 0, b3d = (p.mn3d & 2) != 0, l3d = (p.mn3d & 4) != 0;
+      const unsigned long long wait_ns = p.wait_ns;
+      int* const status = p.status;
       int s = 0;
       uint32_t ph = 0, armed = 0, armed_parity = 0;
       bool ok = true;
@@ -254,33 +310,51 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int t = cta; t < num_tiles && ok; t += nct) {
         int tm, tn;
         raster(t, tiles_m, tiles_n, tm, tn);
-        if (p.wait_mode == 0) tm = (tm + p.rank * tiles_per_src) % tiles_m;   // local shard first
+        if (wait_mode == 0) tm = (tm + rank * tiles_per_src) % tiles_m;   // local shard first
         const int m0 = tm * BM, n0 = tn * BN;
-        if (p.wait_mode == 0) {
-          const int chunk = m0 / p.sub_rows;      // == src * n_sub + sub-chunk
-          if (chunk != last_chunk) {
-            if (!flag_wait_ge(flags_local + chunk, p.epoch, p.wait_ns, p.status, 600)) { ok = false; *abort_flag = 1; break; }
+        // rows of this rank's own shard are read straight from x_shard (map tmL): no copy, no wait
+        bool local_tile = false;
+        if (wait_mode == 0) {
+          local_tile = (m0 / rows_per_rank) == rank;
+          const int chunk = m0 / sub_rows;      // == src * n_sub + sub-chunk
+          if (!local_tile && chunk != last_chunk) {
+            if (!flag_wait_ge(flags_local + chunk, epoch, wait_ns, status, 600)) { ok = false; *abort_flag = 1; break; }
             fence_proxy_async_all();
             last_chunk = chunk;
           }
         }
         for (int kbi = 0; kbi < KB; ++kbi) {
           int kb = kbi;
-          if (p.wait_mode == 1) {
-            kb = (kbi + p.rank * kb_per_src) % KB;
-            const int chunk = (kb * BK) / p.sub_rows;
-            if (chunk != last_chunk) {
-              if (!flag_wait_ge(flags_local + chunk, p.epoch, p.wait_ns, p.status, 610)) { ok = false; *abort_flag = 1; break; }
+          bool local_k = false;
+          if (wait_mode == 1) {
+            kb = kbi + rank * kb_per_src;
+            if (kb >= KB) kb -= KB;
+            local_k = ((kb * BK) / rows_per_rank) == rank;
+            const int chunk = (kb * BK) / sub_rows;
+            if (!local_k && chunk != last_chunk) {
+              if (!flag_wait_ge(flags_local + chunk, epoch, wait_ns, status, 610)) { ok = false; *abort_flag = 1; break; }
               fence_proxy_async_all();
               last_chunk = chunk;
             }
           }
-          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, p.status, 100 + s)) { ok = false; break; }
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, status, 100 + s)) { ok = false; break; }
           mbar_expect_tx(&bars->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
           armed |= 1u << s;
           armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
-          load_stage<A_MN, B_MN>(&tmA, &tmB, sA + s * A_STAGE_BYTES, sB + s * B_STAGE_BYTES, &bars->full[s], m0, n0,
-                                 kb * BK);
+          uint8_t* a_dst = sA + s * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+          const int k0 = kb * BK;
+          if (wait_mode == 0) {
+            if (local_tile) load_a<A_MN>(&tmL, a_dst, &bars->full[s], m0 - local_row0, k0);
+            else load_a<A_MN>(&tmA, a_dst, &bars->full[s], m0, k0);
+            load_b<B_MN>(&tmB, b_dst, &bars->full[s], n0, k0, b3d);
+          } else {
+            const int k0l = k0 - local_row0;
+            if (local_k && !gathered_b) load_a<A_MN>(&tmL, a_dst, &bars->full[s], m0, k0l, l3d);
+            else load_a<A_MN>(&tmA, a_dst, &bars->full[s], m0, k0, a3d);
+            if (local_k && gathered_b) load_b<B_MN>(&tmL, b_dst, &bars->full[s], n0, k0l, l3d);
+            else load_b<B_MN>(&tmB, b_dst, &bars->full[s], n0, k0, b3d);
+          }
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -376,6 +450,7 @@ struct RSParams {
   int rank, nranks;
   int rows_per_rank;
   int epoch;
+  int mn3d;
   unsigned long long peer_counters[MAX_RANKS];  // int32 [tiles_per_dst * tiles_n] on every rank
   unsigned long long peer_ack[MAX_RANKS];       // int32 [nranks] on every rank
   const void* recv_local;                       // bf16 [nranks][rows_per_rank][N]
@@ -430,17 +505,20 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0, armed = 0, armed_parity = 0;
       bool ok = true;
+      const bool a3d = (p.mn3d & 1) != 0, b3d = (p.mn3d & 2) != 0;
+      const int rows_per_rank = p.rows_per_rank;
+      int* const status = p.status;
       for (int t = cta; t < num_tiles && ok; t += nct) {
         int d, tml, tn;
         decode(t, d, tml, tn);
-        const int m0 = d * p.rows_per_rank + tml * BM, n0 = tn * BN;
+        const int m0 = d * rows_per_rank + tml * BM, n0 = tn * BN;
         for (int kb = 0; kb < KB; ++kb) {
-          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, p.status, 100 + s)) { ok = false; break; }
+          if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, status, 100 + s)) { ok = false; break; }
           mbar_expect_tx(&bars->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
           armed |= 1u << s;
           armed_parity = (armed_parity & ~(1u << s)) | (ph << s);
-          load_stage<A_MN, B_MN>(&tmA, &tmB, sA + s * A_STAGE_BYTES, sB + s * B_STAGE_BYTES, &bars->full[s], m0, n0,
-                                 kb * BK);
+          load_a<A_MN>(&tmA, sA + s * A_STAGE_BYTES, &bars->full[s], m0, kb * BK, a3d);
+          load_b<B_MN>(&tmB, sB + s * B_STAGE_BYTES, &bars->full[s], n0, kb * BK, b3d);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
@@ -460,6 +538,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int it = 0, chunk_counter = 0;
     unsigned checked = 0;
     bool alive = true;
+    int* pend_counter = nullptr;
     for (int t = cta; t < num_tiles; t += nct, ++it) {
       int d, tml, tn;
       decode(t, d, tml, tn);
@@ -510,12 +589,22 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tma_store_2d(&maps.dst[d], stage, n0 + c * CW, tml * BM);
           tma_commit_group();
           if (c == NCHUNK - 1) {
-            tma_wait_group<0>();                 // the partial tile has fully landed in rank d's memory
-            __threadfence_system();
-            red_release_sys_add(reinterpret_cast<int*>(p.peer_counters[d]) + tml * tiles_n + tn, 1);
+            // The arrival counter of a tile is bumped one tile later: by then "all but the newest NCHUNK
+            // stores have completed" holds without stalling, and it means the tile has landed on rank d.
+            if (pend_counter != nullptr) {
+              tma_wait_group<NCHUNK>();
+              __threadfence_system();
+              red_release_sys_add(pend_counter, 1);
+            }
+            pend_counter = reinterpret_cast<int*>(p.peer_counters[d]) + tml * tiles_n + tn;
           }
         }
       }
+    }
+    if (epi_tid == 0 && pend_counter != nullptr) {
+      tma_wait_group<0>();
+      __threadfence_system();
+      red_release_sys_add(pend_counter, 1);
     }
     // ---- reduce phase: out[tile] = sum over sources of the partial tiles received for my shard
     const int* counters = reinterpret_cast<const int*>(p.peer_counters[p.rank]);
@@ -532,26 +621,42 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (!okd) { alive = false; break; }
       const int col = tn * BN + (epi_tid & 31) * 8;
       if (col < p.N) {
-        for (int rr = epi_tid >> 5; rr < BM; rr += 4) {
-          const int row = tml * BM + rr;
-          if (row >= p.rows_per_rank) break;
-          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int s = 0; s < p.nranks; ++s) {
-            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(recv + s * slab + static_cast<size_t>(row) * p.N + col));
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+        // 4 rows x nranks sources of 16-byte loads are issued before any is consumed (latency hiding)
+        constexpr int RU = 4;
+        for (int rb = epi_tid >> 5; rb < BM; rb += 4 * RU) {
+          uint4 v[RU][MAX_RANKS];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __bfloat1622float2(h[e]);
-              acc8[2 * e] += f.x;
-              acc8[2 * e + 1] += f.y;
-            }
+          for (int u = 0; u < RU; ++u) {
+            const int row = tml * BM + rb + 4 * u;
+#pragma unroll
+            for (int s = 0; s < MAX_RANKS; ++s)
+              if (s < p.nranks && row < p.rows_per_rank)
+                v[u][s] = __ldcg(reinterpret_cast<const uint4*>(recv + s * slab + static_cast<size_t>(row) * p.N + col));
           }
-          uint4 o;
-          o.x = pack_bf16x2(acc8[0], acc8[1]);
-          o.y = pack_bf16x2(acc8[2], acc8[3]);
-          o.z = pack_bf16x2(acc8[4], acc8[5]);
-          o.w = pack_bf16x2(acc8[6], acc8[7]);
-          *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * p.N + col) = o;
+#pragma unroll
+          for (int u = 0; u < RU; ++u) {
+            const int row = tml * BM + rb + 4 * u;
+            if (row >= p.rows_per_rank) continue;
+            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int s = 0; s < MAX_RANKS; ++s) {
+              if (s < p.nranks) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[u][s]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __bfloat1622float2(h[e]);
+                  acc8[2 * e] += f.x;
+                  acc8[2 * e + 1] += f.y;
+                }
+              }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc8[0], acc8[1]);
+            o.y = pack_bf16x2(acc8[2], acc8[3]);
+            o.z = pack_bf16x2(acc8[4], acc8[5]);
+            o.w = pack_bf16x2(acc8[6], acc8[7]);
+            *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * p.N + col) = o;
+          }
         }
       }
     }
@@ -574,12 +679,14 @@ static int set_smem(KFn k) {
 }
 
 static bool make_ab_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, const void* B, int M, int N, int K, int lda,
-                         int ldb, int a_mn, int b_mn) {
+                         int ldb, int a_mn, int b_mn, int* mn3d) {
   bool ok = true;
+  int a3 = 0, b3 = 0;
   if (!a_mn) ok &= encode_tmap_2d(tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, K, M, uint64_t(lda) * 2, BK, BM);
-  else ok &= encode_tmap_2d(tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, M, K, uint64_t(lda) * 2, 64, BK);
+  else ok &= encode_tmap_mn(tmA, A, M, K, uint64_t(lda) * 2, BM / 64, BK, &a3);
   if (!b_mn) ok &= encode_tmap_2d(tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, K, N, uint64_t(ldb) * 2, BK, BN);
-  else ok &= encode_tmap_2d(tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, N, K, uint64_t(ldb) * 2, 64, BK);
+  else ok &= encode_tmap_mn(tmB, B, N, K, uint64_t(ldb) * 2, BN / 64, BK, &b3);
+  *mn3d = a3 | (b3 << 1);
   return ok;
 }
 
@@ -589,7 +696,7 @@ static bool make_ab_maps(CUtensorMap* tmA, CUtensorMap* tmB, const void* A, cons
 // All-gather -> GEMM.  A / B are the operand pointers the GEMM reads (the gathered one points into the LOCAL
 // staging buffer peer_stage[rank]); see AGParams for the rest.  epi: 0 bf16 store, 1 fp32 store, 2 fp32 accumulate.
 PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                         int a_mn, int b_mn, int epi, const void* x_shard, int rows_per_rank, int sub_rows,
+                         int a_mn, int b_mn, int epi, int gathered_b, const void* x_shard, int rows_per_rank, int sub_rows,
                          int row_elems, int rank, int nranks, int n_comm, int epoch, int wait_mode, int skip_push, int do_ack,
                          const unsigned long long* peer_stage, const unsigned long long* peer_flags,
                          const unsigned long long* peer_ack, int* local_done, int done_base, int wait_ms, int* status,
@@ -600,14 +707,24 @@ PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, in
   if (rows_per_rank % sub_rows || sub_rows % BM || (wait_mode == 0 && rows_per_rank % BM)) return kErrBadShape;
   if ((lda % 8) || (ldb % 8) || (epi == 0 ? (ldc % 8) : (ldc % 4)) || (row_elems % 8)) return kErrAlignment;
   CUtensorMap tmA, tmB, tmC;
-  bool ok = make_ab_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn, b_mn);
+  int mn3d = 0, l3 = 0;
+  bool ok = make_ab_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn, b_mn, &mn3d);
   if (epi == 0) ok &= encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, C, N, M, uint64_t(ldc) * 2, 64, BM);
   else ok &= encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, C, N, M, uint64_t(ldc) * 4, 32, BM);
+  // map over this rank's own shard, in the role the gathered operand plays in this GEMM
+  CUtensorMap tmL;
+  if (wait_mode == 0) {
+    ok &= encode_tmap_2d(&tmL, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, x_shard, K, rows_per_rank, uint64_t(row_elems) * 2, BK, BM);
+  } else if (!gathered_b) {
+    ok &= encode_tmap_mn(&tmL, x_shard, M, rows_per_rank, uint64_t(row_elems) * 2, BM / 64, BK, &l3);
+  } else {
+    ok &= encode_tmap_mn(&tmL, x_shard, N, rows_per_rank, uint64_t(row_elems) * 2, BN / 64, BK, &l3);
+  }
   if (!ok) return kErrTensorMap;
   AGParams p;
   p.M = M; p.N = N; p.K = K; p.rank = rank; p.nranks = nranks; p.rows_per_rank = rows_per_rank;
   p.sub_rows = sub_rows; p.row_elems = row_elems; p.n_comm = n_comm; p.epoch = epoch; p.wait_mode = wait_mode;
-  p.skip_push = skip_push; p.do_ack = do_ack; p.x_shard = x_shard; p.local_done = local_done; p.status = status;
+  p.gathered_b = gathered_b; p.mn3d = mn3d | (l3 << 2); p.skip_push = skip_push; p.do_ack = do_ack; p.x_shard = x_shard; p.local_done = local_done; p.status = status;
   p.wait_ns = static_cast<unsigned long long>(wait_ms) * 1000000ull;
   for (int i = 0; i < MAX_RANKS; ++i) {
     p.peer_stage[i] = i < nranks ? peer_stage[i] : 0;
@@ -628,7 +745,7 @@ PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, in
     static bool cfg = false;                                                                        \
     auto kfn = ag_gemm_kernel<AM, BM_, E>;                                                          \
     if (!cfg) { if (set_smem(kfn)) return kErrCuda; cfg = true; }                                   \
-    kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);                               \
+    kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, tmL, p);                            \
     return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;                                \
   }
   PD_AG_CASE(0, 1, 0)   // forward:  Y = AG(X) W            (tokens = M)
@@ -651,7 +768,8 @@ PD_EXPORT int pd_gemm_rs(const void* A, const void* B, void* out, int M, int N, 
   if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > MAX_RANKS || M != rows_per_rank * nranks) return kErrBadShape;
   if ((lda % 8) || (ldb % 8) || (N % 8)) return kErrAlignment;
   CUtensorMap tmA, tmB;
-  if (!make_ab_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn, b_mn)) return kErrTensorMap;
+  int mn3d = 0;
+  if (!make_ab_maps(&tmA, &tmB, A, B, M, N, K, lda, ldb, a_mn, b_mn, &mn3d)) return kErrTensorMap;
   RSMaps maps;
   const size_t slab_bytes = static_cast<size_t>(rows_per_rank) * N * 2;
   for (int d = 0; d < MAX_RANKS; ++d) {
@@ -662,6 +780,7 @@ PD_EXPORT int pd_gemm_rs(const void* A, const void* B, void* out, int M, int N, 
   }
   RSParams p;
   p.M = M; p.N = N; p.K = K; p.rank = rank; p.nranks = nranks; p.rows_per_rank = rows_per_rank; p.epoch = epoch;
+  p.mn3d = mn3d;
   p.recv_local = reinterpret_cast<const void*>(peer_recv[rank]);
   p.out = out; p.local_done = local_done; p.status = status;
   p.wait_ns = static_cast<unsigned long long>(wait_ms) * 1000000ull;

@@ -55,7 +55,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int* status) {
+                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int mn3d, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -114,6 +114,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* b_dst = sB + s * B_STAGE_BYTES;
           if (!A_MN) {
             tma_load_2d(a_dst, &tmA, &bars->full[s], k0, m0);            // box {64 k, 128 m}
+          } else if (mn3d & 1) {                                           // one box {64 m, 64 k, 2 chunks}
+            tma_load_3d(a_dst, &tmA, &bars->full[s], 0, k0, m0 >> 6);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)                              // boxes {64 m, 64 k}
@@ -121,6 +123,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           if (!B_MN) {
             tma_load_2d(b_dst, &tmB, &bars->full[s], k0, n0);            // box {64 k, 256 n}
+          } else if (mn3d & 2) {                                           // one box {64 n, 64 k, 4 chunks}
+            tma_load_3d(b_dst, &tmB, &bars->full[s], 0, k0, n0 >> 6);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)                              // boxes {64 n, 64 k}
@@ -257,7 +261,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                          int M, int N, int K, int* status, cudaStream_t stream, int max_ctas) {
+                          int M, int N, int K, int mn3d, int* status, cudaStream_t stream, int max_ctas) {
   auto kfn = gemm_bf16_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -268,7 +272,7 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, M, N, K, status);
+  kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, M, N, K, mn3d, status);
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }
 
@@ -292,14 +296,15 @@ PD_EXPORT int pd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, 
   if ((lda % 8) || (ldb % 8) || (epi == kStoreBf16 ? (ldc % 8) : (ldc % 4))) return kErrAlignment;
   CUtensorMap tmA, tmB, tmC;
   bool ok = true;
+  int a3d = 0, b3d = 0;
   if (!a_mn_major)
     ok &= encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, K, M, uint64_t(lda) * 2, BK, BM);
   else
-    ok &= encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, M, K, uint64_t(lda) * 2, 64, BK);
+    ok &= encode_tmap_mn(&tmA, A, M, K, uint64_t(lda) * 2, BM / 64, BK, &a3d);
   if (!b_mn_major)
     ok &= encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, K, N, uint64_t(ldb) * 2, BK, BN);
   else
-    ok &= encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, N, K, uint64_t(ldb) * 2, 64, BK);
+    ok &= encode_tmap_mn(&tmB, B, N, K, uint64_t(ldb) * 2, BN / 64, BK, &b3d);
   if (epi == kStoreBf16)
     ok &= encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, C, N, M, uint64_t(ldc) * 2, 64, BM);
   else
@@ -308,7 +313,7 @@ PD_EXPORT int pd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, 
 
 #define PD_GEMM_CASE(AM, BM_, E)                                                                   \
   if (a_mn_major == AM && b_mn_major == BM_ && epi == E)                                           \
-    return launch_variant<AM, BM_, E>(tmA, tmB, tmC, M, N, K, status, stream, max_ctas);
+    return launch_variant<AM, BM_, E>(tmA, tmB, tmC, M, N, K, a3d | (b3d << 1), status, stream, max_ctas);
   PD_GEMM_CASE(0, 0, 0) PD_GEMM_CASE(0, 1, 0) PD_GEMM_CASE(1, 0, 0) PD_GEMM_CASE(1, 1, 0)
   PD_GEMM_CASE(0, 0, 1) PD_GEMM_CASE(0, 1, 1) PD_GEMM_CASE(1, 0, 1) PD_GEMM_CASE(1, 1, 1)
   PD_GEMM_CASE(0, 0, 2) PD_GEMM_CASE(0, 1, 2) PD_GEMM_CASE(1, 0, 2) PD_GEMM_CASE(1, 1, 2)

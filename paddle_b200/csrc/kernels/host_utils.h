@@ -69,6 +69,23 @@ inline bool encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, const void*
   return encode_tmap(out, dt, 2, base, dims, strides, box, swz);
 }
 
+// Map for an MN-major bf16 operand stored [k_extent rows][mn_extent contiguous].  When mn_extent is a multiple of
+// 64 the matrix is viewed as [mn/64][k][64] so that ONE box {64, box_k, chunks} fills `chunks` consecutive
+// 128B-swizzled 64-column slabs of shared memory (*is3d = 1); otherwise a plain 2-D map with box {64, box_k}
+// is produced and the kernel issues one load per slab.
+inline bool encode_tmap_mn(CUtensorMap* out, const void* base, uint64_t mn_extent, uint64_t k_extent,
+                           uint64_t row_stride_bytes, uint32_t chunks, uint32_t box_k, int* is3d) {
+  if (mn_extent % 64 == 0) {
+    uint64_t dims[3] = {64, k_extent, mn_extent / 64};
+    uint64_t strides[2] = {row_stride_bytes, 128};
+    uint32_t box[3] = {64, box_k, chunks};
+    *is3d = 1;
+    return encode_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  *is3d = 0;
+  return encode_tmap_2d(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, mn_extent, k_extent, row_stride_bytes, 64, box_k);
+}
+
 inline int sm_count() {
   static int n = 0;
   if (n == 0) {

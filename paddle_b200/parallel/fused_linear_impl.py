@@ -96,7 +96,7 @@ def _ag_ok(rows):
 
 
 # ------------------------------------------------------------------------------------------ raw launches
-def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode, push=True, ack=True):
+def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode, push=True, ack=True, gathered_b=False):
     """out (=|+=) op(A) op(B) where one operand is the gathered matrix staged in ``slot``."""
     if push:
         slot.epoch += 1
@@ -104,7 +104,7 @@ def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode
     gemm_ctas = min(_sms() - N_COMM, tiles)
     rc = _lib.kernels().pd_ag_gemm(
         ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
-        c_int(out.stride(0)), c_int(a_mn), c_int(b_mn), c_int(epi), ptr(x_shard), c_int(slot.rows), c_int(SUB_ROWS),
+        c_int(out.stride(0)), c_int(a_mn), c_int(b_mn), c_int(epi), c_int(1 if gathered_b else 0), ptr(x_shard), c_int(slot.rows), c_int(SUB_ROWS),
         c_int(slot.row_elems), c_int(group.rank), c_int(group.nranks), c_int(N_COMM), c_int(slot.epoch),
         c_int(wait_mode), c_int(0 if push else 1), c_int(1 if ack else 0), slot.p_stage, slot.p_flags, slot.p_ack,
         ptr(slot.done), c_int(slot.done_base), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
@@ -126,17 +126,17 @@ def gemm_rs(slot, group, a, b, out, M, N, K, a_mn, b_mn):
     return out
 
 
-def _wgrad(weight, a, b, M, N, K, slot, group, x_shard, push, ack):
+def _wgrad(weight, a, b, M, N, K, slot, group, x_shard, push, ack, gathered_b=False):
     """dW (+)= A^T B with tokens as the reduction dimension; straight into main_grad when present."""
     mg = getattr(weight, "main_grad", None)
     if mg is not None:
-        ag_gemm(slot, group, x_shard, a, b, mg, M, N, K, 1, 1, 2, 1, push, ack)
+        ag_gemm(slot, group, x_shard, a, b, mg, M, N, K, 1, 1, 2, 1, push, ack, gathered_b)
         hook = getattr(weight, "_main_grad_ready_hook", None)
         if hook is not None:
             hook(weight)
         return None
     dw = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
-    ag_gemm(slot, group, x_shard, a, b, dw, M, N, K, 1, 1, 0, 1, push, ack)
+    ag_gemm(slot, group, x_shard, a, b, dw, M, N, K, 1, 1, 0, 1, push, ack, gathered_b)
     return dw
 
 
@@ -207,9 +207,9 @@ class _LinearReduceScatter(torch.autograd.Function):
             # dX = all_gather(dY) W^T ; the gathered dY stays staged for the weight gradient
             ag_gemm(slot, group, dy, slot.stage, weight, dx, T, K, N, 0, 0, 0, 0, push=True, ack=not need_dw)
             if need_dw:
-                dw = _wgrad(ctx.weight_ref, x, slot.stage, K, N, T, slot, group, dy, False, True)
+                dw = _wgrad(ctx.weight_ref, x, slot.stage, K, N, T, slot, group, dy, False, True, True)
         elif need_dw:
-            dw = _wgrad(ctx.weight_ref, x, slot.stage, K, N, T, slot, group, dy, True, True)
+            dw = _wgrad(ctx.weight_ref, x, slot.stage, K, N, T, slot, group, dy, True, True, True)
         return dx, dw, None
 
 
