@@ -15,6 +15,7 @@ from .optimizer import L2Decay, Optimizer
 
 class AdamW(Optimizer):
     _accumulator_names = ("moment1", "moment2", "beta1_pow_acc", "beta2_pow_acc")
+    _handles_skip = True
 
     def __init__(self, learning_rate=0.001, beta1=0.9, beta2=0.999, epsilon=1e-8, parameters=None, weight_decay=0.01,
                  lr_ratio=None, apply_decay_param_fun=None, grad_clip=None, lazy_mode=False, multi_precision=False,

@@ -30,6 +30,7 @@ class L1Decay(L2Decay):
 
 class Optimizer:
     _accumulator_names: tuple = ()
+    _handles_skip = False   # True when the update kernels read the device-side skip flag themselves
 
     def __init__(self, learning_rate=0.001, parameters=None, weight_decay=None, grad_clip=None, name=None,
                  multi_precision=False):
@@ -129,6 +130,8 @@ class Optimizer:
     def step(self):
         pgs = self._collect()
         if not pgs:
+            return
+        if self._skip_flag is not None and not self._handles_skip and int(self._skip_flag.item()) != 0:
             return
         self._create_accumulators([p for p, _, _ in pgs])
         grad_scale = self._aux_grad_scale

@@ -1,0 +1,170 @@
+"""API surface on CPU: Tensor semantics, Layer naming/state dict, optimizers vs formulas, save/load format,
+amp scaler, jit cache, profiler scheduler, io, hapi."""
+import os
+import pickle
+
+import numpy as np
+import pytest
+import torch
+
+import paddle_b200 as paddle
+
+
+def test_tensor_paddle_semantics():
+    x = paddle.to_tensor([[1., 2., 3.], [4., 5., 6.]])
+    assert x.shape == [2, 3] and x.stop_gradient
+    assert x.transpose([1, 0]).shape == [3, 2]
+    assert [t.shape for t in x.split(3, axis=1)] == [[2, 1]] * 3
+    assert np.allclose(x.max(axis=1).numpy(), [3, 6])
+    assert x.astype("int64").dtype == paddle.int64
+    y = paddle.matmul(x, x, transpose_y=True)
+    assert y.shape == [2, 2]
+    x.stop_gradient = False
+    (x * x).sum().backward()
+    assert np.allclose(x.grad.numpy(), 2 * x.numpy())
+    x.clear_gradient()
+    assert float(x.grad.sum()) == 0.0
+    assert isinstance(paddle.concat([x, x], axis=0), paddle.Tensor)
+    assert paddle.arange(5).dtype == paddle.int64 and paddle.full([2], 1.5).dtype == paddle.float32
+
+
+def test_layer_naming_and_state_dict():
+    with paddle.utils.unique_name.guard():
+        net = paddle.nn.Sequential(paddle.nn.Linear(4, 8), paddle.nn.ReLU(), paddle.nn.Linear(8, 2))
+    names = [p.name for p in net.parameters()]
+    assert names == ["linear_0.w_0", "linear_0.b_0", "linear_1.w_0", "linear_1.b_0"]
+    assert list(net.state_dict().keys()) == ["0.weight", "0.bias", "2.weight", "2.bias"]
+    assert net[0].weight.shape == [4, 8]          # [in, out]
+    seen = []
+    h = net.register_forward_post_hook(lambda l, i, o: seen.append(o.shape))
+    net(paddle.ones([3, 4]))
+    h.remove()
+    assert seen == [[3, 2]]
+
+
+def test_adamw_matches_formula_and_state_keys():
+    with paddle.utils.unique_name.guard():
+        l = paddle.nn.Linear(3, 2)
+    w0 = l.weight.detach().clone()
+    opt = paddle.optimizer.AdamW(0.1, parameters=l.parameters(), weight_decay=0.01, beta1=0.9, beta2=0.99)
+    l(paddle.ones([1, 3])).sum().backward()
+    g = l.weight.grad.clone()
+    opt.step()
+    m = 0.1 * g
+    v = 0.01 * g * g
+    ref = w0 * (1 - 0.1 * 0.01) - 0.1 / (1 - 0.9) * m / (v.sqrt() / (1 - 0.99) ** 0.5 + 1e-8)
+    assert torch.allclose(l.weight.detach(), ref, atol=1e-6)
+    sd = opt.state_dict()
+    assert {"linear_0.w_0_moment1_0", "linear_0.w_0_moment2_0", "linear_0.w_0_beta1_pow_acc_0",
+            "linear_0.b_0_beta2_pow_acc_0"} <= set(sd)
+    assert abs(float(sd["linear_0.w_0_beta1_pow_acc_0"]) - 0.81) < 1e-6
+
+
+def test_save_load_format(tmp_path):
+    with paddle.utils.unique_name.guard():
+        l = paddle.nn.Linear(3, 2)
+    l.to(dtype="bfloat16")
+    opt = paddle.optimizer.AdamW(0.1, parameters=l.parameters(), multi_precision=True)
+    l(paddle.ones([1, 3]).astype("bfloat16")).sum().backward()
+    opt.step()
+    p = str(tmp_path / "m.pdparams")
+    paddle.save(l.state_dict(), p)
+    raw = pickle.load(open(p, "rb"))
+    assert raw["StructuredToParameterName@@"] == {"weight": "linear_0.w_0", "bias": "linear_0.b_0"}
+    assert isinstance(raw["weight"], np.ndarray) and raw["weight"].dtype == np.uint16     # bf16 bit pattern
+    back = paddle.load(p)
+    assert back["weight"].dtype == paddle.bfloat16 and torch.equal(back["weight"], l.weight.detach())
+    po = str(tmp_path / "m.pdopt")
+    paddle.save(opt.state_dict(), po)
+    rawo = pickle.load(open(po, "rb"))
+    assert isinstance(rawo["master_weights"]["linear_0.w_0"], tuple)          # (name, ndarray)
+    assert rawo["master_weights"]["linear_0.w_0"][0] == "linear_0.w_0_fp32_master_0"
+    opt2 = paddle.optimizer.AdamW(0.1, parameters=l.parameters(), multi_precision=True)
+    opt2.set_state_dict(paddle.load(po))
+    l(paddle.ones([1, 3]).astype("bfloat16")).sum().backward()
+    opt2.step()
+    assert torch.allclose(opt2._master_weights["linear_0.w_0"], opt2._master_weights["linear_0.w_0"])
+    # protocol 2 big-array split
+    big = {"w": paddle.zeros([10])}
+    paddle.save(big, str(tmp_path / "b.pdparams"), protocol=2)
+    assert paddle.load(str(tmp_path / "b.pdparams"))["w"].shape == [10]
+
+
+def test_grad_scaler_skips_on_inf():
+    l = paddle.nn.Linear(2, 2)
+    opt = paddle.optimizer.SGD(0.1, parameters=l.parameters())
+    sc = paddle.amp.GradScaler(init_loss_scaling=4.0, decr_every_n_nan_or_inf=1)
+    w0 = l.weight.detach().clone()
+    loss = l(paddle.ones([1, 2])).sum() * float("inf")
+    sc.scale(loss).backward()
+    sc.step(opt); sc.update()
+    assert torch.equal(l.weight.detach(), w0) and sc.state_dict()["scale"] == 2.0
+    opt.clear_grad()
+    sc.scale(l(paddle.ones([1, 2])).sum()).backward()
+    sc.step(opt); sc.update()
+    assert not torch.equal(l.weight.detach(), w0)
+
+
+def test_lr_schedulers_and_profiler_states():
+    s = paddle.optimizer.lr.CosineAnnealingDecay(1.0, T_max=10)
+    vals = []
+    for _ in range(3):
+        vals.append(s()); s.step()
+    assert vals[0] == 1.0 and vals[1] < 1.0
+    w = paddle.optimizer.lr.LinearWarmup(paddle.optimizer.lr.StepDecay(0.5, 2), 3, 0.0, 0.5)
+    seq = []
+    for _ in range(6):
+        seq.append(round(w(), 4)); w.step()
+    assert seq[:3] == [0.0, 0.1667, 0.3333] and seq[3] == 0.5
+    sched = paddle.profiler.make_scheduler(closed=1, ready=1, record=2, repeat=1)
+    S = paddle.profiler.ProfilerState
+    assert [sched(i) for i in range(5)] == [S.CLOSED, S.READY, S.RECORD, S.RECORD_AND_RETURN, S.CLOSED]
+
+
+def test_to_static_cache_and_jit_save_load(tmp_path):
+    net = paddle.nn.Linear(4, 2)
+    calls = []
+
+    @paddle.jit.to_static
+    def f(x):
+        calls.append(1)
+        return net(x) * 2
+    a = f(paddle.ones([3, 4])); b = f(paddle.ones([3, 4])); c = f(paddle.ones([5, 4]))
+    assert len(f.program_cache) == 2 and a.shape == [3, 2] and c.shape == [5, 2]
+    paddle.jit.save(net, str(tmp_path / "inf"), input_spec=[paddle.static.InputSpec([None, 4], "float32")])
+    loaded = paddle.jit.load(str(tmp_path / "inf"))
+    assert torch.allclose(loaded(paddle.ones([3, 4])), net(paddle.ones([3, 4])))
+
+
+def test_dataloader_and_distributed_batch_sampler():
+    ds = paddle.io.TensorDataset([paddle.arange(10).astype("float32").reshape([10, 1]), paddle.arange(10)])
+    dl = paddle.io.DataLoader(ds, batch_size=4)
+    shapes = [b[0].shape for b in dl]
+    assert shapes == [[4, 1], [4, 1], [2, 1]]
+    s0 = list(paddle.io.DistributedBatchSampler(ds, 2, num_replicas=2, rank=0))
+    s1 = list(paddle.io.DistributedBatchSampler(ds, 2, num_replicas=2, rank=1))
+    assert sorted(sum(s0 + s1, [])) == list(range(10))
+
+
+def test_hapi_fit():
+    x = np.random.RandomState(0).randn(64, 4).astype(np.float32)
+    y = (x.sum(1) > 0).astype(np.int64)
+    ds = paddle.io.TensorDataset([paddle.to_tensor(x), paddle.to_tensor(y)])
+    net = paddle.nn.Sequential(paddle.nn.Linear(4, 16), paddle.nn.ReLU(), paddle.nn.Linear(16, 2))
+    m = paddle.Model(net)
+    m.prepare(paddle.optimizer.Adam(0.05, parameters=net.parameters()), paddle.nn.CrossEntropyLoss(),
+              paddle.metric.Accuracy())
+    m.fit(ds, batch_size=16, epochs=8, verbose=0)
+    assert m.evaluate(ds, batch_size=16, verbose=0)["acc"] > 0.8
+
+
+def test_flags_and_clip():
+    assert paddle.get_flags("FLAGS_check_nan_inf")["FLAGS_check_nan_inf"] is False
+    with pytest.raises(ValueError):
+        paddle.set_flags({"FLAGS_nope": 1})
+    l = paddle.nn.Linear(2, 2)
+    (l(paddle.ones([1, 2])).sum() * 100).backward()
+    clip = paddle.nn.ClipGradByGlobalNorm(1.0)
+    out = clip([(p, p.grad) for p in l.parameters()])
+    tot = sum(float((g ** 2).sum()) for _, g in out) ** 0.5
+    assert abs(tot - 1.0) < 1e-4
