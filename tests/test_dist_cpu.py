@@ -47,3 +47,14 @@ def test_llama_tp_sp_parity_cpu():
     for r in res:
         assert np.allclose(r["tp"], r["twin"], rtol=1e-4, atol=1e-4), (r["tp"], r["twin"])
         assert r["maxdiff"] < 1e-3, r["maxdiff"]  # Adam turns tiny gradient noise into O(lr) steps
+
+
+@pytest.mark.parametrize("mode", ["1f1b", "vpp"])
+def test_pipeline_parallel_parity_cpu(mode):
+    """2 pipeline stages (1F1B, and 2 virtual chunks per stage over the ring) with a weight tied between the
+    first and the last layer: losses and updated weights equal the single-process twin."""
+    res = run_workers("pp_mlp.py", 2, args=(mode,), timeout=180)
+    for r in res:
+        assert np.allclose(r["twin"], r["pipe"], atol=1e-5), r
+        assert r["maxdiff"] < 1e-5
+    assert res[0]["pipe"] == res[1]["pipe"]
