@@ -44,6 +44,37 @@ __device__ __forceinline__ int find_tensor(const TensorRec* recs, int n, int64_t
   return lo;
 }
 
+// 4-element accessors: fp32 as one 128-bit access, bf16 as one 64-bit access.
+__device__ __forceinline__ float4 load4(const void* base, bool is_bf16, int64_t e) {
+  if (is_bf16) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(base) + e);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  }
+  return *reinterpret_cast<const float4*>(static_cast<const float*>(base) + e);
+}
+__device__ __forceinline__ void store4(void* base, bool is_bf16, int64_t e, float4 x) {
+  if (is_bf16) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(static_cast<bf16*>(base) + e) = raw;
+  } else {
+    *reinterpret_cast<float4*>(static_cast<float*>(base) + e) = x;
+  }
+}
+// A chunk may take the vector path when it lies wholly inside its tensor and every pointer the kernel
+// touches is 16-byte aligned (chunk offsets are multiples of 4096 elements, so only the bases matter).
+__device__ __forceinline__ bool vec_ok(const TensorRec& r, int64_t base, bool need_state) {
+  uintptr_t bits = reinterpret_cast<uintptr_t>(r.param) | reinterpret_cast<uintptr_t>(r.grad);
+  if (need_state)
+    bits |= reinterpret_cast<uintptr_t>(r.master) | reinterpret_cast<uintptr_t>(r.m) |
+            reinterpret_cast<uintptr_t>(r.v);
+  return (bits & 15u) == 0 && base + CHUNK <= r.numel;
+}
+
 struct AdamWArgs {
   float lr, beta1, beta2, eps, coeff, beta1_pow, beta2_pow;
   const float* grad_scale;  // optional device scalar multiplied into every gradient
@@ -66,6 +97,39 @@ __global__ void __launch_bounds__(THREADS) adamw_multi_kernel(const int64_t* __r
     const TensorRec r = recs[find_tensor(recs, n, chunk)];
     const int64_t base = (chunk - r.chunk_prefix) * CHUNK;
     const bool p_bf16 = r.flags & 1, g_bf16 = r.flags & 2, has_master = r.flags & 4;
+    if (vec_ok(r, base, true)) {
+      constexpr int IT = CHUNK / (THREADS * 4);
+      float4 g4[IT], p4[IT], m4[IT], v4[IT];
+#pragma unroll
+      for (int it = 0; it < IT; ++it) {   // all loads first: 4 independent 128-bit streams per thread
+        const int64_t e = base + (it * THREADS + threadIdx.x) * 4;
+        g4[it] = load4(r.grad, g_bf16, e);
+        p4[it] = has_master ? *reinterpret_cast<const float4*>(r.master + e) : load4(r.param, p_bf16, e);
+        m4[it] = *reinterpret_cast<const float4*>(r.m + e);
+        v4[it] = *reinterpret_cast<const float4*>(r.v + e);
+      }
+#pragma unroll
+      for (int it = 0; it < IT; ++it) {
+        const int64_t e = base + (it * THREADS + threadIdx.x) * 4;
+        float* g = reinterpret_cast<float*>(&g4[it]);
+        float* p = reinterpret_cast<float*>(&p4[it]);
+        float* m = reinterpret_cast<float*>(&m4[it]);
+        float* v = reinterpret_cast<float*>(&v4[it]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float gj = g[j] * gscale;
+          p[j] *= decay;
+          m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gj;
+          v[j] = a.beta2 * v[j] + (1.f - a.beta2) * gj * gj;
+          p[j] += (m[j] / (sqrtf(v[j]) * inv_sqrt_bc2 + a.eps)) * step_size;
+        }
+        *reinterpret_cast<float4*>(r.m + e) = m4[it];
+        *reinterpret_cast<float4*>(r.v + e) = v4[it];
+        if (has_master) *reinterpret_cast<float4*>(r.master + e) = p4[it];
+        store4(r.param, p_bf16, e, p4[it]);
+      }
+      continue;
+    }
 #pragma unroll 4
     for (int i = threadIdx.x; i < CHUNK; i += THREADS) {
       const int64_t e = base + i;
@@ -159,6 +223,16 @@ __global__ void __launch_bounds__(THREADS) sq_l2_norm_kernel(const int64_t* __re
     const TensorRec r = recs[find_tensor(recs, n, chunk)];
     const int64_t base = (chunk - r.chunk_prefix) * CHUNK;
     const bool g_bf16 = r.flags & 2;
+    if ((reinterpret_cast<uintptr_t>(r.grad) & 15u) == 0 && base + CHUNK <= r.numel) {
+      constexpr int IT = CHUNK / (THREADS * 4);
+      float4 g4[IT];
+#pragma unroll
+      for (int it = 0; it < IT; ++it) g4[it] = load4(r.grad, g_bf16, base + (it * THREADS + threadIdx.x) * 4);
+#pragma unroll
+      for (int it = 0; it < IT; ++it)
+        acc += g4[it].x * g4[it].x + g4[it].y * g4[it].y + g4[it].z * g4[it].z + g4[it].w * g4[it].w;
+      continue;
+    }
     for (int i = threadIdx.x; i < CHUNK; i += THREADS) {
       const int64_t e = base + i;
       if (e >= r.numel) break;

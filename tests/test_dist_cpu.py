@@ -58,3 +58,16 @@ def test_pipeline_parallel_parity_cpu(mode):
         assert np.allclose(r["twin"], r["pipe"], atol=1e-5), r
         assert r["maxdiff"] < 1e-5
     assert res[0]["pipe"] == res[1]["pipe"]
+
+
+@pytest.mark.parametrize("level", ["os_g", "p_g_os"])
+def test_group_sharded_parity_cpu(level):
+    """ZeRO stage 2 / stage 3 over 2 ranks equals the single-process twin on the full batch; stage 2 keeps
+    optimizer state only for the owned partition."""
+    res = run_workers("group_sharded.py", 2, args=(level,), timeout=180)
+    for r in res:
+        assert np.allclose(r["twin"], r["sharded"], atol=1e-5), r
+        assert r["maxdiff"] < 1e-4
+        assert r["files"] == ["model.pdmodel", "model.pdopt"]
+    if level == "os_g":
+        assert res[0]["nstate"] + res[1]["nstate"] == 28
