@@ -215,22 +215,34 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       int col_limit = p.Sk - 1 - j * BKV;
       if (p.causal) col_limit = min(col_limit, qi + causal_off - j * BKV);
       const bool need_mask = col_limit < BKV - 1;
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_tmem + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
+      // one TMEM read of the whole 128-column row: four loads in flight, one wait
+      uint32_t r[4][32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i <= col_limit) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_tmem + c * 32, r[c]);
+      tmem_ld_wait();
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (c * 32 + i > col_limit) r[c][i] = 0xff800000u;   // -inf: contributes exp2(-inf) = 0
+          }
         }
       }
+      // row maximum with eight independent chains
+      float mxs[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mxs[i] = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) mxs[q] = fmaxf(mxs[q], __uint_as_float(r[c][i + q]));
+        }
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
+                             fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // lazy rescale: only when some row of the warp moved its maximum by more than 2^8
       const bool want = (j == 0) || (m_new - m_used > 8.f);
@@ -242,26 +254,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-      // pass 2: probabilities -> TMEM (packed bf16), row sum
-#pragma unroll 1
+      // probabilities -> TMEM (packed bf16), row sum in four independent chains
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_tmem + c * 32, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float a = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_eff));
-          float b = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_eff));
-          if (need_mask) {
-            if (c * 32 + i > col_limit) a = 0.f;
-            if (c * 32 + i + 1 > col_limit) b = 0.f;
-          }
-          l += a + b;
+          const float a = fast_exp2(fmaf(__uint_as_float(r[c][i]), p.scale_log2, -m_eff));
+          const float b = fast_exp2(fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, -m_eff));
+          if (((i >> 1) & 3) == 0) ls[0] += a + b;
+          else if (((i >> 1) & 3) == 1) ls[1] += a + b;
+          else if (((i >> 1) & 3) == 2) ls[2] += a + b;
+          else ls[3] += a + b;
           pk[i >> 1] = pack_bf16x2(a, b);
         }
         tmem_st_32x16(p_tmem + c * 16, pk);
       }
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tmem_st_wait();
       if (j > 0) {
         // PV_{j-1} must have landed in O before O is rescaled and before PV_j may be issued

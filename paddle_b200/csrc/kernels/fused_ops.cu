@@ -97,6 +97,68 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 constexpr int RN_THREADS = 256;
 constexpr int RN_MAXIT = 4;
 
+// Warp-per-row variant for H = 256 * NV: the row stays in registers as packed bf16 (NV 128-bit words per
+// lane, all loads issued before the first use), the reduction is shuffle-only, no CTA barrier.  With a
+// residual the bf16-rounded sum is what gets normalised (and stored when residual_out is given).
+template <typename WT, int NV>
+__global__ void __launch_bounds__(RN_THREADS, (NV <= 16 ? 2 : 1)) rms_norm_fwd_warp_kernel(
+    const bf16* __restrict__ x, const bf16* __restrict__ residual, const WT* __restrict__ w,
+    bf16* __restrict__ y, bf16* __restrict__ residual_out, float* __restrict__ inv_rms, int64_t rows,
+    float eps) {
+  constexpr int H = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (RN_THREADS / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+  uint4 cache[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) cache[k] = __ldg(xr + lane + 32 * k);
+  if (residual != nullptr) {
+    const uint4* rr = reinterpret_cast<const uint4*>(residual + row * H);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const uint4 rc = __ldg(rr + lane + 32 * k);
+      __nv_bfloat162* a = reinterpret_cast<__nv_bfloat162*>(&cache[k]);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&rc);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = __bfloat1622float2(a[j]), fb = __bfloat1622float2(b[j]);
+        a[j] = __floats2bfloat162_rn(fa.x + fb.x, fa.y + fb.y);
+      }
+      if (residual_out != nullptr)
+        reinterpret_cast<uint4*>(residual_out + row * H)[lane + 32 * k] = cache[k];
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&cache[k]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(a[j]);
+      ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / static_cast<float>(H) + eps);
+  if (lane == 0 && inv_rms != nullptr) inv_rms[row] = r;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    float xv[8], wv[8], o[8];
+    const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&cache[k]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(a[j]);
+      xv[2 * j] = f.x;
+      xv[2 * j + 1] = f.y;
+    }
+    load8(w + (lane + 32 * k) * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = xv[j] * r * wv[j];
+    store8(y + row * H + (lane + 32 * k) * 8, o);
+  }
+}
+
 template <typename WT>
 __global__ void __launch_bounds__(RN_THREADS) rms_norm_fwd_kernel(
     const bf16* __restrict__ x, const bf16* __restrict__ residual, const WT* __restrict__ w,
@@ -638,6 +700,25 @@ PD_EXPORT int pd_rms_norm_fwd(const void* x, const void* residual, const void* w
                               void* residual_out, float* inv_rms, int64_t rows, int H, float eps,
                               cudaStream_t stream) {
   if (H % 8 != 0 || rows <= 0) return kErrBadShape;
+  const bool al = aligned16(x) && aligned16(y) && aligned16(w) && (residual == nullptr || aligned16(residual)) &&
+                  (residual_out == nullptr || aligned16(residual_out));
+#define PD_RMS_WARP(NV)                                                                                  \
+  if (al && H == (NV) * 256) {                                                                           \
+    const unsigned blocks = static_cast<unsigned>((rows + RN_THREADS / 32 - 1) / (RN_THREADS / 32));     \
+    if (w_is_f32)                                                                                        \
+      rms_norm_fwd_warp_kernel<float, NV><<<blocks, RN_THREADS, 0, stream>>>(                            \
+          (const bf16*)x, (const bf16*)residual, (const float*)w, (bf16*)y, (bf16*)residual_out, inv_rms, \
+          rows, eps);                                                                                    \
+    else                                                                                                 \
+      rms_norm_fwd_warp_kernel<bf16, NV><<<blocks, RN_THREADS, 0, stream>>>(                             \
+          (const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)y, (bf16*)residual_out, inv_rms,  \
+          rows, eps);                                                                                    \
+    return PD_CHECK_LAUNCH();                                                                            \
+  }
+  PD_RMS_WARP(8)
+  PD_RMS_WARP(16)
+  PD_RMS_WARP(20)
+#undef PD_RMS_WARP
   if (w_is_f32)
     rms_norm_fwd_kernel<float><<<static_cast<unsigned>(rows), RN_THREADS, 0, stream>>>(
         (const bf16*)x, (const bf16*)residual, (const float*)w, (bf16*)y, (bf16*)residual_out, inv_rms, H, eps);

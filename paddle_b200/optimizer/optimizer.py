@@ -79,7 +79,8 @@ class Optimizer:
         if param.name in self._accumulators[name]:
             return self._accumulators[name][param.name]
         dtype = dtype or (torch.float32 if param.dtype in (torch.bfloat16, torch.float16) else param.dtype)
-        shape = list(param.shape) if shape is None else shape
+        # a distributed parameter reports its global shape; state lives on the local shard
+        shape = list(getattr(param, "_local_shape", param.shape)) if shape is None else shape
         t = as_tensor(torch.full(shape, fill_value, dtype=dtype, device=param.device))
         t.name = f"{param.name}_{name}_0"
         held = self._accumulators_holder.pop(t.name, None)

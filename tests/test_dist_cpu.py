@@ -71,3 +71,18 @@ def test_group_sharded_parity_cpu(level):
         assert r["files"] == ["model.pdmodel", "model.pdopt"]
     if level == "os_g":
         assert res[0]["nstate"] + res[1]["nstate"] == 28
+
+
+def test_auto_parallel_reshard_spmd_checkpoint_cpu():
+    """Reshard pairs, SPMD matmul / data-parallel gradients, plan-driven parallelize vs a dense twin, and the
+    sharded checkpoint (save under one placement, load under another, metadata layout) on a 2-rank mesh."""
+    res = run_workers("auto_parallel_api.py", 2, timeout=180)
+    for r in res:
+        for k in ("r_to_s", "s_to_r", "s_to_s", "p_to_r", "p_to_s", "r_to_p", "unshard", "mp_loss", "mp_gw1", "mp_gw2",
+                  "dp_loss", "dp_gw", "ckpt_w", "ckpt_m", "ckpt_merged"):
+            assert r[k] is True or r[k] == True, (k, r[k])  # noqa: E712
+        assert r["col_out_placement"] == "[Shard(dim=1)]" and r["row_out_placement"] == "[Partial(reduce_type=0)]"
+        assert np.allclose(r["plan_losses"][0], r["plan_losses"][1], atol=1e-6)
+        assert r["plan_w"] < 1e-6 and r["opt_state_dist"] == 8
+        assert r["ckpt_files"] == ["0.metadata", "0_0.distcp", "1_0.distcp"]
+        assert r["ckpt_meta"] == ("paddle.distributed.checkpoint.metadata", ["opt.m", "w"], 2, 1, ("opt", "m"))
