@@ -1,0 +1,143 @@
+"""Failure detection and recovery, with every failure made on the host (a rank that exits or never joins, a
+membership change in a fake key-value service): launcher restart + resume from checkpoint, bounded-time error on
+a missing peer, elastic manager state machine, spawn error propagation."""
+import os
+import subprocess
+import sys
+import tempfile
+import time
+import types
+
+import numpy as np
+import pytest
+
+from dist_utils import ROOT, run_workers
+
+
+def _launch(out, mode, extra=()):
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", PADDLE_DISTRI_BACKEND="gloo", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "paddle_b200.distributed.launch", "--nproc_per_node", "2", "--log_dir",
+           os.path.join(out, "log"), *extra, os.path.join(ROOT, "tests", "dist_workers", "elastic_train.py"), out, mode]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+
+
+def _losses(out):
+    return [float(l.split()[1]) for l in open(os.path.join(out, "loss.txt"))], \
+        [int(l.split()[0]) for l in open(os.path.join(out, "loss.txt"))]
+
+
+def test_launcher_restart_resumes_from_checkpoint():
+    ref = tempfile.mkdtemp()
+    r = _launch(ref, "clean")
+    assert r.returncode == 0, r.stderr[-2000:]
+    out = tempfile.mkdtemp()
+    r = _launch(out, "crash", ("--elastic_level", "1", "--max_restart", "2"))
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "restarting the pod (1/2)" in r.stderr
+    (l_ref, s_ref), (l_out, s_out) = _losses(ref), _losses(out)
+    assert s_ref == s_out == list(range(6))
+    assert np.allclose(l_ref, l_out, atol=1e-6), (l_ref, l_out)
+    assert sorted(os.listdir(os.path.join(out, "log"))) == ["workerlog.0", "workerlog.1"]
+
+
+def test_launcher_fails_without_elastic_level():
+    out = tempfile.mkdtemp()
+    r = _launch(out, "crash")
+    assert r.returncode != 0 and "restarting" not in r.stderr
+    assert "exited with 3" in r.stderr
+
+
+def test_missing_peer_ends_collective_in_bounded_time():
+    res = run_workers("peer_missing.py", 2, timeout=120)
+    assert res[1] == {"left": True}
+    assert res[0]["first"] == [2.0] * 4
+    assert res[0]["error"] is not None and res[0]["elapsed"] < 30, res[0]
+
+
+def _args(**kw):
+    base = dict(np="2", job_id="t", host="10.0.0.1", elastic_timeout=1, elastic_level=None, elastic_server="fake")
+    base.update(kw)
+    return types.SimpleNamespace(**base)
+
+
+class _FakeLauncher:
+    def __init__(self):
+        self.code, self.stopped, self.launched = None, 0, 0
+
+    def launch(self):
+        self.launched += 1
+
+    def watch(self):
+        return self.code
+
+    def stop(self):
+        self.stopped += 1
+
+
+def test_elastic_manager_fault_tolerance_and_scaling():
+    from paddle_b200.distributed.fleet.elastic.manager import ElasticManager, ElasticStatus, MemoryKV
+    kv = MemoryKV()
+    a = ElasticManager(_args(host="10.0.0.1"), kv)
+    b = ElasticManager(_args(host="10.0.0.2"), kv)
+    assert a.wait() and b.wait()
+    assert a.np == 2 and os.environ["PADDLE_TRAINERS_NUM"] == "2"
+    la = _FakeLauncher()
+    a.run(la)
+    assert la.launched == 1
+    b.exit()                                   # the peer leaves: below np -> HOLD (fault tolerance)
+    assert a.watch() == ElasticStatus.HOLD and la.stopped >= 1
+    assert not a.wait()                        # nobody comes back within elastic_timeout
+    c = ElasticManager(_args(host="10.0.0.3"), kv)
+    assert a.wait() and sorted(a.trainers.split(",")) == ["10.0.0.1:6170", "10.0.0.3:6170"]
+    la.code = 0
+    assert a.watch() == ElasticStatus.COMPLETED
+    a.exit(completed=True), c.exit()
+    # elastic range 1:2 -> losing one host restarts with the survivors instead of holding
+    kv2 = MemoryKV()
+    d = ElasticManager(_args(np="1:2", host="10.0.1.1"), kv2)
+    e = ElasticManager(_args(np="1:2", host="10.0.1.2"), kv2)
+    assert d.wait() and d.np == 2
+    ld = _FakeLauncher()
+    d.run(ld)
+    e.exit()
+    assert d.watch() == ElasticStatus.RESTART
+    assert d.wait() and d.np == 1 and d.trainers == "10.0.1.1:6170"
+    ld.code = 101
+    assert d.watch() == ElasticStatus.RESTART    # trainers asked for a relaunch through the elastic exit code
+    d.exit()
+
+
+def test_elastic_lease_expires_without_heartbeat():
+    from paddle_b200.distributed.fleet.elastic.manager import MemoryKV
+    kv = MemoryKV()
+    lease = kv.lease(0.2)
+    kv.put("/paddle/j/nodes/x", "h:1", lease=lease)
+    events = []
+    kv.add_watch_prefix_callback("/paddle/j/nodes", events.append)
+    assert len(kv.get_prefix("/paddle/j/nodes")) == 1
+    time.sleep(0.3)
+    assert kv.get_prefix("/paddle/j/nodes") == [] and events and events[0]["type"] == "delete"
+
+
+def _spawn_ok(path):
+    import paddle_b200.distributed as dist
+    import torch
+    dist.init_parallel_env()
+    t = torch.tensor([float(dist.get_rank() + 1)])
+    dist.all_reduce(t)
+    with open(f"{path}.{dist.get_rank()}", "w") as f:
+        f.write(str(float(t)))
+
+
+def _spawn_bad(path):
+    raise ValueError("boom from the child")
+
+
+def test_spawn_runs_and_propagates_errors():
+    import paddle_b200.distributed as dist
+    base = os.path.join(tempfile.mkdtemp(), "o")
+    env = {"CUDA_VISIBLE_DEVICES": "", "PADDLE_DISTRI_BACKEND": "gloo"}
+    dist.spawn(_spawn_ok, args=(base,), nprocs=2, env=env)
+    assert [open(f"{base}.{r}").read() for r in range(2)] == ["3.0", "3.0"]
+    with pytest.raises(RuntimeError, match="boom from the child"):
+        dist.spawn(_spawn_bad, args=(base,), nprocs=2, env=env)
