@@ -55,7 +55,7 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int mn3d, int* status) {
+                 const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int mn3d, int splits, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -67,8 +67,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
-  const int KB = (K + BK - 1) / BK;
+  const int KB_total = (K + BK - 1) / BK;
+  // split-K: work item w = tile * splits + slice; each slice covers KBS k-blocks (fp32 reduce-add epilogue)
+  const int KBS = (KB_total + splits - 1) / splits;
+  const int num_tiles = tiles_m * tiles_n * splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -102,9 +104,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int tm, tn;
-        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        tile_coords(t / splits, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < KB; ++kb) {
+        const int kb0 = (t % splits) * KBS, kb1 = min(KB_total, kb0 + KBS);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&bars->empty[s], ph ^ 1, abort_flag, status, 100 + s)) { ok = false; break; }
           mbar_expect_tx(&bars->full[s], A_STAGE_BYTES + B_STAGE_BYTES);
           armed |= 1u << s;
@@ -158,7 +161,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&bars->tempty[acc], acc_ph ^ 1, abort_flag, status, 200 + acc)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < KB; ++kb) {
+        const int kb0 = (t % splits) * KBS, kb1 = min(KB_total, kb0 + KBS);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&bars->full[s], ph, abort_flag, status, 300 + s)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
@@ -167,7 +171,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t ad = make_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
             const uint64_t bd = make_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
-            umma_bf16_ss(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_bf16_ss(d_tmem, ad, bd, idesc, ((kb - kb0) | k) != 0 ? 1u : 0u);
           }
           umma_commit(&bars->empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -190,7 +194,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int chunk_counter = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
       int tm, tn;
-      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      tile_coords(t / splits, tiles_m, tiles_n, tm, tn);
       const int m0 = tm * BM, n0 = tn * BN;
       const int acc = it & 1;
       const uint32_t acc_ph = (it >> 1) & 1;
@@ -261,7 +265,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                          int M, int N, int K, int mn3d, int* status, cudaStream_t stream, int max_ctas) {
+                          int M, int N, int K, int mn3d, int* status, cudaStream_t stream, int max_ctas, int splits = 1) {
   auto kfn = gemm_bf16_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -269,10 +273,10 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
       return kErrCuda;
     configured = true;
   }
-  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * splits;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, M, N, K, mn3d, status);
+  kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, M, N, K, mn3d, splits, status);
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }
 
@@ -286,12 +290,19 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
 //   max_ctas: 0 = all SMs; otherwise cap the persistent grid (used to leave SMs to a concurrent
 //   communication kernel).
 // Requirements: pointers 16-byte aligned; lda/ldb/ldc multiples of 8 elements (bf16) / 4 (fp32).
-PD_EXPORT int pd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
-                           int ldc, int a_mn_major, int b_mn_major, int epi, int max_ctas, int* status,
-                           cudaStream_t stream) {
+static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                     int a_mn_major, int b_mn_major, int epi, int max_ctas, int splits, int* status,
+                     cudaStream_t stream) {
   using namespace pd;
   using namespace pd::gemm;
-  if (M <= 0 || N <= 0 || K <= 0) return kErrBadShape;
+  if (M <= 0 || N <= 0 || K <= 0 || splits < 1) return kErrBadShape;
+  if (splits > 1 && epi != kAccumF32) return kErrBadShape;
+  {
+    const int kb_total = (K + BK - 1) / BK;
+    if (splits > kb_total) splits = kb_total;
+    const int kbs = (kb_total + splits - 1) / splits;
+    splits = (kb_total + kbs - 1) / kbs;      // no empty slices
+  }
   if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return kErrAlignment;
   if ((lda % 8) || (ldb % 8) || (epi == kStoreBf16 ? (ldc % 8) : (ldc % 4))) return kErrAlignment;
   CUtensorMap tmA, tmB, tmC;
@@ -313,10 +324,33 @@ PD_EXPORT int pd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, 
 
 #define PD_GEMM_CASE(AM, BM_, E)                                                                   \
   if (a_mn_major == AM && b_mn_major == BM_ && epi == E)                                           \
-    return launch_variant<AM, BM_, E>(tmA, tmB, tmC, M, N, K, a3d | (b3d << 1), status, stream, max_ctas);
+    return launch_variant<AM, BM_, E>(tmA, tmB, tmC, M, N, K, a3d | (b3d << 1), status, stream, max_ctas, splits);
   PD_GEMM_CASE(0, 0, 0) PD_GEMM_CASE(0, 1, 0) PD_GEMM_CASE(1, 0, 0) PD_GEMM_CASE(1, 1, 0)
   PD_GEMM_CASE(0, 0, 1) PD_GEMM_CASE(0, 1, 1) PD_GEMM_CASE(1, 0, 1) PD_GEMM_CASE(1, 1, 1)
   PD_GEMM_CASE(0, 0, 2) PD_GEMM_CASE(0, 1, 2) PD_GEMM_CASE(1, 0, 2) PD_GEMM_CASE(1, 1, 2)
 #undef PD_GEMM_CASE
   return kErrBadShape;
+}
+
+PD_EXPORT int pd_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb,
+                           int ldc, int a_mn_major, int b_mn_major, int epi, int max_ctas, int* status,
+                           cudaStream_t stream) {
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, epi, max_ctas, 1, status, stream);
+}
+
+// Split-K form for skinny problems (few output tiles, long K: decode-time projections): `splits` slices of K
+// are reduced into the fp32 buffer C with TMA reduce-add, so C must hold the value to accumulate onto (zeros).
+PD_EXPORT int pd_gemm_bf16_splitk(const void* A, const void* B, float* C, int M, int N, int K, int lda, int ldb,
+                                  int ldc, int a_mn_major, int b_mn_major, int splits, int* status,
+                                  cudaStream_t stream) {
+  return gemm_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, 2, 0, splits, status, stream);
+}
+// Slices that fill the GPU about once for an [M,N,K] problem (at least 4 k-blocks of 64 per slice).
+PD_EXPORT int pd_gemm_suggest_splits(int M, int N, int K) {
+  using namespace pd::gemm;
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  int s = pd::sm_count() / (tiles > 0 ? tiles : 1);
+  const int kb = (K + BK - 1) / BK;
+  if (s > kb / 4) s = kb / 4;
+  return s < 1 ? 1 : s;
 }

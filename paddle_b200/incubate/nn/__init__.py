@@ -1,0 +1,8 @@
+"""``paddle.incubate.nn``"""
+from . import functional  # noqa: F401
+from .layer.fused_transformer import (FusedBiasDropoutResidualLayerNorm, FusedDropoutAdd, FusedFeedForward,  # noqa: F401
+                                      FusedLinear, FusedMultiHeadAttention, FusedMultiTransformer,
+                                      FusedTransformerEncoderLayer)
+
+__all__ = ["FusedMultiHeadAttention", "FusedFeedForward", "FusedTransformerEncoderLayer", "FusedMultiTransformer",
+           "FusedLinear", "FusedBiasDropoutResidualLayerNorm", "FusedDropoutAdd"]

@@ -1,0 +1,146 @@
+"""``paddle.inference``: predictor API over captured layers (paddle/fluid/inference/api/analysis_predictor.cc,
+python/paddle/inference/__init__.py) plus the paged-KV generation engine used by the fused transformer path."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .paged_kv import PagedKVCache  # noqa: F401
+
+
+class PrecisionType:
+    Float32, Half, Int8, Bfloat16 = 0, 1, 2, 3
+
+
+class PlaceType:
+    UNK, CPU, GPU = -1, 0, 1
+
+
+class Config:
+    """Predictor configuration.  ``Config(prog_file, params_file)`` or ``Config(path_prefix)`` names a model saved
+    by ``paddle.jit.save``."""
+
+    def __init__(self, *args):
+        self._prefix = None
+        if len(args) == 1:
+            self._prefix = args[0][:-len(".pdmodel")] if args[0].endswith(".pdmodel") else args[0]
+        elif len(args) == 2:
+            self._prefix = args[0][:-len(".pdmodel")] if args[0].endswith(".pdmodel") else args[0]
+        self._use_gpu, self._device_id, self._precision = False, 0, PrecisionType.Float32
+        self._cuda_graph = True
+
+    def set_model(self, prog_file, params_file=None):
+        self._prefix = prog_file[:-len(".pdmodel")] if prog_file.endswith(".pdmodel") else prog_file
+
+    def model_dir(self):
+        return self._prefix
+
+    def enable_use_gpu(self, memory_pool_init_size_mb=100, device_id=0, precision_mode=PrecisionType.Float32):
+        self._use_gpu, self._device_id, self._precision = True, device_id, precision_mode
+
+    def disable_gpu(self):
+        self._use_gpu = False
+
+    def use_gpu(self):
+        return self._use_gpu
+
+    def enable_memory_optim(self, *a):
+        pass
+
+    def switch_ir_optim(self, flag=True):
+        self._cuda_graph = bool(flag)
+
+    def enable_tensorrt_engine(self, *a, **k):
+        raise NotImplementedError("TensorRT sub-graph engines are outside this framework; GPU inference runs on "
+                                  "its own kernels and CUDA graphs")
+
+    def disable_glog_info(self):
+        pass
+
+    def set_cpu_math_library_num_threads(self, n):
+        torch.set_num_threads(int(n))
+
+
+class _Handle:
+    def __init__(self, name):
+        self.name, self._value = name, None
+
+    def reshape(self, shape):
+        pass
+
+    def copy_from_cpu(self, arr):
+        self._value = np.asarray(arr)
+
+    def copy_to_cpu(self):
+        return self._value
+
+    def shape(self):
+        return list(self._value.shape) if self._value is not None else []
+
+    def share_external_data(self, t):
+        self._value = t
+
+
+class Predictor:
+    def __init__(self, config: Config):
+        from .. import jit
+        self._config = config
+        self._layer = jit.load(config.model_dir())
+        self._device = torch.device("cuda", config._device_id) if config.use_gpu() and torch.cuda.is_available() \
+            else torch.device("cpu")
+        if self._device.type == "cuda":
+            self._layer.to(device=self._device)
+        if config._cuda_graph:
+            self._fn = jit.to_static(self._layer.forward)
+        else:
+            self._fn = self._layer.forward
+        import inspect
+        try:
+            sig = inspect.signature(self._layer._inner.forward)
+            self._in_names = [p for p in sig.parameters]
+        except (TypeError, ValueError):
+            self._in_names = ["x"]
+        self._inputs = {n: _Handle(n) for n in self._in_names}
+        self._outputs = []
+
+    def get_input_names(self):
+        return list(self._in_names)
+
+    def get_input_handle(self, name):
+        return self._inputs[name]
+
+    def run(self, inputs=None):
+        from .._core.tensor import as_tensor
+        if inputs is None:
+            inputs = [self._inputs[n]._value for n in self._in_names if self._inputs[n]._value is not None]
+        tens = [as_tensor(torch.as_tensor(np.asarray(v) if not isinstance(v, torch.Tensor) else v).to(self._device))
+                for v in inputs]
+        with torch.no_grad():
+            out = self._fn(*tens)
+        outs = list(out) if isinstance(out, (list, tuple)) else [out]
+        self._outputs = []
+        for i, o in enumerate(outs):
+            h = _Handle(f"output_{i}")
+            h._value = o.detach().float().cpu().numpy() if o.dtype == torch.bfloat16 else o.detach().cpu().numpy()
+            self._outputs.append(h)
+        return [h._value for h in self._outputs]
+
+    def get_output_names(self):
+        return [h.name for h in self._outputs] or ["output_0"]
+
+    def get_output_handle(self, name):
+        for h in self._outputs:
+            if h.name == name:
+                return h
+        raise KeyError(name)
+
+    def clone(self):
+        return Predictor(self._config)
+
+
+def create_predictor(config: Config) -> Predictor:
+    return Predictor(config)
+
+
+def get_version():
+    return "paddle_b200 inference"

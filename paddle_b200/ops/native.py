@@ -351,3 +351,84 @@ def adamw_flat(param_bf16, master, grad, m, v, lr, beta1, beta2, eps, coeff, bet
                                       c_float(beta1_pow), c_float(beta2_pow), ptr(grad_scale), ptr(skip), stream())
     check(rc, "pd_adamw_flat")
     _count()
+
+
+# --------------------------------------------------------------------------------------------- decode / inference
+def gemm_splitk(a, b, acc_f32, splits=0, trans_b=False):
+    """``acc_f32 += a @ op(b)`` with K cut into ``splits`` slices that run on different SMs (skinny decode GEMMs).
+    ``splits=0`` picks a count that fills the GPU.  ``acc_f32`` must hold zeros (``splitk_finalize`` re-zeroes it)."""
+    M, K = a.shape
+    N = b.shape[0] if trans_b else b.shape[1]
+    k = _lib.kernels()
+    if splits <= 0:
+        splits = k.pd_gemm_suggest_splits(c_int(M), c_int(N), c_int(K))
+    rc = k.pd_gemm_bf16_splitk(ptr(a), ptr(b), ptr(acc_f32), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
+                               c_int(b.stride(0)), c_int(acc_f32.stride(0)), c_int(0), c_int(0 if trans_b else 1),
+                               c_int(splits), ptr(_lib.status_buffer(a.device)), stream())
+    check(rc, "pd_gemm_bf16_splitk")
+    _count()
+    return acc_f32
+
+
+def suggest_splits(M, N, K):
+    return _lib.kernels().pd_gemm_suggest_splits(c_int(M), c_int(N), c_int(K))
+
+
+def splitk_finalize(acc_f32, out=None, bias=None, residual=None):
+    M, N = acc_f32.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=BF16, device=acc_f32.device)
+    rc = _lib.kernels().pd_splitk_finalize(ptr(acc_f32), ptr(bias), ptr(residual), ptr(out), c_int64(M), c_int(N),
+                                           stream())
+    check(rc, "pd_splitk_finalize")
+    _count()
+    return out
+
+
+def decode_qkv_prep(qkv, bias, cos, sin, seq_lens, block_table, q_out, k_cache, v_cache, Hq, Hkv):
+    B = qkv.shape[0]
+    rc = _lib.kernels().pd_decode_qkv_prep(ptr(qkv), ptr(bias), ptr(cos), ptr(sin), ptr(seq_lens), ptr(block_table),
+                                           ptr(q_out), ptr(k_cache), ptr(v_cache), c_int(B), c_int(Hq), c_int(Hkv),
+                                           c_int(block_table.shape[1]), c_int64(qkv.stride(0)), c_int(cos.shape[0]),
+                                           stream())
+    check(rc, "pd_decode_qkv_prep")
+    _count()
+    return q_out
+
+
+def write_kv_cache(k, v, block_table, k_cache, v_cache, start_pos=0):
+    """k, v: [B, S, Hkv, 128] views (unit inner stride, head stride 128)."""
+    B, S, Hkv, D = k.shape
+    _req(D == 128 and k.stride(3) == 1 and k.stride(2) == 128 and v.stride() == k.stride(), "write_kv_cache: layout")
+    rc = _lib.kernels().pd_write_kv_cache(ptr(k), ptr(v), ptr(block_table), ptr(k_cache), ptr(v_cache), c_int(B),
+                                          c_int(S), c_int(Hkv), c_int(block_table.shape[1]), c_int64(k.stride(1)),
+                                          c_int64(k.stride(0)), c_int(start_pos), stream())
+    check(rc, "pd_write_kv_cache")
+    _count()
+
+
+def decode_attn_splits(B, Hkv, max_pages):
+    return _lib.kernels().pd_decode_attn_splits(c_int(B), c_int(Hkv), c_int(max_pages))
+
+
+def paged_decode_attn(q, k_cache, v_cache, block_table, seq_lens, scale, out=None, nsplit=1, len_offset=0,
+                      workspace=None):
+    """q [B, Hq, 128] bf16; caches [num_blocks, Hkv, 64, 128]; block_table [B, max_blocks] int32; seq_lens [B] int32."""
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[1]
+    _req(D == 128 and q.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous(), "paged attn: layout")
+    if out is None:
+        out = torch.empty_like(q)
+    pa = pm = None
+    if nsplit > 1:
+        if workspace is None:
+            workspace = (torch.empty((B, Hq, nsplit, 128), dtype=F32, device=q.device),
+                         torch.empty((B, Hq, nsplit, 2), dtype=F32, device=q.device))
+        pa, pm = workspace
+    rc = _lib.kernels().pd_paged_decode_attn(ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), ptr(seq_lens),
+                                             ptr(out), ptr(pa), ptr(pm), c_int(B), c_int(Hq), c_int(Hkv),
+                                             c_int(block_table.shape[1]), c_int(nsplit), c_int(len_offset),
+                                             c_float(scale), ptr(_lib.status_buffer(q.device)), stream())
+    check(rc, "pd_paged_decode_attn")
+    _count(2 if nsplit > 1 else 1)
+    return out
