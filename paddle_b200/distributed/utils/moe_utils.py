@@ -14,11 +14,16 @@ from ..._core.tensor import as_tensor
 from .. import collective as C
 
 
+def _nranks(group):
+    if group is None and not C.is_initialized():
+        return 1
+    return C._grp(group).nranks
+
+
 def _exchange(x, send_counts, recv_counts, group, n_local):
     """send_counts / recv_counts: python lists of length world * n_local (rank-major).  Returns rows received, laid
     out rank-major (source rank, local expert)."""
-    g = C._grp(group)
-    n = g.nranks
+    n = _nranks(group)
     in_splits = [sum(send_counts[r * n_local:(r + 1) * n_local]) for r in range(n)]
     out_splits = [sum(recv_counts[r * n_local:(r + 1) * n_local]) for r in range(n)]
     out = torch.empty((sum(out_splits), *x.shape[1:]), dtype=x.dtype, device=x.device)
@@ -51,7 +56,7 @@ class _GlobalScatter(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, local_count, global_count, group):
         lc, gc = [int(v) for v in local_count.tolist()], [int(v) for v in global_count.tolist()]
-        n = C._grp(group).nranks
+        n = _nranks(group)
         n_local = len(lc) // n
         ctx.meta = (lc, gc, group, n, n_local)
         recv = _exchange(C._plain(x), lc, gc, group, n_local)
@@ -68,7 +73,7 @@ class _GlobalGather(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, local_count, global_count, group):
         lc, gc = [int(v) for v in local_count.tolist()], [int(v) for v in global_count.tolist()]
-        n = C._grp(group).nranks
+        n = _nranks(group)
         n_local = len(lc) // n
         ctx.meta = (lc, gc, group, n, n_local)
         rows = _expert_major_to_rank_major(C._plain(x).contiguous(), gc, n, n_local)

@@ -239,8 +239,9 @@ def masked_multihead_attention(x, cache_kv=None, bias=None, src_mask=None, cum_o
         q, k = rot(q), rot(k)
     idx = pos.reshape(B, 1, 1, 1).expand(B, H, 1, D)
     with torch.no_grad():
-        cache_kv[0].scatter_(2, idx, k.reshape(B, H, 1, D))
-        cache_kv[1].scatter_(2, idx, v.reshape(B, H, 1, D))
+        raw = cache_kv.as_subclass(torch.Tensor)
+        torch.Tensor.scatter_(raw[0], 2, idx, k.reshape(B, H, 1, D).as_subclass(torch.Tensor).to(raw.dtype))
+        torch.Tensor.scatter_(raw[1], 2, idx, v.reshape(B, H, 1, D).as_subclass(torch.Tensor).to(raw.dtype))
     keys, vals = cache_kv[0].float(), cache_kv[1].float()
     s = torch.einsum("bhd,bhsd->bhs", q.float(), keys) / math.sqrt(D)
     valid = torch.arange(max_seq, device=x.device)[None, None, :] <= pos.reshape(B, 1, 1)

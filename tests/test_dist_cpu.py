@@ -86,3 +86,11 @@ def test_auto_parallel_reshard_spmd_checkpoint_cpu():
         assert r["plan_w"] < 1e-6 and r["opt_state_dist"] == 8
         assert r["ckpt_files"] == ["0.metadata", "0_0.distcp", "1_0.distcp"]
         assert r["ckpt_meta"] == ("paddle.distributed.checkpoint.metadata", ["opt.m", "w"], 2, 1, ("opt", "m"))
+
+
+def test_moe_expert_parallel_parity_cpu():
+    """2 ranks x 2 local experts, uneven token counts: outputs, input gradients and expert gradients equal the
+    dense evaluation of all four experts."""
+    res = run_workers("moe_ep.py", 2, timeout=180)
+    for r in res:
+        assert r["out"] < 1e-5 and r["dx"] < 1e-4 and r["dw"] < 1e-4 and r["moe_flag"]
