@@ -26,6 +26,7 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=512)
     ap.add_argument("--runs", type=int, default=1)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--nccl-ar", action="store_true", help="baseline: GEMM + NCCL all-reduce instead of the fused kernel")
     args = ap.parse_args()
 
     import torch
@@ -54,6 +55,8 @@ def main():
     cfg = {"llama2-13b": LlamaConfig.llama2_13b, "llama2-7b": LlamaConfig.llama2_7b,
            "tiny": lambda **kw: LlamaConfig.tiny(hidden_size=512, intermediate_size=1024, num_attention_heads=4,
                                                  num_hidden_layers=2, **kw)}[args.model](max_position_embeddings=4096)
+    if args.nccl_ar:
+        os.environ["PD_DECODE_NCCL_AR"] = "1"
     model = LlamaForCausalLMInference(cfg, tp_group=group)
     total = args.prompt + args.new_tokens
     model.prepare(max_batch=args.batch, max_seq_len=total)
@@ -84,7 +87,8 @@ def main():
             "data": "synthetic (uniform random prompt ids, N(0,0.02) random-init weights)", "vs_baseline": None,
             "config": {"model": args.model, "batch": args.batch, "prompt": args.prompt, "new_tokens": args.new_tokens,
                        "kv_cache": "paged, 64-token pages", "parallelism": f"tp{world}",
-                       "cuda_graph": not args.no_graph},
+                       "cuda_graph": not args.no_graph,
+                       "all_reduce": "nccl" if (args.nccl_ar or world == 1) else "fused into the GEMM kernel"},
             "kernel_launcher_calls_outside_graph": launches, "sample": toks[0, :8].tolist()}))
     if world > 1:
         tdist.barrier()

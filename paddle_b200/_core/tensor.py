@@ -17,6 +17,16 @@ from . import dtype as _dt
 from .unique_name import generate as _uniq
 
 
+class _Size(int):
+    def __new__(cls, numel, shape):
+        o = int.__new__(cls, numel)
+        o._shape = shape
+        return o
+
+    def __call__(self, dim=None):
+        return self._shape if dim is None else self._shape[dim]
+
+
 class Tensor(torch.Tensor):
     """Dense tensor with PaddlePaddle's Python surface."""
 
@@ -64,7 +74,9 @@ class Tensor(torch.Tensor):
 
     @property
     def size(self):
-        return torch.Tensor.numel(self)
+        """Paddle: the number of elements (an int).  The returned int is also callable like ``torch.Tensor.size`` so
+        that library code written against torch keeps working on this subclass."""
+        return _Size(torch.Tensor.numel(self), torch.Tensor.shape.__get__(self))
 
     def dim(self):
         return torch.Tensor.dim(self)
@@ -388,6 +400,20 @@ class EagerParamBase(Tensor):
         self.is_distributed = False
         self._persistable = True
         self.main_grad = None
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        """The result of an operator on a parameter is an ordinary tensor (only in-place operators hand the
+        parameter itself back)."""
+        ret = super().__torch_function__(func, types, args, kwargs or {})
+
+        def conv(r):
+            if type(r) is EagerParamBase and not any(r is a for a in args):
+                return r.as_subclass(Tensor)
+            return r
+        if isinstance(ret, (tuple, list)):
+            return type(ret)(conv(r) for r in ret)
+        return conv(ret)
 
     @property
     def trainable(self):

@@ -1,0 +1,193 @@
+"""``paddle.audio`` (python/paddle/audio/): window functions, mel / dB helpers, spectrogram feature layers, wav IO."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .._core.tensor import as_tensor
+from ..nn.layer.layers import Layer
+
+
+def _p(x):
+    return x.as_subclass(torch.Tensor) if isinstance(x, torch.Tensor) else torch.as_tensor(x)
+
+
+class functional:
+    @staticmethod
+    def get_window(window, win_length, fftbins=True, dtype="float64"):
+        name = window if isinstance(window, str) else window[0]
+        fn = {"hann": torch.hann_window, "hamming": torch.hamming_window, "blackman": torch.blackman_window,
+              "bartlett": torch.bartlett_window, "kaiser": torch.kaiser_window}.get(name)
+        if name in ("rect", "boxcar", "ones"):
+            return as_tensor(torch.ones(win_length, dtype=torch.float64))
+        if fn is None:
+            raise ValueError(f"unknown window {name}")
+        return as_tensor(fn(win_length, periodic=fftbins, dtype=torch.float64))
+
+    @staticmethod
+    def hz_to_mel(freq, htk=False):
+        f = torch.as_tensor(freq, dtype=torch.float64)
+        if htk:
+            out = 2595.0 * torch.log10(1.0 + f / 700.0)
+        else:
+            f_sp, min_log_hz = 200.0 / 3, 1000.0
+            min_log_mel, logstep = min_log_hz / f_sp, math.log(6.4) / 27.0
+            out = torch.where(f >= min_log_hz, min_log_mel + torch.log(f.clamp(min=1e-10) / min_log_hz) / logstep, f / f_sp)
+        return float(out) if out.dim() == 0 and not isinstance(freq, torch.Tensor) else as_tensor(out)
+
+    @staticmethod
+    def mel_to_hz(mel, htk=False):
+        m = torch.as_tensor(mel, dtype=torch.float64)
+        if htk:
+            out = 700.0 * (10.0 ** (m / 2595.0) - 1.0)
+        else:
+            f_sp, min_log_hz = 200.0 / 3, 1000.0
+            min_log_mel, logstep = min_log_hz / f_sp, math.log(6.4) / 27.0
+            out = torch.where(m >= min_log_mel, min_log_hz * torch.exp(logstep * (m - min_log_mel)), f_sp * m)
+        return float(out) if out.dim() == 0 and not isinstance(mel, torch.Tensor) else as_tensor(out)
+
+    @staticmethod
+    def mel_frequencies(n_mels=64, f_min=0.0, f_max=11025.0, htk=False, dtype="float32"):
+        lo, hi = functional.hz_to_mel(f_min, htk), functional.hz_to_mel(f_max, htk)
+        return as_tensor(_p(functional.mel_to_hz(torch.linspace(lo, hi, n_mels, dtype=torch.float64), htk)).float())
+
+    @staticmethod
+    def fft_frequencies(sr, n_fft, dtype="float32"):
+        return as_tensor(torch.linspace(0, sr / 2, 1 + n_fft // 2))
+
+    @staticmethod
+    def compute_fbank_matrix(sr, n_fft, n_mels=64, f_min=0.0, f_max=None, htk=False, norm="slaney", dtype="float32"):
+        f_max = f_max or sr / 2
+        fft_f = _p(functional.fft_frequencies(sr, n_fft)).double()
+        mel_f = _p(functional.mel_to_hz(torch.linspace(functional.hz_to_mel(f_min, htk), functional.hz_to_mel(f_max, htk),
+                                                       n_mels + 2, dtype=torch.float64), htk)).double()
+        fdiff = mel_f[1:] - mel_f[:-1]
+        ramps = mel_f[:, None] - fft_f[None]
+        lower, upper = -ramps[:-2] / fdiff[:-1, None], ramps[2:] / fdiff[1:, None]
+        w = torch.clamp(torch.minimum(lower, upper), min=0)
+        if norm == "slaney":
+            w = w * (2.0 / (mel_f[2:] - mel_f[:-2]))[:, None]
+        return as_tensor(w.float())
+
+    @staticmethod
+    def power_to_db(spect, ref_value=1.0, amin=1e-10, top_db=80.0):
+        s = _p(spect)
+        db = 10.0 * torch.log10(s.clamp(min=amin)) - 10.0 * math.log10(max(amin, ref_value))
+        if top_db is not None:
+            db = torch.maximum(db, db.max() - top_db)
+        return as_tensor(db)
+
+    @staticmethod
+    def create_dct(n_mfcc, n_mels, norm="ortho", dtype="float32"):
+        n = torch.arange(n_mels, dtype=torch.float32)
+        k = torch.arange(n_mfcc, dtype=torch.float32)[:, None]
+        dct = torch.cos(math.pi / n_mels * (n + 0.5) * k)
+        if norm == "ortho":
+            dct[0] *= 1.0 / math.sqrt(2.0)
+            dct *= math.sqrt(2.0 / n_mels)
+        else:
+            dct *= 2.0
+        return as_tensor(dct.t().contiguous())
+
+
+class features:
+    class Spectrogram(Layer):
+        def __init__(self, n_fft=512, hop_length=None, win_length=None, window="hann", power=2.0, center=True,
+                     pad_mode="reflect", dtype="float32"):
+            super().__init__()
+            self.n_fft, self.hop, self.win_length = n_fft, hop_length or n_fft // 4, win_length or n_fft
+            self.power, self.center, self.pad_mode = power, center, pad_mode
+            self.window = _p(functional.get_window(window, self.win_length)).float()
+
+        def forward(self, x):
+            s = torch.stft(_p(x), self.n_fft, self.hop, self.win_length, self.window.to(x.device), self.center,
+                           self.pad_mode, return_complex=True)
+            return as_tensor(s.abs() ** self.power)
+
+    class MelSpectrogram(Layer):
+        def __init__(self, sr=22050, n_fft=512, hop_length=None, win_length=None, window="hann", power=2.0, center=True,
+                     pad_mode="reflect", n_mels=64, f_min=50.0, f_max=None, htk=False, norm="slaney", dtype="float32"):
+            super().__init__()
+            self.spec = features.Spectrogram(n_fft, hop_length, win_length, window, power, center, pad_mode)
+            self.fbank = _p(functional.compute_fbank_matrix(sr, n_fft, n_mels, f_min, f_max, htk, norm))
+
+        def forward(self, x):
+            return as_tensor(torch.matmul(self.fbank.to(x.device), _p(self.spec(x))))
+
+    class LogMelSpectrogram(Layer):
+        def __init__(self, sr=22050, n_fft=512, hop_length=None, win_length=None, window="hann", power=2.0, center=True,
+                     pad_mode="reflect", n_mels=64, f_min=50.0, f_max=None, htk=False, norm="slaney", ref_value=1.0,
+                     amin=1e-10, top_db=None, dtype="float32"):
+            super().__init__()
+            self.mel = features.MelSpectrogram(sr, n_fft, hop_length, win_length, window, power, center, pad_mode, n_mels,
+                                               f_min, f_max, htk, norm)
+            self.ref_value, self.amin, self.top_db = ref_value, amin, top_db
+
+        def forward(self, x):
+            return functional.power_to_db(self.mel(x), self.ref_value, self.amin, self.top_db)
+
+    class MFCC(Layer):
+        def __init__(self, sr=22050, n_mfcc=40, n_fft=512, hop_length=None, win_length=None, window="hann", power=2.0,
+                     center=True, pad_mode="reflect", n_mels=64, f_min=50.0, f_max=None, htk=False, norm="slaney",
+                     ref_value=1.0, amin=1e-10, top_db=None, dtype="float32"):
+            super().__init__()
+            self.logmel = features.LogMelSpectrogram(sr, n_fft, hop_length, win_length, window, power, center, pad_mode,
+                                                     n_mels, f_min, f_max, htk, norm, ref_value, amin, top_db)
+            self.dct = _p(functional.create_dct(n_mfcc, n_mels))
+
+        def forward(self, x):
+            lm = _p(self.logmel(x))
+            return as_tensor(torch.matmul(lm.transpose(-1, -2), self.dct.to(lm.device)).transpose(-1, -2))
+
+
+class backends:
+    @staticmethod
+    def list_available_backends():
+        return ["wave_backend"]
+
+    @staticmethod
+    def get_current_backend():
+        return "wave_backend"
+
+    @staticmethod
+    def set_backend(name):
+        if name != "wave_backend":
+            raise NotImplementedError("only the built-in wave backend is available")
+
+
+def load(filepath, frame_offset=0, num_frames=-1, normalize=True, channels_first=True):
+    import wave
+
+    import numpy as np
+    with wave.open(filepath, "rb") as f:
+        sr, nch, width = f.getframerate(), f.getnchannels(), f.getsampwidth()
+        f.setpos(frame_offset)
+        raw = f.readframes(f.getnframes() - frame_offset if num_frames < 0 else num_frames)
+    dt = {1: np.uint8, 2: np.int16, 4: np.int32}[width]
+    a = np.frombuffer(raw, dtype=dt).reshape(-1, nch)
+    t = torch.from_numpy(a.astype(np.float32))
+    if normalize:
+        t = (t - 128.0) / 128.0 if width == 1 else t / float(2 ** (8 * width - 1))
+    return as_tensor(t.t().contiguous() if channels_first else t), sr
+
+
+def save(filepath, src, sample_rate, channels_first=True, encoding=None, bits_per_sample=16):
+    import wave
+
+    import numpy as np
+    t = _p(src).detach().cpu()
+    t = t.t() if channels_first else t
+    a = (t.clamp(-1, 1) * (2 ** (bits_per_sample - 1) - 1)).numpy().astype({16: np.int16, 32: np.int32}[bits_per_sample])
+    with wave.open(filepath, "wb") as f:
+        f.setnchannels(a.shape[1]), f.setsampwidth(bits_per_sample // 8), f.setframerate(sample_rate)
+        f.writeframes(a.tobytes())
+
+
+def info(filepath):
+    import wave
+    with wave.open(filepath, "rb") as f:
+        class _Info:
+            sample_rate, num_frames, num_channels, bits_per_sample = f.getframerate(), f.getnframes(), f.getnchannels(), 8 * f.getsampwidth()
+            encoding = "PCM_S"
+        return _Info

@@ -219,6 +219,15 @@ class FusedMultiTransformer(Layer):
                                    qkv_b=None if self.qkv_biases[i] is None else self.qkv_biases[i].detach()))
         self._packed = packed
         self._tp_group = tp_group if (tp_group is not None and tp_group.nranks > 1) else None
+        self._gar = None
+        if self._tp_group is not None:
+            from ....ops import functional as K
+            from ....parallel import gemm_ar
+            import os
+            nccl_only = os.environ.get("PD_DECODE_NCCL_AR") == "1"     # baseline switch: GEMM + NCCL all-reduce
+            if K.get_kernel_policy() == "fused" and not nccl_only and \
+                    gemm_ar.supported(self._tp_group, E, min(max_batch, 128)):
+                self._gar = gemm_ar.GemmAllReduce(self._tp_group, E, m_cap=min(max_batch, 128))
         dev = self.linear_weights[0].device
         from ....ops import native
         self._ws = {}
@@ -248,25 +257,34 @@ class FusedMultiTransformer(Layer):
             C.all_reduce(t, group=self._tp_group)
         return t
 
+    def _row_parallel(self, name, x, w, h_res):
+        """Row-parallel projection + residual.  Returns (tensor, residual_included).  Single GPU: GEMM with the
+        residual added in its epilogue pass.  Tensor parallel, decode-sized M: ONE kernel does the GEMM and the
+        all-reduce over peer memory and adds the residual.  Otherwise: GEMM, NCCL all-reduce, residual added by the
+        following norm kernel."""
+        if self._tp_group is None:
+            return self._gemm(name, x, w, residual=h_res), True
+        if self._gar is not None and x.shape[0] <= self._gar.m_cap:
+            return self._gar(x, w, residual=h_res), True
+        o = self._gemm(name, x, w)
+        self._all_reduce(o)
+        return o, False
+
     def _mlp_and_out(self, i, h_res, attn_out2d):
-        """Shared tail of a layer: out-projection (+AR) + residual, RMSNorm, SwiGLU MLP (+AR); returns the tensor
-        that the next layer's fused residual+RMSNorm consumes and the running residual."""
+        """Shared tail of a layer: out-projection + residual, RMSNorm, SwiGLU MLP; returns the tensor that the next
+        layer's (residual+)RMSNorm consumes, the running residual, and whether that residual is still pending."""
         from ....ops import native
         P = self._packed[i]
-        tp = self._tp_group is not None
-        o = self._gemm("out", attn_out2d, P["out"], residual=None if tp else h_res)
-        if tp:
-            self._all_reduce(o)
-            y, _, h_res = native.rms_norm_fwd(o, P["ffn_ln"], self.epsilon, residual=h_res, want_residual_out=True)
-        else:
+        o, inc = self._row_parallel("out", attn_out2d, P["out"], h_res)
+        if inc:
             h_res = o
             y, _, _ = native.rms_norm_fwd(o, P["ffn_ln"], self.epsilon)
+        else:
+            y, _, h_res = native.rms_norm_fwd(o, P["ffn_ln"], self.epsilon, residual=h_res, want_residual_out=True)
         g = self._gemm("ffn1", y, P["ffn1"])
         a = native.swiglu_fwd(g)
-        f = self._gemm("ffn2", a, P["ffn2"], residual=None if tp else h_res)
-        if tp:
-            self._all_reduce(f)
-        return f, h_res, tp
+        f, inc = self._row_parallel("ffn2", a, P["ffn2"], h_res)
+        return f, h_res, not inc
 
     def _layer_input(self, i, h, h_res, pending_tp):
         """RMSNorm of the layer input; under TP the previous layer's all-reduced MLP output is added to the residual

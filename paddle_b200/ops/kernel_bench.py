@@ -169,9 +169,92 @@ def bench_adamw(args, timer, hbm, tf):
     return out
 
 
+def bench_decode(args, timer, hbm, tf):
+    """Paged decode attention (bandwidth-bound: every cached K/V byte is read once) and the skinny split-K GEMM."""
+    import math
+
+    from . import native
+    B, H, ctx = (16, 8, 1024) if args.small else (64, 40, 1280)
+    pages = (ctx + 63) // 64
+    nblocks = B * pages
+    kc = torch.randn(nblocks, H, 64, 128, device="cuda").to(torch.bfloat16)
+    vc = torch.randn(nblocks, H, 64, 128, device="cuda").to(torch.bfloat16)
+    q = torch.randn(B, H, 128, device="cuda").to(torch.bfloat16)
+    table = torch.randperm(nblocks, device="cuda").int().reshape(B, pages)
+    lens = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    nsplit = native.decode_attn_splits(B, H, pages)
+    out = []
+    t = timer(lambda: native.paged_decode_attn(q, kc, vc, table, lens, 1 / math.sqrt(128), nsplit=nsplit), args.iters)
+    by = 2.0 * B * ctx * H * 128 * 2
+    rec = dict(op="paged_decode_attn", B=B, heads=H, ctx=ctx, nsplit=nsplit, ms=t, gbs=by / t / 1e6,
+               frac_of_measured=by / t / 1e6 / hbm)
+    print(json.dumps(rec), flush=True)
+    out.append(rec)
+    M = 64
+    for name, K_, N in (("out_proj", 5120, 5120), ("ffn2", 13824, 5120), ("qkv", 5120, 15360), ("ffn1", 5120, 27648)):
+        if args.small and name != "out_proj":
+            continue
+        x = torch.randn(M, K_, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(K_, N, device="cuda") * 0.02).to(torch.bfloat16)
+        s = native.suggest_splits(M, N, K_)
+        acc = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+
+        def run():
+            if s > 1:
+                native.gemm_splitk(x, w, acc, s)
+                native.splitk_finalize(acc)
+            else:
+                native.gemm(x, w)
+        t = timer(run, args.iters)
+        by = 2.0 * K_ * N
+        rec = dict(op="skinny_gemm", name=name, M=M, N=N, K=K_, splits=s, ms=t, gbs=by / t / 1e6,
+                   frac_of_measured=by / t / 1e6 / hbm)
+        if not args.no_baseline:
+            t2 = timer(lambda: torch.matmul(x, w), args.iters)
+            rec.update(lib_ms=t2, lib_gbs=by / t2 / 1e6)
+        print(json.dumps(rec), flush=True)
+        out.append(rec)
+    return out
+
+
+def bench_fused_gemm(args, timer, hbm, tf):
+    """Tensor-core side of the fused all-gather -> GEMM kernel on one GPU: the gathered operand is complete in the
+    staging buffer (no pushes, no flag waits), so the number isolates what the fused kernel's tile loop costs
+    against the plain GEMM on the same shape."""
+    import ctypes
+
+    from . import _lib, native
+    from ._lib import c_int, ptr, stream
+    T, H, N = (2048, 4096, 4096) if args.small else (4096, 4096, 6144)
+    k = _lib.kernels()
+    xfull = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    x = xfull[: T // 2].contiguous()
+    w = (torch.randn(H, N, device="cuda") * 0.05).to(torch.bfloat16)
+    y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    flags = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    ack = torch.zeros(16, dtype=torch.int32, device="cuda")
+    done = torch.zeros(1, dtype=torch.int32, device="cuda")
+    U = ctypes.c_ulonglong * 8
+    ps, pf, pa = U(*([xfull.data_ptr()] * 8)), U(*([flags.data_ptr()] * 8)), U(*([ack.data_ptr()] * 8))
+
+    def ag():
+        rc = k.pd_ag_gemm(ptr(xfull), ptr(w), ptr(y), c_int(T), c_int(N), c_int(H), c_int(H), c_int(N), c_int(N), c_int(0),
+                          c_int(1), c_int(0), c_int(0), ptr(x), c_int(T // 2), c_int(128), c_int(H), c_int(0), c_int(2),
+                          c_int(0), c_int(0), c_int(0), c_int(1), c_int(0), ps, pf, pa, ptr(done), c_int(0), c_int(2000),
+                          ptr(_lib.status_buffer()), stream())
+        _lib.check(rc, "pd_ag_gemm")
+    fl = 2.0 * T * N * H
+    t = timer(ag, args.iters)
+    t2 = timer(lambda: native.gemm(xfull, w), args.iters)
+    rec = dict(op="ag_gemm_tile_loop", M=T, N=N, K=H, ms=t, tflops=fl / t / 1e9, frac_of_measured=fl / t / 1e9 / tf,
+               plain_gemm_ms=t2, plain_gemm_tflops=fl / t2 / 1e9)
+    print(json.dumps(rec), flush=True)
+    return [rec]
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["gemm", "attention", "norm", "adamw", "all"])
+    ap.add_argument("--op", default="all", choices=["gemm", "attention", "norm", "adamw", "decode", "fused_gemm", "all"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--only", default=None)
     ap.add_argument("--iters", type=int, default=10)
@@ -185,7 +268,8 @@ def main(argv=None):
     hbm, tf = _peaks(args.peaks)
     timer = _Timer(flush=not args.no_flush)
     res = []
-    for name, fn in (("gemm", bench_gemm), ("attention", bench_attention), ("norm", bench_norm), ("adamw", bench_adamw)):
+    for name, fn in (("gemm", bench_gemm), ("attention", bench_attention), ("norm", bench_norm), ("adamw", bench_adamw),
+                     ("decode", bench_decode), ("fused_gemm", bench_fused_gemm)):
         if args.op in (name, "all"):
             res += fn(args, timer, hbm, tf)
     _lib.check_status()

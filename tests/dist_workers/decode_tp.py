@@ -1,0 +1,83 @@
+"""Tensor-parallel serving on 2+ GPUs: (1) the fused GEMM -> all-reduce kernel against an fp32 reference over
+several launches (epoch / slot protocol), eager and replayed from a CUDA graph; (2) the TP inference engine
+(fused and NCCL variants) generates the same tokens as the single-GPU engine on the same weights."""
+import os
+import sys
+
+import _common
+import torch
+
+import paddle_b200 as paddle
+import paddle_b200.distributed as dist
+from paddle_b200.distributed import fleet
+from paddle_b200.ops import _lib
+
+n = int(os.environ["PADDLE_TRAINERS_NUM"])
+strategy = fleet.DistributedStrategy()
+strategy.hybrid_configs = {"dp_degree": 1, "mp_degree": n}
+fleet.init(is_collective=True, strategy=strategy)
+rank = dist.get_rank()
+g = fleet.get_hybrid_communicate_group().get_model_parallel_group()
+from paddle_b200.parallel.gemm_ar import GemmAllReduce
+
+res = {}
+M, N, K = 48, 1024, 512
+gar = GemmAllReduce(g, N, m_cap=64)
+errs = []
+torch.manual_seed(5)            # same full operands on every rank; each uses its K slice
+for it in range(5):
+    xf = (torch.randn(M, K * n, device="cuda") * 0.5).bfloat16()
+    wf = (torch.randn(K * n, N, device="cuda") * 0.05).bfloat16()
+    r = torch.randn(M, N, device="cuda").bfloat16()
+    x, w = xf[:, rank * K:(rank + 1) * K].contiguous(), wf[rank * K:(rank + 1) * K].contiguous()
+    out = gar(x, w, residual=r)
+    ref = xf.float() @ wf.float() + r.float()
+    errs.append(float((out.float() - ref).abs().max() / ref.abs().max()))
+res["gemm_ar_err"] = max(errs)
+# graph replay: constant arguments, device-side epoch
+xs = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+ws = (torch.randn(K, N, device="cuda") * 0.05).bfloat16()
+outg = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+side = torch.cuda.Stream()
+side.wait_stream(torch.cuda.current_stream())
+with torch.cuda.stream(side):
+    gar(xs, ws, out=outg)
+torch.cuda.current_stream().wait_stream(side)
+graph = torch.cuda.CUDAGraph()
+with torch.cuda.graph(graph):
+    gar(xs, ws, out=outg)
+    gar(xs, ws, out=outg)
+full = xs.float() @ ws.float()
+dist.all_reduce(full, group=g)
+ge = []
+for it in range(3):
+    outg.zero_()
+    graph.replay()
+    ge.append(float((outg.float() - full).abs().max() / full.abs().max()))
+res["gemm_ar_graph_err"] = max(ge)
+torch.cuda.synchronize()
+_lib.check_status()
+
+# ---- engine parity
+from paddle_b200.models.llama import LlamaConfig, LlamaForCausalLM
+from paddle_b200.models.llama_infer import LlamaForCausalLMInference
+paddle.seed(3)
+cfg = LlamaConfig.tiny(hidden_size=512, intermediate_size=1024, num_attention_heads=4, num_hidden_layers=2,
+                       vocab_size=1024, dtype="bfloat16", max_position_embeddings=512)
+train = LlamaForCausalLM(cfg)
+B, S, NEW = 4, 70, 8
+ids = torch.randint(0, 1024, (B, S), generator=torch.Generator().manual_seed(1)).cuda()
+single = LlamaForCausalLMInference(cfg).load_from_training(train).prepare(B, S + NEW)
+t_single = single.generate(ids, NEW, use_cuda_graph=False)
+for policy in ("fused", "baseline"):
+    if policy == "baseline":
+        os.environ["PD_DECODE_NCCL_AR"] = "1"
+    tp = LlamaForCausalLMInference(cfg, tp_group=g).load_from_training(train, rank=g.rank).prepare(B, S + NEW)
+    os.environ.pop("PD_DECODE_NCCL_AR", None)
+    res[f"{policy}_uses_fused_ar"] = tp.transformer._gar is not None
+    for graph_mode in (False, True):
+        t_tp = tp.generate(ids, NEW, use_cuda_graph=graph_mode)
+        res[f"{policy}_graph{int(graph_mode)}_match"] = float((t_tp == t_single).float().mean())
+torch.cuda.synchronize()
+_lib.check_status()
+_common.dump(res)

@@ -35,3 +35,15 @@ def test_fused_ag_gemm_and_gemm_rs():
     for r in res:
         for k, v in r["errs"].items():
             assert v < 3e-2, (k, v)
+
+
+def test_tp_decode_fused_gemm_allreduce():
+    """Fused GEMM->all-reduce kernel (eager and from a CUDA graph) and the TP serving engine against the single-GPU
+    engine."""
+    res = run_workers("decode_tp.py", 2, backend="nccl", gpus=True, extra_env=ENV, timeout=400)
+    for r in res:
+        assert r["gemm_ar_err"] < 2e-2 and r["gemm_ar_graph_err"] < 2e-2, r
+        assert r["fused_uses_fused_ar"] and not r["baseline_uses_fused_ar"]
+        for k, v in r.items():
+            if k.endswith("_match"):
+                assert v >= 0.9, (k, v)
