@@ -11,7 +11,12 @@
 //   (5) dQ_t^T = K^T dS_t^T      SS   N = 64  -> drained by 4 extra warps, transposed in shared memory
 //       and added to an fp32 dQ accumulator with a TMA reduce (cp.reduce.async.bulk.tensor .add).
 // dK / dV stay in TMEM for the whole walk and are written once.  TMEM columns:
-//   dK 0-127 | dV 128-255 | S^T 256-319 | dP^T 320-383 | P^T 384-415 | dS^T 416-447 | dQ^T 448-511
+//   dK 0-127 | dV 128-255 | work buffer A 256-383 | work buffer B 384-511
+// A work buffer holds S^T (cols 0-63) and dP^T (64-127) of one query sub-tile; after the softmax warps have read
+// both into registers they write P^T (packed bf16, cols 0-31) and dS^T (32-63) over S^T, and GEMM (5) later puts
+// dQ^T over dP^T.  Sub-tiles alternate between A and B, so GEMMs (1),(2) of sub-tile t+1 run on the tensor cores
+// while the softmax warps work on sub-tile t, and GEMMs (3)-(5) of t overlap the softmax of t+1.  The per-column
+// LSE / Delta values are staged in shared memory once per sub-tile and read as broadcasts.
 // Warps: 0-3 softmax (+ final dK/dV store), 4-7 dQ drain, 8 TMA producer, 9 MMA issuer.
 #include <math.h>
 
@@ -30,14 +35,15 @@ constexpr int STAGES = 3;
 constexpr int DS_BYTES = BKV * BQ * 2;        // 16 KB
 constexpr int DQ_STAGE_BYTES = BQ * D * 4;    // 32 KB fp32 [64 q][128 d]
 constexpr int NUM_THREADS = 320;
-constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + DS_BYTES + DQ_STAGE_BYTES + 1024 + 256;
-constexpr uint32_t COL_DK = 0, COL_DV = 128, COL_ST = 256, COL_DPT = 320, COL_PT = 384, COL_DST = 416,
-                   COL_DQT = 448;
+constexpr int STATS_BYTES = 2 * 128 * 4;         // [2][lse2 x64 | delta x64]
+constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + 2 * DS_BYTES + DQ_STAGE_BYTES + STATS_BYTES + 1024 + 256;
+constexpr uint32_t COL_DK = 0, COL_DV = 128, COL_BUF = 256;
+constexpr uint32_t OFF_ST = 0, OFF_DPT = 64, OFF_PT = 0, OFF_DST = 32, OFF_DQT = 64;   // inside a 128-column work buffer
 
 struct Barriers {
   uint64_t kv_full;
   uint64_t qdo_full[STAGES], qdo_empty[STAGES];
-  uint64_t st_full, pds_full, dq_full, dq_empty, dkv_full, drain;
+  uint64_t st_full[2], pds_full[2], dq_full[2], dq_empty[2], dkv_full, drain;
   uint32_t tmem_base;
   int abort_flag;
   int drain_decision;
@@ -80,8 +86,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sV = sK + KV_TILE;
   uint8_t* sQ = sV + KV_TILE;                       // STAGES x [Q tile | dO tile]
   uint8_t* sDS = sQ + STAGES * 2 * Q_TILE;
-  uint8_t* sDQ = sDS + DS_BYTES;
-  Barriers* bars = reinterpret_cast<Barriers*>(sDQ + DQ_STAGE_BYTES);
+  uint8_t* sDQ = sDS + 2 * DS_BYTES;
+  float* stats = reinterpret_cast<float*>(sDQ + DQ_STAGE_BYTES);
+  Barriers* bars = reinterpret_cast<Barriers*>(sDQ + DQ_STAGE_BYTES + STATS_BYTES);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -104,10 +111,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&bars->qdo_full[s], 1);
       mbar_init(&bars->qdo_empty[s], 1);
     }
-    mbar_init(&bars->st_full, 1);
-    mbar_init(&bars->pds_full, 128);
-    mbar_init(&bars->dq_full, 1);
-    mbar_init(&bars->dq_empty, 128);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars->st_full[b], 1);
+      mbar_init(&bars->pds_full[b], 128);
+      mbar_init(&bars->dq_full[b], 1);
+      mbar_init(&bars->dq_empty[b], 128);
+    }
     mbar_init(&bars->dkv_full, 1);
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
@@ -159,55 +168,61 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t idesc_s = make_idesc(BKV, BQ, false, false);   // (1),(2)
       constexpr uint32_t idesc_kv = make_idesc(BKV, D, false, true);    // (3),(4)  A from TMEM
       constexpr uint32_t idesc_dq = make_idesc(D, BQ, true, true);      // (5)
-      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), ds_addr = smem_u32(sDS);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       bool ok = mbar_wait(&bars->kv_full, 0, abort_flag, p.status, 200);
       auto issue_s = [&](int it) -> bool {
         const int s = it % STAGES;
         if (!mbar_wait(&bars->qdo_full[s], (it / STAGES) & 1, abort_flag, p.status, 210 + s)) return false;
         tc_fence_after();
         const uint32_t q_addr = smem_u32(sQ + s * 2 * Q_TILE), do_addr = q_addr + Q_TILE;
+        const uint32_t buf = tmem + COL_BUF + (it & 1) * 128;
+        // dP^T of this buffer's previous use now holds dQ^T: it must have been drained
+        if (!mbar_wait(&bars->dq_empty[it & 1], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 230 + (it & 1))) return false;
+        tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t offa = (ks >> 2) * KV_HALF + (ks & 3) * 32;
           const uint32_t offb = (ks >> 2) * Q_HALF + (ks & 3) * 32;
-          umma_bf16_ss(tmem + COL_ST, make_smem_desc_sw128(k_addr + offa, 16, 1024),
+          umma_bf16_ss(buf + OFF_ST, make_smem_desc_sw128(k_addr + offa, 16, 1024),
                        make_smem_desc_sw128(q_addr + offb, 16, 1024), idesc_s, ks != 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t offa = (ks >> 2) * KV_HALF + (ks & 3) * 32;
           const uint32_t offb = (ks >> 2) * Q_HALF + (ks & 3) * 32;
-          umma_bf16_ss(tmem + COL_DPT, make_smem_desc_sw128(v_addr + offa, 16, 1024),
+          umma_bf16_ss(buf + OFF_DPT, make_smem_desc_sw128(v_addr + offa, 16, 1024),
                        make_smem_desc_sw128(do_addr + offb, 16, 1024), idesc_s, ks != 0 ? 1u : 0u);
         }
-        umma_commit(&bars->st_full);
+        umma_commit(&bars->st_full[it & 1]);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it % STAGES;
+        const int b = it & 1;
         const uint32_t q_addr = smem_u32(sQ + s * 2 * Q_TILE), do_addr = q_addr + Q_TILE;
-        if (!mbar_wait(&bars->pds_full, it & 1, abort_flag, p.status, 220)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks)   // (3) dV += P^T dO
-          umma_bf16_ts(tmem + COL_DV, tmem + COL_PT + ks * 8,
-                       make_smem_desc_sw128(do_addr + ks * 2048, Q_HALF, 1024), idesc_kv, (it | ks) != 0 ? 1u : 0u);
-#pragma unroll
-        for (int ks = 0; ks < BQ / 16; ++ks)   // (4) dK += dS^T Q
-          umma_bf16_ts(tmem + COL_DK, tmem + COL_DST + ks * 8,
-                       make_smem_desc_sw128(q_addr + ks * 2048, Q_HALF, 1024), idesc_kv, (it | ks) != 0 ? 1u : 0u);
-        if (!mbar_wait(&bars->dq_empty, (it & 1) ^ 1, abort_flag, p.status, 230)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < BKV / 16; ++ks)  // (5) dQ^T = K^T dS^T
-          umma_bf16_ss(tmem + COL_DQT, make_smem_desc_sw128(k_addr + ks * 2048, KV_HALF, 1024),
-                       make_smem_desc_sw128(ds_addr + ks * 2048, 16, 1024), idesc_dq, ks != 0 ? 1u : 0u);
-        umma_commit(&bars->dq_full);
-        umma_commit(&bars->qdo_empty[s]);
+        const uint32_t buf = tmem + COL_BUF + b * 128;
+        const uint32_t ds_addr = smem_u32(sDS + b * DS_BYTES);
+        // S^T / dP^T of the NEXT sub-tile go to the other buffer now: they run while the softmax warps work
         if (it + 1 < n_it) {
           if (!issue_s(it + 1)) { ok = false; break; }
         }
+        if (!mbar_wait(&bars->pds_full[b], (it >> 1) & 1, abort_flag, p.status, 220 + b)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks)   // (3) dV += P^T dO
+          umma_bf16_ts(tmem + COL_DV, buf + OFF_PT + ks * 8,
+                       make_smem_desc_sw128(do_addr + ks * 2048, Q_HALF, 1024), idesc_kv, (it | ks) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < BQ / 16; ++ks)   // (4) dK += dS^T Q
+          umma_bf16_ts(tmem + COL_DK, buf + OFF_DST + ks * 8,
+                       make_smem_desc_sw128(q_addr + ks * 2048, Q_HALF, 1024), idesc_kv, (it | ks) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < BKV / 16; ++ks)  // (5) dQ^T = K^T dS^T  (over this buffer's dP^T, already consumed)
+          umma_bf16_ss(buf + OFF_DQT, make_smem_desc_sw128(k_addr + ks * 2048, KV_HALF, 1024),
+                       make_smem_desc_sw128(ds_addr + ks * 2048, 16, 1024), idesc_dq, ks != 0 ? 1u : 0u);
+        umma_commit(&bars->dq_full[b]);
+        umma_commit(&bars->qdo_empty[s]);
       }
       if (ok) umma_commit(&bars->dkv_full);
       else {
@@ -226,46 +241,53 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int it = 0; it < n_it; ++it) {
       const int qh = kv_head * group + it / per_head;
       const int q0 = (t0 + it % per_head) * BQ;
-      // per-column statistics: lane l keeps columns l and l + 32
-      const float* lse_row = p.lse + (static_cast<size_t>(batch) * p.Hq + qh) * p.Sq;
-      const float* dl_row = p.delta + (static_cast<size_t>(batch) * p.Hq + qh) * p.Sq;
-      float lse2[2], dlt[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int qi = q0 + h * 32 + lane;
+      const int b = it & 1;
+      // per-column statistics of this sub-tile -> shared memory (threads 0-63: LSE in log2 units, 64-127: Delta)
+      {
+        const float* src = (row < 64 ? p.lse : p.delta) + (static_cast<size_t>(batch) * p.Hq + qh) * p.Sq;
+        const int qi = q0 + (row & 63);
         const bool in = qi < p.Sq;
-        lse2[h] = in ? lse_row[qi] * 1.4426950408889634f : INFINITY;   // +inf -> p = 0 for padded rows
-        dlt[h] = in ? dl_row[qi] : 0.f;
+        float v = in ? src[qi] : 0.f;
+        if (row < 64) v = in ? v * 1.4426950408889634f : INFINITY;       // +inf -> p = 0 for padded rows
+        stats[b * 128 + row] = v;
       }
-      if (!warp_mbar_wait(&bars->st_full, it & 1, abort_flag, p.status, 300)) { ok = false; break; }
+      named_bar_sync(1, 128);
+      if (!warp_mbar_wait(&bars->st_full[b], (it >> 1) & 1, abort_flag, p.status, 300 + b)) { ok = false; break; }
       tc_fence_after();
       // visible iff kv <= q + off  <=>  q_local >= kvi - off - q0
       const int first_visible = p.causal ? (kvi - causal_off - q0) : 0;
-#pragma unroll 1
+      const uint32_t buf = tmem + lane_base + COL_BUF + b * 128;
+      uint32_t s_r[2][32], dp_r[2][32];
+      tmem_ld_32x32(buf + OFF_ST, s_r[0]);
+      tmem_ld_32x32(buf + OFF_ST + 32, s_r[1]);
+      tmem_ld_32x32(buf + OFF_DPT, dp_r[0]);
+      tmem_ld_32x32(buf + OFF_DPT + 32, dp_r[1]);
+      tmem_ld_wait();                                   // everything is in registers: the buffer may be overwritten
+      const float* st = stats + b * 128;
+      uint8_t* row_ptr = sDS + b * DS_BYTES + row * 128;
+#pragma unroll
       for (int h = 0; h < 2; ++h) {
-        uint32_t s_r[32], dp_r[32];
-        tmem_ld_32x32(tmem + lane_base + COL_ST + h * 32, s_r);
-        tmem_ld_32x32(tmem + lane_base + COL_DPT + h * 32, dp_r);
-        tmem_ld_wait();
         uint32_t pk_p[16], pk_ds[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float pv[2], dsv[2];
+        for (int c = 0; c < 32; c += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(st + h * 32 + c);
+          const float4 d4 = *reinterpret_cast<const float4*>(st + 64 + h * 32 + c);
+          const float l2[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dsv[4];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const float l2 = __shfl_sync(0xffffffffu, lse2[h], c + e);
-            const float dl = __shfl_sync(0xffffffffu, dlt[h], c + e);
-            float pe = fast_exp2(fmaf(__uint_as_float(s_r[c + e]), p.scale_log2, -l2));
+          for (int e = 0; e < 4; ++e) {
+            float pe = fast_exp2(fmaf(__uint_as_float(s_r[h][c + e]), p.scale_log2, -l2[e]));
             if (h * 32 + c + e < first_visible) pe = 0.f;
             pv[e] = pe;
-            dsv[e] = pe * (__uint_as_float(dp_r[c + e]) - dl) * p.scale;
+            dsv[e] = pe * (__uint_as_float(dp_r[h][c + e]) - dl[e]) * p.scale;
           }
           pk_p[c >> 1] = pack_bf16x2(pv[0], pv[1]);
+          pk_p[(c >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
           pk_ds[c >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+          pk_ds[(c >> 1) + 1] = pack_bf16x2(dsv[2], dsv[3]);
         }
-        tmem_st_32x16(tmem + lane_base + COL_PT + h * 16, pk_p);
-        tmem_st_32x16(tmem + lane_base + COL_DST + h * 16, pk_ds);
-        uint8_t* row_ptr = sDS + row * 128;
+        tmem_st_32x16(buf + OFF_PT + h * 16, pk_p);
+        tmem_st_32x16(buf + OFF_DST + h * 16, pk_ds);
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj)
           *reinterpret_cast<uint4*>(row_ptr + (((h * 4 + jj) ^ sw) << 4)) =
@@ -274,7 +296,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_st_wait();
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&bars->pds_full);
+      mbar_arrive(&bars->pds_full[b]);
     }
     // ---- final: dK, dV (fp32 in TMEM) -> bf16 -> swizzled staging (Q/dO ring is idle now) -> TMA store
     if (ok && n_it > 0) ok = warp_mbar_wait(&bars->dkv_full, 0, abort_flag, p.status, 310);
@@ -324,7 +346,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float* stage = reinterpret_cast<float*>(sDQ);
     for (int it = 0; it < n_it; ++it) {
       if (dr == 0) {
-        const bool ok = mbar_wait(&bars->dq_full, it & 1, abort_flag, p.status, 400);
+        const bool ok = mbar_wait(&bars->dq_full[it & 1], (it >> 1) & 1, abort_flag, p.status, 400 + (it & 1));
         if (ok) tma_wait_group_read<0>();             // previous reduce has read the staging tile
         bars->drain_decision = ok ? 1 : 0;
       }
@@ -332,11 +354,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (bars->drain_decision == 0) break;
       tc_fence_after();
       uint32_t r0[32], r1[32];
-      tmem_ld_32x32(tmem + lane_base + COL_DQT, r0);
-      tmem_ld_32x32(tmem + lane_base + COL_DQT + 32, r1);
+      tmem_ld_32x32(tmem + lane_base + COL_BUF + (it & 1) * 128 + OFF_DQT, r0);
+      tmem_ld_32x32(tmem + lane_base + COL_BUF + (it & 1) * 128 + OFF_DQT + 32, r1);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&bars->dq_empty);
+      mbar_arrive(&bars->dq_empty[it & 1]);
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
         stage[c * D + dr] = __uint_as_float(r0[c]);

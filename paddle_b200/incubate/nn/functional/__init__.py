@@ -473,3 +473,23 @@ def fused_moe(x, gate_weight, ffn1_weight, ffn2_weight, ffn1_bias=None, ffn1_sca
     permuted, counts, inv, scales, topk = moe_dispatch(x2, gate, moe_topk)
     out = moe_ffn(permuted, counts, ffn1_weight, ffn2_weight, ffn1_bias)
     return moe_reduce(out, scales, inv, topk, ffn2_bias, norm_topk_prob).reshape(shape)
+
+
+def quantize_expert_weights_fp8(ffn_weight):
+    """bf16 expert weights ``[E, K, N]`` -> (e4m3 ``[E, N, K]``, fp32 scales ``[E, K/128, N/128]``), 128 x 128 blocks."""
+    from ....ops import native
+    return native.fp8_quant_weight(ffn_weight.detach().contiguous())
+
+
+def moe_ffn_fp8(permute_input, token_nums_per_expert, ffn1_q, ffn1_scale, ffn2_q, ffn2_scale):
+    """Expert SwiGLU FFN with block-scaled fp8 GEMMs: activations are quantised per 1 x 128 block on the fly, weights
+    come pre-quantised from :func:`quantize_expert_weights_fp8`; both grouped GEMMs run all experts in one launch."""
+    from ....ops import native
+    counts = token_nums_per_expert.to(torch.int32)
+    offsets = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=counts.device)
+    offsets[1:] = torch.cumsum(counts, 0)
+    xq, xs = native.fp8_quant_1x128(permute_input.contiguous())
+    h = native.grouped_gemm_fp8(xq, xs, ffn1_q, ffn1_scale, offsets)
+    a = native.swiglu_fwd(h)
+    aq, as_ = native.fp8_quant_1x128(a)
+    return as_tensor(native.grouped_gemm_fp8(aq, as_, ffn2_q, ffn2_scale, offsets))

@@ -217,6 +217,32 @@ def bench_decode(args, timer, hbm, tf):
     return out
 
 
+def bench_moe(args, timer, hbm, tf):
+    """Grouped block-scaled fp8 expert GEMM (all experts in one launch) against the per-expert bf16 GEMM loop."""
+    from . import native
+    E, M, K_, N = (4, 4096, 2048, 2048) if args.small else (8, 16384, 4096, 28672)
+    per = M // E
+    x = torch.randn(M, K_, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(E, K_, N, device="cuda") * 0.02).to(torch.bfloat16)
+    offs = torch.arange(0, M + 1, per, dtype=torch.int32, device="cuda")
+    xq, xs = native.fp8_quant_1x128(x)
+    wq, ws = native.fp8_quant_weight(w)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    fl = 2.0 * M * K_ * N
+    t = timer(lambda: native.grouped_gemm_fp8(xq, xs, wq, ws, offs, out=out), args.iters)
+    tq = timer(lambda: native.fp8_quant_1x128(x), args.iters)
+    rec = dict(op="grouped_gemm_fp8", E=E, M=M, K=K_, N=N, ms=t, tflops=fl / t / 1e9, frac_of_measured_bf16_peak=fl / t / 1e9 / tf,
+               act_quant_ms=tq)
+    if not args.no_baseline:
+        def loop():
+            for e in range(E):
+                native.gemm(x[e * per:(e + 1) * per], w[e], out=out[e * per:(e + 1) * per])
+        t2 = timer(loop, args.iters)
+        rec.update(bf16_loop_ms=t2, bf16_loop_tflops=fl / t2 / 1e9)
+    print(json.dumps(rec), flush=True)
+    return [rec]
+
+
 def bench_fused_gemm(args, timer, hbm, tf):
     """Tensor-core side of the fused all-gather -> GEMM kernel on one GPU: the gathered operand is complete in the
     staging buffer (no pushes, no flag waits), so the number isolates what the fused kernel's tile loop costs
@@ -254,7 +280,7 @@ def bench_fused_gemm(args, timer, hbm, tf):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["gemm", "attention", "norm", "adamw", "decode", "fused_gemm", "all"])
+    ap.add_argument("--op", default="all", choices=["gemm", "attention", "norm", "adamw", "decode", "fused_gemm", "moe", "all"])
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--only", default=None)
     ap.add_argument("--iters", type=int, default=10)
@@ -269,7 +295,7 @@ def main(argv=None):
     timer = _Timer(flush=not args.no_flush)
     res = []
     for name, fn in (("gemm", bench_gemm), ("attention", bench_attention), ("norm", bench_norm), ("adamw", bench_adamw),
-                     ("decode", bench_decode), ("fused_gemm", bench_fused_gemm)):
+                     ("decode", bench_decode), ("fused_gemm", bench_fused_gemm), ("moe", bench_moe)):
         if args.op in (name, "all"):
             res += fn(args, timer, hbm, tf)
     _lib.check_status()

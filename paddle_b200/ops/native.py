@@ -432,3 +432,59 @@ def paged_decode_attn(q, k_cache, v_cache, block_table, seq_lens, scale, out=Non
     check(rc, "pd_paged_decode_attn")
     _count(2 if nsplit > 1 else 1)
     return out
+
+
+# --------------------------------------------------------------------------------------------- MoE / fp8
+def moe_topk_softmax(logits, k, normalize=True, counts=None):
+    """logits [T, E] fp32 -> (weights [T, k] fp32, indices [T, k] int32); ``counts`` [E] int32 is incremented."""
+    T, E = logits.shape
+    lg = logits.float().contiguous()
+    w = torch.empty((T, k), dtype=F32, device=lg.device)
+    idx = torch.empty((T, k), dtype=torch.int32, device=lg.device)
+    rc = _lib.kernels().pd_moe_topk_softmax(ptr(lg), c_int(T), c_int(E), c_int(k), c_int(1 if normalize else 0), ptr(w),
+                                            ptr(idx), ptr(counts), stream())
+    check(rc, "pd_moe_topk_softmax")
+    _count()
+    return w, idx
+
+
+def fp8_quant_1x128(x):
+    """bf16 [T, H] -> (e4m3 [T, H], fp32 scales [T, H/128]); dequantised value = q * scale."""
+    T, H = x.shape
+    _req(x.dtype == BF16 and x.is_contiguous() and H % 128 == 0, "fp8_quant_1x128: contiguous bf16 with H % 128 == 0")
+    q = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((T, H // 128), dtype=F32, device=x.device)
+    rc = _lib.kernels().pd_fp8_quant_1x128(ptr(x), ptr(q), ptr(s), c_int64(T), c_int(H), stream())
+    check(rc, "pd_fp8_quant_1x128")
+    _count()
+    return q, s
+
+
+def fp8_quant_weight(w):
+    """bf16 W [K, N] (or [E, K, N]) -> (e4m3 W^T [.., N, K], fp32 scales [.., K/128, N/128]) with 128 x 128 blocks."""
+    ws = w if w.dim() == 3 else w[None]
+    E, K, N = ws.shape
+    _req(ws.dtype == BF16 and ws.is_contiguous() and K % 128 == 0 and N % 128 == 0, "fp8_quant_weight: K, N % 128 == 0")
+    q = torch.empty((E, N, K), dtype=torch.float8_e4m3fn, device=w.device)
+    s = torch.empty((E, K // 128, N // 128), dtype=F32, device=w.device)
+    for e in range(E):
+        rc = _lib.kernels().pd_fp8_quant_128x128_t(ptr(ws[e]), ptr(q[e]), ptr(s[e]), c_int(K), c_int(N), stream())
+        check(rc, "pd_fp8_quant_128x128_t")
+    _count(E)
+    return (q, s) if w.dim() == 3 else (q[0], s[0])
+
+
+def grouped_gemm_fp8(a_q, a_scale, b_q, b_scale, offsets, out=None):
+    """Tokens sorted by expert: rows ``offsets[e]:offsets[e+1]`` of ``a_q`` [M, K] multiply expert ``e`` of
+    ``b_q`` [E, N, K]; returns bf16 [M, N].  ``offsets`` is an int32 device tensor of length E + 1."""
+    M, K = a_q.shape
+    E, N, _ = b_q.shape
+    if out is None:
+        out = torch.empty((M, N), dtype=BF16, device=a_q.device)
+    max_tiles = ((M + 127) // 128 + E) * (N // 128)
+    rc = _lib.kernels().pd_grouped_gemm_fp8(ptr(a_q), ptr(a_scale), ptr(b_q), ptr(b_scale), ptr(offsets), ptr(out),
+                                            c_int(M), c_int(N), c_int(K), c_int(E), c_int(out.stride(0)), c_int(max_tiles),
+                                            ptr(_lib.status_buffer(a_q.device)), stream())
+    check(rc, "pd_grouped_gemm_fp8")
+    _count()
+    return out

@@ -121,3 +121,39 @@ def test_paged_engine_matches_training_forward():
             agree += int(((row.argmax(-1) == toks[:, t]) & clear).sum())
             total += int(clear.sum())
         assert total > 0 and agree == total, (graph, agree, total)
+
+
+def test_withheld_signal_returns_status_not_hang():
+    """Bounded device-side wait: the fused GEMM->all-reduce kernel is launched as rank 0 of 2 while nothing ever
+    plays rank 1 (its slab counter increments go to a dummy array), so the wait on the arrival counter runs out
+    after 200 ms; the kernel returns normally, the status word names the flag wait, and the context stays usable."""
+    import ctypes
+    import time
+
+    from paddle_b200.ops import _lib, native
+    from paddle_b200.ops._lib import c_int, ptr, stream
+    M, N, K_ = 16, 256, 128
+    x = torch.randn(M, K_, device="cuda").bfloat16()
+    w = torch.randn(K_, N, device="cuda").bfloat16()
+    out = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    recv = torch.zeros(2 * 2 * M * N, device="cuda", dtype=torch.bfloat16)
+    cnt_own = torch.zeros(N // 128, dtype=torch.int32, device="cuda")
+    cnt_dummy = torch.zeros(N // 128, dtype=torch.int32, device="cuda")
+    state = torch.zeros(2, dtype=torch.int32, device="cuda")
+    U = ctypes.c_ulonglong * 8
+    p_recv = U(*([recv.data_ptr()] * 8))
+    p_cnt = U(cnt_own.data_ptr(), *([cnt_dummy.data_ptr()] * 7))
+    torch.cuda.synchronize()
+    t0 = time.time()
+    rc = _lib.kernels().pd_gemm_ar(ptr(x), ptr(w), ptr(out), ptr(None), c_int(M), c_int(N), c_int(K_), c_int(K_), c_int(N),
+                                   c_int(N), c_int(0), c_int(2), p_recv, p_cnt, c_int(M), c_int(1), ptr(state), c_int(200),
+                                   ptr(_lib.status_buffer()), stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 5.0
+    with pytest.raises(_lib.KernelStatusError, match="flag wait timed out"):
+        _lib.check_status()
+    assert cnt_own.tolist() == [1, 1]                     # own arrivals were published, the peer's never came
+    ref = (x.float() @ w.float())
+    assert (native.gemm(x, w).float() - ref).abs().max() / ref.abs().max() < 1e-2      # the context still works
+    _lib.check_status()
