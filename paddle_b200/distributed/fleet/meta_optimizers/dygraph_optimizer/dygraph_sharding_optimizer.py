@@ -155,8 +155,26 @@ class DygraphShardingOptimizerV2:
                  "v": torch.zeros(shard, dtype=torch.float32, device=dev)}
             self._buffers.append(b)
 
+    def _fused_rs_adamw(self, b):
+        """One-kernel reduce-scatter + AdamW (peer memory) is used when nothing has to look at the reduced gradient
+        before the update: GPU, bf16 parameters, fused kernel policy, no global-norm clipping."""
+        if "fused" in b:
+            return b["fused"]
+        b["fused"] = None
+        clip = self._inner_opt._grad_clip
+        if self._n > 1 and b["gbuf"].is_cuda and b["dtype"] == torch.bfloat16 and clip is None:
+            from .....ops import functional as K
+            from .....parallel import symm
+            if K.get_kernel_policy() == "fused" and symm.supported() and self._n <= 8:
+                from .....parallel.rs_adamw import FusedRSAdamW
+                b["fused"] = FusedRSAdamW(self._group, b["shard"])
+                b["inv_n"] = torch.tensor([1.0 / self._n], dtype=torch.float32, device=b["gbuf"].device)
+        return b["fused"]
+
     def reduce_gradients(self, parameter_list, hcg):
         for b in self._buffers:
+            if self._fused_rs_adamw(b) is not None:
+                continue                       # the reduction happens inside the update kernel
             C.reduce_scatter(b["gslice"], b["gbuf"], op=C.ReduceOp.AVG, group=self._group)
 
     def _global_norm_sq(self):
@@ -184,7 +202,10 @@ class DygraphShardingOptimizerV2:
         for b in self._buffers:
             lo, shard = b["lo"], b["shard"]
             pslice = b["pbuf"][lo:lo + shard]
-            if b["gslice"].is_cuda:
+            if b.get("fused") is not None:
+                b["fused"].step(b["gbuf"], b["master"], b["m"], b["v"], pslice, lr, b1, b2, eps, coeff, b1 ** t, b2 ** t,
+                                grad_scale=b["inv_n"], skip=opt._skip_flag)
+            elif b["gslice"].is_cuda:
                 from .....ops import native
                 native.adamw_flat(pslice if b["dtype"] == torch.bfloat16 else None, b["master"], b["gslice"], b["m"],
                                   b["v"], lr, b1, b2, eps, coeff, b1 ** t, b2 ** t, scale, opt._skip_flag)

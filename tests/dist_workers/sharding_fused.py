@@ -1,0 +1,73 @@
+"""Fused sharding kernels on 2+ GPUs: (1) reduce-scatter + AdamW in one kernel against NCCL reduce_scatter + the
+plain AdamW formula, several steps; (2) the stage-3 linear whose weight gather is fused into the GEMM, forward and
+backward against the dense computation."""
+import os
+
+import _common
+import torch
+
+import paddle_b200 as paddle
+import paddle_b200.distributed as dist
+from paddle_b200.distributed import fleet
+from paddle_b200.ops import _lib
+
+n = int(os.environ["PADDLE_TRAINERS_NUM"])
+strategy = fleet.DistributedStrategy()
+strategy.hybrid_configs = {"dp_degree": 1, "mp_degree": 1, "sharding_degree": n}
+fleet.init(is_collective=True, strategy=strategy)
+rank = dist.get_rank()
+g = fleet.get_hybrid_communicate_group().get_sharding_parallel_group()
+from paddle_b200.parallel.rs_adamw import FusedRSAdamW
+from paddle_b200.parallel.zero3_linear import zero3_linear
+
+res = {}
+shard = 100003                      # not a multiple of the chunk or of 4: exercises the tails
+fused = FusedRSAdamW(g, shard)
+torch.manual_seed(10 + rank)
+master = torch.randn(shard, device="cuda")
+m, v = torch.zeros(shard, device="cuda"), torch.zeros(shard, device="cuda")
+param = master.bfloat16()
+rm, rmm, rv = master.clone(), m.clone(), v.clone()
+lr, b1, b2, eps, wd = 1e-2, 0.9, 0.95, 1e-8, 0.1
+errs = []
+for step in range(1, 4):
+    grad = torch.randn(n * shard, device="cuda")
+    scale = torch.tensor([1.0 / n], device="cuda")
+    fused.step(grad, master, m, v, param, lr, b1, b2, eps, wd, b1 ** step, b2 ** step, grad_scale=scale)
+    red = torch.empty(shard, device="cuda")
+    dist.reduce_scatter(red, list(grad.chunk(n)), group=g)
+    gg = red / n
+    rm *= 1 - lr * wd
+    rmm = b1 * rmm + (1 - b1) * gg
+    rv = b2 * rv + (1 - b2) * gg * gg
+    rm += -(lr / (1 - b1 ** step)) * rmm / (rv.sqrt() / (1 - b2 ** step) ** 0.5 + eps)
+    errs.append(float((master - rm).abs().max()))
+    errs.append(float((param.float() - rm.bfloat16().float()).abs().max()))
+res["rs_adamw_err"] = max(errs)
+torch.cuda.synchronize()
+_lib.check_status()
+
+# ---- stage-3 linear with the gather fused into the GEMM
+torch.manual_seed(3)                 # same full tensors on every rank
+K, N, M = 256 * n, 512, 384
+w_full = (torch.randn(K, N, device="cuda") * 0.05).bfloat16()
+x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+w_shard = w_full[rank * (K // n):(rank + 1) * (K // n)].clone().requires_grad_(True)
+errs = []
+for it in range(3):
+    y = zero3_linear(x, w_shard, g)
+    dy = (torch.randn(M, N, device="cuda") * 0.1).bfloat16()
+    y.backward(dy)
+    ref = x.detach().float() @ w_full.float()
+    errs.append(float((y.float() - ref).abs().max() / ref.abs().max()))
+    rdx = dy.float() @ w_full.float().t()
+    errs.append(float((x.grad.float() - rdx).abs().max() / rdx.abs().max()))
+    rdw = (x.detach().float().t() @ dy.float()) * n          # every rank holds the same x, dy: the reduce sums n copies
+    sl = rdw[rank * (K // n):(rank + 1) * (K // n)]
+    errs.append(float((w_shard.grad.float() - sl).abs().max() / sl.abs().max()))
+    x.grad = None
+    w_shard.grad = None
+res["zero3_linear_err"] = max(errs)
+torch.cuda.synchronize()
+_lib.check_status()
+_common.dump(res)

@@ -47,3 +47,11 @@ def test_tp_decode_fused_gemm_allreduce():
         for k, v in r.items():
             if k.endswith("_match"):
                 assert v >= 0.9, (k, v)
+
+
+def test_fused_sharding_kernels():
+    """Reduce-scatter + AdamW in one kernel; stage-3 linear with the weight gather fused into the GEMM."""
+    res = run_workers("sharding_fused.py", 2, backend="nccl", gpus=True, extra_env=ENV, timeout=300)
+    for r in res:
+        assert r["rs_adamw_err"] < 1e-2, r
+        assert r["zero3_linear_err"] < 2e-2, r
