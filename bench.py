@@ -170,10 +170,12 @@ def main():
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         last = None
+        h0 = time.perf_counter()
         for _ in range(n_steps):
             last = train_step(from_host)
             if from_host:
                 last = float(last.item())        # device -> host read of the step's loss
+        host_issue_ms[0] = (time.perf_counter() - h0) * 1e3 / n_steps     # host time to ISSUE a step (no sync inside)
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
@@ -183,6 +185,7 @@ def main():
             ms = float(t.item())
         return ms, last
 
+    host_issue_ms = [0.0]
     for _ in range(args.warmup):
         train_step(False)
     sampler = ClockSampler(local_rank)
@@ -190,6 +193,7 @@ def main():
     launches0 = native.LAUNCH_COUNT
     ms, last = timed(args.steps, False)
     launches = native.LAUNCH_COUNT - launches0
+    host_ms = host_issue_ms[0]
     clocks = sampler.stop()
     from paddle_b200.ops import _lib
     _lib.check_status()
@@ -220,7 +224,7 @@ def main():
                        "optimizer": "AdamW fp32 master weights + fp32 main_grad, global-norm clip",
                        "l2": "working set (>= 13 GB of weights per micro-batch) far exceeds the 126 MB L2"},
             "model_tflops_per_gpu": flops / (ms_per_step / 1e3) / 1e12 / world,
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "host_issue_ms_per_step": host_ms,
             "loss": float(last.item()) if hasattr(last, "item") else last,
         }
         if args.layers:

@@ -238,19 +238,24 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     const int sw = row & 7;
     bool ok = true;
+    auto load_stat = [&](int it) -> float {
+      const int qh = kv_head * group + it / per_head;
+      const int qi = (t0 + it % per_head) * BQ + (row & 63);
+      const float* src = (row < 64 ? p.lse : p.delta) + (static_cast<size_t>(batch) * p.Hq + qh) * p.Sq;
+      const bool in = qi < p.Sq;
+      float v = in ? src[qi] : 0.f;
+      if (row < 64) v = in ? v * 1.4426950408889634f : INFINITY;         // +inf -> p = 0 for padded rows
+      return v;
+    };
+    float next_stat = n_it > 0 ? load_stat(0) : 0.f;
     for (int it = 0; it < n_it; ++it) {
       const int qh = kv_head * group + it / per_head;
       const int q0 = (t0 + it % per_head) * BQ;
       const int b = it & 1;
-      // per-column statistics of this sub-tile -> shared memory (threads 0-63: LSE in log2 units, 64-127: Delta)
-      {
-        const float* src = (row < 64 ? p.lse : p.delta) + (static_cast<size_t>(batch) * p.Hq + qh) * p.Sq;
-        const int qi = q0 + (row & 63);
-        const bool in = qi < p.Sq;
-        float v = in ? src[qi] : 0.f;
-        if (row < 64) v = in ? v * 1.4426950408889634f : INFINITY;       // +inf -> p = 0 for padded rows
-        stats[b * 128 + row] = v;
-      }
+      // per-column statistics of this sub-tile -> shared memory (threads 0-63: LSE in log2 units, 64-127: Delta).
+      // The value was fetched one iteration ahead, so the global-memory latency never sits in front of the barrier.
+      stats[b * 128 + row] = next_stat;
+      if (it + 1 < n_it) next_stat = load_stat(it + 1);
       named_bar_sync(1, 128);
       if (!warp_mbar_wait(&bars->st_full[b], (it >> 1) & 1, abort_flag, p.status, 300 + b)) { ok = false; break; }
       tc_fence_after();

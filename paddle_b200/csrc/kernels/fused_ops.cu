@@ -97,17 +97,18 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 constexpr int RN_THREADS = 256;
 constexpr int RN_MAXIT = 4;
 
+constexpr int RNW_THREADS = 128;   // small CTAs: four rows each, so CTA turnover does not idle half an SM
 // Warp-per-row variant for H = 256 * NV: the row stays in registers as packed bf16 (NV 128-bit words per
 // lane, all loads issued before the first use), the reduction is shuffle-only, no CTA barrier.  With a
 // residual the bf16-rounded sum is what gets normalised (and stored when residual_out is given).
 template <typename WT, int NV>
-__global__ void __launch_bounds__(RN_THREADS, (NV <= 16 ? 2 : 1)) rms_norm_fwd_warp_kernel(
+__global__ void __launch_bounds__(RNW_THREADS, (NV <= 16 ? 4 : 2)) rms_norm_fwd_warp_kernel(
     const bf16* __restrict__ x, const bf16* __restrict__ residual, const WT* __restrict__ w,
     bf16* __restrict__ y, bf16* __restrict__ residual_out, float* __restrict__ inv_rms, int64_t rows,
     float eps) {
   constexpr int H = NV * 256;
   const int lane = threadIdx.x & 31;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (RN_THREADS / 32) + (threadIdx.x >> 5);
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (RNW_THREADS / 32) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
   uint4 cache[NV];
@@ -704,13 +705,13 @@ PD_EXPORT int pd_rms_norm_fwd(const void* x, const void* residual, const void* w
                   (residual_out == nullptr || aligned16(residual_out));
 #define PD_RMS_WARP(NV)                                                                                  \
   if (al && H == (NV) * 256) {                                                                           \
-    const unsigned blocks = static_cast<unsigned>((rows + RN_THREADS / 32 - 1) / (RN_THREADS / 32));     \
+    const unsigned blocks = static_cast<unsigned>((rows + RNW_THREADS / 32 - 1) / (RNW_THREADS / 32));   \
     if (w_is_f32)                                                                                        \
-      rms_norm_fwd_warp_kernel<float, NV><<<blocks, RN_THREADS, 0, stream>>>(                            \
+      rms_norm_fwd_warp_kernel<float, NV><<<blocks, RNW_THREADS, 0, stream>>>(                           \
           (const bf16*)x, (const bf16*)residual, (const float*)w, (bf16*)y, (bf16*)residual_out, inv_rms, \
           rows, eps);                                                                                    \
     else                                                                                                 \
-      rms_norm_fwd_warp_kernel<bf16, NV><<<blocks, RN_THREADS, 0, stream>>>(                             \
+      rms_norm_fwd_warp_kernel<bf16, NV><<<blocks, RNW_THREADS, 0, stream>>>(                            \
           (const bf16*)x, (const bf16*)residual, (const bf16*)w, (bf16*)y, (bf16*)residual_out, inv_rms,  \
           rows, eps);                                                                                    \
     return PD_CHECK_LAUNCH();                                                                            \

@@ -37,6 +37,7 @@ class LlamaConfig:
     sequence_parallel: bool = True
     recompute: bool = False
     dtype: str = "bfloat16"
+    fast_dispatch: bool = True
 
     def __post_init__(self):
         if self.num_key_value_heads is None:
@@ -224,6 +225,16 @@ class LlamaForCausalLM(nn.Layer):
             self.to(dtype=config.dtype)
 
     def forward(self, input_ids, labels=None):
+        """The stack runs with the Python-level tensor-subclass dispatch switched off: intermediate results are plain
+        torch tensors (no per-operator ``__torch_function__`` round trip, which costs more host time than a small
+        kernel takes on the GPU); only the returned value is wrapped again."""
+        if not self.config.fast_dispatch:
+            return self._forward(input_ids, labels)
+        with torch._C.DisableTorchFunctionSubclass():
+            out = self._forward(input_ids, labels)
+        return as_tensor(out)
+
+    def _forward(self, input_ids, labels=None):
         h = self.llama(input_ids)
         logits = self.lm_head(h)                                  # [tokens, vocab (/tp)]
         if labels is None:

@@ -24,6 +24,8 @@ kw = dict(hidden_size=256, intermediate_size=512, num_attention_heads=2, num_hid
           dtype=dtype)
 if dtype == "bfloat16":
     kw.update(hidden_size=512, intermediate_size=1024, num_attention_heads=4)
+if len(sys.argv) > 3:
+    kw["intermediate_size"] = int(sys.argv[3])      # e.g. 2752: per-rank FFN width 1376 at 2 ranks, not a multiple of 64
 paddle.seed(7)
 twin = LlamaForCausalLM(LlamaConfig.tiny(**kw))
 tp = LlamaForCausalLM(LlamaConfig.tiny(tensor_parallel_degree=n, sequence_parallel=True, **kw))

@@ -30,6 +30,15 @@ def test_llama_tp_sp_parity_gpu(policy):
             assert r["launches"] > 0
 
 
+def test_llama_tp_sp_parity_gpu_ragged_ffn():
+    """Per-rank FFN width 1376 (the Llama-2 7B shard at TP=8): K of the row-parallel GEMM is not a multiple of the
+    64-wide k-block, N of the column-parallel GEMM is not a multiple of the 256-wide tile."""
+    res = run_workers("llama_tp.py", 2, backend="nccl", gpus=True, args=("bfloat16", "fused", "2752"), extra_env=ENV)
+    for r in res:
+        assert np.allclose(r["twin"], r["tp"], atol=5e-2), r
+        assert r["maxdiff"] < 2e-2
+
+
 def test_fused_ag_gemm_and_gemm_rs():
     res = run_workers("fused_comm.py", 2, backend="nccl", gpus=True, extra_env=ENV)
     for r in res:
