@@ -70,4 +70,43 @@ for it in range(3):
 res["zero3_linear_err"] = max(errs)
 torch.cuda.synchronize()
 _lib.check_status()
+
+# ---- standalone symmetric-memory collectives against NCCL, eager and from a CUDA graph
+from paddle_b200.parallel.symm_collectives import SymmCollectives
+sc = SymmCollectives(g, 1 << 20)
+errs = []
+for dtype, numel in ((torch.float32, 1000), (torch.bfloat16, 70001 * 2), (torch.float32, 262144)):
+    x = torch.randn(numel, device="cuda").to(dtype)
+    ref = x.clone()
+    dist.all_reduce(ref, group=g)
+    errs.append(float((sc.all_reduce(x).float() - ref.float()).abs().max() / ref.float().abs().max()))
+    gathered = sc.all_gather(x)
+    parts = []
+    dist.all_gather(parts, x, group=g)
+    errs.append(float((gathered.float() - torch.cat([p.as_subclass(torch.Tensor) for p in parts]).float()).abs().max()))
+    if numel % n == 0:
+        rs_ref = torch.empty(numel // n, device="cuda", dtype=dtype)
+        dist.reduce_scatter(rs_ref, list(x.chunk(n)), group=g)
+        errs.append(float((sc.reduce_scatter(x).float() - rs_ref.float()).abs().max() / rs_ref.float().abs().max()))
+res["symm_coll_err"] = max(errs)
+xs = torch.randn(4096, device="cuda")
+outg = torch.empty_like(xs)
+side = torch.cuda.Stream()
+side.wait_stream(torch.cuda.current_stream())
+with torch.cuda.stream(side):
+    sc.all_reduce(xs, out=outg)
+torch.cuda.current_stream().wait_stream(side)
+graph = torch.cuda.CUDAGraph()
+with torch.cuda.graph(graph):
+    sc.all_reduce(xs, out=outg)
+ref = xs.clone()
+dist.all_reduce(ref, group=g)
+ge = []
+for _ in range(3):
+    outg.zero_()
+    graph.replay()
+    ge.append(float((outg - ref).abs().max()))
+res["symm_coll_graph_err"] = max(ge)
+torch.cuda.synchronize()
+_lib.check_status()
 _common.dump(res)

@@ -64,3 +64,4 @@ def test_fused_sharding_kernels():
     for r in res:
         assert r["rs_adamw_err"] < 1e-2, r
         assert r["zero3_linear_err"] < 2e-2, r
+        assert r["symm_coll_err"] < 1e-2 and r["symm_coll_graph_err"] < 1e-4, r
