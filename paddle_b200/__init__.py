@@ -95,6 +95,18 @@ Tensor.tril = lambda self, diagonal=0: _torch.tril(self, diagonal)
 Tensor.triu = lambda self, diagonal=0: _torch.triu(self, diagonal)
 
 
+from .tensor import extras as _extras  # noqa: E402
+for _n, _v in vars(_extras).items():
+    if not _n.startswith("_") and _n not in globals():
+        globals()[_n] = _v
+for _n, _v in _extras._make_inplace_table().items():
+    if _n not in globals():
+        globals()[_n] = _v
+    if not hasattr(Tensor, _n):
+        setattr(Tensor, _n, _v)
+del _n, _v
+
+
 def is_compiled_with_cuda():
     return True
 

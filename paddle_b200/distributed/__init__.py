@@ -16,7 +16,12 @@ def __getattr__(name):
     if name == "stream":
         return importlib.import_module(f"{__name__}.communication.stream")
     if name in _LAZY:
-        return importlib.import_module(f"{__name__}.{name}")
+        try:
+            return importlib.import_module(f"{__name__}.{name}")
+        except ModuleNotFoundError as e:
+            if e.name == f"{__name__}.{name}":
+                raise AttributeError(f"module {__name__!r} has no attribute {name!r}") from None
+            raise
     if name == "spawn":
         from .spawn_mod import spawn
         return spawn

@@ -4,3 +4,7 @@ from .clip import ClipGradByGlobalNorm, ClipGradByNorm, ClipGradByValue  # noqa:
 from .layer.common import *  # noqa: F401,F403
 from .layer.layers import Layer, ParamAttr  # noqa: F401
 from . import utils  # noqa: F401
+
+from .layer.extras import *  # noqa: E402,F401,F403
+from .layer.extras import (AdaptiveLogSoftmaxWithLoss, BeamSearchDecoder, BiRNN, Bilinear, GRUCell, HSigmoidLoss, LSTMCell,  # noqa: E402,F401
+                           ParameterDict, RNN, RNNCellBase, SimpleRNNCell, SpectralNorm, dynamic_decode)

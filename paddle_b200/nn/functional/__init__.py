@@ -536,3 +536,7 @@ def temporal_shift(x, seg_num, shift_ratio=0.25, name=None, data_format="NCHW"):
     out[:, 1:, c1:c2] = x5[:, :-1, c1:c2]
     out[:, :, c2:] = x5[:, :, c2:]
     return out.reshape(nt, c, h, w)
+
+
+from .extras import *  # noqa: E402,F401,F403
+from .extras import (elu_, hardtanh_, leaky_relu_, softmax_, tanh_, thresholded_relu_)  # noqa: E402,F401

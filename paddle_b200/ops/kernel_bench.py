@@ -275,7 +275,36 @@ def bench_fused_gemm(args, timer, hbm, tf):
     rec = dict(op="ag_gemm_tile_loop", M=T, N=N, K=H, ms=t, tflops=fl / t / 1e9, frac_of_measured=fl / t / 1e9 / tf,
                plain_gemm_ms=t2, plain_gemm_tflops=fl / t2 / 1e9)
     print(json.dumps(rec), flush=True)
-    return [rec]
+    out = [rec]
+    # GEMM -> reduce-scatter kernel as a group of ONE rank: partial tiles go through the receive buffer and the
+    # reduction pass on the same GPU, so the number shows what the kernel's own structure costs without any link
+    M2, N2, K2 = (2048, 4096, 2048) if args.small else (4096, 4096, 2048)
+    a = torch.randn(M2, K2, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(K2, N2, device="cuda") * 0.05).to(torch.bfloat16)
+    o = torch.empty(M2, N2, device="cuda", dtype=torch.bfloat16)
+    recv = torch.zeros(M2 * N2, device="cuda", dtype=torch.bfloat16)
+    cnt = torch.zeros(((M2 + 127) // 128) * ((N2 + 255) // 256) + 8, dtype=torch.int32, device="cuda")
+    ack2 = torch.zeros(16, dtype=torch.int32, device="cuda")
+    done2 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pr, pc, pa2 = U(*([recv.data_ptr()] * 8)), U(*([cnt.data_ptr()] * 8)), U(*([ack2.data_ptr()] * 8))
+    ep = [0]
+
+    def rs():
+        ep[0] += 1
+        rc = k.pd_gemm_rs(ptr(a), ptr(b), ptr(o), c_int(M2), c_int(N2), c_int(K2), c_int(K2), c_int(N2), c_int(0), c_int(1),
+                          c_int(M2), c_int(0), c_int(1), c_int(ep[0]), pr, pc, pa2, ptr(done2), c_int(2000),
+                          ptr(_lib.status_buffer()), stream())
+        _lib.check(rc, "pd_gemm_rs")
+    fl = 2.0 * M2 * N2 * K2
+    t = timer(rs, args.iters)
+    t2 = timer(lambda: native.gemm(a, b), args.iters)
+    _lib.check_status()
+    ok = bool(torch.equal(o, native.gemm(a, b)))
+    rec = dict(op="gemm_rs_single_rank", M=M2, N=N2, K=K2, ms=t, tflops=fl / t / 1e9, frac_of_measured=fl / t / 1e9 / tf,
+               plain_gemm_ms=t2, plain_gemm_tflops=fl / t2 / 1e9, matches_plain_gemm=ok)
+    print(json.dumps(rec), flush=True)
+    out.append(rec)
+    return out
 
 
 def main(argv=None):
