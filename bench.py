@@ -35,6 +35,9 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--micro-batches", type=int, default=16)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="replay each micro-batch (forward + backward) from a CUDA graph; auto = when --gpus > 1, "
+                         "where the per-GPU work is small enough for the host to become the limit")
     return ap.parse_args()
 
 
@@ -149,16 +152,43 @@ def main():
     host_ids = torch.randint(0, cfg.vocab_size, (n_mb, 1, seq + 1), generator=gen, dtype=torch.int64).pin_memory()
     dev_ids = host_ids.cuda()
 
+    graph = {"g": None, "tok": None, "loss": None, "note": "off"}
+
+    def micro_batch(tok):
+        loss = model(tok[:, :-1], tok[:, 1:]) / n_mb
+        loss.backward()
+        return loss.detach()
+
     def train_step(from_host: bool):
         total = None
         for i in range(n_mb):
-            tok = host_ids[i].cuda(non_blocking=True) if from_host else dev_ids[i]
-            loss = model(tok[:, :-1], tok[:, 1:]) / n_mb
-            loss.backward()
-            total = loss.detach() if total is None else total + loss.detach()
+            src = host_ids[i] if from_host else dev_ids[i]
+            if graph["g"] is not None:
+                graph["tok"].copy_(src, non_blocking=True)
+                graph["g"].replay()
+                loss = graph["loss"]
+            else:
+                loss = micro_batch(src.cuda(non_blocking=True) if from_host else src)
+            total = loss.clone() if total is None else total + loss
         opt.step()
         opt.clear_grad()
         return total
+
+    def capture_micro_batch():
+        """One micro-batch (forward, loss, backward with accumulation into main_grad) as a CUDA graph."""
+        from paddle_b200.device.cuda.graphs import CUDAGraph, cuda_graph_capture
+        tok = dev_ids[0].clone()
+        g = CUDAGraph()
+        try:
+            with cuda_graph_capture(g):
+                loss = micro_batch(tok)
+        except Exception as e:          # stay on the eager path, say why in the JSON line
+            graph["note"] = f"capture failed, eager fallback: {type(e).__name__}: {str(e)[:160]}"
+            torch.cuda.synchronize()
+            return
+        opt.clear_grad()
+        graph.update(g=g, tok=tok, loss=loss, note=f"micro-batch fwd+bwd replayed from a CUDA graph "
+                                                   f"({g.launches_per_replay} kernel launcher calls per replay)")
 
     def barrier():
         if world > 1:
@@ -186,6 +216,10 @@ def main():
         return ms, last
 
     host_issue_ms = [0.0]
+    use_graph = args.graph == "on" or (args.graph == "auto" and world > 1)
+    if use_graph:
+        train_step(False)                # eager once: allocates symmetric buffers, caches, optimizer state
+        capture_micro_batch()
     for _ in range(args.warmup):
         train_step(False)
     sampler = ClockSampler(local_rank)
@@ -225,6 +259,7 @@ def main():
                        "l2": "working set (>= 13 GB of weights per micro-batch) far exceeds the 126 MB L2"},
             "model_tflops_per_gpu": flops / (ms_per_step / 1e3) / 1e12 / world,
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "host_issue_ms_per_step": host_ms,
+            "cuda_graph": graph["note"],
             "loss": float(last.item()) if hasattr(last, "item") else last,
         }
         if args.layers:

@@ -128,17 +128,22 @@ def is_compiled_with_custom_device(name=None):
 
 
 def in_dynamic_mode():
-    return True
+    from .static import graph as _sg
+    return not _sg._S.enabled
 
 
 in_dygraph_mode = in_dynamic_mode
 
 
 def enable_static():
-    raise NotImplementedError("static-graph mode is not part of this framework; use paddle.jit.to_static")
+    """Static-graph mode: calls are recorded into the current ``static.Program`` and replayed by ``static.Executor``."""
+    from .static import graph as _sg
+    _sg.enable()
 
 
 def disable_static(place=None):
+    from .static import graph as _sg
+    _sg.disable()
     if place is not None:
         set_device(place)
 

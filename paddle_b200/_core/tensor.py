@@ -108,8 +108,10 @@ class Tensor(torch.Tensor):
     def pin_memory(self):
         return torch.Tensor.pin_memory(self)
 
-    def clone(self):
-        return torch.Tensor.clone(self)
+    def clone(self, *, memory_format=None):
+        if memory_format is None:
+            return torch.Tensor.clone(self)
+        return torch.Tensor.clone(self, memory_format=memory_format)
 
     def tolist(self):
         return torch.Tensor.tolist(self)

@@ -12,7 +12,7 @@
 // slabs still in flight on other SMs; there is no separate collective launch and no host synchronisation.
 //
 // The epoch lives in device memory (state[0]; the last CTA of a launch advances it), so the kernel can be replayed
-// from a CUDA graph with constant arguments.  Counters grow monotonically (expected = epoch * nranks); the two
+// from a CUDA graph with constant arguments.  Counters grow monotonically (expected = epoch * nranks * ARRIVAL_UNITS, independent of the K split); the two
 // receive slots alternate so that a rank that runs ahead by one launch never overwrites data still being read.
 #include <cuda_bf16.h>
 
@@ -29,6 +29,8 @@ constexpr int STAGE_TILE = BM * BN * 2;                            // 32 KB bf16
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + STAGE_TILE + 1024 + 256;
 constexpr int MAX_RANKS = 8;
+constexpr int MAX_SPLITS = 4;
+constexpr int ARRIVAL_UNITS = 12;      // divisible by every split count 1..MAX_SPLITS
 
 struct Peers {
   bf16* recv[MAX_RANKS];     // each: [2 slots][nranks][m_cap][N] bf16
@@ -177,8 +179,11 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (tid == 0) {
       int ok = mma_ok ? 1 : 0;
       if (ok) {
-        for (int p = 0; p < nranks; ++p) red_release_sys_add(peers.cnt[(rank + p) % nranks] + tile, 1);
-        if (ks == 0) ok = flag_wait_ge(peers.cnt[rank] + tile, epoch * nranks * S, wait_ns, status, 400) ? 1 : 0;
+        // one launch adds ARRIVAL_UNITS per rank to a slab's counter whatever its K split (a K slice adds
+        // ARRIVAL_UNITS / S), so launches with different splits can share the counters and the epoch
+        for (int p = 0; p < nranks; ++p) red_release_sys_add(peers.cnt[(rank + p) % nranks] + tile, ARRIVAL_UNITS / S);
+        if (ks == 0)
+          ok = flag_wait_ge(peers.cnt[rank] + tile, static_cast<int>(static_cast<unsigned>(epoch) * nranks * ARRIVAL_UNITS), wait_ns, status, 400) ? 1 : 0;
       }
       bars->verdict = ok;
     }
@@ -260,6 +265,7 @@ PD_EXPORT int pd_gemm_ar(const void* A, const void* B, void* out, const void* re
     const int kbs = (kb_total + splits - 1) / splits;
     splits = (kb_total + kbs - 1) / kbs;
   }
+  if (splits > MAX_SPLITS) return kErrBadShape;
   if ((N / BN) * splits > sm_count()) return kErrTooLarge;      // every CTA must be resident: they wait on peers
   if (!aligned16(A) || !aligned16(B) || !aligned16(out) || (lda % 8) || (ldb % 8) || (ldc % 8) ||
       (residual && !aligned16(residual)))

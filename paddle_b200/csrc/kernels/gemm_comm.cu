@@ -155,6 +155,8 @@ struct AGParams {
   int skip_push;       // 1: the gathered matrix of this epoch is already staged (second GEMM on the same data)
   int do_ack;          // 1: this launch is the last reader of the epoch's staged data -> acknowledge to all ranks
   int done_target;     // value of *local_done after every GEMM CTA of every acknowledging launch so far
+  const int* bias;     // optional device int[2] added to {epoch, done_target}: lets a CUDA graph replay the launch
+                       // (constant arguments) while the slot's epoch keeps advancing in device memory
   const void* x_shard; // [rows_per_rank, row_elems] bf16, local
   unsigned long long peer_stage[MAX_RANKS];  // staging buffer [nranks*rows_per_rank, row_elems] of every rank
   unsigned long long peer_flags[MAX_RANKS];  // int32 [nranks][n_sub] of every rank
@@ -170,6 +172,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmL,
                const __grid_constant__ AGParams p) {
   extern __shared__ uint8_t smem_raw[];
+  const int epoch_v = p.epoch + (p.bias != nullptr ? __ldg(p.bias) : 0);
+  const int done_target_v = p.done_target + (p.bias != nullptr ? __ldg(p.bias + 1) : 0);
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
@@ -232,7 +236,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       piece_info(q, peer, c, row0, bytes);
       if (!(checked & (1u << peer))) {
         // the peer must have finished reading what the previous epoch put into this slot
-        if (!flag_wait_ge(ack_local + peer, p.epoch - 1, p.wait_ns, p.status, 500 + peer)) { ok = false; break; }
+        if (!flag_wait_ge(ack_local + peer, epoch_v - 1, p.wait_ns, p.status, 500 + peer)) { ok = false; break; }
         checked |= 1u << peer;
       }
       const int slot = q % RING;
@@ -246,14 +250,14 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (pend_flag != nullptr && q - pend_q >= FLAG_LAG) {
         tma_wait_group<FLAG_LAG>();
         __threadfence_system();
-        st_release_sys(pend_flag, p.epoch);
+        st_release_sys(pend_flag, epoch_v);
         pend_flag = nullptr;
       }
       if (q % ppj == ppj - 1) {
         if (pend_flag != nullptr) {                 // (only when a chunk has fewer than FLAG_LAG pieces)
           tma_wait_group<1>();
           __threadfence_system();
-          st_release_sys(pend_flag, p.epoch);
+          st_release_sys(pend_flag, epoch_v);
         }
         pend_flag = reinterpret_cast<int*>(p.peer_flags[peer]) + p.rank * n_sub + c;
         pend_q = q;
@@ -262,7 +266,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (ok && pend_flag != nullptr) {
       tma_wait_group<0>();
       __threadfence_system();
-      st_release_sys(pend_flag, p.epoch);
+      st_release_sys(pend_flag, epoch_v);
     }
     if (!ok) {                                       // drain what is still in flight before leaving
       tma_wait_group<0>();
@@ -299,7 +303,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // everything the loop needs is copied out of the parameter block once: a single thread issues every TMA
       // of this CTA, and re-reading parameters after each asm statement would put it on the critical path
       const int wait_mode = p.wait_mode, rank = p.rank, rows_per_rank = p.rows_per_rank, sub_rows = p.sub_rows;
-      const int epoch = p.epoch, gathered_b = p.gathered_b, local_row0 = p.rank * p.rows_per_rank;
+      const int epoch = epoch_v, gathered_b = p.gathered_b, local_row0 = p.rank * p.rows_per_rank;
       const bool a3d = (p.mn3d & 1) != 0, b3d = (p.mn3d & 2) != 0, l3d = (p.mn3d & 4) != 0;
       const unsigned long long wait_ns = p.wait_ns;
       int* const status = p.status;
@@ -433,9 +437,9 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // all staged data of this epoch has been consumed by this CTA: the last CTA acknowledges to every rank
         __threadfence();
         const int done = atomicAdd(p.local_done, 1) + 1;
-        if (done == p.done_target)
+        if (done == done_target_v)
           for (int r = 0; r < p.nranks; ++r)
-            st_release_sys(reinterpret_cast<int*>(p.peer_ack[r]) + p.rank, p.epoch);
+            st_release_sys(reinterpret_cast<int*>(p.peer_ack[r]) + p.rank, epoch_v);
       }
     }
   }
@@ -450,6 +454,7 @@ struct RSParams {
   int rank, nranks;
   int rows_per_rank;
   int epoch;
+  const int* bias;     // optional device int[2]; bias[0] is added to epoch (CUDA-graph replay)
   int mn3d;
   unsigned long long peer_counters[MAX_RANKS];  // int32 [tiles_per_dst * tiles_n] on every rank
   unsigned long long peer_ack[MAX_RANKS];       // int32 [nranks] on every rank
@@ -468,6 +473,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ RSMaps maps, const __grid_constant__ RSParams p) {
   extern __shared__ uint8_t smem_raw[];
+  const int epoch_v = p.epoch + (p.bias != nullptr ? __ldg(p.bias) : 0);
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
@@ -549,7 +555,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         bool ok = mbar_wait(&bars->tfull[acc], acc_ph, abort_flag, p.status, 400 + acc);
         if (ok && !(checked & (1u << d))) {
           // destination d must have finished reducing the previous epoch out of this slot
-          ok = flag_wait_ge(ack_local + d, p.epoch - 1, p.wait_ns, p.status, 700 + d);
+          ok = flag_wait_ge(ack_local + d, epoch_v - 1, p.wait_ns, p.status, 700 + d);
           if (!ok) *abort_flag = 1;
           checked |= 1u << d;
         }
@@ -614,7 +620,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int u = cta; u < tiles_dst_all && alive; u += nct) {
       const int tml = u % tiles_per_dst, tn = u / tiles_per_dst;
       if (epi_tid == 0)
-        bars->epi_decision = flag_wait_ge(counters + tml * tiles_n + tn, p.nranks * p.epoch, p.wait_ns, p.status, 800) ? 1 : 0;
+        bars->epi_decision = flag_wait_ge(counters + tml * tiles_n + tn, p.nranks * epoch_v, p.wait_ns, p.status, 800) ? 1 : 0;
       named_bar_sync(1, 128);
       const int okd = bars->epi_decision;
       named_bar_sync(1, 128);
@@ -664,8 +670,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (epi_tid == 0 && alive) {
       __threadfence();
       const int done = atomicAdd(p.local_done, 1) + 1;
-      if (done == nct * p.epoch)
-        for (int r = 0; r < p.nranks; ++r) st_release_sys(reinterpret_cast<int*>(p.peer_ack[r]) + p.rank, p.epoch);
+      if (done == nct * epoch_v)
+        for (int r = 0; r < p.nranks; ++r) st_release_sys(reinterpret_cast<int*>(p.peer_ack[r]) + p.rank, epoch_v);
     }
   }
   tc_fence_before();
@@ -699,8 +705,8 @@ PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, in
                          int a_mn, int b_mn, int epi, int gathered_b, const void* x_shard, int rows_per_rank, int sub_rows,
                          int row_elems, int rank, int nranks, int n_comm, int epoch, int wait_mode, int skip_push, int do_ack,
                          const unsigned long long* peer_stage, const unsigned long long* peer_flags,
-                         const unsigned long long* peer_ack, int* local_done, int done_base, int wait_ms, int* status,
-                         cudaStream_t stream) {
+                         const unsigned long long* peer_ack, int* local_done, int done_base, const int* bias, int wait_ms,
+                         int* status, cudaStream_t stream) {
   using namespace pd;
   using namespace pd::gc;
   if (M <= 0 || N <= 0 || K <= 0 || nranks < 1 || nranks > MAX_RANKS) return kErrBadShape;
@@ -724,7 +730,7 @@ PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, in
   AGParams p;
   p.M = M; p.N = N; p.K = K; p.rank = rank; p.nranks = nranks; p.rows_per_rank = rows_per_rank;
   p.sub_rows = sub_rows; p.row_elems = row_elems; p.n_comm = n_comm; p.epoch = epoch; p.wait_mode = wait_mode;
-  p.gathered_b = gathered_b; p.mn3d = mn3d | (l3 << 2); p.skip_push = skip_push; p.do_ack = do_ack; p.x_shard = x_shard; p.local_done = local_done; p.status = status;
+  p.gathered_b = gathered_b; p.mn3d = mn3d | (l3 << 2); p.skip_push = skip_push; p.do_ack = do_ack; p.x_shard = x_shard; p.local_done = local_done; p.status = status; p.bias = bias;
   p.wait_ns = static_cast<unsigned long long>(wait_ms) * 1000000ull;
   for (int i = 0; i < MAX_RANKS; ++i) {
     p.peer_stage[i] = i < nranks ? peer_stage[i] : 0;
@@ -761,7 +767,7 @@ PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, in
 PD_EXPORT int pd_gemm_rs(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int a_mn,
                          int b_mn, int rows_per_rank, int rank, int nranks, int epoch,
                          const unsigned long long* peer_recv, const unsigned long long* peer_counters,
-                         const unsigned long long* peer_ack, int* local_done, int wait_ms, int* status,
+                         const unsigned long long* peer_ack, int* local_done, const int* bias, int wait_ms, int* status,
                          cudaStream_t stream) {
   using namespace pd;
   using namespace pd::gc;
@@ -782,7 +788,7 @@ PD_EXPORT int pd_gemm_rs(const void* A, const void* B, void* out, int M, int N, 
   p.M = M; p.N = N; p.K = K; p.rank = rank; p.nranks = nranks; p.rows_per_rank = rows_per_rank; p.epoch = epoch;
   p.mn3d = mn3d;
   p.recv_local = reinterpret_cast<const void*>(peer_recv[rank]);
-  p.out = out; p.local_done = local_done; p.status = status;
+  p.out = out; p.local_done = local_done; p.status = status; p.bias = bias;
   p.wait_ns = static_cast<unsigned long long>(wait_ms) * 1000000ull;
   for (int i = 0; i < MAX_RANKS; ++i) {
     p.peer_counters[i] = i < nranks ? peer_counters[i] : 0;

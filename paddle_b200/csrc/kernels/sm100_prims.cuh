@@ -119,16 +119,20 @@ __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Spin until *flag >= expected (system scope).  Bounded like mbar_wait; limit_ns may be shorter
-// for tests that withhold a signal on purpose.
+// for tests that withhold a signal on purpose.  Counters and targets grow without bound, so the comparison is
+// done on the wrapped difference: it stays correct after either passes 2^31.
+__device__ __forceinline__ bool flag_reached(const int* flag, int expected) {
+  return static_cast<int>(static_cast<unsigned>(ld_acquire_sys(flag)) - static_cast<unsigned>(expected)) >= 0;
+}
 __device__ __forceinline__ bool flag_wait_ge(const int* flag, int expected,
                                              unsigned long long limit_ns, int* status, int site) {
-  if (ld_acquire_sys(flag) >= expected) return true;
+  if (flag_reached(flag, expected)) return true;
   const unsigned long long t0 = globaltimer_ns();
 #pragma unroll 1
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i) {
-      if (ld_acquire_sys(flag) >= expected) return true;
+      if (flag_reached(flag, expected)) return true;
       __nanosleep(64);
     }
     if (globaltimer_ns() - t0 > limit_ns) {

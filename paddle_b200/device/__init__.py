@@ -64,3 +64,26 @@ def set_stream(stream):
 
 def stream_guard(stream):
     return torch.cuda.stream(stream)
+
+
+def get_cudnn_version():
+    v = torch.backends.cudnn.version() if torch.backends.cudnn.is_available() else None
+    return v
+
+
+class XPUPlace:
+    def __init__(self, dev_id=0):
+        raise RuntimeError("XPU devices are not supported")
+
+
+class IPUPlace:
+    def __init__(self):
+        raise RuntimeError("IPU devices are not supported")
+
+
+def is_compiled_with_ipu():
+    return False
+
+
+def is_compiled_with_distribute():
+    return torch.distributed.is_available()

@@ -64,36 +64,5 @@ def get_device_capability(device=None):
     return torch.cuda.get_device_capability()
 
 
-class CUDAGraph:
-    """Capture / replay (python/paddle/device/cuda/graphs.py ``CUDAGraph``)."""
-
-    def __init__(self, place=None, mode="thread_local"):
-        self._g = torch.cuda.CUDAGraph()
-        self._ctx = None
-
-    def capture_begin(self):
-        self._ctx = torch.cuda.graph(self._g)
-        self._ctx.__enter__()
-
-    def capture_end(self):
-        self._ctx.__exit__(None, None, None)
-        self._ctx = None
-
-    def replay(self):
-        self._g.replay()
-
-    def reset(self):
-        self._g.reset()
-
-
-def is_cuda_graph_supported():
-    return torch.cuda.is_available()
-
-
-@contextlib.contextmanager
-def cuda_graph_capture(graph):
-    graph.capture_begin()
-    try:
-        yield graph
-    finally:
-        graph.capture_end()
+from . import graphs, streams  # noqa: E402,F401
+from .graphs import CUDAGraph, cuda_graph_capture, is_cuda_graph_supported, wrap_cuda_graph  # noqa: E402,F401

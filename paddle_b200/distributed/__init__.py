@@ -33,6 +33,24 @@ def __getattr__(name):
                 "PrepareLayerOutput", "LocalLayer", "to_distributed", "DistAttr", "shard_scaler"):
         from . import auto_parallel
         return getattr(auto_parallel, name)
+    if name in ("InMemoryDataset", "QueueDataset"):
+        from .fleet import dataset
+        return getattr(dataset, name)
+    if name in ("ProbabilityEntry", "CountFilterEntry", "ShowClickEntry"):
+        from . import entry_attr
+        return getattr(entry_attr, name)
+    if name in ("ReduceType", "set_mesh", "get_mesh"):
+        from .auto_parallel import process_mesh
+        return getattr(process_mesh, name)
+    if name == "ParallelMode":
+        from .fleet.base.topology import ParallelMode
+        return ParallelMode
+    if name == "split":
+        from .fleet.layers.mpu.mp_ops import split
+        return split
+    if name in ("gloo_init_parallel_env", "gloo_barrier", "gloo_release"):
+        from . import parallel
+        return getattr(parallel, name)
     if name in ("save_state_dict", "load_state_dict"):
         from . import checkpoint
         return getattr(checkpoint, name)

@@ -27,6 +27,11 @@ allgather_perf = _fleet.allgather_perf
 reduce_scatter_perf = _fleet.reduce_scatter_perf
 collective_perf = _fleet.collective_perf
 fleet = _fleet
+from .base.role_maker import PaddleCloudRoleMaker, Role, UserDefinedRoleMaker  # noqa: E402,F401
+from .base.util_factory import UtilBase  # noqa: E402,F401
+from .data_generator import MultiSlotDataGenerator, MultiSlotStringDataGenerator  # noqa: E402,F401
+
+util = UtilBase()
 
 
 def __getattr__(name):

@@ -206,3 +206,37 @@ class DataParallel(Layer):
 
     def apply_collective_grads(self):
         pass
+
+
+_gloo_group = None
+
+
+def gloo_init_parallel_env(rank_id, rank_num, server_endpoint):
+    """CPU-only process group over gloo with the store on ``server_endpoint`` (python/paddle/distributed/parallel.py
+    ``gloo_init_parallel_env``); used for host-side barriers and small collectives before any GPU context exists."""
+    global _gloo_group
+    import datetime
+
+    import torch.distributed as tdist
+    ip, port = server_endpoint.rsplit(":", 1)
+    store = tdist.TCPStore(ip, int(port), rank_num, rank_id == 0, timeout=datetime.timedelta(seconds=300))
+    if tdist.is_initialized():
+        _gloo_group = tdist.new_group(backend="gloo")
+    else:
+        tdist.init_process_group("gloo", store=store, rank=rank_id, world_size=rank_num)
+        _gloo_group = tdist.group.WORLD
+
+
+def gloo_barrier():
+    import torch.distributed as tdist
+    if _gloo_group is None:
+        raise RuntimeError("call gloo_init_parallel_env first")
+    tdist.barrier(group=_gloo_group)
+
+
+def gloo_release():
+    global _gloo_group
+    import torch.distributed as tdist
+    if _gloo_group is not None and _gloo_group is tdist.group.WORLD and tdist.is_initialized():
+        tdist.destroy_process_group()
+    _gloo_group = None

@@ -36,3 +36,13 @@ def help(repo_dir, model, source="github", force_reload=False):  # noqa: A001
 
 def load(repo_dir, model, source="github", force_reload=False, **kwargs):
     return getattr(_import(repo_dir, source), model)(**kwargs)
+
+
+def load_state_dict_from_url(url, model_dir=None, check_hash=False, file_name=None, map_location=None):
+    """Loads a state dict from a ``file://`` URL or a local path (there is no network access in this build)."""
+    import os
+    from .framework.io import load as _load
+    path = url[len("file://"):] if url.startswith("file://") else url
+    if not os.path.exists(path):
+        raise RuntimeError(f"cannot fetch {url!r}: only local files are reachable")
+    return _load(path)

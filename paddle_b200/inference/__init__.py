@@ -144,3 +144,80 @@ def create_predictor(config: Config) -> Predictor:
 
 def get_version():
     return "paddle_b200 inference"
+
+
+import enum as _enum
+
+import numpy as _np
+
+
+class DataType(_enum.IntEnum):
+    FLOAT32 = 0
+    INT64 = 1
+    INT32 = 2
+    UINT8 = 3
+    INT8 = 4
+    FLOAT16 = 5
+    BOOL = 6
+    FLOAT64 = 7
+    BFLOAT16 = 8
+
+
+Tensor = _Handle
+
+_DT_BYTES = {DataType.FLOAT32: 4, DataType.INT64: 8, DataType.INT32: 4, DataType.UINT8: 1, DataType.INT8: 1,
+             DataType.FLOAT16: 2, DataType.BOOL: 1, DataType.FLOAT64: 8, DataType.BFLOAT16: 2}
+
+
+def get_num_bytes_of_data_type(dtype):
+    return _DT_BYTES[DataType(dtype)]
+
+
+def get_trt_compile_version():
+    return (0, 0, 0)
+
+
+def get_trt_runtime_version():
+    return (0, 0, 0)
+
+
+def _get_phi_kernel_name(op_name):
+    return op_name
+
+
+def convert_to_mixed_precision(model_file, params_file, mixed_model_file, mixed_params_file, mixed_precision,
+                               backend=None, keep_io_types=True, black_list=None, **kwargs):
+    """Rewrites a saved inference model with its floating-point parameters cast to ``mixed_precision``."""
+    import pickle
+    import shutil
+
+    import torch
+    target = {PrecisionType.Half: torch.float16, PrecisionType.Bfloat16: torch.bfloat16}.get(mixed_precision, torch.float32)
+    shutil.copyfile(model_file, mixed_model_file)
+    with open(params_file, "rb") as f:
+        state = pickle.load(f)
+    skip = set(black_list or ())
+    out = {}
+    for k, v in state.items():
+        a = _np.asarray(v)
+        if a.dtype.kind == "f" and k not in skip:
+            t = torch.from_numpy(a.astype(_np.float32)).to(target)
+            a = t.view(torch.int16).numpy().view(_np.uint16) if target is torch.bfloat16 else t.numpy()
+        out[k] = a
+    with open(mixed_params_file, "wb") as f:
+        pickle.dump(out, f)
+
+
+class PredictorPool:
+    def __init__(self, config, size=1):
+        self._preds = [create_predictor(config) for _ in range(max(1, size))]
+
+    def retrieve(self, idx):
+        return self._preds[idx]
+
+    retrive = retrieve
+
+
+class XpuConfig:
+    def __init__(self):
+        raise RuntimeError("XPU devices are not supported")

@@ -176,3 +176,20 @@ def _move(b, dev):
     if isinstance(b, (list, tuple)):
         return type(b)(_move(v, dev) for v in b)
     return b
+
+
+class SubsetRandomSampler(Sampler):
+    """Samples the given indices in random order, without replacement (io/dataloader/sampler.py)."""
+
+    def __init__(self, indices):
+        if len(indices) == 0:
+            raise ValueError("The length of `indices` in SubsetRandomSampler should be greater than 0.")
+        self.indices = list(indices)
+
+    def __iter__(self):
+        import torch
+        for i in torch.randperm(len(self.indices)).tolist():
+            yield self.indices[i]
+
+    def __len__(self):
+        return len(self.indices)

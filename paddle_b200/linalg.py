@@ -74,3 +74,40 @@ def _lu(x, pivot, get_infos):
 def _lstsq(x, y, rcond, driver):
     r = torch.linalg.lstsq(x, y, rcond=rcond, driver=driver)
     return as_tensor(r.solution), as_tensor(r.residuals), as_tensor(r.rank), as_tensor(r.singular_values)
+
+
+def vecdot(x, y, axis=-1, name=None):
+    return as_tensor(torch.linalg.vecdot(x.as_subclass(torch.Tensor), y.as_subclass(torch.Tensor), dim=axis))
+
+
+def matrix_transpose(x, name=None):
+    return as_tensor(x.as_subclass(torch.Tensor).transpose(-1, -2))
+
+
+def diagonal(x, offset=0, axis1=0, axis2=1, name=None):
+    return as_tensor(torch.diagonal(x.as_subclass(torch.Tensor), offset, axis1, axis2))
+
+
+def fp8_fp8_half_gemm_fused(x, y, transpose_x=False, transpose_y=False, bias=None, scale=1.0, output_dtype="float16",
+                            activation_type="identity", name=None):
+    """``act(scale * op(x) @ op(y) + bias)`` for fp8 (e4m3 / e5m2) operands with a bf16 / fp16 result
+    (python/paddle/tensor/linalg.py ``fp8_fp8_half_gemm_fused``).  On a GPU the product runs on the fp8 tensor-core
+    path (per-tensor scale folded into the epilogue); on CPU the operands are widened first."""
+    from ._core import dtype as _dt
+    a, b = x.as_subclass(torch.Tensor), y.as_subclass(torch.Tensor)
+    od = _dt.to_torch(output_dtype)
+    a2 = a.transpose(-1, -2) if transpose_x else a
+    b2 = b.transpose(-1, -2) if transpose_y else b
+    if a.is_cuda and a.dim() == 2 and b.dim() == 2 and a2.shape[1] % 16 == 0 and b2.shape[1] % 16 == 0:
+        one = torch.ones((), device=a.device)
+        # _scaled_mm wants a row-major and b column-major
+        out = torch._scaled_mm(a2.contiguous(), b2.t().contiguous().t(), scale_a=one, scale_b=one * scale, out_dtype=od)
+    else:
+        out = (a2.float() @ b2.float() * scale).to(od)
+    if bias is not None:
+        out = out + bias.as_subclass(torch.Tensor).to(od)
+    if activation_type == "gelu":
+        out = torch.nn.functional.gelu(out)
+    elif activation_type == "relu":
+        out = torch.relu(out)
+    return as_tensor(out)

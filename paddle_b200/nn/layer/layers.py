@@ -86,7 +86,21 @@ class Layer:
     def full_name(self):
         return self._full_name
 
+    def __init_subclass__(cls, **kw):
+        # Layer construction (parameter/buffer creation and initialisation) is never part of a recorded static
+        # program: the reference puts those ops in the startup program, here they simply run once, eagerly.
+        super().__init_subclass__(**kw)
+        init = cls.__dict__.get("__init__")
+        if init is not None:
+            from ...static.graph import no_trace
+            cls.__init__ = no_trace(init)
+
     def create_parameter(self, shape, attr=None, dtype=None, is_bias=False, default_initializer=None):
+        from ...static.graph import suspend
+        with suspend():
+            return self._create_parameter(shape, attr, dtype, is_bias, default_initializer)
+
+    def _create_parameter(self, shape, attr=None, dtype=None, is_bias=False, default_initializer=None):
         from ..initializer import Constant, XavierUniform, _global_initializer
         attr = ParamAttr._to_attr(attr)
         if attr is False:

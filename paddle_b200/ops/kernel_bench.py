@@ -266,7 +266,7 @@ def bench_fused_gemm(args, timer, hbm, tf):
     def ag():
         rc = k.pd_ag_gemm(ptr(xfull), ptr(w), ptr(y), c_int(T), c_int(N), c_int(H), c_int(H), c_int(N), c_int(N), c_int(0),
                           c_int(1), c_int(0), c_int(0), ptr(x), c_int(T // 2), c_int(128), c_int(H), c_int(0), c_int(2),
-                          c_int(0), c_int(0), c_int(0), c_int(1), c_int(0), ps, pf, pa, ptr(done), c_int(0), c_int(2000),
+                          c_int(0), c_int(0), c_int(0), c_int(1), c_int(0), ps, pf, pa, ptr(done), c_int(0), None, c_int(2000),
                           ptr(_lib.status_buffer()), stream())
         _lib.check(rc, "pd_ag_gemm")
     fl = 2.0 * T * N * H
@@ -292,7 +292,7 @@ def bench_fused_gemm(args, timer, hbm, tf):
     def rs():
         ep[0] += 1
         rc = k.pd_gemm_rs(ptr(a), ptr(b), ptr(o), c_int(M2), c_int(N2), c_int(K2), c_int(K2), c_int(N2), c_int(0), c_int(1),
-                          c_int(M2), c_int(0), c_int(1), c_int(ep[0]), pr, pc, pa2, ptr(done2), c_int(2000),
+                          c_int(M2), c_int(0), c_int(1), c_int(ep[0]), pr, pc, pa2, ptr(done2), None, c_int(2000),
                           ptr(_lib.status_buffer()), stream())
         _lib.check(rc, "pd_gemm_rs")
     fl = 2.0 * M2 * N2 * K2

@@ -119,6 +119,24 @@ class LinearWarmup(LRScheduler):
             self.inner.set_state_dict(inner)
 
 
+class LinearLR(LRScheduler):
+    """Multiplies the rate by a factor that moves linearly from ``start_factor`` to ``end_factor`` over ``total_steps``."""
+
+    def __init__(self, learning_rate, total_steps, start_factor=1.0 / 3, end_factor=1.0, last_epoch=-1, verbose=False):
+        if start_factor > 1.0 or start_factor <= 0:
+            raise ValueError(f"`start_factor` must be greater than 0 and less or equal to 1, but got {start_factor}")
+        if end_factor > 1.0 or end_factor < 0:
+            raise ValueError(f"`end_factor` must be greater than 0 and less than 1, but got {end_factor}")
+        if total_steps <= 0:
+            raise ValueError(f"`total_steps` must be greater than 0, but got {total_steps}")
+        self.start_factor, self.end_factor, self.total_steps = start_factor, end_factor, total_steps
+        super().__init__(learning_rate, last_epoch, verbose)
+
+    def get_lr(self):
+        t = min(max(self.last_epoch, 0), self.total_steps)
+        return self.base_lr * (self.start_factor + (self.end_factor - self.start_factor) * t / self.total_steps)
+
+
 class StepDecay(LRScheduler):
     def __init__(self, learning_rate, step_size, gamma=0.1, last_epoch=-1, verbose=False):
         self.step_size, self.gamma = step_size, gamma

@@ -35,8 +35,11 @@ class Optimizer:
     def __init__(self, learning_rate=0.001, parameters=None, weight_decay=None, grad_clip=None, name=None,
                  multi_precision=False):
         if parameters is None:
-            raise ValueError("parameters must be given in dygraph mode")
-        parameters = list(parameters)
+            from ..static import graph as _sg
+            if not _sg._S.enabled:
+                raise ValueError("parameters must be given in dygraph mode")
+            self._deferred_parameters = True      # static mode: minimize() collects the program's parameters
+        parameters = list(parameters or [])
         self._param_groups = []
         if parameters and isinstance(parameters[0], dict):
             for g in parameters:
@@ -156,7 +159,15 @@ class Optimizer:
     def _apply(self, pgs, grad_scale):
         raise NotImplementedError
 
+    def _set_parameters(self, parameters):
+        self._param_groups = [{"params": list(parameters)}]
+        self._parameter_list = list(parameters)
+
     def minimize(self, loss, startup_program=None, parameters=None, no_grad_set=None):
+        from ..static import graph as _sg
+        if _sg.recording():
+            from ..static import _static_minimize
+            return _static_minimize(self, loss, parameters, no_grad_set)
         loss.backward()
         self.step()
         return None, None

@@ -50,6 +50,7 @@ class _AGSlot:
         self.done = torch.zeros(1, dtype=torch.int32, device=self.stage.device)
         self.epoch = 0
         self.done_base = 0
+        _init_bias(self, self.stage.device)
 
 
 class _RSSlot:
@@ -68,6 +69,16 @@ class _RSSlot:
         self.p_ack = _arr(self.block.peer_ptrs(self.off_ack))
         self.done = torch.zeros(1, dtype=torch.int32, device=self.block.local.device)
         self.epoch = 0
+        self.done_base = 0
+        _init_bias(self, self.block.local.device)
+
+
+def _init_bias(slot, device):
+    """Device int[2] added by the kernels to the {epoch, done_target} arguments.  Eager launches pass
+    ``value - bias_host`` so the sum is the true value; a captured launch keeps its constant arguments and every
+    replay of the graph ends by adding the graph's per-replay advance to ``bias`` (see :class:`GraphCapture`)."""
+    slot.bias = torch.zeros(2, dtype=torch.int32, device=device)
+    slot.bias_host = [0, 0]
 
 
 def _slot(kind, group, rows, width):
@@ -81,6 +92,48 @@ def _slot(kind, group, rows, width):
     s = pair["slots"][pair["next"]]
     pair["next"] ^= 1
     return s
+
+
+class GraphCapture:
+    """Bookkeeping that lets launches of the fused communication kernels sit inside a CUDA graph.
+
+    Every slot's epoch (and acknowledgement count) must keep growing across replays although a captured launch has
+    constant arguments.  ``begin()`` notes the counters, ``end_capture()`` (still inside the capture) records one
+    ``bias += delta`` per slot as the last node of the graph, ``finish()`` (after the capture) computes each slot's
+    advance per replay, stores it in ``delta`` and rolls the host counters back (capturing launches nothing), and
+    ``replayed()`` advances the host mirrors after each replay so eager launches and other graphs stay in step."""
+
+    def __init__(self):
+        self._slots = [s for pair in _slots.values() for s in pair["slots"]]
+        self._next = {k: pair["next"] for k, pair in _slots.items()}
+        self._before = [(s.epoch, s.done_base) for s in self._slots]
+        self._delta = [torch.zeros(2, dtype=torch.int32, device=s.bias.device) for s in self._slots]
+        self._adv = None
+        self._n_keys = len(_slots)
+
+    def end_capture(self):
+        if len(_slots) != self._n_keys:
+            raise RuntimeError("a fused-communication slot was created during CUDA-graph capture; run the captured "
+                               "code once eagerly first so that all symmetric buffers exist")
+        for s, d in zip(self._slots, self._delta):
+            s.bias.add_(d)
+
+    def finish(self):
+        self._adv = []
+        for s, (e0, d0), d in zip(self._slots, self._before, self._delta):
+            adv = (s.epoch - e0, s.done_base - d0)
+            self._adv.append(adv)
+            s.epoch, s.done_base = e0, d0
+            d.copy_(torch.tensor(adv, dtype=torch.int32))
+        for k, nxt in self._next.items():
+            _slots[k]["next"] = nxt
+
+    def replayed(self):
+        for s, (de, dd) in zip(self._slots, self._adv):
+            s.epoch += de
+            s.done_base += dd
+            s.bias_host[0] += de
+            s.bias_host[1] += dd
 
 
 def available(x, weight, group=None) -> bool:
@@ -105,9 +158,10 @@ def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode
     rc = _lib.kernels().pd_ag_gemm(
         ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
         c_int(out.stride(0)), c_int(a_mn), c_int(b_mn), c_int(epi), c_int(1 if gathered_b else 0), ptr(x_shard), c_int(slot.rows), c_int(SUB_ROWS),
-        c_int(slot.row_elems), c_int(group.rank), c_int(group.nranks), c_int(N_COMM), c_int(slot.epoch),
+        c_int(slot.row_elems), c_int(group.rank), c_int(group.nranks), c_int(N_COMM), c_int(slot.epoch - slot.bias_host[0]),
         c_int(wait_mode), c_int(0 if push else 1), c_int(1 if ack else 0), slot.p_stage, slot.p_flags, slot.p_ack,
-        ptr(slot.done), c_int(slot.done_base), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
+        ptr(slot.done), c_int(slot.done_base - slot.bias_host[1]), ptr(slot.bias), c_int(WAIT_MS),
+        ptr(_lib.status_buffer(out.device)), stream())
     check(rc, "pd_ag_gemm")
     if ack:
         slot.done_base += gemm_ctas
@@ -119,8 +173,8 @@ def gemm_rs(slot, group, a, b, out, M, N, K, a_mn, b_mn):
     slot.epoch += 1
     rc = _lib.kernels().pd_gemm_rs(
         ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)), c_int(a_mn),
-        c_int(b_mn), c_int(slot.rows), c_int(group.rank), c_int(group.nranks), c_int(slot.epoch), slot.p_recv,
-        slot.p_cnt, slot.p_ack, ptr(slot.done), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
+        c_int(b_mn), c_int(slot.rows), c_int(group.rank), c_int(group.nranks), c_int(slot.epoch - slot.bias_host[0]),
+        slot.p_recv, slot.p_cnt, slot.p_ack, ptr(slot.done), ptr(slot.bias), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
     check(rc, "pd_gemm_rs")
     native._count()
     return out

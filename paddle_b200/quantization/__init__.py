@@ -180,3 +180,25 @@ class QAT(_Quantization):
 
 class PTQ(_Quantization):
     pass
+
+
+class BaseQuanter(BaseObserver):
+    """Base class of trainable quantizers (python/paddle/quantization/base_quanter.py)."""
+
+
+def quanter(class_name):
+    """Class decorator that registers a quanter layer and creates a factory of the given name in the caller's module
+    (python/paddle/quantization/factory.py ``quanter``)."""
+    import sys
+
+    def wrapper(target_class):
+        def init(self, *args, **kwargs):
+            self._args, self._kwargs = args, kwargs
+
+        def _instance(self, layer=None):
+            return target_class(*self._args, **self._kwargs)
+        factory = type(class_name, (_Factory,), {"__init__": init, "_instance": _instance, "_get_class": lambda self: target_class})
+        mod = sys.modules[target_class.__module__]
+        setattr(mod, class_name, factory)
+        return target_class
+    return wrapper

@@ -272,3 +272,253 @@ class RandomRotation(BaseTransform):
         grid = torch.nn.functional.affine_grid(theta, (1, *t.shape), align_corners=False)
         mode = "nearest" if self.interpolation == "nearest" else "bilinear"
         return back(torch.nn.functional.grid_sample(t[None], grid, mode=mode, align_corners=False)[0])
+
+
+# ----------------------------------------------------------------------------- colour and geometric extras
+__all__ += ["SaturationTransform", "HueTransform", "ColorJitter", "RandomAffine", "RandomPerspective", "RandomErasing",
+            "affine", "rotate", "perspective", "adjust_brightness", "adjust_contrast", "adjust_hue", "erase"]
+
+
+def _scale_of(img):
+    return 255.0 if not isinstance(img, torch.Tensor) or img.dtype == torch.uint8 else 1.0
+
+
+def adjust_brightness(img, brightness_factor):
+    t, back = _to_chw_float(img)
+    return back((t * brightness_factor).clamp(0, _scale_of(img)))
+
+
+def adjust_contrast(img, contrast_factor):
+    t, back = _to_chw_float(img)
+    g = (0.299 * t[0] + 0.587 * t[1] + 0.114 * t[2]).mean() if t.shape[0] == 3 else t.mean()
+    return back(((t - g) * contrast_factor + g).clamp(0, _scale_of(img)))
+
+
+def adjust_saturation(img, saturation_factor):
+    t, back = _to_chw_float(img)
+    g = (0.299 * t[0] + 0.587 * t[1] + 0.114 * t[2])[None]
+    return back(((t - g) * saturation_factor + g).clamp(0, _scale_of(img)))
+
+
+def _rgb_to_hsv(t):
+    r, g, b = t
+    mx, mn = t.max(0).values, t.min(0).values
+    d = mx - mn
+    s = torch.where(mx > 0, d / mx.clamp_min(1e-12), torch.zeros_like(mx))
+    dz = d.clamp_min(1e-12)
+    h = torch.where(mx == r, ((g - b) / dz) % 6, torch.where(mx == g, (b - r) / dz + 2, (r - g) / dz + 4)) / 6.0
+    h = torch.where(d == 0, torch.zeros_like(h), h)
+    return torch.stack([h, s, mx])
+
+
+def _hsv_to_rgb(t):
+    h, s, v = t
+    i = torch.floor(h * 6)
+    f = h * 6 - i
+    p, q, u = v * (1 - s), v * (1 - f * s), v * (1 - (1 - f) * s)
+    i = i.long() % 6
+    r = torch.stack([v, q, p, p, u, v]).gather(0, i[None])[0]
+    g = torch.stack([u, v, v, q, p, p]).gather(0, i[None])[0]
+    b = torch.stack([p, p, u, v, v, q]).gather(0, i[None])[0]
+    return torch.stack([r, g, b])
+
+
+def adjust_hue(img, hue_factor):
+    if not -0.5 <= hue_factor <= 0.5:
+        raise ValueError("hue_factor is not in [-0.5, 0.5].")
+    t, back = _to_chw_float(img)
+    if t.shape[0] != 3:
+        return img
+    sc = _scale_of(img)
+    hsv = _rgb_to_hsv(t / sc)
+    hsv[0] = (hsv[0] + hue_factor) % 1.0
+    return back(_hsv_to_rgb(hsv) * sc)
+
+
+def erase(img, i, j, h, w, v, inplace=False):
+    if isinstance(img, torch.Tensor):
+        out = img if inplace else img.clone()
+        out.as_subclass(torch.Tensor)[..., i:i + h, j:j + w] = torch.as_tensor(v, dtype=out.dtype)
+        return out
+    arr = np.asarray(img).copy()
+    arr[i:i + h, j:j + w] = np.asarray(v.numpy() if isinstance(v, torch.Tensor) else v).reshape(-1)[0] if np.ndim(v) == 0 \
+        else np.asarray(v)
+    if not isinstance(img, np.ndarray):
+        from PIL import Image
+        return Image.fromarray(arr)
+    return arr
+
+
+def _warp(img, theta_or_grid, interpolation, fill, homography=None):
+    """Samples the image on an output grid; ``theta`` is the 2x3 output->input map in normalised coordinates."""
+    t, back = _to_chw_float(img)
+    C, H, W = t.shape
+    if homography is None:
+        grid = torch.nn.functional.affine_grid(theta_or_grid[None], (1, C, H, W), align_corners=False)
+    else:
+        ys, xs = torch.meshgrid(torch.arange(H, dtype=torch.float32) + 0.5, torch.arange(W, dtype=torch.float32) + 0.5,
+                                indexing="ij")
+        ones = torch.ones_like(xs)
+        src = torch.einsum("ij,jhw->ihw", homography, torch.stack([xs, ys, ones]))
+        gx, gy = src[0] / src[2] / W * 2 - 1, src[1] / src[2] / H * 2 - 1
+        grid = torch.stack([gx, gy], -1)[None]
+    mode = "nearest" if interpolation == "nearest" else "bilinear"
+    out = torch.nn.functional.grid_sample(t[None], grid, mode=mode, padding_mode="zeros", align_corners=False)[0]
+    if fill:
+        mask = torch.nn.functional.grid_sample(torch.ones(1, 1, H, W), grid, mode=mode, padding_mode="zeros",
+                                               align_corners=False)[0]
+        fv = torch.as_tensor(fill, dtype=torch.float32).reshape(-1, 1, 1)
+        out = out * mask + fv * (1 - mask)
+    return back(out)
+
+
+def _affine_theta(angle, translate, scale, shear, H, W, center=None):
+    """Inverse affine (output -> input) in normalised [-1, 1] coordinates for rotation by ``angle`` degrees
+    counter-clockwise about ``center``, then shear, scale and translation in pixels."""
+    rot = np.deg2rad(angle)
+    sx, sy = [np.deg2rad(s) for s in (shear if isinstance(shear, (list, tuple)) else (shear, 0.0))]
+    cx, cy = ((W * 0.5, H * 0.5) if center is None else center)
+    # forward matrix M = T(center) * T(translate) * R S Sh * T(-center) in pixel coordinates (y down)
+    a = np.cos(rot - sy) / np.cos(sy)
+    b = -np.cos(rot - sy) * np.tan(sx) / np.cos(sy) - np.sin(rot)
+    c = np.sin(rot - sy) / np.cos(sy)
+    d = -np.sin(rot - sy) * np.tan(sx) / np.cos(sy) + np.cos(rot)
+    M = np.array([[a * scale, b * scale, 0.0], [c * scale, d * scale, 0.0], [0, 0, 1.0]])
+    T1 = np.array([[1, 0, cx + translate[0]], [0, 1, cy + translate[1]], [0, 0, 1.0]])
+    T2 = np.array([[1, 0, -cx], [0, 1, -cy], [0, 0, 1.0]])
+    fwd = T1 @ M @ T2
+    inv = np.linalg.inv(fwd)
+    # pixel -> normalised: x_n = 2 x / W - 1
+    N = np.array([[2.0 / W, 0, -1], [0, 2.0 / H, -1], [0, 0, 1]])
+    th = N @ inv @ np.linalg.inv(N)
+    return torch.tensor(th[:2], dtype=torch.float32)
+
+
+def affine(img, angle, translate, scale, shear, interpolation="nearest", fill=0, center=None):
+    t, _ = _to_chw_float(img)
+    H, W = t.shape[-2:]
+    return _warp(img, _affine_theta(angle, translate, scale, shear, H, W, center), interpolation, fill)
+
+
+def rotate(img, angle, interpolation="nearest", expand=False, center=None, fill=0):
+    t, _ = _to_chw_float(img)
+    H, W = t.shape[-2:]
+    return _warp(img, _affine_theta(-angle, (0, 0), 1.0, (0.0, 0.0), H, W, center), interpolation, fill)
+
+
+def _homography(startpoints, endpoints):
+    """3x3 matrix mapping ``endpoints`` (output corners) to ``startpoints`` (input corners)."""
+    A, bvec = [], []
+    for (x, y), (u, v) in zip(endpoints, startpoints):
+        A.append([x, y, 1, 0, 0, 0, -u * x, -u * y])
+        A.append([0, 0, 0, x, y, 1, -v * x, -v * y])
+        bvec += [u, v]
+    h = np.linalg.lstsq(np.asarray(A, dtype=np.float64), np.asarray(bvec, dtype=np.float64), rcond=None)[0]
+    return torch.tensor(np.append(h, 1.0).reshape(3, 3), dtype=torch.float32)
+
+
+def perspective(img, startpoints, endpoints, interpolation="nearest", fill=0):
+    return _warp(img, None, interpolation, fill, homography=_homography(startpoints, endpoints))
+
+
+class SaturationTransform(BrightnessTransform):
+    def _apply_image(self, img):
+        if self.value == 0:
+            return img
+        return adjust_saturation(img, random.uniform(max(0, 1 - self.value), 1 + self.value))
+
+
+class HueTransform(BaseTransform):
+    def __init__(self, value, keys=None):
+        super().__init__(keys)
+        if not 0 <= value <= 0.5:
+            raise ValueError("hue value should be in [0.0, 0.5]")
+        self.value = value
+
+    def _apply_image(self, img):
+        if self.value == 0:
+            return img
+        return adjust_hue(img, random.uniform(-self.value, self.value))
+
+
+class ColorJitter(BaseTransform):
+    def __init__(self, brightness=0, contrast=0, saturation=0, hue=0, keys=None):
+        super().__init__(keys)
+        self.ts = [BrightnessTransform(brightness), ContrastTransform(contrast), SaturationTransform(saturation),
+                   HueTransform(hue)]
+
+    def _apply_image(self, img):
+        order = list(range(4))
+        random.shuffle(order)
+        for i in order:
+            if self.ts[i].value:
+                img = self.ts[i]._apply_image(img)
+        return img
+
+
+class RandomAffine(BaseTransform):
+    def __init__(self, degrees, translate=None, scale=None, shear=None, interpolation="nearest", fill=0, center=None,
+                 keys=None):
+        super().__init__(keys)
+        self.degrees = (-degrees, degrees) if isinstance(degrees, numbers.Number) else tuple(degrees)
+        self.translate, self.scale = translate, scale
+        if isinstance(shear, numbers.Number):
+            shear = (-shear, shear)
+        self.shear, self.interpolation, self.fill, self.center = shear, interpolation, fill, center
+
+    def _apply_image(self, img):
+        t, _ = _to_chw_float(img)
+        H, W = t.shape[-2:]
+        angle = random.uniform(*self.degrees)
+        tr = (0, 0)
+        if self.translate is not None:
+            tr = (round(random.uniform(-self.translate[0] * W, self.translate[0] * W)),
+                  round(random.uniform(-self.translate[1] * H, self.translate[1] * H)))
+        sc = random.uniform(*self.scale) if self.scale is not None else 1.0
+        sh = (0.0, 0.0)
+        if self.shear is not None:
+            sh = (random.uniform(self.shear[0], self.shear[1]),
+                  random.uniform(self.shear[2], self.shear[3]) if len(self.shear) == 4 else 0.0)
+        return affine(img, angle, tr, sc, sh, self.interpolation, self.fill, self.center)
+
+
+class RandomPerspective(BaseTransform):
+    def __init__(self, prob=0.5, distortion_scale=0.5, interpolation="nearest", fill=0, keys=None):
+        super().__init__(keys)
+        self.prob, self.d, self.interpolation, self.fill = prob, distortion_scale, interpolation, fill
+
+    def _apply_image(self, img):
+        if random.random() >= self.prob:
+            return img
+        t, _ = _to_chw_float(img)
+        H, W = t.shape[-2:]
+        hw, hh = int(self.d * W / 2), int(self.d * H / 2)
+        r = random.randint
+        end = [(r(0, hw), r(0, hh)), (W - 1 - r(0, hw), r(0, hh)), (W - 1 - r(0, hw), H - 1 - r(0, hh)),
+               (r(0, hw), H - 1 - r(0, hh))]
+        start = [(0, 0), (W - 1, 0), (W - 1, H - 1), (0, H - 1)]
+        return perspective(img, start, end, self.interpolation, self.fill)
+
+
+class RandomErasing(BaseTransform):
+    def __init__(self, prob=0.5, scale=(0.02, 0.33), ratio=(0.3, 3.3), value=0, inplace=False, keys=None):
+        super().__init__(keys)
+        self.prob, self.scale, self.ratio, self.value, self.inplace = prob, scale, ratio, value, inplace
+
+    def _apply_image(self, img):
+        if random.random() >= self.prob:
+            return img
+        t, _ = _to_chw_float(img)
+        C, H, W = t.shape
+        area = H * W
+        for _ in range(10):
+            a = area * random.uniform(*self.scale)
+            ar = np.exp(random.uniform(np.log(self.ratio[0]), np.log(self.ratio[1])))
+            h, w = int(round(np.sqrt(a * ar))), int(round(np.sqrt(a / ar)))
+            if 0 < h < H and 0 < w < W:
+                i, j = random.randint(0, H - h), random.randint(0, W - w)
+                v = torch.randn(C, h, w) if self.value == "random" else self.value
+                if isinstance(img, torch.Tensor):
+                    return erase(img, i, j, h, w, v, self.inplace)
+                return erase(img, i, j, h, w, 0 if self.value == "random" else v, self.inplace)
+        return img

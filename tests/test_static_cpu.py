@@ -1,0 +1,187 @@
+"""Static-graph mode (record and replay): programs, executor, backward, control flow, persistence.
+Modelled on test/legacy_test/test_executor_*.py, test_cond.py, test_while_loop_op.py, test_inference_model_io.py."""
+import numpy as np
+import pytest
+import torch
+
+import paddle_b200 as paddle
+from paddle_b200 import static
+
+
+@pytest.fixture(autouse=True)
+def _static_mode():
+    paddle.enable_static()
+    yield
+    paddle.disable_static()
+
+
+def _regression_program(opt_cls=None, **opt_kw):
+    main, startup = static.Program(), static.Program()
+    with static.program_guard(main, startup):
+        x = static.data("x", [None, 8], "float32")
+        y = static.data("y", [None, 1], "float32")
+        h = static.nn.fc(x, 16, activation="relu")
+        pred = static.nn.fc(h, 1)
+        loss = paddle.mean(paddle.nn.functional.square_error_cost(pred, y))
+        test_prog = main.clone(for_test=True)
+        if opt_cls is not None:
+            opt_cls(**opt_kw).minimize(loss)
+    return main, startup, test_prog, pred, loss
+
+
+def test_train_loop_converges_and_batch_size_is_free():
+    main, startup, test_prog, pred, loss = _regression_program(paddle.optimizer.Adam, learning_rate=0.02)
+    exe = static.Executor()
+    exe.run(startup)
+    rng = np.random.RandomState(0)
+    W = rng.randn(8, 1).astype("float32")
+    first = last = None
+    for i in range(150):
+        xb = rng.randn(32, 8).astype("float32")
+        last, = exe.run(main, feed={"x": xb, "y": xb @ W}, fetch_list=[loss])
+        first = last if first is None else first
+    assert float(last) < 0.05 * float(first)
+    xb = rng.randn(5, 8).astype("float32")
+    before = [p.numpy().copy() for p in main.all_parameters()]
+    p, = exe.run(test_prog, feed={"x": xb, "y": xb @ W}, fetch_list=[pred])
+    assert p.shape == (5, 1)
+    for b, q in zip(before, main.all_parameters()):          # the test clone does not train
+        np.testing.assert_array_equal(b, q.numpy())
+
+
+def test_append_backward_matches_eager_autograd():
+    main, startup, _, pred, loss = _regression_program()
+    with static.program_guard(main, startup):
+        pg = static.append_backward(loss)
+    assert len(pg) == 4 and all(g.name == p.name + "@GRAD" for p, g in pg)
+    xb = np.random.RandomState(1).randn(6, 8).astype("float32")
+    yb = np.ones((6, 1), "float32")
+    outs = static.Executor().run(main, feed={"x": xb, "y": yb}, fetch_list=[loss] + [g for _, g in pg])
+    paddle.disable_static()                     # the reference below is plain eager autograd
+    params = [p.as_subclass(torch.Tensor).detach().clone().requires_grad_(True) for p, _ in pg]
+    w1, w2 = [p for p in params if p.dim() == 2]
+    b1, b2 = [p for p in params if p.dim() == 1]
+    ref = ((torch.relu(torch.tensor(xb) @ w1 + b1) @ w2 + b2 - torch.tensor(yb)) ** 2).mean()
+    ref.backward()
+    np.testing.assert_allclose(outs[0], ref.item(), rtol=1e-5)
+    for got, p in zip(outs[1:], params):
+        np.testing.assert_allclose(got, p.grad.numpy(), rtol=1e-4, atol=1e-6)
+
+
+def test_gradients_wrt_input():
+    main = static.Program()
+    with static.program_guard(main):
+        x = static.data("x", [None, 3], "float32")
+        x.stop_gradient = False
+        y = paddle.sum(paddle.tanh(x) * 2.0)
+        gx, = static.gradients(y, x)
+    xb = np.random.RandomState(2).randn(4, 3).astype("float32")
+    g, = static.Executor().run(main, feed={"x": xb}, fetch_list=[gx])
+    np.testing.assert_allclose(g, 2 * (1 - np.tanh(xb) ** 2), rtol=1e-5)
+
+
+def test_cond_selects_branch_at_run_time():
+    main = static.Program()
+    with static.program_guard(main):
+        a = static.data("a", [1], "float32")
+        b = static.data("b", [1], "float32")
+        out = static.nn.cond(a < b, lambda: a + b, lambda: a * b)
+    exe = static.Executor()
+    r, = exe.run(main, feed={"a": np.array([2.0], "float32"), "b": np.array([5.0], "float32")}, fetch_list=[out])
+    assert r.item() == 7.0
+    r, = exe.run(main, feed={"a": np.array([6.0], "float32"), "b": np.array([5.0], "float32")}, fetch_list=[out])
+    assert r.item() == 30.0
+
+
+def test_switch_case_and_case():
+    main = static.Program()
+    with static.program_guard(main):
+        idx = static.data("idx", [1], "int32")
+        v = static.data("v", [2], "float32")
+        out = static.nn.switch_case(idx, {0: lambda: v + 1.0, 1: lambda: v * 10.0}, default=lambda: v - 1.0)
+    exe = static.Executor()
+    vb = np.array([1.0, 2.0], "float32")
+    for i, want in [(0, vb + 1), (1, vb * 10), (7, vb - 1)]:
+        r, = exe.run(main, feed={"idx": np.array([i], "int32"), "v": vb}, fetch_list=[out])
+        np.testing.assert_allclose(r, want)
+
+
+def test_while_loop_iterates_on_fed_bound():
+    main = static.Program()
+    with static.program_guard(main):
+        n = static.data("n", [1], "int64")
+        i = paddle.zeros([1], "int64")
+        acc = paddle.zeros([1], "float32")
+        i2, acc2 = static.nn.while_loop(lambda i, acc: i < n, lambda i, acc: [i + 1, acc + 1.5], [i, acc])
+    exe = static.Executor()
+    for bound in (0, 1, 7):
+        ri, ra = exe.run(main, feed={"n": np.array([bound], "int64")}, fetch_list=[i2, acc2])
+        assert ri.item() == bound and ra.item() == pytest.approx(1.5 * bound)
+
+
+def test_for_test_clone_disables_dropout_and_freezes_batch_norm():
+    main = static.Program()
+    with static.program_guard(main):
+        x = static.data("x", [None, 4, 3, 3], "float32")
+        h = static.nn.batch_norm(x)
+        out = paddle.nn.functional.dropout(h, 0.5, training=True)
+        test_prog = main.clone(for_test=True)
+    xb = np.random.RandomState(3).randn(8, 4, 3, 3).astype("float32") * 3 + 1
+    exe = static.Executor()
+    a, = exe.run(test_prog, feed={"x": xb}, fetch_list=[out])
+    b, = exe.run(test_prog, feed={"x": xb}, fetch_list=[out])
+    np.testing.assert_array_equal(a, b)
+    np.testing.assert_allclose(a, xb / np.sqrt(1 + 1e-5), rtol=1e-4, atol=1e-5)     # running stats are still (0, 1)
+    c, = exe.run(main, feed={"x": xb}, fetch_list=[out])
+    assert (c == 0).mean() > 0.2                                                     # train program drops
+
+
+def test_save_load_params_and_inference_model(tmp_path):
+    main, startup, test_prog, pred, loss = _regression_program(paddle.optimizer.SGD, learning_rate=0.1)
+    exe = static.Executor()
+    xb = np.random.RandomState(4).randn(3, 8).astype("float32")
+    want, = exe.run(test_prog, feed={"x": xb, "y": np.zeros((3, 1), "float32")}, fetch_list=[pred])
+    static.save(main, str(tmp_path / "ckpt"))
+    saved = static.load_program_state(str(tmp_path / "ckpt"))
+    assert set(saved) == {p.name for p in main.all_parameters()}
+    x_var = main.global_block().var("x")
+    static.save_inference_model(str(tmp_path / "infer"), [x_var], [pred], exe, program=test_prog)
+    for p in main.all_parameters():
+        with torch.no_grad():
+            p.as_subclass(torch.Tensor).zero_()
+    static.load(main, str(tmp_path / "ckpt"), exe)
+    got, = exe.run(test_prog, feed={"x": xb, "y": np.zeros((3, 1), "float32")}, fetch_list=[pred])
+    np.testing.assert_allclose(got, want, rtol=1e-6)
+    prog, feed_names, fetch_targets = static.load_inference_model(str(tmp_path / "infer"), exe)
+    assert feed_names == ["x"]
+    got2, = exe.run(prog, feed={"x": xb}, fetch_list=fetch_targets)
+    np.testing.assert_allclose(got2, want, rtol=1e-6)
+
+
+def test_scope_and_ema():
+    main, startup, _, pred, loss = _regression_program(paddle.optimizer.SGD, learning_rate=0.1)
+    with static.program_guard(main, startup):
+        ema = static.ExponentialMovingAverage(0.5)
+        ema.update()
+    exe = static.Executor()
+    name = main.all_parameters()[0].name
+    t = static.global_scope().find_var(name).get_tensor()
+    assert t is main.all_parameters()[0]
+    xb = np.ones((4, 8), "float32")
+    for _ in range(3):
+        exe.run(main, feed={"x": xb, "y": np.ones((4, 1), "float32")}, fetch_list=[loss])
+    raw = t.numpy().copy()
+    with ema.apply(exe):
+        assert not np.allclose(t.numpy(), raw)
+    np.testing.assert_array_equal(t.numpy(), raw)
+
+
+def test_unrecorded_autograd_history_is_rejected():
+    main = static.Program()
+    with static.program_guard(main):
+        w = paddle.create_parameter([3], "float32")
+        from paddle_b200.static import graph
+        with graph.suspend():
+            hidden = w * 2.0
+        with pytest.raises(RuntimeError, match="autograd history"):
+            paddle.sum(hidden)
