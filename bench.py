@@ -265,9 +265,22 @@ def main():
         if args.layers:
             out["invalid"] = "debug run with a reduced layer count"
         print(json.dumps(out))
+    used_graph = graph["g"] is not None
+    if used_graph:
+        graph["g"].reset()                # drop the captured work (it references the communicators) before teardown
+        graph.update(g=None, loss=None, tok=None)
+    torch.cuda.synchronize()
     if world > 1:
         tdist.barrier()
-        tdist.destroy_process_group()
+        sys.stdout.flush()
+        # Tearing down communicators whose collectives were captured into a CUDA graph has been seen to block;
+        # all ranks are past the barrier with nothing in flight, so give the teardown a bounded time.
+        import threading
+        t = threading.Thread(target=tdist.destroy_process_group, daemon=True)
+        t.start()
+        t.join(30.0)
+        if t.is_alive() or used_graph:
+            os._exit(0)                   # skip interpreter finalisation as well: nothing is left to flush
     return 0
 
 

@@ -98,3 +98,30 @@ def collect_operator_stats():
 
 def compare_accuracy(dump_path, another_dump_path, output_filename, loss_scale=1, dump_all_tensors=False):
     raise NotImplementedError("compare_accuracy works on dump files produced by the reference's C++ checker")
+
+
+def check_layer_numerics(func):
+    """Decorator for ``Layer.forward``: checks the tensor inputs and outputs of the call for NaN / Inf and raises with
+    the layer's name when one is found (python/paddle/amp/debugging.py ``check_layer_numerics``)."""
+    import functools
+
+    import torch
+
+    def scan(where, owner, values):
+        for i, v in enumerate(values):
+            if isinstance(v, torch.Tensor) and v.is_floating_point():
+                t = v.as_subclass(torch.Tensor)
+                n_nan, n_inf = int(torch.isnan(t).sum()), int(torch.isinf(t).sum())
+                if n_nan or n_inf:
+                    raise RuntimeError(f"[PRECISION] [ERROR] in [layer={type(owner).__name__}, {where}={i}, "
+                                       f"dtype={t.dtype}], numel={t.numel()}, num_nan={n_nan}, num_inf={n_inf}")
+
+    @functools.wraps(func)
+    def wrapper(self, *args, **kwargs):
+        if args and not isinstance(args[0], torch.Tensor):
+            raise RuntimeError("First input of this layer must be tensor.")
+        scan("input", self, args)
+        out = func(self, *args, **kwargs)
+        scan("output", self, out if isinstance(out, (list, tuple)) else [out])
+        return out
+    return wrapper

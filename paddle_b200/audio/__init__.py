@@ -191,3 +191,92 @@ def info(filepath):
             sample_rate, num_frames, num_channels, bits_per_sample = f.getframerate(), f.getnframes(), f.getnchannels(), 8 * f.getsampwidth()
             encoding = "PCM_S"
         return _Info
+
+
+# ----------------------------------------------------------------------------- datasets + importable submodules
+class _AudioFolderDataset:
+    """Common part of the audio classification datasets (python/paddle/audio/datasets/dataset.py): a list of wave
+    files with labels; items are ``(feature, label)`` with ``feat_type`` in raw / spectrogram / melspectrogram /
+    logmelspectrogram / mfcc."""
+
+    def __init__(self, files, labels, feat_type="raw", sample_rate=None, **kwargs):
+        self.files, self.labels, self.feat_type, self.sample_rate, self.feat_config = files, labels, feat_type, sample_rate, kwargs
+        table = {"spectrogram": features.Spectrogram, "melspectrogram": features.MelSpectrogram,
+                 "logmelspectrogram": features.LogMelSpectrogram, "mfcc": features.MFCC}
+        if feat_type != "raw" and feat_type not in table:
+            raise RuntimeError(f"Unknown feat_type: {feat_type}, it must be one in {['raw', *table]}")
+        self._extract = None if feat_type == "raw" else table[feat_type]
+
+    def __len__(self):
+        return len(self.files)
+
+    def __getitem__(self, idx):
+        wav, sr = load(self.files[idx])
+        x = wav[0] if wav.dim() == 2 else wav
+        if self._extract is not None:
+            cfg = dict(self.feat_config)
+            if self.feat_type != "spectrogram":
+                cfg.setdefault("sr", sr)
+            x = self._extract(**cfg)(x.reshape([1, -1]))[0]
+        return x, self.labels[idx]
+
+
+class _Datasets:
+    class ESC50(_AudioFolderDataset):
+        """ESC-50 environmental sounds: ``<root>/audio/*.wav`` and ``<root>/meta/esc50.csv``; ``split`` is the fold
+        held out for the dev set.  The archive has to be present locally (``data_dir``): nothing is downloaded."""
+
+        def __init__(self, mode="train", split=1, feat_type="raw", archive=None, data_dir=None, **kwargs):
+            import csv
+            import os
+            root = data_dir or os.path.expanduser("~/.cache/paddle/dataset/ESC-50-master")
+            meta = os.path.join(root, "meta", "esc50.csv")
+            if not os.path.exists(meta):
+                raise RuntimeError(f"ESC50 is not available offline: expected {meta}")
+            files, labels = [], []
+            with open(meta) as f:
+                for row in csv.DictReader(f):
+                    in_dev = int(row["fold"]) == split
+                    if (mode == "train") != in_dev:
+                        files.append(os.path.join(root, "audio", row["filename"]))
+                        labels.append(int(row["target"]))
+            super().__init__(files, labels, feat_type, sample_rate=44100, **kwargs)
+
+    class TESS(_AudioFolderDataset):
+        """Toronto emotional speech set: wave files named ``<speaker>_<word>_<emotion>.wav`` under ``data_dir``."""
+        label_list = ["angry", "disgust", "fear", "happy", "neutral", "ps", "sad"]
+
+        def __init__(self, mode="train", n_folds=5, split=1, feat_type="raw", archive=None, data_dir=None, **kwargs):
+            import os
+            root = data_dir or os.path.expanduser("~/.cache/paddle/dataset/TESS_Toronto_emotional_speech_set")
+            if not os.path.isdir(root):
+                raise RuntimeError(f"TESS is not available offline: expected {root}")
+            wavs = sorted(os.path.join(d, f) for d, _, fs in os.walk(root) for f in fs if f.endswith(".wav"))
+            files, labels = [], []
+            for i, path in enumerate(wavs):
+                emotion = os.path.basename(path)[:-4].split("_")[-1].lower()
+                in_dev = i % n_folds + 1 == split
+                if (mode == "train") != in_dev and emotion in self.label_list:
+                    files.append(path)
+                    labels.append(self.label_list.index(emotion))
+            super().__init__(files, labels, feat_type, sample_rate=24414, **kwargs)
+
+
+import sys as _sys  # noqa: E402
+import types as _types  # noqa: E402
+
+
+def _namespace_module(ns, name):
+    m = _types.ModuleType(name)
+    for k, v in vars(ns).items():
+        if not k.startswith("__"):
+            setattr(m, k, v.__func__ if isinstance(v, staticmethod) else v)
+    _sys.modules[name] = m
+    return m
+
+
+_functional_ns, _features_ns = functional, features
+functional = _namespace_module(functional, __name__ + ".functional")
+features = _namespace_module(features, __name__ + ".features")
+datasets = _namespace_module(_Datasets, __name__ + ".datasets")
+backends = _namespace_module(backends, __name__ + ".backends")

@@ -1,0 +1,19 @@
+"""``paddle.base``: the legacy namespace that static-graph scripts import their building blocks from
+(python/paddle/base/__init__.py)."""
+from ..static import (BuildStrategy, CompiledProgram, Executor, Program, Variable, default_main_program,  # noqa: F401
+                      default_startup_program, global_scope, name_scope, program_guard, scope_guard)
+from ..static import graph as framework  # noqa: F401
+from ..nn.layer.layers import ParamAttr  # noqa: F401
+from .. import CPUPlace, CUDAPlace  # noqa: F401
+
+__all__ = []
+
+
+def in_dygraph_mode():
+    from .. import in_dynamic_mode
+    return in_dynamic_mode()
+
+
+def is_compiled_with_cuda():
+    import torch
+    return torch.cuda.is_available()

@@ -10,6 +10,9 @@ def __getattr__(name):
     if name in ("distributed", "optimizer", "autograd", "asp", "tensor", "operators", "framework", "multiprocessing",
                 "passes", "xpu", "jit", "layers"):
         return importlib.import_module(f"{__name__}.{name}")
+    if name == "inference":
+        from .jit import inference
+        return inference
     if name in ("LookAhead", "ModelAverage"):
         from . import optimizer
         return getattr(optimizer, name)

@@ -91,3 +91,7 @@ class ModelAverage:
                 for p in self._params:
                     p.copy_(self._backup[p.name])
             self._backup = None
+
+
+from ...optimizer.extras import LBFGS  # noqa: E402,F401
+from . import functional  # noqa: E402,F401

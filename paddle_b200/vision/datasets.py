@@ -112,3 +112,81 @@ class ImageFolder(DatasetFolder):
     def __getitem__(self, i):
         img = self.loader(self.samples[i][0])
         return [self.transform(img) if self.transform is not None else img]
+
+
+class Flowers(Dataset):
+    """Oxford 102 flowers (python/paddle/vision/datasets/flowers.py): ``data_file`` is ``102flowers.tgz``,
+    ``label_file`` ``imagelabels.mat`` and ``setid_file`` ``setid.mat``.  As in the reference, ``train`` uses the
+    (larger) ``tstid`` split, ``test`` uses ``trnid`` and ``valid`` uses ``valid``."""
+    _FLAG = {"train": "tstid", "test": "trnid", "valid": "valid"}
+
+    def __init__(self, data_file=None, label_file=None, setid_file=None, mode="train", transform=None, download=True,
+                 backend=None):
+        assert mode.lower() in ("train", "valid", "test"), f"mode should be 'train', 'valid' or 'test', but got {mode}"
+        root = os.path.expanduser("~/.cache/paddle/dataset/flowers")
+        data_file = data_file or os.path.join(root, "102flowers.tgz")
+        label_file = label_file or os.path.join(root, "imagelabels.mat")
+        setid_file = setid_file or os.path.join(root, "setid.mat")
+        for f in (data_file, label_file, setid_file):
+            if not os.path.exists(f):
+                raise RuntimeError(f"Flowers needs {f}; this build cannot download it")
+        import scipy.io as scio
+        self.backend = backend or "pil"
+        self.transform = transform
+        self.labels = scio.loadmat(label_file)["labels"][0]
+        self.indexes = scio.loadmat(setid_file)[self._FLAG[mode.lower()]][0]
+        self._tar = tarfile.open(data_file)
+        self._members = {m.name: m for m in self._tar.getmembers()}
+
+    def __getitem__(self, idx):
+        import io
+
+        from PIL import Image
+        index = int(self.indexes[idx])
+        raw = self._tar.extractfile(self._members["jpg/image_%05d.jpg" % index]).read()
+        image = Image.open(io.BytesIO(raw))
+        if self.backend == "cv2":
+            image = np.array(image)
+        if self.transform is not None:
+            image = self.transform(image)
+        return image, np.array([self.labels[index - 1]]).astype("int64")
+
+    def __len__(self):
+        return len(self.indexes)
+
+
+class VOC2012(Dataset):
+    """Pascal VOC 2012 segmentation pairs read straight from ``VOCtrainval_11-May-2012.tar``
+    (python/paddle/vision/datasets/voc2012.py); the mode -> image-set mapping is the reference's."""
+    _SET = "VOCdevkit/VOC2012/ImageSets/Segmentation/{}.txt"
+    _DATA = "VOCdevkit/VOC2012/JPEGImages/{}.jpg"
+    _LABEL = "VOCdevkit/VOC2012/SegmentationClass/{}.png"
+    _FLAG = {"train": "trainval", "test": "train", "valid": "val"}
+
+    def __init__(self, data_file=None, mode="train", transform=None, download=True, backend=None):
+        assert mode.lower() in ("train", "valid", "test"), f"mode should be 'train', 'valid' or 'test', but got {mode}"
+        data_file = data_file or os.path.expanduser("~/.cache/paddle/dataset/voc2012/VOCtrainval_11-May-2012.tar")
+        if not os.path.exists(data_file):
+            raise RuntimeError(f"VOC2012 needs {data_file}; this build cannot download it")
+        self.backend = backend or "pil"
+        self.transform = transform
+        self._tar = tarfile.open(data_file)
+        self._members = {m.name: m for m in self._tar.getmembers()}
+        names = self._tar.extractfile(self._members[self._SET.format(self._FLAG[mode.lower()])]).read().decode().split()
+        self.data = [self._DATA.format(n) for n in names]
+        self.labels = [self._LABEL.format(n) for n in names]
+
+    def __getitem__(self, idx):
+        import io
+
+        from PIL import Image
+        data = Image.open(io.BytesIO(self._tar.extractfile(self._members[self.data[idx]]).read()))
+        label = Image.open(io.BytesIO(self._tar.extractfile(self._members[self.labels[idx]]).read()))
+        if self.backend == "cv2":
+            data, label = np.array(data), np.array(label)
+        if self.transform is not None:
+            data = self.transform(data)
+        return data, (label if self.backend == "pil" else label.astype("int64"))
+
+    def __len__(self):
+        return len(self.data)

@@ -75,9 +75,14 @@ for policy in ("fused", "baseline"):
     tp = LlamaForCausalLMInference(cfg, tp_group=g).load_from_training(train, rank=g.rank).prepare(B, S + NEW)
     os.environ.pop("PD_DECODE_NCCL_AR", None)
     res[f"{policy}_uses_fused_ar"] = tp.transformer._gar is not None
+    toks = []
     for graph_mode in (False, True):
         t_tp = tp.generate(ids, NEW, use_cuda_graph=graph_mode)
+        toks.append(t_tp)
         res[f"{policy}_graph{int(graph_mode)}_match"] = float((t_tp == t_single).float().mean())
+        res[f"{policy}_graph{int(graph_mode)}_first_token_match"] = float((t_tp[:, :1] == t_single[:, :1]).float().mean())
+    # the kernels are deterministic: replaying the step from a CUDA graph must give the eager tokens exactly
+    res[f"{policy}_graph_equals_eager"] = bool((toks[0] == toks[1]).all())
 torch.cuda.synchronize()
 _lib.check_status()
 _common.dump(res)

@@ -1,0 +1,264 @@
+"""Breadth checks for the smaller API families: extra optimizers, transforms (against torchvision), sparse
+convolutions, weight-only quantisation, n:m pruning, functional autograd, quasi-Newton minimisers, rpc, readers,
+slot data generators, program passes."""
+import io
+import multiprocessing as mp
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import paddle_b200 as paddle
+
+
+def _quadratic_descent(opt_cls, steps=200, **kw):
+    w = paddle.create_parameter([4], "float32")
+    with torch.no_grad():
+        w.fill_(3.0)
+    opt = opt_cls(parameters=[w], **kw)
+    for _ in range(steps):
+        (w * w).sum().backward()
+        opt.step()
+        opt.clear_grad()
+    return float((w * w).sum())
+
+
+def test_extra_optimizers_minimise_a_quadratic():
+    assert _quadratic_descent(paddle.optimizer.Rprop, learning_rate=0.01) < 1e-6
+    assert _quadratic_descent(paddle.optimizer.ASGD, learning_rate=0.05, batch_num=3) < 1e-6
+    assert _quadratic_descent(paddle.optimizer.RAdam, learning_rate=0.05) < 1.0
+    assert _quadratic_descent(paddle.optimizer.NAdam, learning_rate=0.05) < 1.0
+    w = paddle.create_parameter([4], "float32")
+    opt = paddle.optimizer.LBFGS(parameters=[w], line_search_fn="strong_wolfe")
+
+    def closure():
+        opt.clear_grad()
+        loss = ((w - 1) ** 2).sum()
+        loss.backward()
+        return loss
+    opt.step(closure)
+    np.testing.assert_allclose(w.numpy(), np.ones(4), atol=1e-5)
+
+
+def test_asgd_matches_definition():
+    w = paddle.create_parameter([2], "float32")
+    with torch.no_grad():
+        w.copy_(torch.tensor([1.0, -2.0]))
+    opt = paddle.optimizer.ASGD(learning_rate=0.1, batch_num=2, parameters=[w])
+    x = np.array([1.0, -2.0])
+    d, ys = np.zeros(2), [np.zeros(2), np.zeros(2)]
+    for m in range(5):
+        g = 2 * x * (m + 1)
+        d = d - ys[m % 2] + g
+        ys[m % 2] = g
+        x = x - 0.1 * d / min(m + 1, 2)
+        ((w * w).sum() * (m + 1)).backward()
+        opt.step()
+        opt.clear_grad()
+    np.testing.assert_allclose(w.numpy(), x, rtol=1e-5)
+
+
+def test_linear_lr():
+    s = paddle.optimizer.lr.LinearLR(0.3, 4, 1 / 3, 1.0)
+    got = []
+    for _ in range(6):
+        got.append(s())
+        s.step()
+    np.testing.assert_allclose(got, [0.1, 0.15, 0.2, 0.25, 0.3, 0.3], rtol=1e-6)
+
+
+def test_transforms_match_torchvision():
+    TF = pytest.importorskip("torchvision.transforms.functional")
+    from paddle_b200.vision import transforms as T
+    torch.manual_seed(0)
+    img = torch.rand(3, 16, 20)
+    B = TF.InterpolationMode.BILINEAR
+    pairs = [
+        (T.adjust_hue(img, 0.2), TF.adjust_hue(img, 0.2)),
+        (T.adjust_contrast(img, 1.5), TF.adjust_contrast(img, 1.5)),
+        (T.adjust_brightness(img, 0.7), TF.adjust_brightness(img, 0.7)),
+        (T.rotate(img, 30, "bilinear"), TF.rotate(img, 30, B)),
+        (T.affine(img, 15, (2, -1), 1.2, (5.0, 3.0), "bilinear"), TF.affine(img, 15, [2, -1], 1.2, [5.0, 3.0], B)),
+        (T.perspective(img, [(0, 0), (19, 0), (19, 15), (0, 15)], [(2, 1), (17, 2), (18, 14), (1, 13)], "bilinear"),
+         TF.perspective(img, [(0, 0), (19, 0), (19, 15), (0, 15)], [(2, 1), (17, 2), (18, 14), (1, 13)], B)),
+    ]
+    for got, want in pairs:
+        assert float((torch.as_tensor(got) - want).abs().max()) < 1e-4
+    u8 = (np.random.rand(16, 20, 3) * 255).astype(np.uint8)
+    assert T.ColorJitter(0.4, 0.4, 0.4, 0.1)(u8).shape == (16, 20, 3)
+    assert T.RandomErasing(1.0)(img).shape == img.shape
+    assert T.RandomAffine(10, (0.1, 0.1), (0.8, 1.2), 5)(u8).dtype == np.uint8
+
+
+def test_vision_models_forward():
+    from paddle_b200.vision import models as M
+    x = paddle.randn([1, 3, 64, 64])
+    for f in (M.mobilenet_v3_small, M.shufflenet_v2_x0_25):
+        m = f(num_classes=7)
+        m.eval()
+        assert m(x).shape == [1, 7]
+    assert sum(p.numel() for p in M.mobilenet_v3_large().parameters()) == 5483032
+    assert sum(p.numel() for p in M.shufflenet_v2_x1_0().parameters()) == 2278604
+
+
+def test_sparse_submanifold_and_regular_conv():
+    from paddle_b200.sparse import nn as snn
+    torch.manual_seed(0)
+    dense = torch.zeros(2, 4, 5, 6, 3)
+    for n, d, h, w in [[0, 0, 0, 0], [1, 2, 3, 0], [1, 3, 0, 2], [0, 3, 4, 1]]:
+        dense[n, d, h, w] = torch.randn(3)
+    x = dense.to_sparse(4)
+    conv = snn.SubmConv3D(3, 8, 3)
+    y = conv(x)
+    ref = torch.nn.functional.conv3d(dense.permute(0, 4, 1, 2, 3), conv.weight.as_subclass(torch.Tensor).permute(4, 3, 0, 1, 2),
+                                     conv.bias.as_subclass(torch.Tensor), padding=1).permute(0, 2, 3, 4, 1)
+    active = (dense != 0).any(-1)
+    yd = y.to_dense().detach()
+    assert float((yd[active] - ref[active]).abs().max()) < 1e-5
+    assert float(yd[~active].abs().max()) == 0.0              # the active set does not grow
+    y2 = snn.Conv3D(3, 4, 3, stride=2, padding=1)(x)
+    assert list(y2.shape) == [2, 2, 3, 3, 4] and y2.coalesce().indices().shape[1] > 0
+
+
+def test_weight_only_quantisation_roundtrip():
+    from paddle_b200.nn import quant as Q
+    torch.manual_seed(1)
+    w, x = paddle.randn([128, 64]), paddle.randn([4, 128])
+    ref = x @ w
+    for algo, wd, tol in (("weight_only_int8", "int8", 0.02), ("weight_only_int4", "int4", 0.2)):
+        for gs in (-1, 64):
+            q, s = Q.weight_quantize(w, algo, group_size=gs)
+            y = Q.weight_only_linear(x, q, None, s, wd, group_size=gs)
+            assert float((y - ref).abs().max() / ref.abs().max()) < tol
+            wdq = Q.weight_dequantize(q, s, algo, "float32", gs)
+            assert float((y - x @ wdq).abs().max()) < 1e-4
+    q, s = Q.weight_quantize(w, "llm.int8")
+    xo = x.clone()
+    xo[:, 3] = 20.0
+    assert float((Q.llm_int8_linear(xo, q, None, s) - xo @ w).abs().max() / (xo @ w).abs().max()) < 0.02
+
+
+def test_asp_two_four_sparsity_survives_training():
+    from paddle_b200.incubate import asp
+    net = paddle.nn.Sequential(paddle.nn.Linear(16, 8), paddle.nn.ReLU(), paddle.nn.Linear(8, 4))
+    masks = asp.prune_model(net)
+    assert all(abs(asp.calculate_density(m) - 0.5) < 1e-6 for m in masks.values())
+    opt = asp.decorate(paddle.optimizer.SGD(0.1, parameters=net.parameters()))
+    net(paddle.randn([2, 16])).sum().backward()
+    opt.step()
+    assert asp.check_sparsity(net[0].weight.t()) and abs(asp.calculate_density(net[0].weight) - 0.5) < 1e-6
+    m2 = asp.create_mask(paddle.randn([8, 8]), "mask_2d_best")
+    assert m2.sum(0).tolist() == [4.0] * 8 and m2.sum(1).tolist() == [4.0] * 8
+
+
+def test_incubate_autograd_and_bfgs():
+    from paddle_b200.incubate.autograd import Hessian, Jacobian, jvp, vjp
+    from paddle_b200.incubate.optimizer.functional import minimize_bfgs, minimize_lbfgs
+    x = paddle.ones([2, 2])
+    f = lambda t: paddle.matmul(t, t)       # noqa: E731
+    assert vjp(f, x)[1].numpy().tolist() == [[4.0, 4.0], [4.0, 4.0]]
+    assert jvp(f, x)[1].numpy().tolist() == [[4.0, 4.0], [4.0, 4.0]]
+    J = Jacobian(lambda t: t * t, paddle.to_tensor([1.0, 2.0, 3.0]))
+    np.testing.assert_allclose(J[:].numpy(), np.diag([2.0, 4.0, 6.0]))
+    H = Hessian(lambda t: (t ** 3).sum(), paddle.to_tensor([1.0, 2.0]))
+    np.testing.assert_allclose(H[:].numpy(), np.diag([6.0, 12.0]))
+    rosen = lambda t: (1 - t[0]) ** 2 + 100 * (t[1] - t[0] ** 2) ** 2      # noqa: E731
+    for fn in (minimize_bfgs, minimize_lbfgs):
+        r = fn(rosen, paddle.to_tensor([-1.0, 2.0]), max_iters=200)
+        assert bool(r[0])
+        np.testing.assert_allclose(r[2].numpy(), [1.0, 1.0], atol=1e-3)
+
+
+def _rpc_worker(rank, port, q):
+    import operator
+
+    import paddle_b200.distributed.rpc as rpc
+    rpc.init_rpc(f"w{rank}", rank, 2, f"127.0.0.1:{port}")
+    ok = rpc.rpc_sync(f"w{1 - rank}", operator.add, args=(rank, 10)) == rank + 10
+    ok &= rpc.rpc_async(f"w{1 - rank}", pow, args=(2, 5)).wait() == 32
+    try:
+        rpc.rpc_sync(f"w{1 - rank}", operator.truediv, args=(1, 0))
+        ok = False
+    except ZeroDivisionError:
+        pass
+    ok &= [w.name for w in rpc.get_all_worker_infos()] == ["w0", "w1"]
+    rpc.shutdown()
+    q.put(ok)
+
+
+def test_rpc_two_workers():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29000 + os.getpid() % 900
+    ps = [ctx.Process(target=_rpc_worker, args=(r, port, q)) for r in range(2)]
+    [p.start() for p in ps]
+    [p.join(90) for p in ps]
+    assert [p.exitcode for p in ps] == [0, 0]
+    assert q.get() and q.get()
+
+
+def test_readers_and_data_generator():
+    import paddle_b200.reader as R
+    from paddle_b200.distributed import fleet
+    r = R.firstn(R.chain(lambda: iter(range(5)), lambda: iter(range(5, 10))), 7)
+    assert list(r()) == list(range(7))
+    assert list(R.xmap_readers(lambda v: v * 2, lambda: iter(range(5)), 2, 4, order=True)()) == [0, 2, 4, 6, 8]
+    assert sorted(R.buffered(lambda: iter(range(4)), 2)()) == [0, 1, 2, 3]
+    assert list(R.compose(lambda: iter([1, 2]), lambda: iter([(3, 4), (5, 6)]))()) == [(1, 3, 4), (2, 5, 6)]
+
+    class Gen(fleet.MultiSlotDataGenerator):
+        def generate_sample(self, line):
+            def it():
+                yield [("words", [1926, 8, 17]), ("label", [1])]
+            return it
+    out = io.StringIO()
+    Gen()._run(["x"], out)
+    assert out.getvalue() == "3 1926 8 17 1 1\n"
+    assert fleet.util.get_file_shard(["a", "b", "c"]) == ["a", "b", "c"]
+    rm = fleet.UserDefinedRoleMaker(current_id=1, role=fleet.Role.WORKER, worker_num=2, worker_endpoints=["a:1", "b:2"])
+    assert rm._worker_index() == 1 and rm._worker_num() == 2 and not rm._is_first_worker()
+
+
+def test_slot_dataset_feeds_static_program(tmp_path):
+    from paddle_b200 import static
+    from paddle_b200.distributed import InMemoryDataset
+    path = tmp_path / "part-0"
+    path.write_text("".join(f"2 {i} {i + 1} 1 {i % 2}\n" for i in range(10)))
+    paddle.enable_static()
+    try:
+        main = static.Program()
+        with static.program_guard(main):
+            ids = static.data("ids", [None, 2], "int64")
+            lab = static.data("lab", [None, 1], "int64")
+            total = paddle.sum(ids) + paddle.sum(lab)
+        ds = InMemoryDataset()
+        ds.init(batch_size=4, use_var=[ids, lab])
+        ds.set_filelist([str(path)])
+        ds.load_into_memory()
+        assert ds.get_memory_data_size() == 10
+        exe = static.Executor()
+        sums = [float(exe.run(main, feed=b, fetch_list=[total])[0]) for b in ds]
+        assert len(sums) == 3 and sum(sums) == sum(2 * i + 1 + i % 2 for i in range(10))
+    finally:
+        paddle.disable_static()
+
+
+def test_pass_manager_prunes_static_program():
+    from paddle_b200 import static
+    from paddle_b200.distributed.passes import PassManager, new_pass
+    paddle.enable_static()
+    try:
+        main = static.Program()
+        with static.program_guard(main):
+            x = static.data("x", [None, 4], "float32")
+            kept = paddle.tanh(x)
+            _unused = paddle.exp(x) * 3.0
+        n0 = len(main.global_block().ops)
+        pm = PassManager([new_pass("fuse_elewise_add_act"), new_pass("prune_side_effect_free", {"fetch": [kept]})])
+        pm.apply([main], [static.Program()])
+        assert len(main.global_block().ops) < n0 and pm.names == ["fuse_elewise_add_act", "prune_side_effect_free"]
+        out, = static.Executor().run(main, feed={"x": np.ones((2, 4), "float32")}, fetch_list=[kept])
+        np.testing.assert_allclose(out, np.tanh(np.ones((2, 4))), rtol=1e-6)
+    finally:
+        paddle.disable_static()
