@@ -135,12 +135,21 @@ __global__ void __launch_bounds__(256) quant_128x128_t_kernel(const bf16* __rest
 }
 
 // ------------------------------------------------------------------------------------------------ grouped fp8 GEMM
-constexpr int BM = 128, BN = 128, BK = 128, STAGES = 4;
-constexpr int A_STAGE = BM * BK, B_STAGE = BN * BK;          // 16 KB each (1 byte per element)
-constexpr int NUM_THREADS = 192;
+constexpr int BM = 128, BK = 128, STAGES = 4;
+constexpr int SCALE_BLOCK = 128;                               // weight-scale granularity along N (and K)
+constexpr int A_STAGE = BM * BK;                               // 16 KB (1 byte per element)
 constexpr int MAX_EXPERTS = 64;
 constexpr int OFF_SLOTS = 80;                                  // >= MAX_EXPERTS + 1, keeps the barriers 16-byte aligned
-constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + OFF_SLOTS * 4 + 1024 + 256;
+// NWG epilogue warpgroups own 128 accumulator columns each: the tile is 128 x (128 * NWG).  With one warpgroup the
+// promotion (TMEM read + 128 FMAs per thread per 128-deep K block) takes about twice as long as the fp8 MMA of the
+// block; two warpgroups on a 128 x 256 tile halve the promotion work per MMA cycle and bring the two into balance.
+template <int NWG> struct Cfg {
+  static constexpr int BN = SCALE_BLOCK * NWG;
+  static constexpr int B_STAGE = BN * BK;
+  static constexpr int THREADS = 128 * NWG + 64;
+  static constexpr int SMEM = STAGES * (A_STAGE + B_STAGE) + OFF_SLOTS * 4 + 1024 + 256;
+  static constexpr int TMEM_COLS = 2 * BN;                    // two accumulator buffers
+};
 
 struct Bars {
   uint64_t full[STAGES], empty[STAGES], tfull[2], tempty[2], drain;
@@ -159,14 +168,15 @@ struct GParams {
 };
 
 // tile id -> (expert, first row, rows, n0); returns false when id is past the end
-__device__ __forceinline__ bool locate(const int* offs, int E, int tiles_n, int id, int& e, int& m0, int& m_end, int& n0) {
+__device__ __forceinline__ bool locate(const int* offs, int E, int tiles_n, int bn, int id, int& e, int& m0, int& m_end,
+                                       int& n0) {
   for (e = 0; e < E; ++e) {
     const int rows = offs[e + 1] - offs[e];
     const int t = ((rows + BM - 1) / BM) * tiles_n;
     if (id < t) {
       m0 = offs[e] + (id / tiles_n) * BM;
       m_end = offs[e + 1];
-      n0 = (id % tiles_n) * BN;
+      n0 = (id % tiles_n) * bn;
       return true;
     }
     id -= t;
@@ -174,8 +184,11 @@ __device__ __forceinline__ bool locate(const int* offs, int E, int tiles_n, int 
   return false;
 }
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int NWG>
+__global__ void __launch_bounds__(Cfg<NWG>::THREADS, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GParams p) {
+  constexpr int BN = Cfg<NWG>::BN, B_STAGE = Cfg<NWG>::B_STAGE, EPI_WARPS = 4 * NWG;
+  constexpr int TMA_WARP = EPI_WARPS, MMA_WARP = EPI_WARPS + 1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -187,7 +200,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   const int tiles_n = p.N / BN;
   const int KB = p.K / BK;
 
-  for (int i = threadIdx.x; i <= p.E; i += NUM_THREADS) sOff[i] = p.offsets[i];
+  for (int i = threadIdx.x; i <= p.E; i += Cfg<NWG>::THREADS) sOff[i] = p.offsets[i];
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
@@ -195,20 +208,20 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->tfull[a], 1);
-      mbar_init(&bars->tempty[a], 128);
+      mbar_init(&bars->tempty[a], 128 * NWG);
     }
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
     bars->verdict = 0;
     fence_mbar_init();
   }
-  if (warp == 5) tmem_alloc(&bars->tmem_base, 256);
+  if (warp == MMA_WARP) tmem_alloc(&bars->tmem_base, Cfg<NWG>::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     if (lane == 0) {
       prefetch_tmap(&tmA);
       prefetch_tmap(&tmB);
@@ -216,13 +229,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       bool ok = true;
       for (int id = blockIdx.x; ok; id += gridDim.x) {
         int e, m0, m_end, n0;
-        if (!locate(sOff, p.E, tiles_n, id, e, m0, m_end, n0)) break;
+        if (!locate(sOff, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&bars->empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, 100 + s)) { ok = false; break; }
           mbar_expect_tx(&bars->full[s], A_STAGE + B_STAGE);
           tma_load_2d(sA + s * A_STAGE, &tmA, &bars->full[s], kb * BK, m0);            // box {128 k, 128 m}
-          tma_load_3d(sB + s * B_STAGE, &tmB, &bars->full[s], kb * BK, n0, e);         // box {128 k, 128 n, 1}
+#pragma unroll
+          for (int g = 0; g < NWG; ++g)                                                  // box {128 k, 128 n, 1}
+            tma_load_3d(sB + s * B_STAGE + g * (SCALE_BLOCK * BK), &tmB, &bars->full[s], kb * BK, n0 + g * SCALE_BLOCK, e);
           armed = it + 1;
         }
       }
@@ -231,14 +246,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(BM, BN, false, false, 0, 0);        // e4m3 x e4m3, both K-major
       int it = 0;
       bool ok = true;
       for (int id = blockIdx.x; ok; id += gridDim.x) {
         int e, m0, m_end, n0;
-        if (!locate(sOff, p.E, tiles_n, id, e, m0, m_end, n0)) break;
+        if (!locate(sOff, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES, acc = it & 1;
           if (!mbar_wait(&bars->tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 200 + acc)) { ok = false; break; }
@@ -260,25 +275,28 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ promotion + store (warps 0..3, thread = row)
-    const int tid = threadIdx.x;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    // ------------------------------------------------------------ promotion + store: thread = row, warpgroup = 128 columns
+    const int wg = warp >> 2;
+    const int tid = threadIdx.x & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int kbn = p.K / 128, nbn = p.N / 128;
     int it = 0;
     bool ok = true;
     for (int id = blockIdx.x; ok; id += gridDim.x) {
       int e, m0, m_end, n0;
-      if (!locate(sOff, p.E, tiles_n, id, e, m0, m_end, n0)) break;
+      if (!locate(sOff, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
       const int row = m0 + tid;
       const bool live = row < m_end;
-      float acc[BN];
+      float acc[SCALE_BLOCK];
 #pragma unroll
-      for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < SCALE_BLOCK; ++i) acc[i] = 0.f;
       const float* as_row = p.a_scale + static_cast<size_t>(live ? row : m0) * kbn;
-      const float* bs = p.b_scale + (static_cast<size_t>(e) * kbn) * nbn + n0 / 128;
+      const float* bs = p.b_scale + (static_cast<size_t>(e) * kbn) * nbn + n0 / 128 + wg;
+      float sc_next = as_row[0] * bs[0];
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int a = it & 1;
-        const float sc = as_row[kb] * bs[static_cast<size_t>(kb) * nbn];
+        const float sc = sc_next;
+        if (kb + 1 < KB) sc_next = as_row[kb + 1] * bs[static_cast<size_t>(kb + 1) * nbn];   // hidden behind the wait
         int good = 1;
         if (lane == 0) good = mbar_wait(&bars->tfull[a], (it >> 1) & 1, abort_flag, p.status, 400 + a) ? 1 : 0;
         good = __shfl_sync(0xffffffffu, good, 0);
@@ -287,22 +305,26 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         for (int i = 0; i < 1024 && !mbar_try_wait(&bars->tfull[a], (it >> 1) & 1); ++i) {
         }
         tc_fence_after();
+        const uint32_t t_acc = tmem_base + lane_base + a * BN + wg * SCALE_BLOCK;
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + lane_base + a * BN + c * 32, r);
+        for (int c = 0; c < SCALE_BLOCK / 64; ++c) {
+          uint32_t r0[32], r1[32];                     // two TMEM reads in flight per wait
+          tmem_ld_32x32(t_acc + c * 64, r0);
+          tmem_ld_32x32(t_acc + c * 64 + 32, r1);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(r[i]), sc, acc[c * 32 + i]);
+          for (int i = 0; i < 32; ++i) acc[c * 64 + i] = fmaf(__uint_as_float(r0[i]), sc, acc[c * 64 + i]);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c * 64 + 32 + i] = fmaf(__uint_as_float(r1[i]), sc, acc[c * 64 + 32 + i]);
         }
         tc_fence_before();
         mbar_arrive(&bars->tempty[a]);
       }
       if (!ok) break;
       if (live) {
-        bf16* dst = p.c + static_cast<size_t>(row) * p.ldc + n0;
+        bf16* dst = p.c + static_cast<size_t>(row) * p.ldc + n0 + wg * SCALE_BLOCK;
 #pragma unroll
-        for (int j = 0; j < BN / 8; ++j) {
+        for (int j = 0; j < SCALE_BLOCK / 8; ++j) {
           uint4 v;
           v.x = pack_bf16x2(acc[8 * j + 0], acc[8 * j + 1]);
           v.y = pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]);
@@ -315,7 +337,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) tmem_dealloc(tmem_base, 256);
+  if (warp == MMA_WARP) tmem_dealloc(tmem_base, Cfg<NWG>::TMEM_COLS);
 }
 
 }  // namespace moe
@@ -355,24 +377,31 @@ PD_EXPORT int pd_fp8_quant_128x128_t(const void* w, void* wt, float* scales, int
 PD_EXPORT int pd_grouped_gemm_fp8(const void* A, const float* a_scale, const void* B, const float* b_scale,
                                   const int* offsets, void* C, int M_total, int N, int K, int E, int ldc, int max_tiles,
                                   int* status, cudaStream_t stream) {
-  if (M_total <= 0 || N <= 0 || K <= 0 || E <= 0 || E > MAX_EXPERTS || (N % BN) || (K % BK)) return kErrBadShape;
+  if (M_total <= 0 || N <= 0 || K <= 0 || E <= 0 || E > MAX_EXPERTS || (N % SCALE_BLOCK) || (K % BK)) return kErrBadShape;
   if (!aligned16(A) || !aligned16(B) || !aligned16(C) || (ldc % 8)) return kErrAlignment;
   CUtensorMap tmA, tmB;
   bool ok = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, K, M_total, uint64_t(K), BK, BM);
   uint64_t dims[3] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(E)};
   uint64_t strides[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(K) * N};
-  uint32_t box[3] = {BK, BN, 1};
+  uint32_t box[3] = {BK, SCALE_BLOCK, 1};
   ok &= encode_tmap(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return kErrTensorMap;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(grouped_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(grouped_gemm_fp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(grouped_gemm_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM) != cudaSuccess)
       return kErrCuda;
     configured = true;
   }
   GParams p{offsets, a_scale, b_scale, (bf16*)C, E, N, K, ldc, status};
-  int grid = max_tiles < sm_count() ? max_tiles : sm_count();
+  // max_tiles counts 128 x 128 tiles; the 128 x 256 kernel has half as many
+  const bool wide = (N % Cfg<2>::BN) == 0;
+  const int tiles = wide ? (max_tiles + 1) / 2 : max_tiles;
+  int grid = tiles < sm_count() ? tiles : sm_count();
   if (grid < 1) grid = 1;
-  grouped_gemm_fp8_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  if (wide)
+    grouped_gemm_fp8_kernel<2><<<grid, Cfg<2>::THREADS, Cfg<2>::SMEM, stream>>>(tmA, tmB, p);
+  else
+    grouped_gemm_fp8_kernel<1><<<grid, Cfg<1>::THREADS, Cfg<1>::SMEM, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }

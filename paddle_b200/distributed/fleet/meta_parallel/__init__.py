@@ -66,7 +66,8 @@ class SegmentParallel(MetaParallelBase):
 
 
 def __getattr__(name):
-    if name in ("PipelineParallel", "PipelineParallelWithInterleave", "PipelineParallelWithInterleaveFthenB"):
+    if name in ("PipelineParallel", "PipelineParallelWithInterleave", "PipelineParallelWithInterleaveFthenB",
+                "PipelineParallelWithInterleaveWindowed"):
         from . import pipeline_parallel as pp
         return getattr(pp, name)
     if name in ("LayerDesc", "SharedLayerDesc", "PipelineLayer", "SegmentLayers"):

@@ -411,10 +411,10 @@ class PipelineParallelWithInterleaveFthenB(PipelineParallel):
         return self._broadcast_final_loss()
 
 
-class PipelineParallelWithInterleave(PipelineParallelWithInterleaveFthenB):
-    """Interleaved virtual-stage pipeline (reference :1308).  Same systolic item order as the F-then-B class,
-    run window by window: a window of ``P`` micro-batches (one group) goes forward through all chunks and then
-    backward, so live activations are bounded by one group instead of the whole batch."""
+class PipelineParallelWithInterleaveWindowed(PipelineParallelWithInterleaveFthenB):
+    """Same systolic item order as the F-then-B class, run window by window: a window of ``P`` micro-batches (one
+    group) goes forward through all chunks and then backward, so live activations are bounded by one group instead
+    of the whole batch."""
 
     def forward_backward_pipeline(self, data, scaler=None, forward_only=False):
         P = self.num_stages
@@ -435,3 +435,23 @@ class PipelineParallelWithInterleave(PipelineParallelWithInterleaveFthenB):
         finally:
             self.accumulate_steps = acc
         return total / acc
+
+
+class PipelineParallelWithInterleave(PipelineParallel):
+    """Interleaved 1F1B over virtual stages (reference :1308): each rank holds ``V`` chunks, warm-up is
+    ``(P - rank - 1) * 2 + (V - 1) * P`` forwards, then forwards and backwards alternate, so the bubble shrinks by
+    ``V`` compared with plain 1F1B.  The order is generated as data and run by the schedule executor
+    (``pipeline_schedules.py``); ``schedule_mode`` in ``pipeline_configs`` selects another generator."""
+
+    def __init__(self, layers, hcg, strategy):
+        super().__init__(layers, hcg, strategy)
+        from . import pipeline_schedules as S
+        self._V = layers.get_num_virtual_stages()
+        mode = strategy.pipeline_configs.get("schedule_mode", "VPP") if hasattr(strategy.pipeline_configs, "get") else "VPP"
+        if mode == "1F1B" and self._V > 1:
+            mode = "VPP"
+        self._executor = S.ScheduleExecutor(self, S.SCHEDULES.get(mode, S.interleaved_1f1b))
+        S.validate(self._executor.fn, self.num_stages, self._V, self.accumulate_steps)
+
+    def forward_backward_pipeline(self, data, scaler=None, forward_only=False):
+        return self._executor.run(data, scaler, forward_only)

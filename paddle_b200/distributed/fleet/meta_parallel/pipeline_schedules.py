@@ -1,0 +1,232 @@
+"""Pipeline schedules as data plus one executor.
+
+A *schedule* is, per pipeline rank, a list of steps ``("F" | "B", chunk, micro_batch)``.  ``interleaved_1f1b``
+generates the virtual-pipeline order of python/paddle/distributed/fleet/meta_parallel/pipeline_parallel.py
+``PipelineParallelWithInterleave`` (:1308-2390): warm-up forwards ``(P - rank - 1) * 2 + (V - 1) * P``, then one
+forward / one backward, then the remaining backwards; virtual micro-batch ``k`` maps to chunk
+``(k % (P * V)) // P`` (mirrored for backward) and micro-batch ``(k // (P * V)) * P + k % P``.
+
+``ScheduleExecutor`` runs any such schedule.  A step's input (activation from virtual stage ``vs - 1`` or gradient
+from ``vs + 1``) travels as one message on the channel (source rank -> this rank).  Because the schedule is static,
+every rank derives the exact message order of each of its incoming channels by replaying the sender's list, and
+receives strictly in that order (stashing what arrives early).  Sends are asynchronous and every ordered rank pair
+has its own communicator, on which one side only sends and the other only receives, in the same order: a send can
+never be stuck behind a receive, on NCCL as well as on gloo, so any dependency-respecting schedule runs without
+deadlock and without the combined send/receive calls hand-written per schedule phase."""
+from __future__ import annotations
+
+import torch
+
+from ... import collective as C
+from ...._core.tensor import as_tensor
+
+
+def f_then_b(P, V, M, rank):
+    steps = [("F", c, m) for c, m in _virtual_order(P, V, M)]
+    return steps + [("B", V - 1 - c, m) for c, m in _virtual_order(P, V, M)]
+
+
+def one_f_one_b(P, V, M, rank):
+    assert V == 1
+    warm = min(P - rank - 1, M)
+    steps = [("F", 0, m) for m in range(warm)]
+    for i in range(M - warm):
+        steps += [("F", 0, warm + i), ("B", 0, i)]
+    return steps + [("B", 0, m) for m in range(M - warm, M)]
+
+
+def _virtual_order(P, V, M):
+    """(chunk, micro-batch) of virtual micro-batch k = 0 .. M * V - 1 in forward order."""
+    out = []
+    for k in range(M * V):
+        g, r = divmod(k, P * V)
+        out.append((r // P, g * P + r % P))
+    return out
+
+
+def interleaved_1f1b(P, V, M, rank):
+    if M % P != 0:
+        raise ValueError("interleaved 1F1B needs accumulate_steps to be a multiple of the pipeline degree")
+    N = M * V
+    fwd = _virtual_order(P, V, M)
+    bwd = [(V - 1 - c, m) for c, m in fwd]
+    warm = min((P - rank - 1) * 2 + (V - 1) * P, N)
+    steps = [("F", *fwd[k]) for k in range(warm)]
+    for i in range(N - warm):
+        steps += [("F", *fwd[warm + i]), ("B", *bwd[i])]
+    return steps + [("B", *bwd[k]) for k in range(N - warm, N)]
+
+
+SCHEDULES = {"FThenB": f_then_b, "1F1B": one_f_one_b, "VPP": interleaved_1f1b, "interleaved_1f1b": interleaved_1f1b}
+
+
+def validate(schedule_fn, P, V, M):
+    """Checks on the host that the per-rank lists form a deadlock-free global order: every step's input is produced
+    by an earlier step of some rank.  Returns the number of rounds of a greedy simulation (a proxy for the bubble)."""
+    lists = [list(schedule_fn(P, V, M, r)) for r in range(P)]
+    pos = [0] * P
+    done = set()
+    last_vs = P * V - 1
+    rounds = 0
+    while any(pos[r] < len(lists[r]) for r in range(P)):
+        progressed = []
+        for r in range(P):
+            if pos[r] >= len(lists[r]):
+                continue
+            kind, c, m = lists[r][pos[r]]
+            vs = c * P + r
+            need = None
+            if kind == "F" and vs > 0:
+                need = ("F", vs - 1, m)
+            elif kind == "B":
+                need = ("B", vs + 1, m) if vs < last_vs else ("F", vs, m)
+            if need is None or need in done:
+                progressed.append((r, (kind, vs, m)))
+        if not progressed:
+            raise RuntimeError(f"schedule deadlocks at positions {pos}")
+        for r, item in progressed:
+            done.add(item)
+            pos[r] += 1
+        rounds += 1
+    return rounds
+
+
+class ScheduleExecutor:
+    def __init__(self, owner, schedule_fn):
+        self.o = owner
+        hcg = owner._hcg
+        self.P, self.rank = owner.num_stages, owner.stage_id
+        self.V = owner._layers.get_num_virtual_stages() if hasattr(owner._layers, "get_num_virtual_stages") else 1
+        self.fn = schedule_fn
+        ranks = [hcg.get_rank_from_stage(s) for s in range(self.P)]
+        self._global = ranks
+        # one communicator per ordered neighbour pair of the ring (every rank creates all of them, in the same order)
+        self._chan = {}
+        for s in range(self.P):
+            d = (s + 1) % self.P
+            if self.P == 1:
+                break
+            for a, b in ((s, d), (d, s)):
+                if (a, b) not in self._chan:
+                    self._chan[(a, b)] = C.new_group(sorted({ranks[a], ranks[b]}))
+        self._meta = {}              # "act" / "grad" per virtual stage -> (shape, dtype, requires_grad)
+
+    # ------------------------------------------------------------------ static analysis
+    def _producer(self, kind, vs):
+        """(rank, message kind) that produces the input of a step of virtual stage ``vs``."""
+        if kind == "F":
+            return (vs - 1) % self.P
+        return (vs + 1) % self.P
+
+    def _sends_of(self, steps, r):
+        """Messages rank ``r`` emits, in order: (dst rank, ("act" | "grad", consumer vs, mb))."""
+        last = self.P * self.V - 1
+        out = []
+        for kind, c, m in steps:
+            vs = c * self.P + r
+            if kind == "F" and vs < last:
+                out.append(((r + 1) % self.P, ("act", vs + 1, m)))
+            elif kind == "B" and vs > 0:
+                out.append(((r - 1) % self.P, ("grad", vs - 1, m)))
+        return out
+
+    # ------------------------------------------------------------------ messaging
+    def _send(self, t, dst, pending):
+        g = self._chan[(self.rank, dst)]
+        t = t.detach().contiguous()
+        pending.append((C.isend(t, self._global[dst], g), t))
+
+    def _recv_next(self, src, msg, like):
+        from ...._core.dtype import default_device
+        shape, dtype = like
+        buf = torch.empty(shape, dtype=dtype, device=default_device())
+        C.recv(buf, self._global[src], self._chan[(src, self.rank)])
+        return buf
+
+    def run(self, data, scaler=None, forward_only=False):
+        o, P, V, r = self.o, self.P, self.V, self.rank
+        M = o.accumulate_steps
+        inputs, labels = data if isinstance(data, (tuple, list)) and len(data) == 2 else (data, None)
+        sched = {q: list(self.fn(P, V, M, q)) for q in range(P)}
+        if forward_only:
+            sched = {q: [s for s in sched[q] if s[0] == "F"] for q in range(P)}
+        incoming = {}                 # src rank -> ordered message ids destined to this rank
+        for q in range(P):
+            if q == r:
+                continue
+            for dst, msg in self._sends_of(sched[q], q):
+                if dst == r:
+                    incoming.setdefault(q, []).append(msg)
+        if P == 1:
+            incoming = {}
+        cursor = {q: 0 for q in incoming}
+        stash, pending = {}, []
+        last_vs = P * V - 1
+        ins, outs = {}, {}
+        o.total_loss = None
+        act_like = getattr(self, "_act_like", None)
+
+        def need(src, msg, like):
+            while msg not in stash:
+                nxt = incoming[src][cursor[src]]
+                cursor[src] += 1
+                stash[nxt] = self._recv_next(src, nxt, like)
+            return stash.pop(msg)
+
+        for kind, c, m in sched[r]:
+            vs = c * P + r
+            if kind == "F":
+                if vs == 0:
+                    x = o._load_micro_batch(inputs, m)
+                else:
+                    if act_like is None:
+                        act_like = self._act_like = self._exchange_meta(None, (vs - 1) % P)
+                    x = as_tensor(need((vs - 1) % P, ("act", vs, m), act_like[:2]))
+                    x.requires_grad_(act_like[2] and x.is_floating_point() and not forward_only)
+                out = o._layers.forward(x, chunk_id=c) if V > 1 else o._layers.forward(x)
+                if vs == last_vs:
+                    lab = o._load_micro_batch(labels, m)
+                    loss = o._layers._loss_fn(out, lab) if not isinstance(lab, (tuple, list)) else o._layers._loss_fn(out, *lab)
+                    if M > 1 and not o._delay_scale_loss:
+                        loss = loss / M
+                    o.total_loss = loss.detach() if o.total_loss is None else o.total_loss + loss.detach()
+                    out = loss
+                else:
+                    if not getattr(self, "_meta_sent", False):
+                        self._exchange_meta(out, (r + 1) % P)
+                        self._meta_sent = True
+                    self._send(out, (r + 1) % P, pending)
+                if not forward_only:
+                    ins[(c, m)], outs[(c, m)] = x, out
+            else:
+                x, y = ins.pop((c, m)), outs.pop((c, m))
+                if vs == last_vs:
+                    (scaler.scale(y) if scaler else y).backward()
+                else:
+                    g = need((vs + 1) % P, ("grad", vs, m), (list(y.shape), y.dtype))
+                    torch.autograd.backward([C._plain(y)], [C._plain(g)])
+                if vs > 0 and isinstance(x, torch.Tensor) and x.requires_grad:
+                    self._send(x.grad, (r - 1) % P, pending)
+                    x.grad = None
+        for w, _ in pending:
+            w.wait()
+        assert not stash and all(cursor[q] == len(incoming[q]) for q in incoming), "pipeline messages left over"
+        if not forward_only:
+            o._layers.allreduce_shared_weight_gradients()
+        return o._broadcast_final_loss()
+
+    def _exchange_meta(self, out, peer):
+        """First activation of a run: the producer tells its consumer shape / dtype / requires_grad (all activations
+        between stages share them)."""
+        from ...._core.dtype import default_device
+        from .pipeline_parallel import _DT
+        n = 16
+        if out is not None:
+            m = [out.dim(), _DT.index(out.dtype), int(out.requires_grad), *out.shape]
+            t = torch.tensor(m + [0] * (n - len(m)), dtype=torch.int64, device=default_device())
+            C.send(t, self._global[peer], self._chan[(self.rank, peer)])
+            return None
+        t = torch.zeros(n, dtype=torch.int64, device=default_device())
+        C.recv(t, self._global[peer], self._chan[(peer, self.rank)])
+        m = t.tolist()
+        return (m[3:3 + m[0]], _DT[m[1]], bool(m[2]))

@@ -141,3 +141,25 @@ def test_spawn_runs_and_propagates_errors():
     assert [open(f"{base}.{r}").read() for r in range(2)] == ["3.0", "3.0"]
     with pytest.raises(RuntimeError, match="boom from the child"):
         dist.spawn(_spawn_bad, args=(base,), nprocs=2, env=env)
+
+
+def test_pipeline_schedules_are_deadlock_free_and_have_the_expected_bubble():
+    """Host-side check of the generated per-rank orders: every step's input is produced earlier somewhere, the
+    greedy makespan is 2*M*V + 2*(P-1) virtual steps (the interleaved bubble), and a broken order is reported."""
+    from paddle_b200.distributed.fleet.meta_parallel import pipeline_schedules as S
+    for P, V, M in [(2, 2, 4), (4, 2, 8), (4, 3, 8), (8, 2, 16)]:
+        assert S.validate(S.interleaved_1f1b, P, V, M) == 2 * M * V + 2 * (P - 1)
+        steps = S.interleaved_1f1b(P, V, M, 0)
+        warm = next(i for i, s in enumerate(steps) if s[0] == "B")
+        assert warm == min((P - 1) * 2 + (V - 1) * P, M * V) + 1          # warm-up forwards + the first steady forward
+        assert sorted(s for s in steps if s[0] == "F") == sorted(("F", c, m) for c in range(V) for m in range(M))
+    for P, M in [(2, 4), (4, 8)]:
+        assert S.validate(S.one_f_one_b, P, 1, M) == 2 * M + 2 * (P - 1)
+
+    def broken(P, V, M, rank):           # backward before its forward
+        return [("B", 0, 0), ("F", 0, 0)]
+    import pytest
+    with pytest.raises(RuntimeError, match="deadlocks"):
+        S.validate(broken, 2, 1, 1)
+    with pytest.raises(ValueError):
+        S.interleaved_1f1b(4, 2, 6, 0)
