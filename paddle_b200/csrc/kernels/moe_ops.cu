@@ -170,13 +170,17 @@ struct GParams {
 // tile id -> (expert, first row, rows, n0); returns false when id is past the end
 __device__ __forceinline__ bool locate(const int* offs, int E, int tiles_n, int bn, int id, int& e, int& m0, int& m_end,
                                        int& n0) {
+  // Within an expert the row tiles vary fastest: the CTAs running at one time then share a few weight column
+  // blocks (each read from HBM once and hit in L2 by the other row tiles) instead of streaming the whole weight
+  // matrix once per row tile; the expert's activations (rows x K bytes) stay L2-resident either way.
   for (e = 0; e < E; ++e) {
     const int rows = offs[e + 1] - offs[e];
-    const int t = ((rows + BM - 1) / BM) * tiles_n;
+    const int tm = (rows + BM - 1) / BM;
+    const int t = tm * tiles_n;
     if (id < t) {
-      m0 = offs[e] + (id / tiles_n) * BM;
+      m0 = offs[e] + (id % tm) * BM;
       m_end = offs[e + 1];
-      n0 = (id % tiles_n) * bn;
+      n0 = (id / tm) * bn;
       return true;
     }
     id -= t;
@@ -292,11 +296,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       for (int i = 0; i < SCALE_BLOCK; ++i) acc[i] = 0.f;
       const float* as_row = p.a_scale + static_cast<size_t>(live ? row : m0) * kbn;
       const float* bs = p.b_scale + (static_cast<size_t>(e) * kbn) * nbn + n0 / 128 + wg;
-      float sc_next = as_row[0] * bs[0];
+      // The scales of block kb + 1 are LOADED here and only multiplied at the top of the next iteration: issue is in
+      // order, so using them now would park the warp on the load for a full memory latency every block.
+      float a_nx = as_row[0], b_nx = bs[0];
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const int a = it & 1;
-        const float sc = sc_next;
-        if (kb + 1 < KB) sc_next = as_row[kb + 1] * bs[static_cast<size_t>(kb + 1) * nbn];   // hidden behind the wait
+        const float sc = a_nx * b_nx;
+        if (kb + 1 < KB) {
+          a_nx = as_row[kb + 1];
+          b_nx = bs[static_cast<size_t>(kb + 1) * nbn];
+        }
         int good = 1;
         if (lane == 0) good = mbar_wait(&bars->tfull[a], (it >> 1) & 1, abort_flag, p.status, 400 + a) ? 1 : 0;
         good = __shfl_sync(0xffffffffu, good, 0);

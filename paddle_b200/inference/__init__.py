@@ -85,9 +85,12 @@ class Predictor:
     def __init__(self, config: Config):
         from .. import jit
         self._config = config
-        self._layer = jit.load(config.model_dir())
         self._device = torch.device("cuda", config._device_id) if config.use_gpu() and torch.cuda.is_available() \
             else torch.device("cpu")
+        self._program = self._load_static_program(config.model_dir())
+        if self._program is not None:
+            return
+        self._layer = jit.load(config.model_dir())
         if self._device.type == "cuda":
             self._layer.to(device=self._device)
         if config._cuda_graph:
@@ -103,6 +106,46 @@ class Predictor:
         self._inputs = {n: _Handle(n) for n in self._in_names}
         self._outputs = []
 
+    def _load_static_program(self, prefix):
+        """Models written by ``static.save_inference_model`` hold a recorded program instead of a pickled layer."""
+        from .. import static
+        try:
+            with open(prefix + ".pdmodel", "rb") as f:
+                program = static.deserialize_program(f.read())
+        except Exception:
+            return None
+        static.deserialize_persistables(program, static.load_from_file(prefix + ".pdiparams"))
+        if self._device.type == "cuda":
+            for slot, t in list(program._captured.items()):
+                t.data = t.data.to(self._device)
+            for name, (slot, ex) in list(program._placeholders.items()):
+                ex.data = ex.data.to(self._device)
+        bs = static.BuildStrategy()
+        bs.use_cuda_graph = bool(self._config._cuda_graph) and self._device.type == "cuda"
+        self._compiled = static.CompiledProgram(program, bs)
+        self._in_names = list(program._feed_names)
+        self._inputs = {n: _Handle(n) for n in self._in_names}
+        self._fetch = []
+        for s in program._fetch_slots:
+            h = torch.empty(0)
+            program._slot_of_id[id(h)] = s
+            program._keep.append(h)
+            self._fetch.append(h)
+        self._outputs = []
+        return program
+
+    def _run_program(self, inputs):
+        from ..static import graph as g
+        feed = {n: (v if isinstance(v, torch.Tensor) else np.asarray(v)) for n, v in zip(self._in_names, inputs)}
+        with g.suspend():
+            outs = self._compiled._run(feed, self._fetch)
+        self._outputs = []
+        for i, o in enumerate(outs):
+            h = _Handle(f"output_{i}")
+            h._value = o.detach().float().cpu().numpy() if o.dtype == torch.bfloat16 else o.detach().cpu().numpy()
+            self._outputs.append(h)
+        return [h._value for h in self._outputs]
+
     def get_input_names(self):
         return list(self._in_names)
 
@@ -113,6 +156,8 @@ class Predictor:
         from .._core.tensor import as_tensor
         if inputs is None:
             inputs = [self._inputs[n]._value for n in self._in_names if self._inputs[n]._value is not None]
+        if self._program is not None:
+            return self._run_program(inputs)
         tens = [as_tensor(torch.as_tensor(np.asarray(v) if not isinstance(v, torch.Tensor) else v).to(self._device))
                 for v in inputs]
         with torch.no_grad():

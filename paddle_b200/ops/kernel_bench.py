@@ -220,7 +220,7 @@ def bench_decode(args, timer, hbm, tf):
 def bench_moe(args, timer, hbm, tf):
     """Grouped block-scaled fp8 expert GEMM (all experts in one launch) against the per-expert bf16 GEMM loop."""
     from . import native
-    E, M, K_, N = (4, 4096, 2048, 2048) if args.small else (8, 16384, 4096, 28672)
+    E, M, K_, N = (4, 8192, 4096, 8192) if args.small else (8, 16384, 4096, 28672)
     per = M // E
     x = torch.randn(M, K_, device="cuda").to(torch.bfloat16)
     w = (torch.randn(E, K_, N, device="cuda") * 0.02).to(torch.bfloat16)

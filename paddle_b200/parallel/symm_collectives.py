@@ -29,6 +29,7 @@ class SymmCollectives:
         v = self.block.peer_ptrs(self.off_cnt)
         self.p_cnt = U64x8(*(v + [0] * (8 - len(v))))
         self.state = torch.zeros(2, dtype=torch.int32, device=self.block.local.device)
+        self.seen = torch.zeros(nchunks, dtype=torch.int32, device=self.block.local.device)
 
     def _run(self, kind, src, dst, row_bytes):
         assert row_bytes <= self.row_pad, "message larger than the buffer this object was created for"
@@ -36,7 +37,7 @@ class SymmCollectives:
         rc = _lib.kernels().pd_symm_collective(
             c_int(kind), ptr(src), ptr(dst), c_int64(row_bytes), c_int64(self.row_pad),
             c_int(1 if src.dtype == torch.bfloat16 else 0), c_int(self.group.rank), c_int(self.n), self.p_recv, self.p_cnt,
-            ptr(self.state), c_int(WAIT_MS), ptr(_lib.status_buffer(src.device)), stream())
+            ptr(self.state), ptr(self.seen), c_int(WAIT_MS), ptr(_lib.status_buffer(src.device)), stream())
         check(rc, "pd_symm_collective")
         from ..ops import native
         native._count()

@@ -29,7 +29,7 @@ m, v = torch.zeros(shard, device="cuda"), torch.zeros(shard, device="cuda")
 param = master.bfloat16()
 rm, rmm, rv = master.clone(), m.clone(), v.clone()
 lr, b1, b2, eps, wd = 1e-2, 0.9, 0.95, 1e-8, 0.1
-errs = []
+errs, perr = [], []
 for step in range(1, 4):
     grad = torch.randn(n * shard, device="cuda")
     scale = torch.tensor([1.0 / n], device="cuda")
@@ -42,8 +42,10 @@ for step in range(1, 4):
     rv = b2 * rv + (1 - b2) * gg * gg
     rm += -(lr / (1 - b1 ** step)) * rmm / (rv.sqrt() / (1 - b2 ** step) ** 0.5 + eps)
     errs.append(float((master - rm).abs().max()))
-    errs.append(float((param.float() - rm.bfloat16().float()).abs().max()))
+    # the bf16 copy may round a master value that sits on a rounding boundary the other way: allow one bf16 ulp there
+    perr.append(float(((param.float() - rm.bfloat16().float()).abs() / rm.abs().clamp_min(1.0)).max()))
 res["rs_adamw_err"] = max(errs)
+res["rs_adamw_param_ulp_err"] = max(perr)
 torch.cuda.synchronize()
 _lib.check_status()
 

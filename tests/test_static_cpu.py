@@ -156,6 +156,13 @@ def test_save_load_params_and_inference_model(tmp_path):
     assert feed_names == ["x"]
     got2, = exe.run(prog, feed={"x": xb}, fetch_list=fetch_targets)
     np.testing.assert_allclose(got2, want, rtol=1e-6)
+    # the same files serve the inference API
+    from paddle_b200 import inference
+    pred = inference.create_predictor(inference.Config(str(tmp_path / "infer.pdmodel"), str(tmp_path / "infer.pdiparams")))
+    assert pred.get_input_names() == ["x"]
+    pred.get_input_handle("x").copy_from_cpu(xb)
+    pred.run()
+    np.testing.assert_allclose(pred.get_output_handle(pred.get_output_names()[0]).copy_to_cpu(), want, rtol=1e-6)
 
 
 def test_scope_and_ema():
