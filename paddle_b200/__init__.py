@@ -105,6 +105,18 @@ for _n, _v in _extras._make_inplace_table().items():
     if not hasattr(Tensor, _n):
         setattr(Tensor, _n, _v)
 del _n, _v
+# remaining Tensor methods of the reference's tensor_method_func list that exist as functions
+import importlib as _il  # noqa: E402
+_la = _il.import_module(__name__ + ".linalg")
+for _n in ("create_parameter", "histogram_bin_edges", "matrix_transpose", "reduce_as", "multigammaln", "block_diag", "isin",
+           "gammaincc", "gammainc", "reverse", "gammaln", "bitwise_invert", "cumulative_trapezoid", "polar", "i0e", "i1",
+           "i1e", "combinations", "top_p_sampling", "put_along_axis_", "pca_lowrank", "svd_lowrank", "create_tensor"):
+    _v = globals().get(_n) or getattr(_la, _n, None)
+    if _v is None and _n == "create_tensor":
+        _v = lambda self, dtype=None, name=None, persistable=False: zeros([0], dtype or self.dtype)   # noqa: E731
+    if _v is not None and not hasattr(Tensor, _n):
+        setattr(Tensor, _n, _v)
+del _n, _v
 
 
 def is_compiled_with_cuda():

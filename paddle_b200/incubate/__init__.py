@@ -8,7 +8,7 @@ from . import nn  # noqa: F401
 
 def __getattr__(name):
     if name in ("distributed", "optimizer", "autograd", "asp", "tensor", "operators", "framework", "multiprocessing",
-                "passes", "xpu", "jit", "layers"):
+                "passes", "xpu", "jit", "layers", "autotune"):
         return importlib.import_module(f"{__name__}.{name}")
     if name == "inference":
         from .jit import inference

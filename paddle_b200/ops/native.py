@@ -361,7 +361,21 @@ def gemm_splitk(a, b, acc_f32, splits=0, trans_b=False):
     N = b.shape[0] if trans_b else b.shape[1]
     k = _lib.kernels()
     if splits <= 0:
-        splits = k.pd_gemm_suggest_splits(c_int(M), c_int(N), c_int(K))
+        heuristic = k.pd_gemm_suggest_splits(c_int(M), c_int(N), c_int(K))
+        from . import autotune
+        if autotune._cfg["enable"]:
+            def run(c):
+                rc_ = k.pd_gemm_bf16_splitk(ptr(a), ptr(b), ptr(acc_f32), c_int(M), c_int(N), c_int(K),
+                                            c_int(a.stride(0)), c_int(b.stride(0)), c_int(acc_f32.stride(0)), c_int(0),
+                                            c_int(0 if trans_b else 1), c_int(c), ptr(_lib.status_buffer(a.device)), stream())
+                check(rc_, "pd_gemm_bf16_splitk")
+            cands = sorted({1, 2, 3, 4, 6, 8, heuristic} & set(range(1, max(2, K // 256) + 1)))
+            tuned_before = autotune._stats["tuned"]
+            splits = autotune.choose("gemm_splitk", (M, N, K, int(trans_b)), cands, run, heuristic)
+            if autotune._stats["tuned"] != tuned_before:
+                acc_f32.zero_()                    # the timing launches accumulated into it
+        else:
+            splits = heuristic
     rc = k.pd_gemm_bf16_splitk(ptr(a), ptr(b), ptr(acc_f32), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)),
                                c_int(b.stride(0)), c_int(acc_f32.stride(0)), c_int(0), c_int(0 if trans_b else 1),
                                c_int(splits), ptr(_lib.status_buffer(a.device)), stream())

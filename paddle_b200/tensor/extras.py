@@ -280,3 +280,38 @@ class finfo:
 
 
 pstring, raw = "pstring", "raw"
+
+
+def top_p_sampling(x, ps, threshold=None, topp_seed=None, seed=-1, k=0, mode="truncated", return_top=False, name=None):
+    """Nucleus sampling over the last axis of probabilities ``x`` [batch, vocab] with per-row ``ps`` [batch, 1]:
+    returns ``(sampled probability [batch, 1], sampled id [batch, 1])`` (python/paddle/tensor/search.py
+    ``top_p_sampling``)."""
+    import torch
+    from .._core.tensor import as_tensor
+    p = x.as_subclass(torch.Tensor).float()
+    tp = ps.as_subclass(torch.Tensor).float().reshape(-1, 1)
+    sp, si = torch.sort(p, dim=-1, descending=True)
+    cum = torch.cumsum(sp, -1)
+    keep = (cum - sp) < tp                                   # the token that crosses the threshold stays in
+    if k and k > 0:
+        keep[:, k:] = False
+    if threshold is not None:
+        keep &= sp >= threshold.as_subclass(torch.Tensor).float().reshape(-1, 1)
+    keep[:, 0] = True
+    sp = torch.where(keep, sp, torch.zeros_like(sp))
+    g = None
+    if seed is not None and seed >= 0:
+        g = torch.Generator(device=p.device)
+        g.manual_seed(int(seed))
+    pick = torch.multinomial(sp / sp.sum(-1, keepdim=True), 1, generator=g)
+    ids = si.gather(-1, pick)
+    probs = p.gather(-1, ids).to(x.dtype)
+    return as_tensor(probs), as_tensor(ids)
+
+
+def put_along_axis_(arr, indices, values, axis, reduce="assign", include_self=True, broadcast=True):
+    import torch
+    from .manipulation import put_along_axis
+    out = put_along_axis(arr, indices, values, axis, reduce, include_self, broadcast)
+    arr.as_subclass(torch.Tensor).copy_(out.as_subclass(torch.Tensor))
+    return arr

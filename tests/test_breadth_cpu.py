@@ -262,3 +262,31 @@ def test_pass_manager_prunes_static_program():
         np.testing.assert_allclose(out, np.tanh(np.ones((2, 4))), rtol=1e-6)
     finally:
         paddle.disable_static()
+
+
+def test_kernel_autotune_cache():
+    from paddle_b200.incubate import autotune as cfg
+    from paddle_b200.ops import autotune as at
+    at.clear()
+    calls = []
+    cost = {1: 5.0, 2: 3.0, 4: 4.0}
+    timer = lambda fn: (fn(), cost[calls[-1]])[1]          # noqa: E731
+    run = calls.append
+    assert at.choose("k", (8, 8), [1, 2, 4], run, 1, timer) == 1 and not calls       # disabled: heuristic
+    cfg.set_config({"kernel": {"enable": True, "tuning_range": [1, 3]}})
+    assert at.choose("k", (8, 8), [1, 2, 4], run, 1, timer) == 2 and calls == [1, 2, 4]
+    assert at.choose("k", (8, 8), [1, 2, 4], run, 1, timer) == 2 and calls == [1, 2, 4]   # cached
+    for _ in range(5):
+        at.step()
+    assert at.choose("k", (16, 8), [1, 2, 4], run, 4, timer) == 4                     # past the tuning range
+    st = at.status()
+    assert st["cache_size"] == 1 and st["tuned"] == 1 and not st["use_autotune"]
+    import tempfile, os
+    path = os.path.join(tempfile.mkdtemp(), "tune.json")
+    at.save(path)
+    at.clear()
+    assert at.load(path) == 1 and at.choose("k", (8, 8), [1, 2, 4], run, 1, timer) == 2
+    with pytest.raises(TypeError):
+        cfg.set_config({"kernel": {"enable": "yes"}})
+    cfg.set_config({"kernel": {"enable": False}})
+    at.clear()
