@@ -300,8 +300,11 @@ def softmax_cross_entropy(logits, labels, ignore_index=-100):
         if not l2.is_contiguous():
             l2 = l2.contiguous()
         return as_tensor(_SoftmaxCEFn.apply(l2, labels.reshape(-1), ignore_index)).view(lead)
-    return torch.nn.functional.cross_entropy(logits.reshape(-1, V).float(), labels.reshape(-1).long(),
-                                             reduction="none", ignore_index=ignore_index).view(lead)
+    l2 = logits.reshape(-1, V)
+    if l2.dtype != torch.float64:                       # low precision is promoted to fp32, double stays double
+        l2 = l2.float()
+    return torch.nn.functional.cross_entropy(l2, labels.reshape(-1).long(), reduction="none",
+                                             ignore_index=ignore_index).view(lead)
 
 
 # ------------------------------------------------------------------------------------------- embedding
