@@ -8,12 +8,9 @@
 //   warp 4 : TMA producer (Q once, K/V tiles through two 2-stage rings, 128B swizzle)
 //   warp 5 : tcgen05.mma issuer:  S_j = Q K_j^T (SS, both K-major) into a double-buffered TMEM tile,
 //            O += P_j V_j (A = P from TMEM, B = V MN-major from smem)
-//   warps 0-7 : softmax, two warpgroups: thread (row, half) owns 64 of the 128 key columns of one query row
-//            (= one TMEM lane; warps w and w + 4 share a lane quadrant): tcgen05.ld S, row maximum combined
-//            across the two halves through shared memory (one named barrier per tile), exp2 / partial row
-//            sum, lazy rescaling of its 64 columns of the O accumulator, P written back to TMEM as packed
-//            bf16, final O / l through a swizzled staging tile and TMA store.  One warpgroup alone needs about
-//            twice the tensor-core time of a tile for the softmax arithmetic; two bring them level.
+//   warps 0-3 : softmax, one query row per thread (= one TMEM lane): tcgen05.ld S, online max /
+//            exp2 / sum with lazy rescaling of the O accumulator in TMEM, P written back to TMEM as
+//            packed bf16, final O / l through a swizzled staging tile and TMA store.
 // The S_{j+1} GEMM is issued before the softmax of S_j finishes, so tensor cores and the softmax
 // warps overlap.  TMEM columns: S0 0-127, S1 128-255, O 256-383, P0 384-447, P1 448-511.
 #include <math.h>
@@ -28,11 +25,8 @@ constexpr int BQ = 128, BKV = 128, D = 128;
 constexpr int TILE_BYTES = 128 * D * 2;       // 32 KB: two 16 KB swizzled boxes of [128 rows x 64 d]
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int KV_STAGES = 2;
-constexpr int SOFTMAX_THREADS = 256;            // warps 0..7
-constexpr int TMA_WARP = 8, MMA_WARP = 9;
-constexpr int NUM_THREADS = SOFTMAX_THREADS + 64;
-constexpr int XCHG_BYTES = 3 * 2 * 128 * 4;        // row-maximum exchange [tile parity][half][row] + final row sums [half][row]
-constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + XCHG_BYTES + 1024 + 256;
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = TILE_BYTES * (1 + 2 * KV_STAGES) + 1024 + 256;
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
 
 struct Barriers {
@@ -84,8 +78,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sQ = smem;                               // also the output staging tile at the end
   uint8_t* sK = sQ + TILE_BYTES;
   uint8_t* sV = sK + KV_STAGES * TILE_BYTES;
-  float* xchg = reinterpret_cast<float*>(sV + KV_STAGES * TILE_BYTES);
-  Barriers* bars = reinterpret_cast<Barriers*>(sV + KV_STAGES * TILE_BYTES + XCHG_BYTES);
+  Barriers* bars = reinterpret_cast<Barriers*>(sV + KV_STAGES * TILE_BYTES);
   volatile int* abort_flag = &bars->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -109,20 +102,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->p_full[s], SOFTMAX_THREADS);
+      mbar_init(&bars->p_full[s], 128);
     }
     mbar_init(&bars->o_full, 1);
     mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == MMA_WARP) tmem_alloc(&bars->tmem_base, 512);
+  if (warp == 5) tmem_alloc(&bars->tmem_base, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == TMA_WARP) {
+  if (warp == 4) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       prefetch_tmap(&tmQ);
@@ -157,7 +150,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp == MMA_WARP) {
+  } else if (warp == 5) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t idesc_qk = make_idesc(BQ, BKV, false, false);
@@ -207,70 +200,51 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ---------------------------------------------------------------- softmax + epilogue (warps 0..7)
-    const int row = threadIdx.x & 127;           // query row within the tile == TMEM lane
-    const int half = threadIdx.x >> 7;           // which 64 key columns (and which 64 columns of O) this thread owns
+    // ---------------------------------------------------------------- softmax + epilogue (warps 0..3)
+    const int row = threadIdx.x;                 // query row within the tile == TMEM lane
     const int qi = q0 + row;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    float m_used = -INFINITY, l = 0.f;           // l: partial row sum over this thread's columns
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      // A warp whose bounded wait failed keeps iterating without touching TMEM, so that all 256 threads meet at
-      // the exchange barrier of every tile (a hardware barrier has no time limit); its later waits fail at once
-      // because the abort flag is set.
-      if (ok && !warp_mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1, abort_flag, p.status, 300 + (j & 1))) ok = false;
+      if (!warp_mbar_wait(&bars->s_full[j & 1], (j >> 1) & 1, abort_flag, p.status, 300 + (j & 1))) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_tmem = tmem + lane_base + COL_S + (j & 1) * 128 + half * 64;
-      const uint32_t p_tmem = tmem + lane_base + COL_P + (j & 1) * 64 + half * 32;
-      // highest visible key column (local to this thread's 64 columns) for this row
+      const uint32_t s_tmem = tmem + lane_base + COL_S + (j & 1) * 128;
+      const uint32_t p_tmem = tmem + lane_base + COL_P + (j & 1) * 64;
+      // highest visible key column (local to this tile) for this row
       int col_limit = p.Sk - 1 - j * BKV;
       if (p.causal) col_limit = min(col_limit, qi + causal_off - j * BKV);
-      col_limit -= half * 64;
-      const bool need_mask = col_limit < 63;
-      uint32_t r[2][32];
-      if (ok) {
+      const bool need_mask = col_limit < BKV - 1;
+      // one TMEM read of the whole 128-column row: four loads in flight, one wait
+      uint32_t r[4][32];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) tmem_ld_32x32(s_tmem + c * 32, r[c]);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[c][i] = 0xff800000u;
-        }
-      }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_tmem + c * 32, r[c]);
+      tmem_ld_wait();
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             if (c * 32 + i > col_limit) r[c][i] = 0xff800000u;   // -inf: contributes exp2(-inf) = 0
           }
         }
       }
+      // row maximum with eight independent chains
       float mxs[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) mxs[i] = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) mxs[q] = fmaxf(mxs[q], __uint_as_float(r[c][i + q]));
         }
       }
-      float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
-                       fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
-      // combine with the other half of the row (buffers alternate with the tile parity: a thread is never two
-      // barriers behind, so the slot written for tile j + 2 is no longer being read for tile j)
-      float* slot = xchg + (j & 1) * 256;
-      slot[half * 128 + row] = mx;
-      named_bar_sync(2, SOFTMAX_THREADS);
-      mx = fmaxf(mx, slot[(half ^ 1) * 128 + row]);
-      if (!ok) continue;
+      const float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
+                             fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
-      // lazy rescale: only when some row of the warp moved its maximum by more than 2^8 (both halves of a row see
-      // the same maxima, and warps w / w + 4 hold the same rows, so they decide alike)
+      // lazy rescale: only when some row of the warp moved its maximum by more than 2^8
       const bool want = (j == 0) || (m_new - m_used > 8.f);
       const bool warp_want = __any_sync(0xffffffffu, want);
       float factor = 1.f;
@@ -280,9 +254,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_new;
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+      // probabilities -> TMEM (packed bf16), row sum in four independent chains
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -300,17 +275,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_st_wait();
       if (j > 0) {
         // PV_{j-1} must have landed in O before O is rescaled and before PV_j may be issued
-        if (!warp_mbar_wait(&bars->o_full, (j - 1) & 1, abort_flag, p.status, 310)) { ok = false; continue; }
+        if (!warp_mbar_wait(&bars->o_full, (j - 1) & 1, abort_flag, p.status, 310)) { ok = false; break; }
         tc_fence_after();
         if (warp_want) {
 #pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            uint32_t ro[32];
-            tmem_ld_32x32(tmem + lane_base + COL_O + half * 64 + c * 32, ro);
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem + lane_base + COL_O + c * 32, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ro[i] = __float_as_uint(__uint_as_float(ro[i]) * factor);
-            tmem_st_32x32(tmem + lane_base + COL_O + half * 64 + c * 32, ro);
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
+            tmem_st_32x32(tmem + lane_base + COL_O + c * 32, r);
           }
           tmem_st_wait();
         }
@@ -320,43 +295,39 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     // ---- epilogue: O / l -> bf16 -> swizzled staging (reuses the Q tile) -> TMA store; LSE
     if (ok && n_kv > 0) ok = warp_mbar_wait(&bars->o_full, (n_kv - 1) & 1, abort_flag, p.status, 320);
-    // total row sum = the two partial sums (same running maximum on both sides)
-    xchg[512 + half * 128 + row] = l;
-    named_bar_sync(1, SOFTMAX_THREADS);          // also: every softmax warp is past its last S read, the Q tile is free
+    named_bar_sync(1, 128);   // every softmax warp is past its last S read: the Q tile is free
     if (ok) {
       tc_fence_after();
-      const float l_tot = l + xchg[512 + (half ^ 1) * 128 + row];
-      const float inv_l = (l_tot > 0.f) ? 1.f / l_tot : 0.f;
+      const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
       const int sw = row & 7;
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;              // 32-column group of O
-        uint32_t ro[32];
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
         if (n_kv > 0) {
-          tmem_ld_32x32(tmem + lane_base + COL_O + c * 32, ro);
+          tmem_ld_32x32(tmem + lane_base + COL_O + c * 32, r);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ro[i] = 0u;
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
         }
         uint8_t* row_ptr = sQ + (c >> 1) * HALF_BYTES + row * 128;
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
           uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(ro[8 * jj + 0]) * inv_l, __uint_as_float(ro[8 * jj + 1]) * inv_l);
-          v.y = pack_bf16x2(__uint_as_float(ro[8 * jj + 2]) * inv_l, __uint_as_float(ro[8 * jj + 3]) * inv_l);
-          v.z = pack_bf16x2(__uint_as_float(ro[8 * jj + 4]) * inv_l, __uint_as_float(ro[8 * jj + 5]) * inv_l);
-          v.w = pack_bf16x2(__uint_as_float(ro[8 * jj + 6]) * inv_l, __uint_as_float(ro[8 * jj + 7]) * inv_l);
+          v.x = pack_bf16x2(__uint_as_float(r[8 * jj + 0]) * inv_l, __uint_as_float(r[8 * jj + 1]) * inv_l);
+          v.y = pack_bf16x2(__uint_as_float(r[8 * jj + 2]) * inv_l, __uint_as_float(r[8 * jj + 3]) * inv_l);
+          v.z = pack_bf16x2(__uint_as_float(r[8 * jj + 4]) * inv_l, __uint_as_float(r[8 * jj + 5]) * inv_l);
+          v.w = pack_bf16x2(__uint_as_float(r[8 * jj + 6]) * inv_l, __uint_as_float(r[8 * jj + 7]) * inv_l);
           *reinterpret_cast<uint4*>(row_ptr + ((((c & 1) * 4 + jj) ^ sw) << 4)) = v;
         }
       }
-      if (half == 0 && qi < p.Sq && p.lse != nullptr) {
-        const float lse = (l_tot > 0.f) ? (m_used * 0.6931471805599453f + logf(l_tot)) : -INFINITY;
+      if (qi < p.Sq && p.lse != nullptr) {
+        const float lse = (l > 0.f) ? (m_used * 0.6931471805599453f + logf(l)) : -INFINITY;
         p.lse[(static_cast<size_t>(batch) * p.Hq + head) * p.Sq + qi] = lse;
       }
       fence_proxy_async_smem();
     }
-    named_bar_sync(1, SOFTMAX_THREADS);
+    named_bar_sync(1, 128);
     if (ok && threadIdx.x == 0) {
       tma_store_4d(&tmO, sQ, 0, head, q0, batch);
       tma_store_4d(&tmO, sQ + HALF_BYTES, 64, head, q0, batch);
@@ -366,7 +337,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == MMA_WARP) tmem_dealloc(tmem, 512);
+  if (warp == 5) tmem_dealloc(tmem, 512);
 }
 
 // 4-D map over [B, S, H, 128] bf16 with element strides (token, batch); box = {64, 1, 128 rows, 1}

@@ -10,6 +10,7 @@ import paddle_b200.distributed as dist
 from paddle_b200.distributed import fleet
 from paddle_b200.ops import _lib, native
 
+os.environ["PD_AG_COMM_CTAS"] = "8"          # the sweep sets FL.N_COMM itself
 n = int(os.environ["PADDLE_TRAINERS_NUM"])
 strategy = fleet.DistributedStrategy()
 strategy.hybrid_configs = {"dp_degree": 1, "mp_degree": n}

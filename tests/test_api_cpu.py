@@ -168,3 +168,51 @@ def test_flags_and_clip():
     out = clip([(p, p.grad) for p in l.parameters()])
     tot = sum(float((g ** 2).sum()) for _, g in out) ** 0.5
     assert abs(tot - 1.0) < 1e-4
+
+
+def test_tensor_semantics_table():
+    """Paddle-specific conventions of creation, dtype promotion, indexing, autograd switches and persistence."""
+    import os
+    import tempfile
+
+    import numpy as np
+
+    import paddle_b200 as paddle
+    assert paddle.to_tensor(1.5).dtype == paddle.float32 and paddle.to_tensor([1, 2]).dtype == paddle.int64
+    assert paddle.to_tensor(np.ones(2)).dtype == paddle.float64 and paddle.to_tensor([True]).dtype == paddle.bool
+    x = paddle.ones([2, 3])
+    assert x.stop_gradient and x.shape == [2, 3] and isinstance(x.shape, list)
+    assert (paddle.to_tensor([1]) + 1.5).dtype == paddle.float32 and (paddle.to_tensor([3]) / 2).dtype == paddle.float32
+    w = paddle.create_parameter([2], "float32")
+    assert not w.stop_gradient
+    (w * 2).sum().backward()
+    (w * 3).sum().backward()
+    assert np.allclose(w.grad.numpy(), 5)                 # gradients accumulate until cleared
+    w.clear_grad()
+    assert w.grad is None or np.allclose(w.grad.numpy(), 0)
+    a = paddle.arange(12).reshape([3, 4])
+    assert a[..., 1].tolist() == [1, 5, 9] and a[a > 9].tolist() == [10, 11]
+    assert a[[0, 2]].shape == [2, 4] and a[None, 1].shape == [1, 4] and a.T.shape == [4, 3]
+    b = paddle.zeros([3, 4])
+    b[1] = 1.0
+    b[:, 0] = paddle.to_tensor([7.0, 8.0, 9.0])
+    assert b.numpy()[1].tolist() == [8, 1, 1, 1]
+    assert a.ndim == 2 and a.dim() == 2 and int(a.numel()) == 12 and len(a) == 3
+    assert a.astype("float16").dtype == paddle.float16 and paddle.to_tensor(3.5).item() == 3.5
+    g = paddle.grad((w * w).sum(), w)[0]
+    assert np.allclose(g.numpy(), 2 * w.numpy())
+    with paddle.no_grad():
+        assert (w * 2).stop_gradient
+    assert (w * 2).detach().stop_gradient and not (w * 1).clone().stop_gradient
+    d = tempfile.mkdtemp()
+    lin = paddle.nn.Linear(3, 2)
+    paddle.save(lin.state_dict(), os.path.join(d, "m.pdparams"))
+    sd = paddle.load(os.path.join(d, "m.pdparams"))
+    assert set(sd) == {"weight", "bias"} and sd["weight"].shape == [3, 2] and lin.weight.shape == [3, 2]
+    assert paddle.argmax(a, axis=1).tolist() == [3, 3, 3] and paddle.unique(paddle.to_tensor([3, 1, 3, 2])).tolist() == [1, 2, 3]
+    assert paddle.nonzero(paddle.to_tensor([0, 1, 0, 2])).tolist() == [[1], [3]] and paddle.shape(a).tolist() == [3, 4]
+    paddle.seed(1)
+    r1 = paddle.rand([3]).tolist()
+    paddle.seed(1)
+    assert paddle.rand([3]).tolist() == r1
+    assert paddle.matmul(paddle.ones([2, 2], "bfloat16"), paddle.ones([2, 2], "bfloat16")).dtype == paddle.bfloat16
