@@ -190,7 +190,13 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // memory -> the peer's staging buffer (cp.async.bulk store over NVLink).  Many KB stay in flight per CTA
     // without occupying load/store units, so a handful of CTAs saturate the link.
     if (p.skip_push || threadIdx.x != 0) return;
-    constexpr int RING = 12, LOOKAHEAD = 8, PIECE_MAX = 16384, FLAG_LAG = 3;
+    // RING slots of PIECE_MAX bytes.  A slot is in one of two states: loaded and waiting for its store (at most
+    // LOOKAHEAD pieces ahead; local HBM reads are fast, so a few suffice) or stored and still being read by the
+    // copy engine (its bytes are on the wire).  Before piece q + LOOKAHEAD is loaded into the slot that piece
+    // q + LOOKAHEAD - RING used, all but the newest RING - LOOKAHEAD - 1 stores must have finished reading shared
+    // memory; that bound is what the wait below enforces, and it leaves RING - LOOKAHEAD - 1 pieces in flight.
+    constexpr int RING = 12, LOOKAHEAD = 3, PIECE_MAX = 16384, FLAG_LAG = 3;
+    constexpr int STORES_IN_FLIGHT = RING - LOOKAHEAD - 1;
     uint64_t* ring_bar = reinterpret_cast<uint64_t*>(smem + RING * PIECE_MAX);
     for (int i = 0; i < RING; ++i) mbar_init(&ring_bar[i], 1);
     fence_mbar_init();
@@ -228,7 +234,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int pend_q = 0;
     for (int q = 0; q < total && ok; ++q) {
       if (q + LOOKAHEAD < total) {
-        tma_wait_group_read<LOOKAHEAD - 1>();      // the store that last read this slot has drained it
+        tma_wait_group_read<STORES_IN_FLIGHT>();   // the store that last read this slot has drained it
         issue_load(q + LOOKAHEAD);
       }
       int peer, c, row0;
