@@ -170,6 +170,14 @@ class StaticFunction:
 
 def to_static(function=None, input_spec=None, build_strategy=None, backend=None, full_graph=False, **kwargs):
     def decorate(fn):
+        if full_graph:
+            # whole-graph conversion: Python control flow on tensors becomes cond / while_loop nodes of a recorded
+            # static program that is replayed on later calls (dy2static.py)
+            from .dy2static import ProgramFunction
+            if isinstance(fn, Layer):
+                fn.__dict__["forward"] = ProgramFunction(fn.forward, fn)
+                return fn
+            return ProgramFunction(fn)
         if isinstance(fn, Layer):
             layer = fn
             sf = StaticFunction(layer.forward, input_spec, layer=layer)

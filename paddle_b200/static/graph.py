@@ -257,14 +257,15 @@ class Program:
             raise ValueError("fetch target does not belong to this program")
         return s
 
-    def _execute(self, feed, fetch_list):
+    def _execute(self, feed, fetch_list, keep_graph=False):
+        """``keep_graph``: fed tensors stay attached to the caller's autograd graph (dy2static replays)."""
         env = {}
         for name, (slot, example) in self._placeholders.items():
             if name in feed:
                 v = feed[name]
                 t = v.as_subclass(torch.Tensor) if isinstance(v, torch.Tensor) else torch.as_tensor(v)
                 t = t.to(device=example.device, dtype=example.dtype)
-                if example.requires_grad:
+                if example.requires_grad and not keep_graph:
                     t = t.detach().requires_grad_(True)
                 env[slot] = t
         slots = [self._slot_of(v) for v in fetch_list]
