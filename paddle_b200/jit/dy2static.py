@@ -89,6 +89,12 @@ def or_(*thunks):
     return val
 
 
+def range_cond(i, stop, step):
+    """Loop test of a converted ``for .. in range``: a tensor step is assumed positive."""
+    descending = not isinstance(step, torch.Tensor) and step < 0
+    return i > stop if descending else i < stop
+
+
 def not_(x):
     if isinstance(x, torch.Tensor) and _recording():
         import paddle_b200 as paddle
@@ -191,7 +197,7 @@ def _assigned_names(nodes):
         visit_SetComp = visit_DictComp = visit_GeneratorExp = visit_ListComp
     for n in nodes:
         V().visit(n)
-    return [n for n in names if not n.startswith("__jst_")]
+    return [n for n in names if not n.startswith("__jst_") or n.startswith("__jst_i_")]
 
 
 def _has_jump(nodes):
@@ -275,6 +281,35 @@ def __jst_set_{uid}(__jst_v):
         out = self._prelude(names) + [pred, fn(f"__jst_true_{uid}", node.body), fn(f"__jst_false_{uid}", node.orelse)] \
             + self._accessors(uid, names) + [call]
         return [ast.copy_location(n, node) for n in out]
+
+    def visit_For(self, node):
+        """``for i in range(...)`` becomes a counted ``while`` (so that a tensor bound gives a graph loop)."""
+        it = node.iter
+        if not (isinstance(it, ast.Call) and isinstance(it.func, ast.Name) and it.func.id == "range" and not it.keywords
+                and 1 <= len(it.args) <= 3 and isinstance(node.target, ast.Name) and not node.orelse
+                and not _has_jump(node.body)):
+            self.generic_visit(node)
+            return node
+        uid = self._uid()
+        a = it.args
+        start = a[0] if len(a) >= 2 else ast.Constant(value=0)
+        stop = a[1] if len(a) >= 2 else a[0]
+        step = a[2] if len(a) == 3 else ast.Constant(value=1)
+        c, e, st = f"__jst_i_{uid}", f"__jst_stop_{uid}", f"__jst_step_{uid}"
+        init = [ast.Assign(targets=[ast.Name(id=c, ctx=ast.Store())], value=start),
+                ast.Assign(targets=[ast.Name(id=e, ctx=ast.Store())], value=stop),
+                ast.Assign(targets=[ast.Name(id=st, ctx=ast.Store())], value=step)]
+        loop = _parse_stmt(f"while _jst.range_cond({c}, {e}, {st}):\n    {node.target.id} = {c}\n    {c} = {c} + {st}")[0]
+        loop.body = [loop.body[0]] + node.body + [loop.body[1]]
+        out = init + [loop]
+        out = [ast.copy_location(n, node) for n in out]
+        for n in out:
+            ast.fix_missing_locations(n)
+        res = []
+        for n in out:
+            r = self.visit(n)
+            res.extend(r if isinstance(r, list) else [r])
+        return res
 
     def visit_While(self, node):
         self.generic_visit(node)

@@ -120,3 +120,18 @@ def test_python_conditions_keep_python_semantics():
     x = paddle.to_tensor([1.0])
     assert float(sf(x, True)) == 16.0 and float(sf(x, False)) == 0.0
     assert len(sf._programs) == 2                      # Python values are part of the signature
+
+
+def test_for_range_with_tensor_bound():
+    def f(x, n):
+        acc = paddle.zeros([1])
+        for i in range(n):
+            acc = acc + x * (i + 1)
+        return acc
+    sf = paddle.jit.to_static(f, full_graph=True)
+    x = paddle.to_tensor([3.0])
+    for n in (0, 2, 4):
+        nt = paddle.to_tensor([n], dtype="int64")
+        assert float(sf(x, nt)) == 3.0 * sum(range(1, n + 1))
+    assert len(sf._programs) == 1
+    assert float(sf(x, 3)) == 18.0 and float(f(x, 3)) == 18.0         # Python bound: unrolled at trace time
