@@ -17,8 +17,35 @@ def free_port():
         return s.getsockname()[1]
 
 
-def run_workers(script, nranks, backend="gloo", extra_env=None, timeout=240, args=(), gpus=False):
-    port = free_port()
+def free_port_block(n):
+    """First port of ``n`` consecutive ports that are all free right now."""
+    for _ in range(50):
+        p = free_port()
+        ok = True
+        for i in range(1, n):
+            with socket.socket() as s:
+                try:
+                    s.bind(("127.0.0.1", p + i))
+                except OSError:
+                    ok = False
+                    break
+        if ok:
+            return p
+    return free_port()
+
+
+def run_workers(script, nranks, backend="gloo", extra_env=None, timeout=240, args=(), gpus=False, _retry=True):
+    try:
+        return _run_workers(script, nranks, backend, extra_env, timeout, args, gpus)
+    except AssertionError as e:
+        # another process can grab a rendezvous port between the probe and the workers' bind: try once more
+        if _retry and ("ddress already in use" in str(e) or "EADDRINUSE" in str(e)):
+            return _run_workers(script, nranks, backend, extra_env, timeout, args, gpus)
+        raise
+
+
+def _run_workers(script, nranks, backend, extra_env, timeout, args, gpus):
+    port = free_port_block(nranks)
     eps = ",".join(f"127.0.0.1:{port + i}" for i in range(nranks))
     out = os.path.join(tempfile.mkdtemp(prefix="pdtest_"), "out")
     procs = []

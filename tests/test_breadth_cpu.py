@@ -190,7 +190,8 @@ def _rpc_worker(rank, port, q):
 def test_rpc_two_workers():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29000 + os.getpid() % 900
+    from dist_utils import free_port
+    port = free_port()
     ps = [ctx.Process(target=_rpc_worker, args=(r, port, q)) for r in range(2)]
     [p.start() for p in ps]
     [p.join(90) for p in ps]
