@@ -88,3 +88,27 @@ def test_reshard_planner():
     assert plan([0], [1]) == [(5, 0, 1)]                  # s -> s : all_to_all
     assert plan([0, -2], [-1, -1]) == [(2, 1, -1), (1, 0, 0)]
     assert rt.pd_comm_static_check(1, 8, 16, 0, 2, 0) == 0 and rt.pd_comm_static_check(1, 8, 8, 0, 2, 0) == 3
+
+
+def test_push_cta_count_rule(monkeypatch):
+    """Number of communication CTAs of the all-gather GEMM: a per-degree base, plus SMs the GEMM's last wave leaves
+    idle, never more than there are push jobs, none for a launch that does not push; the environment overrides."""
+    import os
+
+    from paddle_b200.parallel import fused_linear_impl as FL
+    monkeypatch.setattr(FL, "_sms", lambda: 148)
+    monkeypatch.delenv("PD_AG_COMM_CTAS", raising=False)
+    assert FL._comm_ctas(8, 96, 28, True) == 28            # qkv at TP8: one wave of 96 tiles, 52 SMs idle, 28 jobs
+    assert FL._comm_ctas(8, 352, 28, True) == 28           # gate_up at TP8: 3 waves of <= 118
+    assert FL._comm_ctas(4, 192, 24, True) == 24
+    assert FL._comm_ctas(2, 768, 16, True) == 8            # two ranks keep the measured setting
+    assert FL._comm_ctas(8, 96, 28, False) == 0
+    c = FL._comm_ctas(8, 5000, 28, True)                   # a large GEMM: base plus what keeps the wave count (41)
+    assert c == 26 and -(-5000 // (148 - c)) == -(-5000 // (148 - 24))
+    for n, tiles, jobs in [(8, 96, 28), (8, 352, 28), (4, 704, 24), (2, 768, 16), (8, 1, 4)]:
+        c = FL._comm_ctas(n, tiles, jobs, True)
+        assert 1 <= c <= max(jobs, 1) or c == FL._COMM_BASE[n]
+        assert 148 - c >= 1
+    monkeypatch.setenv("PD_AG_COMM_CTAS", "8")
+    monkeypatch.setattr(FL, "N_COMM", 8)
+    assert FL._comm_ctas(8, 96, 28, True) == 8
