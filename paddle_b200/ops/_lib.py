@@ -59,7 +59,13 @@ def runtime() -> ctypes.CDLL:
     if _runtime is None:
         with _lock:
             if _runtime is None:
-                _runtime = _load("libpd_runtime.so", "build_runtime")
+                san = os.environ.get("PD_RUNTIME_SANITIZER")
+                if san:
+                    from . import build as _build
+                    _build.build_runtime(sanitize=san)
+                    _runtime = _load(f"libpd_runtime_{san}.so", "build_runtime")
+                else:
+                    _runtime = _load("libpd_runtime.so", "build_runtime")
     return _runtime
 
 

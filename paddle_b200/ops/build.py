@@ -87,34 +87,64 @@ def build_kernels(verbose: bool = False, force: bool = False) -> str:
     return out
 
 
-def build_runtime(verbose: bool = False, force: bool = False) -> str:
-    """Compile ``csrc/runtime/*.cc`` into ``libpd_runtime.so`` (host-only C++)."""
+def build_runtime(verbose: bool = False, force: bool = False, sanitize: str | None = None) -> str:
+    """Compile ``csrc/runtime/*.cc`` into ``libpd_runtime.so`` (host-only C++).  ``sanitize`` = ``"address"`` or
+    ``"thread"`` builds ``libpd_runtime_<sanitize>.so`` with that sanitizer (the reference's ``-DSANITIZER_TYPE``
+    builds, CMakeLists.txt:311-378); it is loaded when ``PD_RUNTIME_SANITIZER`` names it and the sanitizer run-time
+    is preloaded into the interpreter."""
+    if sanitize not in (None, "address", "thread", "undefined"):
+        raise ValueError("sanitize must be 'address', 'thread' or 'undefined'")
     rdir = os.path.join(CSRC, "runtime")
     os.makedirs(OBJ_DIR, exist_ok=True)
-    out = os.path.join(LIB_DIR, "libpd_runtime.so")
+    tag = f"_{sanitize}" if sanitize else ""
+    out = os.path.join(LIB_DIR, f"libpd_runtime{tag}.so")
     srcs = sorted(f for f in os.listdir(rdir) if f.endswith(".cc"))
     if not srcs:
         return ""
     hdr_t = _newest_header(rdir)
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    if sanitize:
+        cxx = _sanitizer_toolchain(sanitize)[0]
+        if cxx is None:
+            raise RuntimeError(f"no installed compiler ships the {sanitize} sanitizer run-time")
+    san = [f"-fsanitize={sanitize}", "-g", "-O1", "-fno-omit-frame-pointer"] if sanitize else []
+    flags = [f for f in CXX_FLAGS if not (sanitize and f.startswith("-O"))] + san
     jobs, objs = [], []
     for s in srcs:
         src = os.path.join(rdir, s)
-        obj = os.path.join(OBJ_DIR, "rt_" + s[:-3] + ".o")
+        obj = os.path.join(OBJ_DIR, f"rt{tag}_" + s[:-3] + ".o")
         objs.append(obj)
         if (not force and os.path.exists(obj)
                 and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_t)):
             continue
-        jobs.append(([cxx, *CXX_FLAGS, "-I", rdir, "-c", src, "-o", obj], src, obj, obj + ".log"))
+        jobs.append(([cxx, *flags, "-I", rdir, "-c", src, "-o", obj], src, obj, obj + ".log"))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             for fut in [ex.submit(_compile_one, *j) for j in jobs]:
                 fut.result()
     if jobs or not os.path.exists(out):
-        p = subprocess.run([cxx, "-shared", "-o", out, *objs, "-pthread"], capture_output=True, text=True)
+        p = subprocess.run([cxx, "-shared", "-o", out, *objs, "-pthread", *san[:1]], capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError("link failed:\n" + p.stdout + p.stderr)
     return out
+
+
+def _sanitizer_toolchain(sanitize: str):
+    """(compiler, path of its sanitizer run-time): the first of $CXX, g++ on PATH, /usr/bin/g++ that ships one."""
+    name = {"address": "libasan.so", "thread": "libtsan.so", "undefined": "libubsan.so"}[sanitize]
+    for cxx in (os.environ.get("CXX"), shutil.which("g++"), "/usr/bin/g++", shutil.which("gcc")):
+        if not cxx or not os.path.exists(cxx):
+            continue
+        p = subprocess.run([cxx, f"-print-file-name={name}"], capture_output=True, text=True).stdout.strip()
+        if os.path.isabs(p) and os.path.exists(p):
+            return cxx, os.path.realpath(p)
+    return None, ""
+
+
+def sanitizer_runtime_library(sanitize: str) -> str:
+    """Path of the sanitizer run-time to put in ``LD_PRELOAD`` of a process that loads the sanitized runtime into
+    an unsanitized interpreter ("" when no installed compiler ships it)."""
+    return _sanitizer_toolchain(sanitize)[1]
 
 
 def build_all(verbose: bool = False, force: bool = False):

@@ -91,6 +91,23 @@ for dtype, numel in ((torch.float32, 1000), (torch.bfloat16, 70001 * 2), (torch.
         dist.reduce_scatter(rs_ref, list(x.chunk(n)), group=g)
         errs.append(float((sc.reduce_scatter(x).float() - rs_ref.float()).abs().max() / rs_ref.float().abs().max()))
 res["symm_coll_err"] = max(errs)
+# poisoned receive buffers: every byte a collective reads must have been written by a peer in THIS call, so filling
+# both receive slots with NaN beforehand may not change any result (a read-before-arrival would surface as NaN)
+poison_bad = 0
+for it in range(4):
+    dist.barrier(group=g)
+    torch.cuda.synchronize()
+    sc.block.local[:sc.off_cnt].view(torch.float32).fill_(float("nan"))
+    torch.cuda.synchronize()
+    dist.barrier(group=g)
+    x = torch.randn(3 * 8192 + 100, device="cuda")
+    ref = x.clone()
+    dist.all_reduce(ref, group=g)
+    got = sc.all_reduce(x)
+    poison_bad += int(torch.isnan(got).any()) + int((got - ref).abs().max() > 1e-4 * ref.abs().max())
+    gat = sc.all_gather(x)
+    poison_bad += int(torch.isnan(gat).any())
+res["symm_coll_poisoned_bad"] = poison_bad
 xs = torch.randn(4096, device="cuda")
 outg = torch.empty_like(xs)
 side = torch.cuda.Stream()

@@ -112,3 +112,28 @@ def test_push_cta_count_rule(monkeypatch):
     monkeypatch.setenv("PD_AG_COMM_CTAS", "8")
     monkeypatch.setattr(FL, "N_COMM", 8)
     assert FL._comm_ctas(8, 96, 28, True) == 8
+
+
+@pytest.mark.parametrize("sanitizer", ["address", "thread"])
+def test_runtime_under_sanitizer(sanitizer):
+    """The C++ host runtime (TCP store with its server / waiter threads, watchdog, bucket assignment, reshard
+    planner) rebuilt with AddressSanitizer / ThreadSanitizer passes the same tests with no report."""
+    import os
+    import subprocess
+    import sys
+
+    from paddle_b200.ops import build
+    lib = build.sanitizer_runtime_library(sanitizer)
+    if not lib:
+        pytest.skip(f"no compiler with the {sanitizer} sanitizer run-time is installed")
+    build.build_runtime(sanitize=sanitizer)
+    env = dict(os.environ, PD_RUNTIME_SANITIZER=sanitizer, LD_PRELOAD=lib, CUDA_VISIBLE_DEVICES="",
+               ASAN_OPTIONS="detect_leaks=0:abort_on_error=0:exitcode=23",
+               TSAN_OPTIONS="exitcode=23:report_signal_unsafe=0")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-p", "no:cacheprovider",
+                        os.path.join(root, "tests", "test_runtime_cpu.py"), "-k",
+                        "tcp_store or assign_group or watchdog or reshard_planner"],
+                       env=env, cwd=root, capture_output=True, text=True, timeout=600)
+    report = [l for l in (p.stdout + p.stderr).splitlines() if "Sanitizer" in l and ("ERROR" in l or "WARNING" in l)]
+    assert p.returncode == 0 and not report, (p.stdout[-1500:], p.stderr[-1500:])
