@@ -38,6 +38,9 @@ def __getattr__(name):
     if name in ("recompute", "recompute_hybrid", "recompute_sequential"):
         from . import recompute as r
         return getattr(r, name) if name != "recompute" else r
+    if name == "metrics":
+        import importlib
+        return importlib.import_module(__name__ + ".metrics")
     if name == "auto":
         from .. import auto_parallel
         return auto_parallel

@@ -291,3 +291,13 @@ def test_kernel_autotune_cache():
         cfg.set_config({"kernel": {"enable": "yes"}})
     cfg.set_config({"kernel": {"enable": False}})
     at.clear()
+
+
+def test_fleet_metrics_single_worker():
+    from paddle_b200.distributed import fleet
+    m = fleet.metrics
+    assert m.sum(np.array([1.0, 2.0])).tolist() == [1.0, 2.0] and m.acc(np.array([3.0]), np.array([4.0])) == 0.75
+    assert m.rmse(np.array([8.0]), np.array([2.0])) == 2.0 and m.mae(np.array([3.0]), np.array([6.0])) == 0.5
+    # 4 positives (one in the middle bucket, three in the top one), 4 negatives (three at the bottom, one in the
+    # middle): 15.5 of 16 ordered pairs are ranked correctly (a tie counts one half)
+    assert m.auc(np.array([0, 1, 3.0]), np.array([3, 1, 0.0])) == pytest.approx(15.5 / 16)
