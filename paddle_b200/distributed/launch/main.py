@@ -209,6 +209,14 @@ class CollectiveController:
             time.sleep(self.args.poll_interval)
 
     def run(self):
+        from .watcher import Watcher
+        watcher = Watcher(self.args.log_dir, interval=getattr(self.args, "gpu_watch_interval", 30.0)).start()
+        try:
+            return self._run()
+        finally:
+            watcher.stop()
+
+    def _run(self):
         a = self.args
         while True:
             self.build_pod()

@@ -163,3 +163,20 @@ def test_pipeline_schedules_are_deadlock_free_and_have_the_expected_bubble():
         S.validate(broken, 2, 1, 1)
     with pytest.raises(ValueError):
         S.interleaved_1f1b(4, 2, 6, 0)
+
+
+def test_launcher_gpu_watcher_writes_samples(tmp_path):
+    import time
+
+    from paddle_b200.distributed.launch.watcher import Watcher
+    fake = lambda: [{"index": "0", "utilization.gpu": "97", "memory.used": "1000"},       # noqa: E731
+                    {"index": "1", "utilization.gpu": "3", "memory.used": "10"}]
+    w = Watcher(str(tmp_path), interval=0.05, sampler=fake, devices=[0]).start()
+    time.sleep(0.3)
+    w.stop()
+    lines = (tmp_path / "gpu.log").read_text().strip().splitlines()
+    assert w.samples >= 2 and len(lines) == w.samples and all("index=0 utilization.gpu=97" in l for l in lines)
+    silent = Watcher(str(tmp_path / "none"), interval=0.05, sampler=lambda: []).start()
+    time.sleep(0.15)
+    silent.stop()
+    assert not (tmp_path / "none" / "gpu.log").exists()
