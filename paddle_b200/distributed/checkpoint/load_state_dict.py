@@ -25,6 +25,27 @@ class ReadItem:
     lengths: tuple
 
 
+class CheckpointCorruptError(RuntimeError):
+    """A checkpoint shard does not match the checksum written next to it, or cannot be decoded."""
+
+
+def _load_verified(fn):
+    side = fn + ".crc"
+    if os.path.exists(side):
+        from .save_state_dict import file_crc32
+        want_crc, want_size = open(side).read().split()
+        crc, size = file_crc32(fn)
+        if size != int(want_size) or crc != int(want_crc, 16):
+            raise CheckpointCorruptError(
+                f"checkpoint shard {fn} is corrupt: size {size} / crc {crc:08x}, expected {want_size} / {want_crc}")
+    try:
+        return _load(fn)
+    except CheckpointCorruptError:
+        raise
+    except Exception as e:  # noqa: BLE001 - any decoding failure of a shard is a corrupt checkpoint
+        raise CheckpointCorruptError(f"checkpoint shard {fn} cannot be decoded: {type(e).__name__}: {e}") from e
+
+
 def compute_overlap(cur_offset, cur_shape, src_offset, src_shape):
     cur_off, src_off, lengths = [], [], []
     for co, cs, so, ss in zip(cur_offset, cur_shape, src_offset, src_shape):
@@ -78,7 +99,7 @@ def load_state_dict(state_dict, path, process_group=None, coordinator_rank=0, un
     with torch.no_grad():
         for it in items:
             if it.file_name not in cache:
-                cache[it.file_name] = _load(os.path.join(path, it.file_name))
+                cache[it.file_name] = _load_verified(os.path.join(path, it.file_name))
             src = cache[it.file_name][it.tensor_key].as_subclass(torch.Tensor)
             dst = describe(flat[it.tensor_key])[0]
             s_idx = tuple(slice(o, o + n) for o, n in zip(it.storage_offset, it.lengths))
@@ -91,7 +112,7 @@ def load_state_dict(state_dict, path, process_group=None, coordinator_rank=0, un
                 from .metadata import LocalTensorIndex
                 fn = md.storage_metadata[LocalTensorIndex(key, ())]
                 if fn not in cache:
-                    cache[fn] = _load(os.path.join(path, fn))
+                    cache[fn] = _load_verified(os.path.join(path, fn))
                 _assign(state_dict, md.flat_mapping.get(key, (key,)), cache[fn][key])
     if C.is_initialized() and C.get_world_size() > 1:
         C.barrier(process_group)
@@ -119,7 +140,7 @@ def load_merged_state_dict(path, prefix=None, unique_id=None, offload=False):
             for c in chunks:
                 fn = md.storage_metadata[LocalTensorIndex(key, tuple(c.global_offset))]
                 if fn not in cache:
-                    cache[fn] = _load(os.path.join(path, fn))
+                    cache[fn] = _load_verified(os.path.join(path, fn))
                 src = cache[fn][key].as_subclass(torch.Tensor)
                 if full is None:
                     full = torch.zeros(gshape, dtype=src.dtype)

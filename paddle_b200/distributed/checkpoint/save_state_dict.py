@@ -25,8 +25,23 @@ def _unique_id(path):
     return max(ids) + 1 if ids else 0
 
 
+def file_crc32(fn):
+    import zlib
+    crc, size = 0, 0
+    with open(fn, "rb") as f:
+        for chunk in iter(lambda: f.read(1 << 22), b""):
+            crc = zlib.crc32(chunk, crc)
+            size += len(chunk)
+    return crc & 0xFFFFFFFF, size
+
+
 def _write(obj, fn):
+    """Writes the shard, then a ``<shard>.crc`` side file (``crc32 size``) that the loader checks: a truncated or
+    bit-flipped shard is reported by name instead of surfacing as a wrong tensor or an unpickling error."""
     _save(obj, fn)
+    crc, size = file_crc32(fn)
+    with open(fn + ".crc", "w") as f:
+        f.write(f"{crc:08x} {size}\n")
 
 
 def save_state_dict(state_dict, path, process_group=None, coordinator_rank=0, unique_id=None, async_save=False):

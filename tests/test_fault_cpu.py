@@ -180,3 +180,30 @@ def test_launcher_gpu_watcher_writes_samples(tmp_path):
     time.sleep(0.15)
     silent.stop()
     assert not (tmp_path / "none" / "gpu.log").exists()
+
+
+def test_corrupt_checkpoint_shard_is_reported_by_name(tmp_path):
+    """Host-injected failure: a bit flip and a truncation in a distributed-checkpoint shard are detected at load."""
+    import numpy as np
+    import pytest
+
+    import paddle_b200 as paddle
+    from paddle_b200.distributed import checkpoint as ckpt
+    sd = {"w": paddle.to_tensor(np.arange(4096, dtype="float32")), "step": 7}
+    ckpt.save_state_dict(sd, str(tmp_path))
+    shard = next(p for p in tmp_path.iterdir() if p.name.endswith(".distcp"))
+    assert (tmp_path / (shard.name + ".crc")).exists()
+    fresh = {"w": paddle.zeros([4096]), "step": 0}
+    ckpt.load_state_dict(fresh, str(tmp_path))
+    assert fresh["step"] == 7 and float(fresh["w"][100]) == 100.0
+    raw = bytearray(shard.read_bytes())
+    raw[len(raw) // 2] ^= 0x40
+    shard.write_bytes(bytes(raw))
+    with pytest.raises(ckpt.CheckpointCorruptError, match=shard.name):
+        ckpt.load_state_dict({"w": paddle.zeros([4096]), "step": 0}, str(tmp_path))
+    shard.write_bytes(bytes(raw[:100]))
+    with pytest.raises(ckpt.CheckpointCorruptError, match="corrupt"):
+        ckpt.load_state_dict({"w": paddle.zeros([4096]), "step": 0}, str(tmp_path))
+    (tmp_path / (shard.name + ".crc")).unlink()                 # without the side file the decoder still reports it
+    with pytest.raises(ckpt.CheckpointCorruptError, match="cannot be decoded"):
+        ckpt.load_state_dict({"w": paddle.zeros([4096]), "step": 0}, str(tmp_path))
