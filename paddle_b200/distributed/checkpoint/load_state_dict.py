@@ -61,7 +61,7 @@ def _metadata_files(path, unique_id=None):
     if unique_id is not None:
         files = [f for f in files if f == f"{unique_id}.metadata"]
     assert files, f"no .metadata file under {path}"
-    return [_load(os.path.join(path, f)) for f in files]
+    return [_load_verified(os.path.join(path, f)) for f in files]
 
 
 def get_read_items(path, flat, metas):

@@ -85,7 +85,7 @@ def test_auto_parallel_reshard_spmd_checkpoint_cpu():
         assert np.allclose(r["plan_losses"][0], r["plan_losses"][1], atol=1e-6)
         assert r["plan_w"] < 1e-6 and r["opt_state_dist"] == 8
         assert [f for f in r["ckpt_files"] if not f.endswith(".crc")] == ["0.metadata", "0_0.distcp", "1_0.distcp"]
-        assert [f for f in r["ckpt_files"] if f.endswith(".crc")] == ["0_0.distcp.crc", "1_0.distcp.crc"]
+        assert [f for f in r["ckpt_files"] if f.endswith(".crc")] == ["0.metadata.crc", "0_0.distcp.crc", "1_0.distcp.crc"]
         assert r["ckpt_meta"] == ("paddle.distributed.checkpoint.metadata", ["opt.m", "w"], 2, 1, ("opt", "m"))
 
 
