@@ -122,3 +122,25 @@ class ParallelCrossEntropy(Layer):
     def forward(self, input, label):
         return mp_ops._c_softmax_with_cross_entropy(input, label, group=self.model_parallel_group,
                                                     ignore_index=self.ignore_index)
+
+
+class MPScale(torch.autograd.Function):
+    """Forward divides by the tensor-parallel degree, backward passes the gradient through (mp_layers.py ``MPScale``)."""
+
+    @staticmethod
+    def forward(ctx, x, mp_degree):
+        return x / mp_degree
+
+    @staticmethod
+    def backward(ctx, dout):
+        return dout, None
+
+
+def is_fused_matmul_bias_supported():
+    """The bias add is an epilogue of this framework's GEMM kernel whenever the GPU library is loaded."""
+    return torch.cuda.is_available()
+
+
+def is_fused_linear_param_grad_add_supported():
+    """Weight gradients are accumulated into fp32 ``main_grad`` by the GEMM epilogue on GPU."""
+    return torch.cuda.is_available()

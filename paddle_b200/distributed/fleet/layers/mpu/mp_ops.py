@@ -186,3 +186,10 @@ def split(x, size, operation, axis=0, num_partitions=1, gather_out=True, weight_
         return ColumnParallelLinear(size[0], size[1], weight_attr=weight_attr, has_bias=bias_attr is not False,
                                     gather_output=gather_out)(x)
     raise ValueError(f"unknown operation {operation}")
+
+
+# eager-mode names of the reference (mp_ops.py ``c_identity_eager`` ...): the autograd functions themselves
+c_identity_eager = _CIdentity
+mp_allreduce_eager = _MpAllReduce
+c_split_eager = _CSplit
+c_concat_eager = _CConcat

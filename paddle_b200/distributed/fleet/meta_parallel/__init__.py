@@ -70,6 +70,9 @@ def __getattr__(name):
                 "PipelineParallelWithInterleaveWindowed"):
         from . import pipeline_parallel as pp
         return getattr(pp, name)
+    if name in ("RNGStatesTracker", "get_rng_state_tracker", "model_parallel_random_seed"):
+        from ..layers.mpu import random as _r
+        return getattr(_r, name)
     if name in ("LayerDesc", "SharedLayerDesc", "PipelineLayer", "SegmentLayers"):
         from .parallel_layers import pp_layers
         return getattr(pp_layers, name)

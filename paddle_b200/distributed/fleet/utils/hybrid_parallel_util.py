@@ -93,3 +93,32 @@ def fused_allreduce_gradients(parameter_list, hcg):
 def sharding_reduce_gradients(parameter_list, hcg):
     g = hcg.get_sharding_parallel_group()
     fused_allreduce_gradients_with_group(parameter_list, g)
+
+
+def obtain_optimizer_parameters_list(optimizer):
+    """Flat parameter list of an optimizer, whether it was built from tensors or from parameter groups."""
+    plist = getattr(optimizer, "_parameter_list", None) or []
+    out = []
+    for p in plist:
+        if isinstance(p, dict):
+            out.extend(p["params"])
+        else:
+            out.append(p)
+    return out
+
+
+def unwrap_optimizer(optimizer, optimizer_instances=()):
+    """Peels wrapper optimizers (``_inner_opt`` / ``_optim`` / ``_optimizer``) until an instance of
+    ``optimizer_instances`` (or the innermost optimizer) is reached."""
+    cur = optimizer
+    while True:
+        if optimizer_instances and isinstance(cur, tuple(optimizer_instances)):
+            return cur
+        nxt = None
+        for attr in ("_inner_opt", "_optim", "_optimizer", "_inner_optimizer"):
+            nxt = cur.__dict__.get(attr) if hasattr(cur, "__dict__") else None
+            if nxt is not None:
+                break
+        if nxt is None:
+            return cur
+        cur = nxt

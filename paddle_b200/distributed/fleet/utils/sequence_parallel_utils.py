@@ -236,3 +236,55 @@ class RowSequenceParallelLinear(Layer):
 
 
 SPInnerOverlapLinear = ColumnSequenceParallelLinear
+
+
+from ..layers.mpu.mp_layers import (MPScale, is_fused_linear_param_grad_add_supported,  # noqa: E402,F401
+                                    is_fused_matmul_bias_supported)
+
+
+def create_non_fused_allreduce_gradient_hook(param, accumulation_steps):
+    """Hook that all-reduces ``param``'s gradient over the mp group every ``accumulation_steps`` calls."""
+    g = _group()
+    state = {"step": 0}
+
+    def hook(*_):
+        state["step"] += 1
+        if state["step"] % accumulation_steps == 0 and g is not None and g.nranks > 1:
+            mg = getattr(param, "main_grad", None)
+            gr = mg if mg is not None else torch.Tensor.grad.__get__(param)
+            if gr is not None:
+                C.all_reduce(gr, group=g)
+    return hook
+
+
+def create_fused_allreduce_gradient_hook(parameter_list, accumulation_steps):
+    """One hook shared by ``parameter_list``: when all of them have seen ``accumulation_steps`` backward passes their
+    gradients are all-reduced over the mp group in one flattened buffer per dtype."""
+    g = _group()
+    params = list(parameter_list)
+    state = {"step": 0, "total": len(params) * accumulation_steps}
+
+    def hook(*_):
+        state["step"] += 1
+        if state["step"] < state["total"]:
+            return
+        state["step"] = 0
+        if g is None or g.nranks == 1:
+            return
+        grads = []
+        for p in params:
+            mg = getattr(p, "main_grad", None)
+            gr = mg if mg is not None else torch.Tensor.grad.__get__(p)
+            if gr is not None:
+                grads.append(gr)
+        by_dtype = {}
+        for gr in grads:
+            by_dtype.setdefault(gr.dtype, []).append(gr)
+        for gs in by_dtype.values():
+            flat = torch.cat([x.reshape(-1) for x in gs])
+            C.all_reduce(flat, group=g)
+            off = 0
+            for x in gs:
+                x.copy_(flat[off:off + x.numel()].view_as(x))
+                off += x.numel()
+    return hook
