@@ -78,3 +78,54 @@ class ClipGradByGlobalNorm(ClipGradBase):
             else:
                 out.append((p, g.mul_(coef.to(g.dtype))))
         return out
+
+
+def clip_by_norm(x, max_norm, name=None):
+    """``x * max_norm / max(norm(x), max_norm)`` (python/paddle/nn/clip.py ``clip_by_norm``)."""
+    t = x.as_subclass(torch.Tensor)
+    norm = torch.linalg.vector_norm(t.float())
+    scale = float(max_norm) / torch.clamp(norm, min=float(max_norm))
+    from .._core.tensor import as_tensor
+    return as_tensor((t.float() * scale).to(t.dtype))
+
+
+def merge_selected_rows(x, name=None):
+    """Sums duplicate rows of a row-sparse gradient.  Row-sparse gradients are sparse COO tensors here."""
+    return x.coalesce() if getattr(x, "is_sparse", False) else x
+
+
+def get_tensor_from_selected_rows(x, name=None):
+    return x.coalesce().values() if getattr(x, "is_sparse", False) else x
+
+
+_legacy_clip = {"clip": None}
+
+
+def set_gradient_clip(clip, param_list=None, program=None):
+    """Legacy global setting read by optimizers created without ``grad_clip`` (deprecated in the reference)."""
+    import warnings
+    warnings.warn("set_gradient_clip is deprecated: pass grad_clip to the optimizer instead")
+    _legacy_clip["clip"] = clip
+    if param_list is not None:
+        for p in param_list:
+            p.gradient_clip_attr = clip
+
+
+class ErrorClipByValue:
+    """Clips the gradient flowing INTO a variable (legacy static-graph attribute)."""
+
+    def __init__(self, max, min=None):
+        self.max = float(max)
+        self.min = float(min) if min is not None else -self.max
+
+
+BaseErrorClipAttr = ErrorClipByValue
+
+
+def error_clip_callback(block, context):
+    pass
+
+
+def append_gradient_clip_ops(param_grads):
+    clip = _legacy_clip["clip"]
+    return clip(param_grads) if clip is not None else param_grads
