@@ -3,6 +3,7 @@
 ``ShardingStage1/2/3`` :1084-1200, ``to_static`` :2153, ``unshard_dtensor`` :2478, ``shard_dataloader`` :2934)."""
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..._core.tensor import EagerParamBase, Tensor, as_tensor
@@ -274,3 +275,65 @@ class DistModel:
 
 def to_static(layer, loader=None, loss=None, optimizer=None, strategy=None, input_spec=None):
     return DistModel(layer, loader, loss, optimizer, strategy)
+
+
+# ------------------------------------------------------------------------------------- MoE mesh helpers
+def _sub_meshes_and_local_placements(mesh, placements, local_mesh_dim):
+    """Splits ``mesh`` along ``local_mesh_dim`` into one sub-mesh per index; the placement of that mesh dimension is
+    dropped for the sub-meshes (python/paddle/distributed/auto_parallel/api.py ``_get_sub_meshes_and_local_placements``)."""
+    a = local_mesh_dim if local_mesh_dim >= 0 else mesh.ndim + local_mesh_dim
+    arr = np.asarray(mesh.mesh)
+    names = [n for i, n in enumerate(mesh.dim_names) if i != a]
+    subs = []
+    for i in range(arr.shape[a]):
+        sub = np.take(arr, i, axis=a)
+        subs.append(ProcessMesh(sub if sub.ndim else sub.reshape(1), names or ["d0"]))
+    local_pl = [p for i, p in enumerate(placements) if i != a] or [Replicate()]
+    return subs, local_pl
+
+
+def moe_global_mesh_tensor(local_tensor_list, mesh, placements, local_mesh_dim=-1):
+    """Views the per-sub-mesh tensors of an expert-parallel layer (one per index of ``local_mesh_dim``; this rank holds
+    the one of its own sub-mesh) as ONE distributed tensor over ``mesh`` with ``placements``; no data moves."""
+    a = local_mesh_dim if local_mesh_dim >= 0 else mesh.ndim + local_mesh_dim
+    coord = mesh.coord_of(C.get_rank() if C.is_initialized() else 0)
+    idx = 0 if coord is None else coord[a]
+    t = local_tensor_list[idx]
+    local = local_of(t) if isinstance(t, DistTensor) else t
+    return DistTensor.wrap(local.as_subclass(torch.Tensor), mesh, list(placements))
+
+
+def moe_sub_mesh_tensors(dist_tensor, global_mesh=None, local_mesh_dim=-1, global_placements=None):
+    """Inverse of :func:`moe_global_mesh_tensor`: one distributed tensor per sub-mesh along ``local_mesh_dim``; the
+    entry of this rank's sub-mesh carries its local shard, the others are placeholders of the same local shape."""
+    mesh = global_mesh or dist_tensor.process_mesh
+    placements = list(global_placements or dist_tensor.placements)
+    subs, local_pl = _sub_meshes_and_local_placements(mesh, placements, local_mesh_dim)
+    a = local_mesh_dim if local_mesh_dim >= 0 else mesh.ndim + local_mesh_dim
+    coord = mesh.coord_of(C.get_rank() if C.is_initialized() else 0)
+    mine = 0 if coord is None else coord[a]
+    local = local_of(dist_tensor).as_subclass(torch.Tensor)
+    out = []
+    for i, sub in enumerate(subs):
+        out.append(DistTensor.wrap(local if i == mine else torch.empty_like(local), sub, list(local_pl)))
+    return out
+
+
+def in_auto_parallel_align_mode():
+    import os
+    return os.environ.get("FLAGS_enable_auto_parallel_align_mode", "0").lower() in ("1", "true")
+
+
+class FusePasses:
+    """Switches of the fusion passes in ``Strategy.fused_passes``; the fusions are properties of the kernels here, the
+    object only carries the configuration."""
+
+    def __init__(self, config_dict=None):
+        self.enable = False
+        self.gemm_epilogue = False
+        self.dropout_add = False
+        for k, v in (config_dict or {}).items():
+            setattr(self, k, v)
+
+
+DistAttr = dict      # {'process_mesh': ..., 'placements': ...}: what ``DistTensor.dist_attr`` returns
