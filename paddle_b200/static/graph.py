@@ -61,7 +61,13 @@ class Node:
         kwargs = pytree.tree_map(res, self.kwargs)
         if prog._for_test:
             args, kwargs = _eval_mode_args(self.func, args, kwargs)
-        out = self.func(*args, **kwargs)
+        try:
+            out = self.func(*args, **kwargs)
+        except RuntimeError:
+            fixed = _repair_baked_shape(self.name, args)
+            if fixed is None:
+                raise
+            out = self.func(*fixed, **kwargs)
         if self.out_slots:
             leaves = [o for o in pytree.tree_leaves(out) if isinstance(o, torch.Tensor)]
             for s, o in zip(self.out_slots, leaves):
@@ -73,6 +79,25 @@ class Node:
 
     def __repr__(self):
         return f"{self.out_slots} = {self.name}({self.args}, {self.kwargs})"
+
+
+def _repair_baked_shape(name, args):
+    """Unknown (-1 / None) extents are traced with extent 1, so Python code that turned a shape into integers has
+    baked a 1 into ``view`` / ``reshape`` sizes.  When such a call fails at replay because the element count no longer
+    matches, the missing factor is put into the first size that was 1 (the batch dimension in practice)."""
+    if name not in ("view", "reshape", "_unsafe_view") or len(args) < 2 or not isinstance(args[0], torch.Tensor):
+        return None
+    sizes = list(args[1]) if isinstance(args[1], (list, tuple, torch.Size)) and len(args) == 2 else list(args[1:])
+    if not sizes or not all(isinstance(v, int) for v in sizes) or -1 in sizes or 1 not in sizes:
+        return None
+    prod = 1
+    for v in sizes:
+        prod *= v
+    numel = args[0].numel()
+    if prod == 0 or numel % prod != 0 or numel == prod:
+        return None
+    sizes[sizes.index(1)] = numel // prod
+    return (args[0], sizes)
 
 
 _TRAIN_FLAG_POS = {}

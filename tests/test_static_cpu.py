@@ -192,3 +192,33 @@ def test_unrecorded_autograd_history_is_rejected():
             hidden = w * 2.0
         with pytest.raises(RuntimeError, match="autograd history"):
             paddle.sum(hidden)
+
+
+def test_conv_net_trains_with_batch_sizes_other_than_the_traced_one():
+    """conv + batch-norm + pool + dropout + fc + cross-entropy + accuracy; the program is traced with batch 1 (sizes that
+    Python code baked into view / reshape calls are repaired at replay) and run with batches of 32 and 96."""
+    main, startup = static.Program(), static.Program()
+    with static.program_guard(main, startup):
+        img = static.data("img", [None, 1, 8, 8], "float32")
+        lab = static.data("lab", [None, 1], "int64")
+        h = static.nn.conv2d(img, 4, 3, padding=1, act="relu")
+        h = static.nn.batch_norm(h)
+        h = paddle.flatten(paddle.nn.functional.max_pool2d(h, 2), 1)
+        logits = static.nn.fc(paddle.nn.functional.dropout(h, 0.1), 3)
+        loss = paddle.nn.functional.cross_entropy(logits, lab)
+        acc = static.accuracy(paddle.nn.functional.softmax(logits), lab)
+        test_prog = main.clone(for_test=True)
+        paddle.optimizer.Adam(0.01).minimize(loss)
+    exe = static.Executor()
+    rng = np.random.RandomState(0)
+    X = rng.randn(96, 1, 8, 8).astype("float32")
+    Y = ((X.mean((1, 2, 3)) > 0).astype("int64") + (X[:, 0, 0, 0] > 1).astype("int64")).reshape(-1, 1)
+    first = None
+    for _ in range(25):
+        for i in range(0, 96, 32):
+            l, a = exe.run(main, feed={"img": X[i:i + 32], "lab": Y[i:i + 32]}, fetch_list=[loss, acc])
+            first = float(l) if first is None else first
+    l2, a2 = exe.run(test_prog, feed={"img": X, "lab": Y}, fetch_list=[loss, acc])
+    assert float(l2) < 0.6 * first and float(a2) > 0.8
+    out, = exe.run(static.CompiledProgram(test_prog), feed={"img": X[:5], "lab": Y[:5]}, fetch_list=[logits])
+    assert out.shape == (5, 3) and len(main.all_parameters()) == 6
