@@ -222,3 +222,19 @@ def test_conv_net_trains_with_batch_sizes_other_than_the_traced_one():
     assert float(l2) < 0.6 * first and float(a2) > 0.8
     out, = exe.run(static.CompiledProgram(test_prog), feed={"img": X[:5], "lab": Y[:5]}, fetch_list=[logits])
     assert out.shape == (5, 3) and len(main.all_parameters()) == 6
+
+
+def test_transformer_layer_program_matches_eager_at_another_batch_size():
+    emb = paddle.nn.Embedding(50, 16)
+    enc = paddle.nn.TransformerEncoderLayer(16, 4, 32, dropout=0.0)
+    enc.eval()
+    x = np.random.RandomState(0).randint(0, 50, (7, 10))
+    paddle.disable_static()
+    ref = enc(emb(paddle.to_tensor(x))).mean(1).numpy()
+    paddle.enable_static()
+    main = static.Program()
+    with static.program_guard(main):
+        ids = static.data("ids", [None, 10], "int64")
+        out = enc(emb(ids)).mean(1)
+    got, = static.Executor().run(main, feed={"ids": x}, fetch_list=[out])
+    np.testing.assert_allclose(got, ref, rtol=1e-6, atol=1e-7)
