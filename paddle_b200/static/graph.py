@@ -434,6 +434,12 @@ class _Recorder(TorchFunctionMode):
             _S.suspended -= 1
         if name == "__set__" or (name == "__get__" and not isinstance(out, torch.Tensor)):
             return out
+        if name in ("__bool__", "__int__", "__float__", "__index__", "item") and args \
+                and isinstance(args[0], torch.Tensor) and id(args[0]) in _S.main._slot_of_id:
+            import warnings
+            warnings.warn(f"static graph: Python read the value of a recorded variable ({name}); the example value is "
+                          "baked into the program - use static.nn.cond / while_loop (or to_static(full_graph=True)) "
+                          "for data-dependent control flow", stacklevel=3)
         inplace = name.endswith("_") and not name.endswith("__")
         _S.main.record(func, args, kwargs, out, inplace=inplace)
         return out
