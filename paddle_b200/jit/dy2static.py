@@ -16,8 +16,10 @@ a tensor under static recording.  ``ProgramFunction`` is the ``to_static(full_gr
 converted function into a ``static.Program`` once per input signature and replays the program afterwards, with
 autograd flowing through the replay to the inputs and captured parameters.
 
-Limits: an ``if`` / ``while`` that contains ``return`` / ``break`` / ``continue`` / ``yield`` is left as Python
-control flow (its test must then be a Python value at trace time); variables assigned in only one branch must not be
+A ``return`` that ends a branch of an ``if`` is lifted first (``__jst_ret = value`` in the branch, the statements after
+the ``if`` move into its ``else``, one ``return __jst_ret`` at the end).  Limits: any other ``if`` / ``while`` that
+contains ``return`` / ``break`` / ``continue`` / ``yield`` is left as Python control flow (its test must then be a
+Python value at trace time); variables assigned in only one branch must not be
 read afterwards when the other branch ran."""
 from __future__ import annotations
 
@@ -197,7 +199,7 @@ def _assigned_names(nodes):
         visit_SetComp = visit_DictComp = visit_GeneratorExp = visit_ListComp
     for n in nodes:
         V().visit(n)
-    return [n for n in names if not n.startswith("__jst_") or n.startswith("__jst_i_")]
+    return [n for n in names if not n.startswith("__jst_") or n.startswith("__jst_i_") or n == "__jst_ret"]
 
 
 def _has_jump(nodes):
@@ -331,6 +333,63 @@ def __jst_set_{uid}(__jst_v):
         return [ast.copy_location(n, node) for n in out]
 
 
+def _lift_early_returns(stmts):
+    """``if c: ...; return X`` followed by more statements becomes ``if c: ...; __jst_ret = X`` / ``else: <rest>`` with
+    one ``return __jst_ret`` at the end, so that the ``if`` has no jump and can be converted (the reference's
+    ReturnTransformer handles the general case; this covers a return as the LAST statement of a branch)."""
+    def ends_with_return(body):
+        return bool(body) and isinstance(body[-1], ast.Return)
+
+    def only_tail_return(body):
+        return ends_with_return(body) and not _has_jump(body[:-1])
+
+    def to_assign(ret):
+        return ast.Assign(targets=[ast.Name(id="__jst_ret", ctx=ast.Store())],
+                          value=ret.value if ret.value is not None else ast.Constant(value=None))
+
+    def lift(body):
+        """Returns a statement list without returns that leaves the result in ``__jst_ret``, or None."""
+        for i, st in enumerate(body):
+            if isinstance(st, ast.Return):
+                return body[:i] + [to_assign(st)] if not _has_jump(body[:i]) else None
+            if isinstance(st, ast.If) and (_has_jump(st.body) or _has_jump(st.orelse)):
+                if _has_jump(body[:i]):
+                    return None
+                rest = body[i + 1:]
+                t = lift(st.body) if ends_with_return(st.body) or _has_jump(st.body) else st.body
+                if t is None:
+                    return None
+                if ends_with_return(st.body) or _returns_on_all_paths(st.body):
+                    f = lift(st.orelse + rest)
+                else:
+                    return None
+                if f is None:
+                    return None
+                new_if = ast.If(test=st.test, body=t, orelse=f)
+                return body[:i] + [ast.copy_location(new_if, st)]
+            if _has_jump([st]):
+                return None
+        return body + [ast.Assign(targets=[ast.Name(id="__jst_ret", ctx=ast.Store())], value=ast.Constant(value=None))]
+
+    if not any(isinstance(st, ast.If) and _has_jump(st.body + st.orelse) for st in stmts):
+        return stmts
+    lifted = lift(stmts)
+    if lifted is None:
+        return stmts
+    return lifted + [ast.Return(value=ast.Name(id="__jst_ret", ctx=ast.Load()))]
+
+
+def _returns_on_all_paths(body):
+    if not body:
+        return False
+    last = body[-1]
+    if isinstance(last, ast.Return):
+        return True
+    if isinstance(last, ast.If):
+        return _returns_on_all_paths(last.body) and _returns_on_all_paths(last.orelse)
+    return False
+
+
 _converted = {}
 
 
@@ -349,6 +408,8 @@ def convert_function(fn):
         if not isinstance(fdef, (ast.FunctionDef, ast.AsyncFunctionDef)):
             return fn
         fdef.decorator_list = []
+        fdef.body = _lift_early_returns(fdef.body)
+        ast.fix_missing_locations(tree)
         _Transformer().visit(fdef)
         ast.fix_missing_locations(tree)
         import sys

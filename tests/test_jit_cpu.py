@@ -135,3 +135,20 @@ def test_for_range_with_tensor_bound():
         assert float(sf(x, nt)) == 3.0 * sum(range(1, n + 1))
     assert len(sf._programs) == 1
     assert float(sf(x, 3)) == 18.0 and float(f(x, 3)) == 18.0         # Python bound: unrolled at trace time
+
+
+def test_early_return_in_tensor_dependent_if():
+    def f(x):
+        y = x * 2
+        if y.sum() > 10:
+            return y - 10
+        z = y + 1
+        if z.max() < 0:
+            return z * 0
+        return z
+
+    sf = paddle.jit.to_static(f, full_graph=True)
+    for v in ([10.0, 10.0], [1.0, 2.0], [-3.0, -4.0]):
+        t = paddle.to_tensor(v)
+        np.testing.assert_allclose(sf(t).numpy(), f(t).numpy())
+    assert len(sf._programs) == 1
