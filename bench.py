@@ -42,7 +42,7 @@ def parse_args():
 
 
 REFERENCE_UNAVAILABLE = (
-    "pip install --no-index --no-build-isolation of /root/reference fails at metadata generation "
+    "pip install --no-index --no-build-isolation of the reference source tree fails at metadata generation "
     "(setup.py: 'Missing build dependency: opteinsum'); third_party/ submodules are absent and the build "
     "has no sm_100 target, so the reference cannot be built offline")
 

@@ -59,7 +59,7 @@ def test_grouped_gemm_fp8_matches_dequantised_reference(N):
         start += r
     assert (out.float() - ref).abs().max() / ref.abs().max() < 1e-2
     full = torch.cat([x[s:s + r].float() @ w[e].float() for e, (s, r) in enumerate(zip([0, 200, 200, 277], rows))])
-    assert (out.float() - full).abs().max() / full.abs().max() < 0.08      # fp8 quantisation error budget
+    assert (out.float() - full).abs().max() / full.abs().max() < 0.08      # fp8 quantisation error allowance
 
 
 def test_fused_moe_fp8_path_close_to_bf16():
