@@ -60,6 +60,31 @@ class Config:
     def set_cpu_math_library_num_threads(self, n):
         torch.set_num_threads(int(n))
 
+    def enable_mkldnn(self, *a, **k):
+        pass                                   # CPU inference runs on the tensor library's own CPU kernels
+
+    def gpu_device_id(self):
+        return self._device_id
+
+    def ir_optim(self):
+        return self._cuda_graph
+
+    def summary(self):
+        return (f"model: {self._prefix}\nuse_gpu: {self._use_gpu}\ndevice_id: {self._device_id}\n"
+                f"precision: {self._precision}\ncuda_graph: {self._cuda_graph}")
+
+    _TOLERATED_PREFIXES = ("enable_", "disable_", "switch_", "set_", "delete_", "exp_", "collect_")
+
+    def __getattr__(self, name):
+        # The reference's AnalysisConfig has ~150 tuning switches for its pass pipeline and third-party engines
+        # (analysis_config.cc); the ones without a meaning here are accepted and ignored so deployment scripts run.
+        if name.startswith(Config._TOLERATED_PREFIXES):
+            def ignored(*a, **k):
+                return None
+            ignored.__name__ = name
+            return ignored
+        raise AttributeError(name)
+
 
 class _Handle:
     def __init__(self, name):
