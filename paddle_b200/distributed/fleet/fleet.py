@@ -160,7 +160,10 @@ class Fleet:
         if mode == ParallelMode.PIPELINE_PARALLEL:
             from .meta_parallel.pipeline_parallel import PipelineParallel, PipelineParallelWithInterleave
             vpp = getattr(model, "get_num_virtual_stages", lambda: 1)()
-            cls = PipelineParallelWithInterleave if vpp > 1 else PipelineParallel
+            cfg = strategy.pipeline_configs
+            mode = cfg.get("schedule_mode", "1F1B") if hasattr(cfg, "get") else "1F1B"
+            # the schedules that exist only as generated step lists (zero bubble) run on the schedule executor
+            cls = PipelineParallelWithInterleave if vpp > 1 or mode in ("ZBH1",) else PipelineParallel
             return cls(model, hcg, strategy=strategy)
         if mode == ParallelMode.TENSOR_PARALLEL:
             return mp.TensorParallel(model, hcg, strategy=strategy)

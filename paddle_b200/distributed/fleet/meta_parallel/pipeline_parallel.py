@@ -302,7 +302,7 @@ class PipelineParallelWithInterleaveFthenB(PipelineParallel):
 
     def __init__(self, layers, hcg, strategy):
         super().__init__(layers, hcg, strategy)
-        self._V = layers.get_num_virtual_stages()
+        self._V = layers.get_num_virtual_stages() if hasattr(layers, "get_num_virtual_stages") else 1
         if self._V > 1:
             assert self.accumulate_steps % self.num_stages == 0, \
                 "accumulate_steps must be a multiple of the pipeline degree for interleaved scheduling"
@@ -448,8 +448,10 @@ class PipelineParallelWithInterleave(PipelineParallel):
         from . import pipeline_schedules as S
         self._V = layers.get_num_virtual_stages()
         mode = strategy.pipeline_configs.get("schedule_mode", "VPP") if hasattr(strategy.pipeline_configs, "get") else "VPP"
-        if mode == "1F1B" and self._V > 1:
+        if self._V > 1 and mode in ("1F1B", "ZBH1"):
             mode = "VPP"
+        elif self._V == 1 and mode in ("VPP", "interleaved_1f1b"):
+            mode = "1F1B"
         self._executor = S.ScheduleExecutor(self, S.SCHEDULES.get(mode, S.interleaved_1f1b))
         S.validate(self._executor.fn, self.num_stages, self._V, self.accumulate_steps)
 

@@ -1,6 +1,8 @@
 """Pipeline schedules as data plus one executor.
 
-A *schedule* is, per pipeline rank, a list of steps ``("F" | "B", chunk, micro_batch)``.  ``interleaved_1f1b``
+A *schedule* is, per pipeline rank, a list of steps ``(kind, chunk, micro_batch)`` with kind ``"F"`` (forward),
+``"B"`` (whole backward), ``"Bx"`` (backward for the input gradient only; weight gradients are queued) or ``"W"``
+(the queued weight gradients of an earlier ``"Bx"``).  ``interleaved_1f1b``
 generates the virtual-pipeline order of python/paddle/distributed/fleet/meta_parallel/pipeline_parallel.py
 ``PipelineParallelWithInterleave`` (:1308-2390): warm-up forwards ``(P - rank - 1) * 2 + (V - 1) * P``, then one
 forward / one backward, then the remaining backwards; virtual micro-batch ``k`` maps to chunk
@@ -57,38 +59,79 @@ def interleaved_1f1b(P, V, M, rank):
     return steps + [("B", *bwd[k]) for k in range(N - warm, N)]
 
 
-SCHEDULES = {"FThenB": f_then_b, "1F1B": one_f_one_b, "VPP": interleaved_1f1b, "interleaved_1f1b": interleaved_1f1b}
+def zero_bubble_h1(P, V, M, rank):
+    """ZB-H1: 1F1B with one more warm-up forward per stage, whose bubble is filled by postponing weight gradients.
+    Stage ``rank`` runs its first ``rank`` backwards as ``Bx`` and pays their ``W`` steps at the very end, where
+    1F1B would idle waiting for the upstream stages to drain; the memory peak stays that of 1F1B's first stage.
+    Step counts follow python/paddle/distributed/passes/pipeline_scheduler_pass/pipeline_zero_bubble.py:66-140."""
+    assert V == 1
+    if M < P:
+        raise ValueError("ZB-H1 needs at least as many micro-batches as pipeline stages")
+    warm = P - rank
+    steps = [("F", 0, m) for m in range(warm)]
+    f, b = warm, 0
+    while f < M:                                   # steady state: the first `rank` backwards leave W for later
+        steps += [("Bx" if b < rank else "B", 0, b), ("F", 0, f)]
+        f, b = f + 1, b + 1
+    while b < M - 1:
+        steps.append(("B", 0, b))
+        b += 1
+    steps += [("Bx", 0, b), ("W", 0, b)] if rank > 0 else [("B", 0, b)]
+    return steps + [("W", 0, m) for m in range(rank)]
 
 
-def validate(schedule_fn, P, V, M):
-    """Checks on the host that the per-rank lists form a deadlock-free global order: every step's input is produced
-    by an earlier step of some rank.  Returns the number of rounds of a greedy simulation (a proxy for the bubble)."""
+SCHEDULES = {"FThenB": f_then_b, "1F1B": one_f_one_b, "VPP": interleaved_1f1b, "interleaved_1f1b": interleaved_1f1b,
+             "ZBH1": zero_bubble_h1}
+
+
+STEP_COST = {"F": 1.0, "B": 2.0, "Bx": 1.0, "W": 1.0}
+
+
+def validate(schedule_fn, P, V, M, cost=None):
+    """Checks on the host that the per-rank lists form a deadlock-free global order (every step's input is produced
+    by an earlier step of some rank, every ``Bx`` has exactly one later ``W``) and returns the makespan of a
+    simulation in which a step starts when its rank is free and its input has been produced, with the step costs of
+    ``cost`` (default: forward 1, input-gradient half 1, weight-gradient half 1, whole backward 2)."""
+    cost = cost or STEP_COST
     lists = [list(schedule_fn(P, V, M, r)) for r in range(P)]
-    pos = [0] * P
-    done = set()
+    pos, clock = [0] * P, [0.0] * P
+    done = {}                                      # (kind, virtual stage, micro-batch) -> finish time
+    open_w = set()
     last_vs = P * V - 1
-    rounds = 0
     while any(pos[r] < len(lists[r]) for r in range(P)):
-        progressed = []
+        moved = False
         for r in range(P):
-            if pos[r] >= len(lists[r]):
-                continue
-            kind, c, m = lists[r][pos[r]]
-            vs = c * P + r
-            need = None
-            if kind == "F" and vs > 0:
-                need = ("F", vs - 1, m)
-            elif kind == "B":
-                need = ("B", vs + 1, m) if vs < last_vs else ("F", vs, m)
-            if need is None or need in done:
-                progressed.append((r, (kind, vs, m)))
-        if not progressed:
+            while pos[r] < len(lists[r]):
+                kind, c, m = lists[r][pos[r]]
+                vs = c * P + r
+                need = None
+                if kind == "F" and vs > 0:
+                    need = ("F", vs - 1, m)
+                elif kind in ("B", "Bx"):
+                    if ("F", vs, m) not in done:
+                        raise RuntimeError(f"rank {r} runs the backward of micro-batch {m} before its forward")
+                    need = ("B", vs + 1, m) if vs < last_vs else ("F", vs, m)
+                elif kind == "W":
+                    if (vs, m) not in open_w:
+                        raise RuntimeError(f"rank {r} runs W of micro-batch {m} without an earlier Bx")
+                    open_w.discard((vs, m))
+                if need is not None and need not in done:
+                    if kind == "W":
+                        open_w.add((vs, m))
+                    break
+                start = max(clock[r], done.get(need, 0.0))
+                clock[r] = start + cost[kind]
+                if kind == "Bx":
+                    open_w.add((vs, m))
+                if kind != "W":
+                    done[("B" if kind == "Bx" else kind, vs, m)] = clock[r]
+                pos[r] += 1
+                moved = True
+        if not moved:
             raise RuntimeError(f"schedule deadlocks at positions {pos}")
-        for r, item in progressed:
-            done.add(item)
-            pos[r] += 1
-        rounds += 1
-    return rounds
+    if open_w:
+        raise RuntimeError("a Bx step has no W step: its weight gradients would be lost")
+    return max(clock)
 
 
 class ScheduleExecutor:
@@ -126,7 +169,7 @@ class ScheduleExecutor:
             vs = c * self.P + r
             if kind == "F" and vs < last:
                 out.append(((r + 1) % self.P, ("act", vs + 1, m)))
-            elif kind == "B" and vs > 0:
+            elif kind in ("B", "Bx") and vs > 0:
                 out.append(((r - 1) % self.P, ("grad", vs - 1, m)))
         return out
 
@@ -173,8 +216,15 @@ class ScheduleExecutor:
                 stash[nxt] = self._recv_next(src, nxt, like)
             return stash.pop(msg)
 
+        from ....ops.functional import WeightGradStore
+        deferred = {}                 # (chunk, micro-batch) -> weight-gradient closures queued by its Bx step
+        WeightGradStore.split = any(s[0] == "Bx" for s in sched[r])
         for kind, c, m in sched[r]:
             vs = c * P + r
+            if kind == "W":
+                WeightGradStore.run(deferred.pop((c, m)))
+                continue
+            WeightGradStore.enabled = kind == "Bx"
             if kind == "F":
                 if vs == 0:
                     x = o._load_micro_batch(inputs, m)
@@ -208,6 +258,10 @@ class ScheduleExecutor:
                 if vs > 0 and isinstance(x, torch.Tensor) and x.requires_grad:
                     self._send(x.grad, (r - 1) % P, pending)
                     x.grad = None
+                if kind == "Bx":
+                    deferred[(c, m)] = WeightGradStore.pop()
+        WeightGradStore.split = WeightGradStore.enabled = False
+        assert not deferred, "weight gradients left in the store"
         for w, _ in pending:
             w.wait()
         assert not stash and all(cursor[q] == len(incoming[q]) for q in incoming), "pipeline messages left over"

@@ -130,3 +130,25 @@ class PruneSideEffectFree(PassBase):
             return
         slots = [main_program._slot_of(t) for t in targets]
         main_program._nodes[:] = g.prune(main_program._nodes, slots)
+
+
+class _PipelineSchedulerPass(PassBase):
+    """``pipeline_scheduler_<mode>``: the reference rewrites a program into per-micro-batch jobs
+    (python/paddle/distributed/passes/pipeline_scheduler_pass/); here the job list is the generated step list of
+    ``fleet/meta_parallel/pipeline_schedules.py``, returned in ``context`` under ``"job_list"`` after validation."""
+    mode = "1F1B"
+
+    def _apply_single_impl(self, main_program, startup_program, context):
+        from ..fleet.meta_parallel import pipeline_schedules as S
+        P, M = int(self.get_attr("pp_degree")), int(self.get_attr("num_micro_batches"))
+        V = int(self.get_attr("vpp_degree") or 1)
+        fn = S.SCHEDULES[self.mode]
+        S.validate(fn, P, V, M)
+        jobs = fn(P, V, M, int(self.get_attr("pp_stage") or 0))
+        if context is not None:
+            context.set_attr("job_list", jobs)
+        return jobs
+
+
+for _mode in ("FThenB", "1F1B", "VPP", "ZBH1"):
+    register_pass(f"pipeline_scheduler_{_mode}")(type(f"PipelineScheduler{_mode}", (_PipelineSchedulerPass,), {"mode": _mode}))

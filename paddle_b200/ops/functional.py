@@ -78,7 +78,100 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db
 
 
+class WeightGradStore:
+    """Deferred weight gradients for zero-bubble pipeline schedules.  While ``split`` is set, ``linear`` records a
+    node whose backward can leave out the weight gradient; while ``enabled`` is set as well, that backward produces
+    only the input gradient and queues the weight (and bias) gradient as a closure.  ``flush()`` runs what has been
+    queued, ``pop()`` hands that batch to the caller so a schedule can run it in a later "W" step.
+    The reference splits matmul_grad into two matmul ops for the same purpose
+    (python/paddle/distributed/passes/pipeline_scheduler_pass/pipeline_zero_bubble.py:38-60)."""
+    split = False
+    enabled = False
+    _queue: list = []
+
+    @classmethod
+    def put(cls, fn):
+        cls._queue.append(fn)
+
+    @classmethod
+    def pop(cls):
+        batch, cls._queue = cls._queue, []
+        return batch
+
+    @classmethod
+    def flush(cls):
+        for fn in cls.pop():
+            fn()
+
+    @staticmethod
+    def run(batch):
+        for fn in batch:
+            fn()
+
+
+class _SplitLinearFn(torch.autograd.Function):
+    """Linear whose backward returns dX at once and leaves dW / db to ``WeightGradStore``."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = x.reshape(-1, x.shape[-1])
+        use_native = _native(x) and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and weight.shape[1] % 8 == 0
+        if use_native and not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y = native.gemm(x2, weight) if use_native else x2 @ weight
+        if bias is not None:
+            y = y + bias
+        ctx.save_for_backward(x2, weight)
+        ctx.use_native, ctx.x_shape = use_native, x.shape
+        ctx.weight_ref, ctx.bias_ref = weight, bias
+        return y.view(*x.shape[:-1], weight.shape[1])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if ctx.use_native and not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = (native.gemm(dy2, weight, trans_b=True) if ctx.use_native else dy2 @ weight.t()).view(ctx.x_shape)
+        w, b, use_native = ctx.weight_ref, ctx.bias_ref, ctx.use_native
+        need_w, need_b = ctx.needs_input_grad[1], b is not None and ctx.needs_input_grad[2]
+
+        def weight_grad():
+            with torch.no_grad():
+                if need_w:
+                    mg = getattr(w, "main_grad", None)
+                    if mg is not None and use_native:
+                        native.gemm(x2, dy2, trans_a=True, out=mg, accumulate=True)
+                    else:
+                        dw = native.gemm(x2, dy2, trans_a=True) if use_native else x2.t() @ dy2
+                        if mg is not None:
+                            mg.add_(dw)
+                        elif w.grad is None:
+                            w.grad = dw
+                        else:
+                            w.grad.add_(dw)
+                    hook = getattr(w, "_main_grad_ready_hook", None)
+                    if mg is not None and hook is not None:
+                        hook(w)
+                if need_b:
+                    db = dy2.sum(0).to(b.dtype)
+                    if b.grad is None:
+                        b.grad = db
+                    else:
+                        b.grad.add_(db)
+
+        if WeightGradStore.enabled:
+            WeightGradStore.put(weight_grad)
+        else:
+            weight_grad()
+        return dx, None, None
+
+
 def linear(x, weight, bias=None):
+    if WeightGradStore.split and x.dim() >= 2 and weight.dim() == 2 and torch.is_grad_enabled():
+        return as_tensor(_SplitLinearFn.apply(x, weight, bias))
     if _native(x) and weight.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and weight.shape[1] % 8 == 0:
         return as_tensor(_LinearFn.apply(x, weight, bias))
     y = torch.matmul(x, weight)

@@ -1,6 +1,6 @@
 """Pipeline parallel vs single-rank twin (pattern of test/collective/fleet/hybrid_parallel_pp_layer.py and
 hybrid_parallel_shared_weight.py): the same stack of layers, built from one seed, trained for three steps
-with 1F1B (argv[1] == "1f1b") or interleaved virtual stages (argv[1] == "vpp"); dumps per-step losses of
+with 1F1B (argv[1] == "1f1b"), interleaved virtual stages ("vpp") or the zero-bubble H1 order ("zbh1"); dumps per-step losses of
 both and the final parameters of this stage next to the twin's."""
 import os
 import sys
@@ -20,6 +20,8 @@ H, VOC, MB, ACC = 16, 32, 2, 4
 strategy = fleet.DistributedStrategy()
 strategy.hybrid_configs = {"dp_degree": 1, "mp_degree": 1, "pp_degree": n}
 strategy.pipeline_configs = {"accumulate_steps": ACC, "micro_batch_size": MB}
+if mode == "zbh1":          # zero-bubble H1: weight gradients of the first backwards are postponed to the end
+    strategy.pipeline_configs["schedule_mode"] = "ZBH1"
 fleet.init(is_collective=True, strategy=strategy)
 rank = dist.get_rank()
 
@@ -114,4 +116,4 @@ if not V:
         if isinstance(f, nn.Layer):
             for (k, p), (_, q) in zip(f.state_dict().items(), twin_layers[parts[rank] + i][0].state_dict().items()):
                 maxdiff = max(maxdiff, float((p - q).abs().max()))
-_common.dump({"twin": lt, "pipe": lp, "maxdiff": maxdiff, "eval": ev, "parts": parts})
+_common.dump({"twin": lt, "pipe": lp, "maxdiff": maxdiff, "eval": ev, "parts": parts, "wrapper": type(model).__name__})

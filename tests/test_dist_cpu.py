@@ -49,7 +49,7 @@ def test_llama_tp_sp_parity_cpu():
         assert r["maxdiff"] < 1e-3, r["maxdiff"]  # Adam turns tiny gradient noise into O(lr) steps
 
 
-@pytest.mark.parametrize("mode", ["1f1b", "vpp"])
+@pytest.mark.parametrize("mode", ["1f1b", "vpp", "zbh1"])
 def test_pipeline_parallel_parity_cpu(mode):
     """2 pipeline stages (1F1B, and 2 virtual chunks per stage over the ring) with a weight tied between the
     first and the last layer: losses and updated weights equal the single-process twin."""
@@ -58,6 +58,8 @@ def test_pipeline_parallel_parity_cpu(mode):
         assert np.allclose(r["twin"], r["pipe"], atol=1e-5), r
         assert r["maxdiff"] < 1e-5
     assert res[0]["pipe"] == res[1]["pipe"]
+    if mode == "zbh1":
+        assert res[0]["wrapper"] == "PipelineParallelWithInterleave"       # the schedule executor ran it
 
 
 @pytest.mark.parametrize("level", ["os_g", "p_g_os"])

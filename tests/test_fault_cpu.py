@@ -147,20 +147,42 @@ def test_pipeline_schedules_are_deadlock_free_and_have_the_expected_bubble():
     """Host-side check of the generated per-rank orders: every step's input is produced earlier somewhere, the
     greedy makespan is 2*M*V + 2*(P-1) virtual steps (the interleaved bubble), and a broken order is reported."""
     from paddle_b200.distributed.fleet.meta_parallel import pipeline_schedules as S
+    unit = {"F": 1, "B": 1, "Bx": 1, "W": 1}
     for P, V, M in [(2, 2, 4), (4, 2, 8), (4, 3, 8), (8, 2, 16)]:
-        assert S.validate(S.interleaved_1f1b, P, V, M) == 2 * M * V + 2 * (P - 1)
+        assert S.validate(S.interleaved_1f1b, P, V, M, cost=unit) == 2 * M * V + 2 * (P - 1)
         steps = S.interleaved_1f1b(P, V, M, 0)
         warm = next(i for i, s in enumerate(steps) if s[0] == "B")
         assert warm == min((P - 1) * 2 + (V - 1) * P, M * V) + 1          # warm-up forwards + the first steady forward
         assert sorted(s for s in steps if s[0] == "F") == sorted(("F", c, m) for c in range(V) for m in range(M))
     for P, M in [(2, 4), (4, 8)]:
-        assert S.validate(S.one_f_one_b, P, 1, M) == 2 * M + 2 * (P - 1)
+        assert S.validate(S.one_f_one_b, P, 1, M, cost=unit) == 2 * M + 2 * (P - 1)
+    # with a backward that costs two forwards, 1F1B idles 3 * (P - 1) units; ZB-H1 fills part of that with the
+    # postponed weight gradients, and every Bx is matched by exactly one later W on the same rank
+    for P, M in [(2, 2), (4, 4), (4, 8), (8, 16)]:
+        assert S.validate(S.one_f_one_b, P, 1, M) == 3 * M + 3 * (P - 1)
+        zb = S.validate(S.zero_bubble_h1, P, 1, M)
+        assert 3 * M + (P - 1) <= zb < 3 * M + 3 * (P - 1)
+        for r in range(P):
+            steps = S.zero_bubble_h1(P, 1, M, r)
+            assert sorted(m for k, _, m in steps if k == "Bx") == sorted(m for k, _, m in steps if k == "W")
+            assert sorted(m for k, _, m in steps if k in ("B", "Bx")) == list(range(M))
+
+    def lost_w(P, V, M, rank):
+        return [("F", 0, 0), ("Bx", 0, 0)]
+    import pytest
+    with pytest.raises(RuntimeError, match="no W step"):
+        S.validate(lost_w, 1, 1, 1)
 
     def broken(P, V, M, rank):           # backward before its forward
         return [("B", 0, 0), ("F", 0, 0)]
     import pytest
-    with pytest.raises(RuntimeError, match="deadlocks"):
+    with pytest.raises(RuntimeError, match="before its forward"):
         S.validate(broken, 2, 1, 1)
+
+    def cyclic(P, V, M, rank):           # stage 1 wants the gradient path first, stage 0 never produces for it
+        return [("F", 0, 0), ("B", 0, 0)] if rank == 0 else [("F", 0, 1), ("F", 0, 0), ("B", 0, 0)]
+    with pytest.raises(RuntimeError, match="deadlocks"):
+        S.validate(cyclic, 2, 1, 2)
     with pytest.raises(ValueError):
         S.interleaved_1f1b(4, 2, 6, 0)
 
@@ -207,3 +229,32 @@ def test_corrupt_checkpoint_shard_is_reported_by_name(tmp_path):
     (tmp_path / (shard.name + ".crc")).unlink()                 # without the side file the decoder still reports it
     with pytest.raises(ckpt.CheckpointCorruptError, match="cannot be decoded"):
         ckpt.load_state_dict({"w": paddle.zeros([4096]), "step": 0}, str(tmp_path))
+
+
+def test_weight_grad_store_defers_and_matches_plain_backward():
+    """Split backward of linear layers: with the store enabled, backward yields only input gradients; running the
+    queued closures afterwards gives the same weight / bias gradients as an ordinary backward."""
+    import torch
+    import paddle_b200 as paddle
+    from paddle_b200.ops.functional import WeightGradStore
+    paddle.seed(3)
+    net = paddle.nn.Sequential(paddle.nn.Linear(6, 5), paddle.nn.Tanh(), paddle.nn.Linear(5, 4))
+    x = paddle.randn([3, 6])
+    x.stop_gradient = False
+    net(x).square().sum().backward()
+    ref = [p.grad.clone() for p in net.parameters()] + [x.grad.clone()]
+    for p in net.parameters():
+        p.clear_gradient()
+    x.clear_gradient()
+    WeightGradStore.split = WeightGradStore.enabled = True
+    try:
+        net(x).square().sum().backward()
+        assert all(p.grad is None or not bool(p.grad.any()) for p in net.parameters())
+        assert torch.allclose(x.grad, ref[-1], atol=1e-6)
+        batch = WeightGradStore.pop()
+        assert len(batch) == 2
+    finally:
+        WeightGradStore.split = WeightGradStore.enabled = False
+    WeightGradStore.run(batch)
+    for p, g in zip(net.parameters(), ref):
+        assert torch.allclose(p.grad, g, atol=1e-6)
