@@ -42,11 +42,16 @@ class MoELayer(nn.Layer):
         self.world_size = moe_group.nranks if moe_group is not None else 1
         self.num_expert = len(experts)
         self.d_model = d_model
-        self.experts = experts if isinstance(experts, nn.LayerList) else nn.LayerList(list(experts))
-        for e in self.experts:
-            for p in e.parameters():
-                p.is_moe_param = True          # not synchronised by data parallelism: every rank owns other experts
-                p.no_sync = True
+        # either one layer per local expert, or one layer that holds all of them with stacked weights and runs them
+        # as grouped GEMMs (``grouped = True``; ``forward(x, counts)``)
+        self._grouped = bool(getattr(experts, "grouped", False))
+        if self._grouped or isinstance(experts, nn.LayerList):
+            self.experts = experts
+        else:
+            self.experts = nn.LayerList(list(experts))
+        for p in self.experts.parameters():
+            p.is_moe_param = True              # not synchronised by data parallelism: every rank owns other experts
+            p.no_sync = True
         if isinstance(gate, dict):
             self.top_k = gate.get("top_k", 2)
             kind = gate.get("type", "gshard")
@@ -63,6 +68,8 @@ class MoELayer(nn.Layer):
         self.gate = gate
 
     def _experts_forward(self, x, fwd_expert_count):
+        if self._grouped:
+            return self.experts(x, fwd_expert_count)
         outs, start = [], 0
         counts = [int(c) for c in fwd_expert_count.tolist()]
         for e, n in enumerate(counts):

@@ -23,11 +23,15 @@ class MixtralConfig(LlamaConfig):
     num_experts_per_tok: int = 2
     router_aux_loss_coef: float = 0.02
     capacity_factor: float = 1.25
+    expert_impl: str = "loop"           # "loop": one pair of Linear layers per expert; "grouped_fp8": stacked weights,
+                                        # all local experts in one block-scaled fp8 grouped GEMM per projection
 
     @classmethod
     def mixtral_8x7b(cls, **kw):
-        return cls(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
-                   num_key_value_heads=8, **kw)
+        base = dict(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                    num_key_value_heads=8)
+        base.update(kw)
+        return cls(**base)
 
     @classmethod
     def tiny(cls, **kw):
@@ -63,13 +67,15 @@ class SoftmaxTopKGate(NaiveGate):
         val, idx = torch.topk(probs, self.top_k, dim=-1)
         val = val / val.sum(-1, keepdim=True)
         E = self.tot_expert
-        frac = torch.bincount(idx.reshape(-1), minlength=E).to(probs.dtype) / idx.numel()
+        # one pass over a [T * k, E] one-hot gives the per-expert counts (no bincount: that one waits for the host)
+        # and, through a running sum, each routed copy's arrival number at its expert
+        flat = idx.reshape(-1)
+        onehot = torch.nn.functional.one_hot(flat, E).to(torch.int32)
+        frac = onehot.sum(0).to(probs.dtype) / flat.numel()
         self.set_loss(as_tensor(E * (frac * probs.mean(0)).sum()))
         if self.capacity_factor and self.capacity_factor > 0:
             cap = int(self.capacity_factor * x.shape[0] * self.top_k / E) + 1
-            flat = idx.reshape(-1)
-            onehot = torch.nn.functional.one_hot(flat, E)
-            rank_in = (onehot.cumsum(0) - onehot).gather(1, flat[:, None]).squeeze(1)
+            rank_in = ((onehot.cumsum(0) - onehot) * onehot).sum(1)
             idx = torch.where(rank_in < cap, flat, torch.full_like(flat, -1)).reshape(idx.shape)
         return as_tensor(val.to(x.dtype)), as_tensor(idx)
 
@@ -84,8 +90,12 @@ class MixtralDecoderLayer(nn.Layer):
         assert config.num_local_experts % world == 0
         n_local = config.num_local_experts // world
         gate = SoftmaxTopKGate(config.hidden_size, n_local, world, config.num_experts_per_tok, config.capacity_factor)
-        self.moe = MoELayer(config.hidden_size, nn.LayerList([MixtralExpert(config) for _ in range(n_local)]), gate=gate,
-                            moe_group=moe_group)
+        if config.expert_impl == "grouped_fp8":
+            from ..incubate.distributed.models.moe.fp8_experts import FP8GroupedExperts
+            experts = FP8GroupedExperts(n_local, config.hidden_size, config.intermediate_size, config.initializer_range)
+        else:
+            experts = nn.LayerList([MixtralExpert(config) for _ in range(n_local)])
+        self.moe = MoELayer(config.hidden_size, experts, gate=gate, moe_group=moe_group)
 
     def forward(self, hidden, residual, batch, seq):
         if residual is None:

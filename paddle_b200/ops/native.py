@@ -317,6 +317,7 @@ class TensorTable:
                                            c_float(beta2_pow), ptr(grad_scale), ptr(skip), stream())
         check(rc, "pd_adamw_multi")
         _count()
+        self._bump_versions()
 
     def momentum(self, lr, mu, wd, nesterov, use_momentum, grad_scale=None):
         rc = _lib.kernels().pd_momentum_multi(ptr(self.table), c_int64(self.total_chunks), c_float(lr), c_float(mu),
@@ -324,6 +325,12 @@ class TensorTable:
                                               ptr(grad_scale), stream())
         check(rc, "pd_momentum_multi")
         _count()
+        self._bump_versions()
+
+    def _bump_versions(self):
+        """The kernels write the parameters through raw pointers; tell autograd (saved-tensor checks) and the caches
+        keyed on a parameter's version (quantised weight copies) that their contents changed."""
+        torch.autograd.graph.increment_version(self.keepalive[0])
 
     def sq_l2_norm(self, out=None, accumulate=False):
         k = _lib.kernels()

@@ -81,3 +81,52 @@ def test_fused_moe_fp8_path_close_to_bf16():
     assert err < 0.1, float(err)
     y = IF.moe_reduce(out, scales, inv, topk, norm_topk_prob=True)
     assert y.shape == [T, H]
+
+
+def test_fp8_grouped_experts_train_step_matches_bf16_experts():
+    """The trainable grouped fp8 expert block against per-expert bf16 matmuls with the same weights: output, input
+    gradient and both weight gradients (uneven expert sizes, one empty expert); the quantised weights are cached
+    across micro-batches and refreshed when the parameters change."""
+    import paddle_b200 as paddle
+    from paddle_b200.incubate.distributed.models.moe.fp8_experts import FP8GroupedExperts
+    torch.manual_seed(5)
+    E, H, F = 4, 256, 384
+    counts = [200, 0, 33, 331]
+    M = sum(counts)
+    paddle.seed(5)
+    ex = FP8GroupedExperts(E, H, F, initializer_range=0.05).to(device="cuda", dtype="bfloat16")
+    x = torch.randn(M, H, device="cuda").bfloat16()
+    xt = paddle.to_tensor(x)
+    xt.stop_gradient = False
+    dy = (torch.randn(M, H, device="cuda") * 0.1).bfloat16()
+    y = ex(xt, counts)
+    y.backward(dy)
+    w1, w2 = ex.gate_up_weight, ex.down_weight
+    xr = x.detach().float().requires_grad_(True)
+    w1r, w2r = w1.detach().float().requires_grad_(True), w2.detach().float().requires_grad_(True)
+    outs, s = [], 0
+    for e, n in enumerate(counts):
+        if n:
+            h = xr[s:s + n] @ w1r[e]
+            g, u = h.chunk(2, -1)
+            outs.append((torch.nn.functional.silu(g) * u) @ w2r[e])
+        s += n
+    yr = torch.cat(outs, 0)
+    yr.backward(dy.float())
+
+    def rel(a, b):
+        return float((a.float() - b).abs().max() / b.abs().max())
+    assert rel(y, yr) < 0.08, rel(y, yr)
+    assert rel(xt.grad, xr.grad) < 0.1, rel(xt.grad, xr.grad)
+    assert rel(w1.grad, w1r.grad) < 0.1, rel(w1.grad, w1r.grad)
+    assert rel(w2.grad, w2r.grad) < 0.1, rel(w2.grad, w2r.grad)
+    assert float(w1.grad[1].abs().max()) == 0.0                     # the empty expert gets a zero gradient
+    # cache: a second micro-batch reuses the e4m3 weights; an in-place update invalidates them
+    q_first = ex._cache[1].fwd[0]
+    ex(paddle.to_tensor(x), counts)
+    assert ex._cache[1].fwd[0] is q_first
+    with torch.no_grad():
+        w2.mul_(0.5)                                                  # the down projection is linear in its weight
+    y2 = ex(paddle.to_tensor(x), counts)
+    assert ex._cache[1].fwd[0] is not q_first
+    assert rel(y2, yr.detach() * 0.5) < 0.08
