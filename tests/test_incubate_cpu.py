@@ -142,3 +142,33 @@ def test_mixtral_tiny_trains_on_cpu():
         losses.append(float(loss))
     assert losses[-1] < losses[0] and all(np.isfinite(losses))
     assert all(getattr(p, "is_moe_param", False) for p in m.layers[0].moe.experts.parameters())
+
+
+def test_mixtral_grouped_experts_equal_per_expert_layers():
+    """``expert_impl="grouped_fp8"`` stacks the experts' weights; off the GPU it computes plain per-expert products, so
+    loss and gradients equal those of the per-expert Linear layers holding the same weights."""
+    import torch
+    import paddle_b200 as paddle
+    from paddle_b200.models.mixtral import MixtralConfig, MixtralForCausalLM
+    paddle.seed(0)
+    grouped = MixtralForCausalLM(MixtralConfig.tiny(dtype="float32", expert_impl="grouped_fp8"))
+    paddle.seed(0)
+    loop = MixtralForCausalLM(MixtralConfig.tiny(dtype="float32"))
+    named = dict(loop.named_parameters())
+    with torch.no_grad():
+        for lg, ll in zip(grouped.layers, loop.layers):
+            for e, ex in enumerate(ll.moe.experts):
+                ex.gate_up_proj.weight.copy_(lg.moe.experts.gate_up_weight[e])
+                ex.down_proj.weight.copy_(lg.moe.experts.down_weight[e])
+        for k, p in grouped.named_parameters():
+            if "experts" not in k:
+                named[k].copy_(p)
+    ids = paddle.to_tensor(torch.randint(0, 512, (2, 16), generator=torch.Generator().manual_seed(1)).numpy())
+    a, b = grouped(ids, ids), loop(ids, ids)
+    a.backward(); b.backward()
+    assert abs(float(a) - float(b)) < 1e-6
+    lg, ll = grouped.layers[0], loop.layers[0]
+    for e, ex in enumerate(ll.moe.experts):
+        assert torch.allclose(lg.moe.experts.gate_up_weight.grad[e], ex.gate_up_proj.weight.grad, atol=1e-6)
+        assert torch.allclose(lg.moe.experts.down_weight.grad[e], ex.down_proj.weight.grad, atol=1e-6)
+    assert all(getattr(p, "is_moe_param", False) for p in lg.moe.experts.parameters())
