@@ -6,12 +6,13 @@ The reference runs every expert as its own pair of ``Linear`` layers on that exp
 stacked (``[E, K, N]``) and all experts run in one launch per GEMM:
 
 * forward   ``Y = grouped(Xq, Wq)``          X quantised per 1 x 128 block, W per 128 x 128 block (e4m3, fp32 scales)
-* dgrad     ``dX = grouped(dYq, (W^T)q)``    the same kernel on the transposed weights
+* dgrad     ``dX = grouped(dYq, (W^T)q)``    the same kernel on a byte-transposed copy of the e4m3 weights
 * wgrad     ``dW[e] = X_e^T dY_e``           bf16 operands on the plain tcgen05 GEMM, fp32 accumulation into
                                             ``main_grad`` when the parameter carries one
 
-Quantised weights are cached between optimizer steps (micro-batches of one step reuse them); call
-``weights_updated()`` after the optimizer has changed the parameters.  Off the GPU the same module computes the
+Quantised weights are cached between optimizer steps (micro-batches of one step reuse them) and keyed on the
+parameter's version counter, which this library's optimizers advance; ``weights_updated()`` drops them by hand for
+code that writes the parameters through other means.  Off the GPU the same module computes the
 per-expert products with plain matmuls, so routing and parity tests run anywhere."""
 from __future__ import annotations
 

@@ -75,7 +75,8 @@ class SoftmaxTopKGate(NaiveGate):
         self.set_loss(as_tensor(E * (frac * probs.mean(0)).sum()))
         if self.capacity_factor and self.capacity_factor > 0:
             cap = int(self.capacity_factor * x.shape[0] * self.top_k / E) + 1
-            rank_in = ((onehot.cumsum(0) - onehot) * onehot).sum(1)
+            oh_t = onehot.t().contiguous()              # scan along the contiguous axis: [E, T * k]
+            rank_in = ((oh_t.cumsum(1) - oh_t) * oh_t).sum(0)
             idx = torch.where(rank_in < cap, flat, torch.full_like(flat, -1)).reshape(idx.shape)
         return as_tensor(val.to(x.dtype)), as_tensor(idx)
 
