@@ -11,3 +11,4 @@ from .process_mesh import (Partial, Placement, ProcessMesh, ReduceType, Replicat
                            set_mesh)
 
 DistAttr = dict
+from .engine import Engine  # noqa: F401,E402

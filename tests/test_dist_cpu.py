@@ -97,3 +97,16 @@ def test_moe_expert_parallel_parity_cpu():
     res = run_workers("moe_ep.py", 2, timeout=180)
     for r in res:
         assert r["out"] < 1e-5 and r["dx"] < 1e-4 and r["dw"] < 1e-4 and r["moe_flag"]
+
+
+def test_auto_parallel_engine_two_ranks_cpu(tmp_path):
+    """``auto.Engine``: fit (gradient merge over 2 steps, global batch split over 2 ranks), evaluate, save / load.
+    Both ranks hold the same parameters after training and the loss falls."""
+    res = run_workers("auto_engine.py", 2, args=(str(tmp_path),), timeout=180)
+    assert abs(res[0]["checksum"] - res[1]["checksum"]) < 1e-4
+    for r in res:
+        assert r["steps"] == 5 * 8 and r["last"] < 0.5 * r["first"]
+        assert abs(r["restored"] - r["checksum"]) < 1e-5
+        assert r["eval"]["acc"] > 0.7
+    assert res[0]["eval"]["loss"] == res[1]["eval"]["loss"]           # averaged over ranks
+    assert res[0]["files"] == ["ck_dist0.pdopt", "ck_dist0.pdparams", "ck_dist1.pdopt", "ck_dist1.pdparams"]
