@@ -47,6 +47,12 @@ register("global_scatter", _lazy("paddle_b200.distributed.utils.moe_utils", "glo
 register("global_gather", _lazy("paddle_b200.distributed.utils.moe_utils", "global_gather"))
 register("fused_multi_transformer_", _lazy("paddle_b200.incubate.nn.functional", "fused_multi_transformer"))
 register("fused_linear_param_grad_add", _lazy("paddle_b200.incubate.nn.functional", "fused_linear_param_grad_add"))
+register("skip_layernorm", _lazy("paddle_b200.incubate.nn.functional", "skip_layernorm"))
+register("fused_embedding_eltwise_layernorm", _lazy("paddle_b200.incubate.nn.functional", "fused_embedding_eltwise_layernorm"))
+register("fused_gate_attention", _lazy("paddle_b200.incubate.nn.functional", "fused_gate_attention"))
+register("fused_dot_product_attention", _lazy("paddle_b200.incubate.nn.functional", "fused_dot_product_attention"))
+register("calc_reduced_attn_scores", _lazy("paddle_b200.nn.functional.flash_attention", "calc_reduced_attention_scores"))
+register("memory_efficient_attention", _lazy("paddle_b200.incubate.nn.memory_efficient_attention", "memory_efficient_attention"))
 register("number_count", _lazy("paddle_b200.distributed.models.moe.utils", "_number_count"))
 register("assign_pos", _lazy("paddle_b200.distributed.models.moe.utils", "_assign_pos"))
 register("limit_by_capacity", _lazy("paddle_b200.distributed.models.moe.utils", "_limit_by_capacity"))

@@ -6,3 +6,5 @@ from .layer.fused_transformer import (FusedBiasDropoutResidualLayerNorm, FusedDr
 
 __all__ = ["FusedMultiHeadAttention", "FusedFeedForward", "FusedTransformerEncoderLayer", "FusedMultiTransformer",
            "FusedLinear", "FusedBiasDropoutResidualLayerNorm", "FusedDropoutAdd"]
+from . import attn_bias  # noqa: F401,E402
+from .memory_efficient_attention import memory_efficient_attention  # noqa: F401,E402

@@ -493,3 +493,123 @@ def moe_ffn_fp8(permute_input, token_nums_per_expert, ffn1_q, ffn1_scale, ffn2_q
     a = native.swiglu_fwd(h)
     aq, as_ = native.fp8_quant_1x128(a)
     return as_tensor(native.grouped_gemm_fp8(aq, as_, ffn2_q, ffn2_scale, offsets))
+
+
+# ------------------------------------------------------------------ gate attention / cuDNN-style attention
+def fused_gate_attention(query, key=None, query_weight=None, key_weight=None, value_weight=None, qkv_weight=None,
+                         gate_linear_weight=None, gate_linear_bias=None, out_linear_weight=None, out_linear_bias=None,
+                         nonbatched_bias=None, attn_mask=None, has_gating=True, merge_qkv=True, use_flash_attn=False):
+    """AlphaFold-style gated self / cross attention over ``[batch, msa, res, dim]``
+    (python/paddle/incubate/nn/functional/fused_gate_attention.py:26): per-head projections, additive ``attn_mask``
+    and ``nonbatched_bias`` on the logits, a sigmoid gate on the attended values, output projection.
+    ``merge_qkv=True`` takes ``qkv_weight [3, heads, head_dim, q_dim]``; otherwise separate ``[dim, heads, head_dim]``
+    weights and an optional ``key`` tensor."""
+    q_data = query
+    if merge_qkv:
+        assert key is None and qkv_weight is not None
+        m_data = q_data
+        qkv = torch.einsum("nbqa,thca->tnbqhc", q_data, qkv_weight)
+        q, k, v = qkv[0], qkv[1], qkv[2]
+    else:
+        m_data = key if key is not None else q_data
+        q = torch.einsum("nbqa,ahc->nbqhc", q_data, query_weight)
+        k = torch.einsum("nbka,ahc->nbkhc", m_data, key_weight)
+        v = torch.einsum("nbka,ahc->nbkhc", m_data, value_weight)
+    q = q * (q.shape[-1] ** -0.5)
+    logits = torch.einsum("nbqhc,nbkhc->nbhqk", q, k)
+    if attn_mask is not None:
+        logits = logits + attn_mask
+    if nonbatched_bias is not None:
+        logits = logits + nonbatched_bias.unsqueeze(1)
+    weights = torch.softmax(logits, -1)
+    avg = torch.einsum("nbhqk,nbkhc->nbqhc", weights, v)
+    if has_gating:
+        gate = torch.einsum("nbqc,chv->nbqhv", q_data, gate_linear_weight) + gate_linear_bias
+        avg = avg * torch.sigmoid(gate)
+    out = torch.einsum("nbqhc,hco->nbqo", avg, out_linear_weight)
+    return as_tensor(out + out_linear_bias if out_linear_bias is not None else out)
+
+
+def fused_dot_product_attention(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=False,
+                                scaling_factor=None, training=True, name=None):
+    """``[batch, seq, heads, dim]`` attention (fused_dot_product_attention.py:129); ``attn_mask`` is boolean or 0/1
+    (nonzero = may attend) of shape ``[batch, 1 | heads, seq_q, seq_k]``.  Unmasked and causal calls without dropout
+    run on this library's flash-attention kernel."""
+    from ....nn.functional.flash_attention import _attention_math
+    from ....ops import functional as K
+    drop = dropout_p if training else 0.0
+    if attn_mask is None and drop == 0.0:
+        return as_tensor(K.flash_attention(query, key, value, is_causal, scaling_factor))
+    mask = None
+    if attn_mask is not None:
+        mask = attn_mask if attn_mask.dtype == torch.bool else attn_mask != 0
+        if is_causal:
+            mask = mask & torch.ones(query.shape[1], key.shape[1], dtype=torch.bool, device=mask.device).tril()
+    return as_tensor(_attention_math(query, key, value, mask, drop, is_causal, scaling_factor))
+
+
+def cudnn_flash_attention(q, k, v, bias=None, cu_seqlen_q=None, cu_seqlen_k=None, scaling_factor=1.0,
+                          dropout_prob=0.0, training=True, mask_type=None, bias_type=None, name=None):
+    """fused_dot_product_attention.py:21: ``mask_type`` in (None, "causal", "padding", "padding_causal"); padding
+    masks come from ``cu_seqlen_q`` / ``cu_seqlen_k`` (per-sequence valid lengths as prefix sums); ``bias`` is added
+    to the logits when ``bias_type`` is "pre_scale_bias" / "post_scale_bias"."""
+    from ....nn.functional.flash_attention import _attention_math
+    from ....ops import functional as K
+    causal = mask_type in ("causal", "padding_causal")
+    drop = dropout_prob if training else 0.0
+    if mask_type in (None, "causal") and bias is None and drop == 0.0:
+        return as_tensor(K.flash_attention(q, k, v, causal, scaling_factor))
+    B, Sq, Sk = q.shape[0], q.shape[1], k.shape[1]
+    add = torch.zeros(B, 1, Sq, Sk, dtype=q.dtype, device=q.device)
+    if mask_type in ("padding", "padding_causal"):
+        lq = (cu_seqlen_q[1:] - cu_seqlen_q[:-1]).reshape(B, 1, 1, 1)
+        lk = (cu_seqlen_k[1:] - cu_seqlen_k[:-1]).reshape(B, 1, 1, 1)
+        ok = (torch.arange(Sq, device=q.device).reshape(1, 1, Sq, 1) < lq) & \
+             (torch.arange(Sk, device=q.device).reshape(1, 1, 1, Sk) < lk)
+        add = add.masked_fill(~ok, float("-inf"))
+    if causal:
+        tri = torch.ones(Sq, Sk, dtype=torch.bool, device=q.device).tril()
+        add = add.masked_fill(~tri, float("-inf"))
+    if bias is not None and bias_type in ("pre_scale_bias", "post_scale_bias"):
+        add = add + (bias * scaling_factor if bias_type == "pre_scale_bias" else bias)
+    out = _attention_math(q, k, v, add, drop, False, scaling_factor)
+    return as_tensor(torch.nan_to_num(out))          # fully padded query rows produce zeros
+
+
+def fused_linear_param_grad_add(x, dout, dweight=None, dbias=None, multi_precision=True, has_bias=True):
+    """``dweight (+)= x^T dout`` and ``dbias (+)= sum(dout)`` accumulated into existing (fp32 when ``multi_precision``)
+    buffers, created when absent (paddle/phi/ops/yaml/fused_ops.yaml:382; kernel
+    paddle/phi/kernels/fusion/gpu/fused_linear_param_grad_add_kernel.cu:36).  bf16 operands with an fp32 ``dweight``
+    run on the tcgen05 GEMM with its reduce-add epilogue, so no temporary dW is written."""
+    from ....ops import native
+    x2, d2 = x.reshape(-1, x.shape[-1]), dout.reshape(-1, dout.shape[-1])
+    acc_dtype = torch.float32 if multi_precision else x.dtype
+    if dweight is None:
+        dweight = torch.zeros(x2.shape[1], d2.shape[1], dtype=acc_dtype, device=x.device)
+    if (x.is_cuda and x2.dtype == torch.bfloat16 and d2.dtype == torch.bfloat16 and dweight.dtype == torch.float32
+            and x2.shape[1] % 8 == 0 and d2.shape[1] % 8 == 0 and dweight.is_contiguous()):
+        native.gemm(x2.contiguous(), d2.contiguous(), trans_a=True, out=dweight, accumulate=True)
+    else:
+        dweight.add_((x2.float().t() @ d2.float()).to(dweight.dtype))
+    if has_bias:
+        if dbias is None:
+            dbias = torch.zeros(d2.shape[1], dtype=acc_dtype, device=x.device)
+        dbias.add_(d2.float().sum(0).to(dbias.dtype))
+    return as_tensor(dweight), (as_tensor(dbias) if has_bias else None)
+
+
+def skip_layernorm(x, y, scale, bias, epsilon, begin_norm_axis):
+    """``layer_norm(x + y)`` (paddle/phi/ops/yaml/fused_ops.yaml:787)."""
+    from ....ops import functional as K
+    s = x + y
+    return as_tensor(K.layer_norm(s, s.shape[begin_norm_axis:], scale, bias, epsilon))
+
+
+def fused_embedding_eltwise_layernorm(ids, embs, bias, scale, epsilon=1e-5):
+    """Sum of several embedding lookups followed by layer norm over the hidden axis (fused_ops.yaml:363)."""
+    from ....ops import functional as K
+    acc = None
+    for i, w in zip(ids, embs):
+        e = torch.nn.functional.embedding(i.squeeze(-1) if i.dim() == 3 else i, w)
+        acc = e if acc is None else acc + e
+    return as_tensor(K.layer_norm(acc, acc.shape[-1:], scale, bias, epsilon))

@@ -95,3 +95,74 @@ class ModelAverage:
 
 from ...optimizer.extras import LBFGS  # noqa: E402,F401
 from . import functional  # noqa: E402,F401
+
+
+class DistributedFusedLamb:
+    """LAMB whose gradients are averaged over all ranks before the update
+    (python/paddle/incubate/optimizer/distributed_fused_lamb.py:121).  The reference keeps every parameter, gradient
+    and moment in fused flat buffers sharded over the ranks of a node; here the update itself is
+    ``paddle.optimizer.Lamb`` with fp32 master weights, preceded by one all-reduce per gradient, global-norm clipping
+    before or after that all-reduce (``clip_after_allreduce``) and gradient accumulation over
+    ``gradient_accumulation_steps`` calls of ``step``."""
+
+    def __init__(self, learning_rate=0.001, lamb_weight_decay=0.01, beta1=0.9, beta2=0.999, epsilon=1e-6,
+                 parameters=None, grad_clip=None, exclude_from_weight_decay_fn=None, clip_after_allreduce=True,
+                 is_grad_scaled_by_nranks=True, alignment=128, use_master_param_norm=True,
+                 gradient_accumulation_steps=1, use_master_acc_grad=True, nproc_per_node=None,
+                 use_hierarchical_allreduce=False, name=None):
+        from ...optimizer import Lamb
+        self._inner = Lamb(learning_rate, lamb_weight_decay, beta1, beta2, epsilon, parameters, None,
+                           exclude_from_weight_decay_fn, multi_precision=True, name=name)
+        self._clip, self._clip_after = grad_clip, clip_after_allreduce
+        self._scaled_by_nranks = is_grad_scaled_by_nranks
+        self._acc_steps, self._acc_i = int(gradient_accumulation_steps), 0
+        self._scale = None
+
+    def __getattr__(self, name):
+        return getattr(self.__dict__["_inner"], name)
+
+    def _set_scale(self, scale):
+        """Loss-scaling factor the gradients carry (divided out before the update)."""
+        self._scale = scale
+
+    def _params_with_grad(self):
+        return [p for p in self._inner._parameter_list if getattr(p, "grad", None) is not None]
+
+    def _apply_clip(self, params):
+        if self._clip is not None:
+            for (p, g) in self._clip([(p, p.grad) for p in params]):
+                if g is not p.grad:
+                    p.grad.copy_(g)
+
+    def step(self):
+        from ...distributed import collective as C
+        self._acc_i += 1
+        if self._acc_i % self._acc_steps != 0:
+            return                                       # gradients keep accumulating in .grad
+        params = self._params_with_grad()
+        world = C.get_world_size() if C.is_initialized() else 1
+        if self._scale is not None:
+            for p in params:
+                p.grad.div_(float(self._scale))
+        if not self._clip_after:
+            self._apply_clip(params)
+        if world > 1:
+            for p in params:
+                C.all_reduce(p.grad)
+                if not self._scaled_by_nranks:
+                    p.grad.div_(world)
+        if self._acc_steps > 1:
+            for p in params:
+                p.grad.div_(self._acc_steps)
+        if self._clip_after:
+            self._apply_clip(params)
+        self._inner.step()
+
+    def clear_grad(self, set_to_zero=True):
+        if self._acc_i % self._acc_steps == 0:
+            self._inner.clear_grad(set_to_zero)
+
+    def minimize(self, loss, startup_program=None, parameters=None, no_grad_set=None):
+        loss.backward()
+        self.step()
+        self.clear_grad()

@@ -83,3 +83,22 @@ def flashmask_attention(query, key, value, startend_row_indices=None, *, dropout
                 (rows >= idx[..., 2].unsqueeze(2)) & (rows < idx[..., 3].unsqueeze(2)))
     mask = torch.zeros(masked.shape, dtype=query.dtype, device=query.device).masked_fill(masked, float("-inf"))
     return _attention_math(query, key, value, mask, dropout if training else 0.0, False)
+
+
+def calc_reduced_attention_scores(query, key, softmax_lse):
+    """``sum over queries of softmax(Q K^T / sqrt(d))`` -> ``[batch, heads, 1, seq_k]`` fp32
+    (python/paddle/nn/functional/flash_attention.py:2033), from the row log-sum-exp the attention forward returned
+    (``[batch, heads, >= seq_q]``), so the probabilities are rebuilt one key block at a time and never stored whole."""
+    b, sq, h, d = query.shape
+    sk = key.shape[1]
+    qh = query.transpose(1, 2).float() * (d ** -0.5)
+    kh = key.transpose(1, 2).float()
+    if kh.shape[1] != h:
+        kh = kh.repeat_interleave(h // kh.shape[1], 1)
+    lse = softmax_lse[:, :, :sq].float().unsqueeze(-1)
+    out = torch.empty(b, h, 1, sk, dtype=torch.float32, device=query.device)
+    blk = 2048
+    for s0 in range(0, sk, blk):
+        p = torch.exp(qh @ kh[:, :, s0:s0 + blk].transpose(-1, -2) - lse)
+        out[:, :, 0, s0:s0 + blk] = p.sum(2)
+    return out

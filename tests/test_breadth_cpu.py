@@ -301,3 +301,79 @@ def test_fleet_metrics_single_worker():
     # 4 positives (one in the middle bucket, three in the top one), 4 negatives (three at the bottom, one in the
     # middle): 15.5 of 16 ordered pairs are ranked correctly (a tie counts one half)
     assert m.auc(np.array([0, 1, 3.0]), np.array([3, 1, 0.0])) == pytest.approx(15.5 / 16)
+
+
+def test_memory_efficient_attention_masks_and_related_fused_attention_ops():
+    """attn_bias descriptions (causal, block-diagonal packed sequences, padded-key decoding) against dense per-sequence
+    attention; fused_gate_attention merged vs separate projections; fused_dot_product_attention mask vs causal flag;
+    cudnn_flash_attention padding mask; calc_reduced_attention_scores against the dense softmax."""
+    import torch
+    from paddle_b200.incubate.nn import attn_bias as ab
+    from paddle_b200.incubate.nn import functional as IF
+    from paddle_b200.incubate.nn.memory_efficient_attention import memory_efficient_attention as mea
+    from paddle_b200.nn.functional.flash_attention import calc_reduced_attention_scores
+    sdpa = torch.nn.functional.scaled_dot_product_attention
+    torch.manual_seed(0)
+
+    def dense(q, k, v, causal=False):
+        return sdpa(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal).transpose(1, 2)
+    q, k, v = (torch.randn(1, 10, 2, 8) for _ in range(3))
+    ref = torch.cat([dense(q[:, a:b], k[:, a:b], v[:, a:b], True) for a, b in ((0, 4), (4, 10))], 1)
+    mask = ab.BlockDiagonalCausalMask.from_seqlens([4, 6])
+    assert torch.allclose(mea(q, k, v, mask), ref, atol=1e-6)
+    assert torch.allclose(mea(q, k, v, torch.as_tensor(mask.materialize((1, 2, 10, 10)))), ref, atol=1e-6)
+    assert torch.allclose(mea(q, k, v, ab.LowerTriangularMask()), dense(q, k, v, True), atol=1e-6)
+    m2, packed = ab.BlockDiagonalMask.from_tensor_list([torch.randn(2, 3, 2, 8), torch.randn(1, 4, 2, 8)])
+    assert packed.shape == [1, 10, 2, 8] and [t.shape[0] for t in m2.split(packed)] == [2, 1]
+    pm = ab.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens([1, 1], 8, [5, 3])
+    qq, kk = torch.randn(1, 2, 2, 8), torch.randn(1, 16, 2, 8)
+    out = mea(qq, kk, kk, pm)
+    assert torch.allclose(out[:, :1], dense(qq[:, :1], kk[:, :5], kk[:, :5]), atol=1e-6)
+    assert torch.allclose(out[:, 1:], dense(qq[:, 1:], kk[:, 8:11], kk[:, 8:11]), atol=1e-6)
+
+    n, b, r, a, h, c = 2, 3, 5, 8, 2, 4
+    x = torch.randn(n, b, r, a)
+    qkv, gw, gb, ow, ob = torch.randn(3, h, c, a), torch.randn(a, h, c), torch.randn(h, c), torch.randn(h, c, a), torch.randn(a)
+    nb, am = torch.randn(n, h, r, r), torch.zeros(n, b, 1, 1, r)
+    kw = dict(gate_linear_weight=gw, gate_linear_bias=gb, out_linear_weight=ow, out_linear_bias=ob, nonbatched_bias=nb, attn_mask=am)
+    o1 = IF.fused_gate_attention(x, qkv_weight=qkv, **kw)
+    o2 = IF.fused_gate_attention(x, key=x, query_weight=qkv[0].permute(2, 0, 1), key_weight=qkv[1].permute(2, 0, 1),
+                                 value_weight=qkv[2].permute(2, 0, 1), merge_qkv=False, **kw)
+    assert o1.shape == [n, b, r, a] and torch.allclose(o1, o2, atol=1e-5)
+
+    y = torch.randn(2, 6, 2, 8)
+    assert torch.allclose(IF.fused_dot_product_attention(y, y, y, attn_mask=torch.ones(2, 1, 6, 6).tril()),
+                          IF.fused_dot_product_attention(y, y, y, is_causal=True), atol=1e-6)
+    cu = torch.tensor([0, 4, 10])
+    o3 = IF.cudnn_flash_attention(y, y, y, cu_seqlen_q=cu, cu_seqlen_k=cu, scaling_factor=8 ** -0.5, mask_type="padding")
+    assert torch.allclose(o3[:1, :4], dense(y[:1, :4], y[:1, :4], y[:1, :4]), atol=1e-6) and float(o3[0, 4:].abs().max()) == 0
+
+    q5, k7 = torch.randn(2, 5, 3, 8), torch.randn(2, 7, 3, 8)
+    s = (q5.transpose(1, 2) @ k7.transpose(1, 2).transpose(-1, -2)) * 8 ** -0.5
+    red = calc_reduced_attention_scores(q5, k7, torch.logsumexp(s, -1))
+    assert red.shape == (2, 3, 1, 7) and torch.allclose(red[:, :, 0], torch.softmax(s, -1).sum(2), atol=1e-5)
+
+
+def test_fused_linear_param_grad_add_and_distributed_fused_lamb():
+    import torch
+    import paddle_b200 as paddle
+    from paddle_b200 import _C_ops
+    from paddle_b200.incubate.optimizer import DistributedFusedLamb
+    x, d = torch.randn(6, 8), torch.randn(6, 4)
+    dw, db = _C_ops.fused_linear_param_grad_add(x, d, None, None, True, True)
+    dw, db = _C_ops.fused_linear_param_grad_add(x, d, dw, db, True, True)
+    assert torch.allclose(dw, 2 * x.t() @ d, atol=1e-5) and torch.allclose(db, 2 * d.sum(0), atol=1e-5)
+    s = _C_ops.skip_layernorm(x, x, torch.ones(8), torch.zeros(8), 1e-5, 1)
+    assert torch.allclose(s, torch.nn.functional.layer_norm(2 * x, (8,)), atol=1e-5)
+    paddle.seed(0)
+    lin = paddle.nn.Linear(4, 3)
+    opt = DistributedFusedLamb(0.01, parameters=lin.parameters(), gradient_accumulation_steps=2,
+                               grad_clip=paddle.nn.ClipGradByGlobalNorm(1.0))
+    w0 = lin.weight.clone()
+    moved = []
+    for _ in range(2):
+        lin(paddle.randn([5, 4])).sum().backward()
+        opt.step()
+        opt.clear_grad()
+        moved.append(float((lin.weight - w0).abs().max()))
+    assert moved[0] == 0.0 and moved[1] > 0.0           # the update happens on every second call
