@@ -377,3 +377,34 @@ def test_fused_linear_param_grad_add_and_distributed_fused_lamb():
         opt.clear_grad()
         moved.append(float((lin.weight - w0).abs().max()))
     assert moved[0] == 0.0 and moved[1] > 0.0           # the update happens on every second call
+
+
+def test_pp_parallel_adaptor_repartitions_stage_checkpoints(tmp_path):
+    """4 pipeline stages -> 2 stages x 2 virtual chunks -> 1 stage: the layers keep their global order and values."""
+    import torch
+    import paddle_b200 as paddle
+    from paddle_b200.distributed.fleet.utils.pp_parallel_adaptor import ParallelConfig, PipeLineModelAdaptor
+    n_layers = 10                                  # embedding + 8 blocks + head
+    cuts = [0, 3, 5, 7, 10]
+    src = tmp_path / "pp4"
+    for k in range(4):
+        sd = {}
+        for local, g in enumerate(range(cuts[k], cuts[k + 1])):
+            sd[f"_layers.{local}.weight"] = torch.full((2, 2), float(g))
+            sd[f"_layers.{local}.fc.bias"] = torch.full((2,), float(g) + 0.5)
+        if k in (0, 3):
+            sd["_layers.shared_layers.emb.weight"] = torch.ones(3)
+        d = src / f"mp_00_sharding_00_pp_{k:02d}"
+        d.mkdir(parents=True)
+        paddle.save(sd, str(d / "model.pdparams"))
+    mid, one = tmp_path / "pp2v2", tmp_path / "pp1"
+    PipeLineModelAdaptor(ParallelConfig(1, 4), ParallelConfig(1, 2, vpp=2), 8, "layer").apply(str(src), str(mid))
+    r0 = paddle.load(str(mid / "mp_00_sharding_00_pp_00" / "model.pdparams"))
+    # rank 0 holds virtual stages 0 and 2: layers 0-2 (embedding + 2 blocks) and 5-6
+    assert float(r0["_layers.0.0.weight"][0, 0]) == 0.0 and float(r0["_layers.0.2.weight"][0, 0]) == 2.0
+    assert float(r0["_layers.1.0.weight"][0, 0]) == 5.0 and float(r0["_layers.1.1.fc.bias"][0]) == 6.5
+    assert "_layers.shared_layers.emb.weight" in r0
+    PipeLineModelAdaptor(ParallelConfig(1, 2, vpp=2), ParallelConfig(1, 1), 8, "uniform").apply(str(mid), str(one))
+    full = paddle.load(str(one / "mp_00_sharding_00_pp_00" / "model.pdparams"))
+    assert [float(full[f"_layers.{g}.weight"][0, 0]) for g in range(n_layers)] == [float(g) for g in range(n_layers)]
+    assert float(full["_layers.9.fc.bias"][1]) == 9.5
