@@ -144,3 +144,55 @@ def is_fused_matmul_bias_supported():
 def is_fused_linear_param_grad_add_supported():
     """Weight gradients are accumulated into fp32 ``main_grad`` by the GEMM epilogue on GPU."""
     return torch.cuda.is_available()
+
+
+class InnerOverlapLinear(torch.autograd.Function):
+    """Column-parallel linear whose backward starts the all-reduce of the input gradient over the tensor-parallel
+    group and computes the weight / bias gradients while it is in flight (mp_layers.py:190).  With
+    ``mp_fused_linear_param_grad_add`` the weight gradient is accumulated straight into ``weight.main_grad``."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, fuse_matmul_bias, mp_async_allreduce, mp_skip_c_identity,
+                mp_fused_linear_param_grad_add, model_parallel_group):
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias, ctx.group, ctx.fused_add, ctx.w_ref, ctx.b_ref = bias is not None, model_parallel_group, \
+            mp_fused_linear_param_grad_add, weight, bias
+        y = torch.matmul(x, weight)
+        return y if bias is None else y + bias
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .... import collective as C
+        x, weight = ctx.saved_tensors
+        dx = torch.matmul(dy, weight.t())
+        g = ctx.group
+        task = C.all_reduce(dx, group=g, sync_op=False) if (g is not None and g.nranks > 1) else None
+        x2, d2 = x.reshape(-1, x.shape[-1]), dy.reshape(-1, dy.shape[-1])
+        dw = db = None
+        if ctx.fused_add and getattr(ctx.w_ref, "main_grad", None) is not None:
+            from .....incubate.nn.functional import fused_linear_param_grad_add
+            bias_acc = getattr(ctx.b_ref, "main_grad", None) if ctx.has_bias else None
+            fused_linear_param_grad_add(x2, d2, ctx.w_ref.main_grad, bias_acc, True, ctx.has_bias and bias_acc is not None)
+            if ctx.has_bias and bias_acc is None:
+                db = d2.sum(0)
+        else:
+            dw = x2.t() @ d2
+            db = d2.sum(0) if ctx.has_bias else None
+        if task is not None:
+            task.wait()
+        return dx, dw, db, None, None, None, None, None
+
+
+class ParallelMultiLabelCrossEntropy(Layer):
+    """Vocab-parallel cross entropy with several weighted labels per row (mp_layers.py:796)."""
+
+    def __init__(self, mp_group=None, name=None, ignore_index=-100, sum_multi_label_loss=True):
+        super().__init__()
+        self.name = name
+        self.model_parallel_group = mp_group
+        self.ignore_index, self.sum_multi_label_loss = ignore_index, sum_multi_label_loss
+
+    def forward(self, input, label, smooth_weight):
+        return mp_ops._c_softmax_with_multi_label_cross_entropy(
+            input, label, smooth_weight, group=self.model_parallel_group, ignore_index=self.ignore_index,
+            sum_multi_label_loss=self.sum_multi_label_loss)

@@ -174,6 +174,23 @@ def _c_softmax_with_cross_entropy(logits, label, group=None, return_softmax=Fals
     return loss
 
 
+def _c_softmax_with_multi_label_cross_entropy(logits, label, smooth_weight, group=None, return_softmax=False,
+                                              ignore_index=-100, sum_multi_label_loss=True):
+    """Vocab-parallel cross entropy against several labels per row, each weighted by ``smooth_weight``
+    (mp_ops.py:461): ``loss[..., l] = smooth_weight[..., l] * CE(logits, label[..., l])``, summed over ``l`` when
+    ``sum_multi_label_loss``.  ``label`` and ``smooth_weight`` are ``[..., L]``."""
+    if label.shape != smooth_weight.shape:
+        raise ValueError(f"label {list(label.shape)} and smooth_weight {list(smooth_weight.shape)} must agree")
+    if label.dim() == logits.dim() - 1:
+        label, smooth_weight = label.unsqueeze(-1), smooth_weight.unsqueeze(-1)
+    losses = []
+    for l in range(label.shape[-1]):
+        one = _c_softmax_with_cross_entropy(logits, label[..., l], group=group, ignore_index=ignore_index)
+        losses.append(one * smooth_weight[..., l].to(one.dtype))
+    out = torch.stack(losses, -1)
+    return as_tensor(out.sum(-1, keepdim=True) if sum_multi_label_loss else out)
+
+
 def split(x, size, operation, axis=0, num_partitions=1, gather_out=True, weight_attr=None, bias_attr=None, name=None):
     """Build a parallel linear / embedding on the fly (mp_ops.py:773)."""
     from .mp_layers import ColumnParallelLinear, RowParallelLinear, VocabParallelEmbedding

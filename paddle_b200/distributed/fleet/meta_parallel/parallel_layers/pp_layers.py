@@ -261,3 +261,20 @@ class PipelineLayer(Layer):
                 fn = os.path.join(path, self._ckpt_name(self._start_pos + i, mp_rank))
                 if os.path.exists(fn):
                     f.set_state_dict(load(fn))
+
+
+class PipelineSublayers(Layer):
+    """The callables of one pipeline chunk as a Layer: sub-layers are registered under their position so that
+    ``state_dict`` keys are ``<index>.<parameter>`` (pp_layers.py:241)."""
+
+    def __init__(self, run_function):
+        super().__init__()
+        self.run_function = run_function
+        for idx, sub in enumerate(run_function):
+            if isinstance(sub, Layer):
+                self.add_sublayer(str(idx), sub)
+
+    def forward(self, x):
+        for f in self.run_function:
+            x = f(x)
+        return x

@@ -288,3 +288,15 @@ def create_fused_allreduce_gradient_hook(parameter_list, accumulation_steps):
                 x.copy_(flat[off:off + x.numel()].view_as(x))
                 off += x.numel()
     return hook
+
+
+def is_fused_matmul_bias_supported():
+    """Whether GEMM + bias runs as one kernel (sequence_parallel_utils.py:229 asks for cuBLASLt's epilogue): here
+    when the sm_100a kernel library is loadable on a GPU."""
+    if not torch.cuda.is_available():
+        return False
+    try:
+        from ....ops import _lib
+        return _lib.kernels() is not None
+    except Exception:
+        return False

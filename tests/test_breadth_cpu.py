@@ -408,3 +408,65 @@ def test_pp_parallel_adaptor_repartitions_stage_checkpoints(tmp_path):
     full = paddle.load(str(one / "mp_00_sharding_00_pp_00" / "model.pdparams"))
     assert [float(full[f"_layers.{g}.weight"][0, 0]) for g in range(n_layers)] == [float(g) for g in range(n_layers)]
     assert float(full["_layers.9.fc.bias"][1]) == 9.5
+
+
+def test_sharding_grad_views_and_storage_helpers():
+    """build_reduce_scatter_buffer: parameters live in one flat buffer cut into equal shards; each view knows the slice
+    its rank owns; gradients written by backward land in the flat gradient buffer.  filter_params / obtain_storage."""
+    import torch
+    import paddle_b200 as paddle
+    from paddle_b200.distributed.fleet.utils import tensor_fusion_helper as H
+    paddle.seed(0)
+    net = paddle.nn.Sequential(paddle.nn.Linear(10, 7), paddle.nn.Linear(7, 3))
+    params = list(net.parameters())
+    before = [p.detach().clone() for p in params]
+    views, total, pbuf, gbuf = H.build_reduce_scatter_buffer(params, sharding_degree=2, rank=1)
+    assert total % (2 * 64) == 0 and pbuf.numel() == total and gbuf.numel() == total
+    for p, b in zip(params, before):
+        assert torch.equal(p, b) and p.data_ptr() >= pbuf.data_ptr()          # same values, now inside the buffer
+    net(paddle.randn([4, 10])).sum().backward()
+    off = views[params[0].name]._index
+    assert torch.equal(gbuf[off:off + 70].view(10, 7), params[0].grad)
+    shard = total // 2
+    owned = sum(max(0, v._param_end - v._param_begin) for v in views.values())
+    assert 0 < owned <= shard
+    for v in views.values():
+        assert v._param_begin >= shard or v._param_begin >= v._param_end       # rank 1 owns the upper half only
+    sl = paddle.zeros([1])
+    last = views[params[-1].name]
+    last.assign_slice_grad(sl)
+    assert sl.numel() == last._param_end - last._param_begin and sl.grad.numel() == sl.numel()
+    fp32, dt = H.filter_params(params, is_fp32=True, is_distributed=False, need_clip=True)
+    assert len(fp32) == 4 and dt == torch.float32
+    assert H.filter_params(params, False, False, True) == ([], None)
+    net2 = paddle.nn.Linear(6, 6)
+    storage, bufs = H.obtain_storage(list(net2.parameters()), comm_overlap=True, comm_group=None)
+    assert len(storage) == 1 and storage[0].need_clip and len(bufs) == 1
+    net2(paddle.randn([2, 6])).sum().backward()
+    assert sum(bufs[0]._checked_in.values()) == 2                              # both gradients checked in by their hooks
+    assert H.get_grad_address(net2.weight, False) == net2.weight.grad.data_ptr()
+
+
+def test_inner_overlap_linear_and_multi_label_parallel_cross_entropy():
+    import torch
+    import paddle_b200 as paddle
+    from paddle_b200.distributed.fleet.layers.mpu.mp_layers import InnerOverlapLinear, ParallelMultiLabelCrossEntropy
+    torch.manual_seed(0)
+    x, w, b = torch.randn(3, 5, 4, requires_grad=True), torch.randn(4, 6, requires_grad=True), torch.randn(6, requires_grad=True)
+    InnerOverlapLinear.apply(x, w, b, False, True, True, False, None).square().sum().backward()
+    x2, w2, b2 = (t.detach().clone().requires_grad_(True) for t in (x, w, b))
+    (x2 @ w2 + b2).square().sum().backward()
+    for a, r in ((x, x2), (w, w2), (b, b2)):
+        assert torch.allclose(a.grad, r.grad, atol=1e-5)
+    w.main_grad = torch.zeros(4, 6)
+    w.grad = None
+    InnerOverlapLinear.apply(x, w, None, False, True, True, True, None).square().sum().backward()
+    assert w.grad is None and float(w.main_grad.abs().sum()) > 0            # accumulated into main_grad
+    one_rank = type("Group", (), {"nranks": 1, "rank": 0})()
+    logits, lab, sw = torch.randn(4, 10), torch.randint(0, 10, (4, 3)), torch.rand(4, 3)
+    loss = ParallelMultiLabelCrossEntropy(mp_group=one_rank)(paddle.to_tensor(logits), paddle.to_tensor(lab), paddle.to_tensor(sw))
+    ref = sum(torch.nn.functional.cross_entropy(logits, lab[:, l], reduction="none") * sw[:, l] for l in range(3))
+    assert loss.shape == [4, 1] and torch.allclose(loss.squeeze(-1), ref, atol=1e-5)
+    per = ParallelMultiLabelCrossEntropy(mp_group=one_rank, sum_multi_label_loss=False)(
+        paddle.to_tensor(logits), paddle.to_tensor(lab), paddle.to_tensor(sw))
+    assert per.shape == [4, 3]
