@@ -80,6 +80,19 @@ def decorate(models, optimizers=None, level="O1", dtype="float16", master_weight
 amp_decorate = decorate
 
 
+def _optimizer_chain(optimizer):
+    """``optimizer`` and every optimizer it wraps (HybridParallelOptimizer -> sharding optimizer -> AdamW ...)."""
+    chain, seen = [], set()
+    o = optimizer
+    while o is not None and id(o) not in seen:
+        chain.append(o)
+        seen.add(id(o))
+        d = getattr(o, "__dict__", {})
+        o = next((d[k] for k in ("_inner_opt", "_optim", "_inner_optimizer", "_optimizer", "_opt") if d.get(k) is not None),
+                 None)
+    return chain
+
+
 class GradScaler:
     """Dynamic loss scaling: ``scale(loss)``, ``step(opt)`` (unscale + finite check + conditional
     update, all on device), ``update()``."""
@@ -123,8 +136,19 @@ class GradScaler:
     def unscale_(self, optimizer):
         if not self._enable or self._unscaled:
             return
+        # an optimizer facade may still hold reductions that produce gradients (sharding stage 3 finishes the
+        # reduce-scatter of its last units here): they must land before anything is unscaled or checked
+        pre = getattr(optimizer, "_before_unscale", None)
+        if pre is not None:
+            pre()
         grads = self._grads(optimizer)
         if not grads:
+            # a rank without local gradients still takes part in the agreement on found_inf: the wrappers for
+            # hybrid / sharded training all-reduce inside _sync_found_inf and every rank has to call it
+            params = getattr(optimizer, "_parameter_list", None) or []
+            dev = params[0].device if params else torch.device("cpu")
+            self._found_inf = self._sync_found_inf(torch.zeros(1, dtype=torch.int32, device=dev))
+            self._unscaled = True
             return
         dev = grads[0].device
         found = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -148,12 +172,24 @@ class GradScaler:
         if not self._enable:
             return optimizer.step()
         self.unscale_(optimizer)
-        optimizer._skip_flag = self._found_inf
+        # the flag has to reach the optimizer that applies the update: the hybrid / sharding wrappers delegate
+        # attribute reads to the optimizer they wrap but keep what is assigned on themselves
+        chain = _optimizer_chain(optimizer)
+        for o in chain:
+            o._skip_flag = self._found_inf
+        counts = [(o, o.__dict__["_step_count"]) for o in chain if "_step_count" in getattr(o, "__dict__", {})]
         try:
             optimizer.step()
         finally:
-            optimizer._skip_flag = None
+            for o in chain:
+                o._skip_flag = None
         self._cache_founf_inf = bool(self._found_inf.item()) if self._found_inf is not None else False
+        if self._cache_founf_inf:
+            # the update kernels left parameters and moments untouched (device-side flag); the host-side step counter
+            # that feeds the bias correction must not advance either (the reference's adamw skips its beta-power
+            # update under found_inf: paddle/phi/kernels/gpu/adamw_kernel.cu, skip_update)
+            for o, c in counts:
+                o._step_count = c
 
     def minimize(self, optimizer, *args, **kwargs):
         self.step(optimizer)

@@ -56,10 +56,46 @@ def compute_overlap(cur_offset, cur_shape, src_offset, src_shape):
     return tuple(cur_off), tuple(src_off), tuple(lengths)
 
 
+def get_max_id(path):
+    """Newest checkpoint version under ``path``: the largest numeric id among ``{id}.metadata`` /
+    ``{rank}_{id}.distcp`` files (python/paddle/distributed/checkpoint/utils.py:124).  Ids are compared as
+    integers: a lexicographic order would put version 9 after version 10."""
+    ids = []
+    for f in os.listdir(path):
+        stem, dot, ext = f.rpartition(".")
+        if ext == "metadata" and stem.isdigit():
+            ids.append(int(stem))
+        elif ext == "distcp":
+            tail = stem.rpartition("_")[2]
+            if tail.isdigit():
+                ids.append(int(tail))
+    return max(ids) if ids else None
+
+
+def _agree_on_id(unique_id, process_group, coordinator_rank=0):
+    """Every rank must read the same version: the coordinator's choice is broadcast (a periodic save that is running
+    while a late rank lists the directory would otherwise let ranks pick different ids;
+    python/paddle/distributed/checkpoint/utils.py:135 ``check_unique_id``)."""
+    if C.is_initialized() and C.get_world_size() > 1:
+        box = [unique_id]
+        ranks = getattr(process_group, "ranks", None)
+        src = ranks[coordinator_rank] if ranks else coordinator_rank
+        C.broadcast_object_list(box, src=src, group=process_group)
+        return box[0]
+    return unique_id
+
+
 def _metadata_files(path, unique_id=None):
-    files = sorted(f for f in os.listdir(path) if f.endswith(".metadata"))
+    """The metadata of ONE checkpoint version: ``unique_id`` or, when it is None, the newest one under ``path``
+    (load_state_dict.py:590,871 use ``get_max_id``).  Metadata files whose name is not a number (hand-made merges)
+    are only read when no numbered version exists."""
+    if unique_id is None:
+        unique_id = get_max_id(path)
     if unique_id is not None:
-        files = [f for f in files if f == f"{unique_id}.metadata"]
+        files = [f"{unique_id}.metadata"]
+        assert os.path.exists(os.path.join(path, files[0])), f"no {files[0]} under {path}"
+    else:
+        files = sorted(f for f in os.listdir(path) if f.endswith(".metadata"))
     assert files, f"no .metadata file under {path}"
     return [_load_verified(os.path.join(path, f)) for f in files]
 
@@ -93,6 +129,8 @@ def load_state_dict(state_dict, path, process_group=None, coordinator_rank=0, un
     """Fills the tensors of ``state_dict`` in place."""
     assert isinstance(state_dict, dict)
     flat, _ = flatten_state_dict(state_dict)
+    if unique_id is None:
+        unique_id = _agree_on_id(get_max_id(path), process_group, coordinator_rank)
     metas = _metadata_files(path, unique_id)
     items = get_read_items(path, flat, metas)
     cache = {}

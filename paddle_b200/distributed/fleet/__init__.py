@@ -36,7 +36,8 @@ util = UtilBase()
 
 def __getattr__(name):
     if name in ("recompute", "recompute_hybrid", "recompute_sequential"):
-        from . import recompute as r
+        import importlib
+        r = importlib.import_module(__name__ + ".recompute")    # ("from . import" would re-enter this hook)
         return getattr(r, name) if name != "recompute" else r
     if name == "metrics":
         import importlib

@@ -150,9 +150,7 @@ def recompute_sequential(ctx, functions, *args, **kwargs):
     return x
 
 
-def recompute_hybrid(ctx, function, *args, **kwargs):
-    """Recompute with saved inputs partitioned over the model-parallel group (``ctx['mp_group']``) and/or
-    offloaded to host memory (``ctx['offload']``)."""
-    return recompute(function, *args, offload=ctx.get("offload", False),
-                     _partition_group=ctx.get("mp_group") if ctx.get("partition", False) else None,
-                     preserve_rng_state=ctx.get("preserve_rng_state", True), **kwargs)
+# the module of the same name is imported first and the name is then re-bound to the function, as in the reference
+# package (python/paddle/distributed/fleet/recompute/__init__.py)
+from . import recompute as _recompute_module  # noqa: E402,F401
+from .recompute_hybrid import recompute_hybrid  # noqa: E402,F401

@@ -131,6 +131,9 @@ class GroupShardedStage2(Layer):
             self._finish_reduce()
             inner_step()
         self._opt.step = step
+        # GradScaler.unscale_ runs before step(): the reductions in flight must have landed (and been averaged)
+        # before gradients are unscaled and checked for inf
+        self._opt._before_unscale = self._finish_reduce
 
     def _make_hook(self, p):
         owner = self._opt.param2rank[p.name]
@@ -411,6 +414,12 @@ class _Stage3Optimizer:
     def __init__(self, optim, model):
         self._optim, self._model = optim, model
 
+    def _before_unscale(self):
+        """Called by ``GradScaler.unscale_``: the reduce-scatter of the units whose backward ran last (embeddings,
+        first layer) has to finish before the gradients are unscaled, or those would be applied still multiplied
+        by the loss scale."""
+        self._model._finish_backward()
+
     def step(self):
         self._model._finish_backward()
         self._optim.step()
@@ -427,20 +436,24 @@ class _Stage3Optimizer:
 
 
 class GroupShardedScaler:
-    """GradScaler whose found-inf flag is agreed across the sharding group (group_sharded_utils.py:262)."""
+    """GradScaler whose found-inf flag is agreed across the sharding group: every rank checks only the gradient
+    partition it holds, so a rank that saw no inf must still skip the step when another did
+    (python/paddle/distributed/fleet/meta_parallel/sharding/group_sharded_utils.py:262-330, which all-reduces the flag
+    with MAX after ``check_finite_and_unscale``).  The scaler object itself is returned, with its
+    ``_sync_found_inf`` hook replaced; ``GradScaler.unscale_`` calls the hook on every rank, also on one that
+    holds no gradients."""
 
     def __new__(cls, scaler, group=None):
-        inner_unscale = scaler._unscale
         g = group or C._get_default_group()
 
-        def unscale(optimizer):
-            inner_unscale(optimizer)
-            f = scaler._found_inf
-            if f is not None:
-                t = f.to(torch.int32)
+        def sync(found):
+            if g is not None and g.nranks > 1:
+                t = found.to(torch.int32)
                 C.all_reduce(t, op=C.ReduceOp.MAX, group=g)
-                f.copy_(t.to(f.dtype))
-        scaler._unscale = unscale
+                found = t
+            return found
+        scaler._sync_found_inf = sync
+        scaler._sharding_group = g
         return scaler
 
 

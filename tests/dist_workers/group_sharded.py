@@ -50,10 +50,38 @@ for step in range(4):
                                            paddle.to_tensor(lab[sl].numpy()).reshape([-1]))
     b.backward(); opt.step(); opt.clear_grad()
     t = torch.tensor([float(b)]); dist.all_reduce(t); lp.append(float(t) / n)
+
+# ---- loss scaling through the scaler that group_sharded_parallel returns: a step whose loss is inf on rank 1 only must
+# be skipped on BOTH ranks; the next (finite) scaled step must equal the twin's plain step
+scaler_res = None
+if len(sys.argv) > 2 and sys.argv[2] == "scaler":
+    from paddle_b200.amp import GradScaler
+    from paddle_b200.distributed.sharding.group_sharded import GroupShardedScaler
+    scaler = GroupShardedScaler(GradScaler(init_loss_scaling=1024.0, decr_every_n_nan_or_inf=1))
+    before = {k: v.clone() for k, v in wrapped.state_dict().items()}
+    ids = torch.randint(0, 50, (4, 6), generator=gen)
+    out = wrapped(paddle.to_tensor(ids.numpy())).sum()
+    bad = out * (float("inf") if rank == 1 else 1.0)
+    scaler.scale(bad).backward()
+    scaler.step(opt); scaler.update(); opt.clear_grad()
+    after = wrapped.state_dict()
+    skipped = max(float((after[k].float() - v.float()).abs().max()) for k, v in before.items())
+    scale_after_inf = scaler._scale
+    ids = torch.randint(0, 50, (4 * n, 6), generator=gen)
+    lab = torch.randint(0, 50, (4 * n, 6), generator=gen)
+    a = paddle.nn.functional.cross_entropy(twin(paddle.to_tensor(ids.numpy())).reshape([-1, 50]),
+                                           paddle.to_tensor(lab.numpy()).reshape([-1]))
+    a.backward(); opt_t.step(); opt_t.clear_grad()
+    sl = slice(rank * 4, rank * 4 + 4)
+    b = paddle.nn.functional.cross_entropy(wrapped(paddle.to_tensor(ids[sl].numpy())).reshape([-1, 50]),
+                                           paddle.to_tensor(lab[sl].numpy()).reshape([-1]))
+    scaler.scale(b).backward(); scaler.step(opt); scaler.update(); opt.clear_grad()
+    scaler_res = {"skipped_maxdiff": skipped, "scale_after_inf": scale_after_inf}
+
 sd = wrapped.state_dict()
 maxdiff = max(float((sd[k].float() - v.float()).abs().max()) for k, v in twin.state_dict().items())
 nstate = len(opt.state_dict())
 out = tempfile.mkdtemp()
 save_group_sharded_model(wrapped, out, opt)
 files = sorted(os.listdir(out))
-_common.dump({"twin": lt, "sharded": lp, "maxdiff": maxdiff, "nstate": nstate, "files": files})
+_common.dump({"scaler": scaler_res, "twin": lt, "sharded": lp, "maxdiff": maxdiff, "nstate": nstate, "files": files})

@@ -75,6 +75,18 @@ def test_group_sharded_parity_cpu(level):
         assert res[0]["nstate"] + res[1]["nstate"] == 28
 
 
+@pytest.mark.parametrize("level", ["os_g", "p_g_os"])
+def test_group_sharded_scaler_cpu(level):
+    """The scaler handed to group_sharded_parallel agrees on found_inf over the sharding group: an inf seen by rank 1
+    only skips the step on both ranks and halves the scale; the next scaled step (stage 3: the embedding's gradient
+    is reduce-scattered only when the optimizer facade finishes backward) still matches the twin."""
+    res = run_workers("group_sharded.py", 2, args=(level, "scaler"), timeout=180)
+    for r in res:
+        assert r["scaler"]["skipped_maxdiff"] == 0.0, r["scaler"]
+        assert r["scaler"]["scale_after_inf"] == 512.0
+        assert r["maxdiff"] < 1e-4, r["maxdiff"]
+
+
 def test_auto_parallel_reshard_spmd_checkpoint_cpu():
     """Reshard pairs, SPMD matmul / data-parallel gradients, plan-driven parallelize vs a dense twin, and the
     sharded checkpoint (save under one placement, load under another, metadata layout) on a 2-rank mesh."""

@@ -231,6 +231,33 @@ def test_corrupt_checkpoint_shard_is_reported_by_name(tmp_path):
         ckpt.load_state_dict({"w": paddle.zeros([4096]), "step": 0}, str(tmp_path))
 
 
+def test_checkpoint_load_picks_newest_of_eleven_versions(tmp_path, monkeypatch):
+    """Eleven periodic saves into one directory (ids 0..10): loading without an id restores version 10 - ids compare as
+    numbers, '9' does not beat '10' - and reads no other version's files; an explicit id still selects an old one."""
+    import numpy as np
+
+    import paddle_b200 as paddle
+    from paddle_b200.distributed import checkpoint as ckpt
+    import importlib
+    L = importlib.import_module("paddle_b200.distributed.checkpoint.load_state_dict")
+    for v in range(11):
+        ckpt.save_state_dict({"w": paddle.to_tensor(np.full(8, float(v), dtype="float32")), "step": v}, str(tmp_path))
+    assert sorted(int(p.name.split(".")[0]) for p in tmp_path.iterdir() if p.name.endswith(".metadata")) == list(range(11))
+    assert L.get_max_id(str(tmp_path)) == 10
+    read = []
+    real = L._load_verified
+    monkeypatch.setattr(L, "_load_verified", lambda fn: (read.append(fn.rsplit("/", 1)[1]), real(fn))[1])
+    fresh = {"w": paddle.zeros([8]), "step": -1}
+    ckpt.load_state_dict(fresh, str(tmp_path))
+    assert fresh["step"] == 10 and float(fresh["w"][3]) == 10.0
+    assert sorted(set(read)) == ["0_10.distcp", "10.metadata"], read
+    merged = ckpt.load_merged_state_dict(str(tmp_path))
+    assert float(merged["w"][0]) == 10.0
+    old = {"w": paddle.zeros([8]), "step": -1}
+    ckpt.load_state_dict(old, str(tmp_path), unique_id=9)
+    assert old["step"] == 9 and float(old["w"][0]) == 9.0
+
+
 def test_weight_grad_store_defers_and_matches_plain_backward():
     """Split backward of linear layers: with the store enabled, backward yields only input gradients; running the
     queued closures afterwards gives the same weight / bias gradients as an ordinary backward."""
