@@ -13,7 +13,10 @@
 #include <float.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "host_utils.h"
+#include "pd_no_alloc.h"
 
 namespace pd {
 namespace ew {
@@ -887,18 +890,21 @@ PD_EXPORT int pd_rms_norm_bwd_static(const void* dy, const void* x, const void* 
                                      int dw_accumulate, int64_t rows, int H, cudaStream_t stream) {
   if (H % 8 != 0 || rows <= 0) return kErrBadShape;
   if (H > NA_MAX_H || H > 8 * RN_THREADS * RN_MAXIT) return kErrTooLarge;
+  if (rows > 2147483647ll) return kErrTooLarge;      // the kernels index rows with 32-bit integers
   // The array's name is only a host-side handle: the device address is looked up once per device, with that
-  // device current, and passed to the kernels.
-  static float* scratch_of_device[64] = {nullptr};
+  // device current, and passed to the kernels.  The per-device cache is atomic: host threads that make their first
+  // call on a device at the same time each look the address up and store the same value.
+  static std::atomic<float*> scratch_of_device[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return kErrCuda;
-  if (scratch_of_device[dev] == nullptr) {
+  float* partial = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (partial == nullptr) {
     float* p = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rms_bwd_scratch) != cudaSuccess || p == nullptr)
       return kErrCuda;
-    scratch_of_device[dev] = p;
+    scratch_of_device[dev].store(p, std::memory_order_release);
+    partial = p;
   }
-  float* partial = scratch_of_device[dev];
   const int parts = rows < NA_MAX_PARTS ? static_cast<int>(rows) : NA_MAX_PARTS;
   if (w_is_f32)
     rms_norm_bwd_kernel<float><<<parts, RN_THREADS, 0, stream>>>(

@@ -69,6 +69,16 @@ inline bool encode_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, const void*
   return encode_tmap(out, dt, 2, base, dims, strides, box, swz);
 }
 
+// dims {inner, mid, outer} with byte strides of mid and outer; box {box_inner, box_mid, box_outer}.
+inline bool encode_tmap_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t mid,
+                           uint64_t outer, uint64_t mid_stride_bytes, uint64_t outer_stride_bytes, uint32_t box_inner,
+                           uint32_t box_mid, uint32_t box_outer, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
+  uint64_t dims[3] = {inner, mid, outer};
+  uint64_t strides[2] = {mid_stride_bytes, outer_stride_bytes};
+  uint32_t box[3] = {box_inner, box_mid, box_outer};
+  return encode_tmap(out, dt, 3, base, dims, strides, box, swz);
+}
+
 // Map for an MN-major bf16 operand stored [k_extent rows][mn_extent contiguous].  When mn_extent is a multiple of
 // 64 the matrix is viewed as [mn/64][k][64] so that ONE box {64, box_k, chunks} fills `chunks` consecutive
 // 128B-swizzled 64-column slabs of shared memory (*is3d = 1); otherwise a plain 2-D map with box {64, box_k}

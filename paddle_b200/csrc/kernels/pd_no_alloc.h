@@ -14,9 +14,11 @@
 //
 // Limits and rules:
 //   * H (row length) must be a multiple of 8 and at most 8192; larger sizes return -5 (size beyond the
-//     supported maximum) without launching anything.  rows is unlimited: at most 128 CTAs share the work.
+//     supported maximum) without launching anything.  rows may be anything up to 2^31 - 1 (larger counts also
+//     return -5): at most 128 CTAs share the work.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
-//     device current).  Make that first call outside any stream capture.
+//     device current).  Make that first call outside any stream capture.  Host threads may make their first
+//     calls on a device concurrently: the cached address is an atomic and every thread stores the same value.
 //   * All calls share the one array.  Nothing in it has to start at zero — each call overwrites the rows it
 //     later sums — but two calls whose kernels overlap on the GPU (different streams, no ordering) race on it.
 //     Serialise them on one stream or with events.

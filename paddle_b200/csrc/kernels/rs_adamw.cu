@@ -35,6 +35,8 @@ struct Args {
   float lr, beta1, beta2, eps, coeff, beta1_pow, beta2_pow;
   const float* grad_scale;       // optional device scalar
   const int* skip;               // optional device flag: nonzero -> reduce only, no update
+  float* gout;                   // optional [shard]: store the reduced, scaled gradient here and do NOT update (the
+                                 // two-phase form: global-norm clipping needs the norm of the reduced gradient first)
   int* state;                    // [0] epoch, [1] finished CTAs
   unsigned long long wait_ns;
   int* status;
@@ -80,7 +82,7 @@ __global__ void __launch_bounds__(THREADS) rs_adamw_kernel(Args a) {
     __syncthreads();
     const bool ok = verdict != 0;
     __syncthreads();
-    if (!ok || skip) continue;
+    if (!ok || (skip && a.gout == nullptr)) continue;
     const int64_t e0 = static_cast<int64_t>(c) * CHUNK;
     const int64_t n = min(static_cast<int64_t>(CHUNK), a.shard - e0);
     for (int64_t i = threadIdx.x * 4; i < n; i += THREADS * 4) {
@@ -94,6 +96,10 @@ __global__ void __launch_bounds__(THREADS) rs_adamw_kernel(Args a) {
         } else {
           for (int j = 0; j < w; ++j) g[j] += __ldcg(row + j);
         }
+      }
+      if (a.gout != nullptr) {                 // phase A of the two-phase form: reduced gradient out, no update
+        for (int j = 0; j < w; ++j) a.gout[e0 + i + j] = g[j] * gscale;
+        continue;
       }
       for (int j = 0; j < w; ++j) {
         const int64_t e = e0 + i + j;
@@ -128,11 +134,13 @@ PD_EXPORT int pd_rs_adamw_chunk() { return pd::rsa::CHUNK; }
 // grad: fp32 [nranks * shard]; peer_recv[r] -> rank r's buffer [2][nranks][shard_padded] fp32; peer_cnt[r] -> rank r's
 // int32 [ceil(shard / 8192)] counters (zeroed once); state: 2 local int32 (zeroed once).  shard_padded >= shard and a
 // multiple of 4.  The grid is capped at 2 CTAs per SM; every rank must call with the same shapes.
+// grad_out (last argument, may be null): when given, the reduced gradient (x grad_scale) of the owned slice is written
+// there and nothing is updated - master / m / v / param_bf16 are not touched and may be null.
 PD_EXPORT int pd_rs_adamw(const float* grad, int64_t shard, int64_t shard_padded, int rank, int nranks,
                           const unsigned long long* peer_recv, const unsigned long long* peer_cnt, float* master, float* m,
                           float* v, void* param_bf16, float lr, float beta1, float beta2, float eps, float coeff,
                           float beta1_pow, float beta2_pow, const float* grad_scale, const int* skip, int* state,
-                          int wait_ms, int* status, cudaStream_t stream) {
+                          int wait_ms, int* status, cudaStream_t stream, float* grad_out) {
   using namespace pd;
   using namespace pd::rsa;
   if (shard <= 0 || shard_padded < shard || (shard_padded % 4) || nranks < 1 || nranks > MAX_RANKS) return kErrBadShape;
@@ -146,7 +154,7 @@ PD_EXPORT int pd_rs_adamw(const float* grad, int64_t shard, int64_t shard_padded
   a.shard = shard; a.shard_padded = shard_padded; a.rank = rank; a.nranks = nranks;
   a.chunks = static_cast<int>((shard + CHUNK - 1) / CHUNK);
   a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.coeff = coeff; a.beta1_pow = beta1_pow; a.beta2_pow = beta2_pow;
-  a.grad_scale = grad_scale; a.skip = skip; a.state = state;
+  a.grad_scale = grad_scale; a.skip = skip; a.state = state; a.gout = grad_out;
   a.wait_ns = static_cast<unsigned long long>(wait_ms) * 1000000ull;
   a.status = status;
   const int64_t items = static_cast<int64_t>(a.chunks) * nranks;

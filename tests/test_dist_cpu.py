@@ -49,6 +49,18 @@ def test_llama_tp_sp_parity_cpu():
         assert r["maxdiff"] < 1e-3, r["maxdiff"]  # Adam turns tiny gradient noise into O(lr) steps
 
 
+def test_mp2_sharding2_split_param_clip_parity_cpu():
+    """Tensor parallel x sharding with split parameters (4 ranks) under global-norm clipping equals the single-process
+    twin: the norm sums tensor-parallel parameters over the mp group and counts replicated ones once, buckets are
+    reduced from the gradient hooks (several buckets: 0.25 MB), and the gathered optimizer state has the reference's
+    per-parameter keys and full shapes."""
+    res = run_workers("llama_tp.py", 4, args=("float32", "fused", "512", "sharding2"), timeout=300)
+    for r in res:
+        assert np.allclose(r["tp"], r["twin"], rtol=1e-4, atol=1e-4), (r["tp"], r["twin"])
+        assert r["maxdiff"] < 1e-3, r["maxdiff"]
+        assert r["opt_keys_ok"] and r["moment_shape_ok"] and r["n_buckets"] > 1
+
+
 @pytest.mark.parametrize("mode", ["1f1b", "vpp", "zbh1"])
 def test_pipeline_parallel_parity_cpu(mode):
     """2 pipeline stages (1F1B, and 2 virtual chunks per stage over the ring) with a weight tied between the

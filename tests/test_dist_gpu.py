@@ -39,9 +39,21 @@ def test_llama_tp_sp_parity_gpu_ragged_ffn():
         assert r["maxdiff"] < 2e-2
 
 
-def test_fused_ag_gemm_and_gemm_rs():
-    res = run_workers("fused_comm.py", 2, backend="nccl", gpus=True, extra_env=ENV)
+@pytest.mark.parametrize("form", ["ring", "vector", "nvls"])
+def test_fused_ag_gemm_and_gemm_rs(form):
+    """All-gather->GEMM and GEMM->reduce-scatter, forward and backward, three calls in a row, against fp32 references
+    built from NCCL collectives.  ``ring`` / ``vector``: the two plain peer-store push forms with the push
+    reduce-scatter; ``nvls``: multimem.st push and multimem.ld_reduce reduce-scatter (skipped where the fabric has
+    no multicast).  The kept-gather path (backward reuses the matrix gathered in forward) is on in all three."""
+    env = dict(ENV)
+    env.update({"ring": {"PD_AG_PUSH_MODE": "0", "PD_RS_MODE": "0"}, "vector": {"PD_AG_PUSH_MODE": "1", "PD_RS_MODE": "0"},
+                "nvls": {"PD_AG_PUSH_MODE": "2", "PD_RS_MODE": "1"}}[form])
+    res = run_workers("fused_comm.py", 2, backend="nccl", gpus=True, extra_env=env)
+    if form == "nvls" and not res[0]["multicast"]:
+        pytest.skip("no NVLink multicast on this box")
     for r in res:
+        assert r["push_mode"] == {"ring": 0, "vector": 1, "nvls": 2}[form]
+        assert r["rs_mc"] == (form == "nvls")
         for k, v in r["errs"].items():
             assert v < 3e-2, (k, v)
 

@@ -1,9 +1,18 @@
 """tcgen05 GEMM vs an fp32 PyTorch reference: every operand-layout combination, ragged edges,
-bf16 / fp32 / fp32-accumulate epilogues."""
+bf16 / fp32 / fp32-accumulate epilogues, for both tile schemes (128 x 256 per SM; 256 x 256 per SM pair with
+tcgen05 cta_group::2)."""
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(params=["1cta", "2cta"], autouse=True)
+def gemm_impl(request):
+    from paddle_b200.ops import native
+    prev = native.set_gemm_impl(request.param)
+    yield request.param
+    native.set_gemm_impl(prev)
 
 
 def _ref(a, b, ta, tb):
@@ -20,7 +29,7 @@ def _mk(M, N, K, ta, tb, dev="cuda"):
 
 
 @pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 776, 200), (1000, 264, 1032)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 776, 200), (1000, 264, 1032), (136, 144, 72)])
 def test_gemm_layouts(ta, tb, M, N, K):
     from paddle_b200.ops import _lib, native
     a, b = _mk(M, N, K, ta, tb)

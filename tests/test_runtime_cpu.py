@@ -92,9 +92,8 @@ def test_reshard_planner():
 
 def test_push_cta_count_rule(monkeypatch):
     """Number of communication CTAs of the all-gather GEMM: a per-degree base, plus SMs the GEMM's last wave leaves
-    idle, never more than there are push jobs, none for a launch that does not push; the environment overrides."""
-    import os
-
+    idle, never more than there are push jobs, none for a launch that does not push; the environment overrides.
+    The multicast push issues one store per 16 bytes whatever the degree and keeps its small base."""
     from paddle_b200.parallel import fused_linear_impl as FL
     monkeypatch.setattr(FL, "_sms", lambda: 148)
     monkeypatch.delenv("PD_AG_COMM_CTAS", raising=False)
@@ -105,10 +104,13 @@ def test_push_cta_count_rule(monkeypatch):
     assert FL._comm_ctas(8, 96, 28, False) == 0
     c = FL._comm_ctas(8, 5000, 28, True)                   # a large GEMM: base plus what keeps the wave count (41)
     assert c == 26 and -(-5000 // (148 - c)) == -(-5000 // (148 - 24))
-    for n, tiles, jobs in [(8, 96, 28), (8, 352, 28), (4, 704, 24), (2, 768, 16), (8, 1, 4)]:
-        c = FL._comm_ctas(n, tiles, jobs, True)
-        assert 1 <= c <= max(jobs, 1) or c == FL._COMM_BASE[n]
-        assert 148 - c >= 1
+    for mode, table in ((0, FL._COMM_BASE), (1, FL._COMM_VEC), (2, FL._COMM_MC)):
+        for n, tiles, jobs in [(8, 96, 28), (8, 352, 32), (4, 704, 24), (2, 768, 128), (8, 1, 4)]:
+            c = FL._comm_ctas(n, tiles, jobs, True, mode)
+            assert 1 <= c <= max(jobs, 1) or c == table[n]
+            assert 148 - c >= 1
+    assert FL._comm_ctas(8, 192, 32, True, 2) == FL._COMM_MC[8]      # multicast: no growth with the degree
+    assert FL._comm_ctas(8, 96, 32, True, 1) == 32                   # vector push takes the idle SMs, up to the jobs
     monkeypatch.setenv("PD_AG_COMM_CTAS", "8")
     monkeypatch.setattr(FL, "N_COMM", 8)
     assert FL._comm_ctas(8, 96, 28, True) == 8
