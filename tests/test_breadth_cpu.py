@@ -470,3 +470,68 @@ def test_inner_overlap_linear_and_multi_label_parallel_cross_entropy():
     per = ParallelMultiLabelCrossEntropy(mp_group=one_rank, sum_multi_label_loss=False)(
         paddle.to_tensor(logits), paddle.to_tensor(lab), paddle.to_tensor(sw))
     assert per.shape == [4, 3]
+
+
+def test_sharding_v2_bucket_accounting_and_state_keys():
+    """Split-parameter sharding optimizer on one rank: buckets fill in reverse parameter order up to the configured
+    size; a bucket's reduction starts from the gradient hook only when every parameter has been accumulated
+    ``accumulate_steps`` times (the rule of FusedCommBuffer.add_grad, tensor_fusion_helper.py:623-646) and a further
+    arrival is an error; per-class learning rate / decay follow the wrapped AdamW; the optimizer state uses the
+    reference's per-parameter keys and round-trips."""
+    import numpy as np
+    import pytest
+    import torch
+
+    import paddle_b200 as paddle
+    from paddle_b200.distributed.fleet.meta_optimizers.dygraph_optimizer.dygraph_sharding_optimizer import (
+        DygraphShardingOptimizerV2)
+
+    class HCG:
+        def get_sharding_parallel_group(self): return None
+        def get_sharding_parallel_world_size(self): return 1
+        def get_sharding_parallel_rank(self): return 0
+        def get_model_parallel_group(self): return None
+        def get_pipe_parallel_group(self): return None
+
+    paddle.seed(5)
+    net = paddle.nn.Sequential(paddle.nn.Linear(16, 32), paddle.nn.LayerNorm(32), paddle.nn.Linear(32, 8))
+    twin = paddle.nn.Sequential(paddle.nn.Linear(16, 32), paddle.nn.LayerNorm(32), paddle.nn.Linear(32, 8))
+    twin.set_state_dict({k: v.clone() for k, v in net.state_dict().items()})
+    no_decay = lambda name: "b_" not in name and "layer_norm" not in name      # noqa: E731
+    mk = lambda m: paddle.optimizer.AdamW(1e-2, parameters=m.parameters(), weight_decay=0.1,                     # noqa: E731
+                                          apply_decay_param_fun=no_decay, grad_clip=paddle.nn.ClipGradByGlobalNorm(0.05))
+    ref_opt = mk(twin)
+    opt = DygraphShardingOptimizerV2(mk(net), HCG(), {"comm_buffer_size_MB": 0.001, "accumulate_steps": 2,
+                                                      "comm_overlap": True})
+    bufs = opt.__dict__["_buffers"]
+    assert len(bufs) >= 2                                   # 0.001 MB buckets: the 6 parameters do not fit one
+    assert bufs[0].params[0].name in {p.name for p in list(net.parameters())[-2:]}      # reverse order: last layer first
+    assert all(len({k for _, _, k in b.segments}) >= 1 for b in bufs)
+    x = paddle.randn([4, 16])
+    for step in range(2):
+        for micro in range(2):
+            (net(x).pow(2).mean() / 2).backward()
+            assert all(b.launched == (micro == 1) for b in bufs), (step, micro, [b.launched for b in bufs])
+            (twin(x).pow(2).mean() / 2).backward()
+        opt.step(); opt.clear_grad()
+        ref_opt.step(); ref_opt.clear_grad()
+    for (k, a), (_, b) in zip(net.state_dict().items(), twin.state_dict().items()):
+        assert np.allclose(a.numpy(), b.numpy(), atol=1e-6), k
+    # a third arrival within one step breaks the accounting
+    for _ in range(2):
+        (net(x).sum()).backward()
+    with pytest.raises(RuntimeError, match="arrived 3 times"):
+        (net(x).sum()).backward()
+    opt.clear_grad()
+    sd = opt.state_dict()
+    names = [p.name for p in net.parameters()]
+    assert all(f"{n}_moment1_0" in sd and f"{n}_moment2_0" in sd and f"{n}_beta1_pow_acc_0" in sd for n in names)
+    assert sd["sharding_v2_meta"]["degree"] == 1
+    full = opt.state_dict(gather=True)
+    assert tuple(full[f"{names[0]}_moment1_0"].shape) == tuple(list(net.parameters())[0].shape)
+    m_before = bufs[0].m.clone()
+    bufs[0].m.zero_()
+    opt.set_state_dict(full)
+    assert torch.equal(bufs[0].m, m_before)
+    with pytest.raises(TypeError, match="AdamW"):
+        DygraphShardingOptimizerV2(paddle.optimizer.SGD(0.1, parameters=net.parameters()), HCG(), {})
