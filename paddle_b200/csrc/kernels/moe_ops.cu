@@ -147,7 +147,7 @@ template <int NWG> struct Cfg {
   static constexpr int BN = SCALE_BLOCK * NWG;
   static constexpr int B_STAGE = BN * BK;
   static constexpr int THREADS = 128 * NWG + 64;
-  static constexpr int SMEM = STAGES * (A_STAGE + B_STAGE) + OFF_SLOTS * 4 + 1024 + 256;
+  static constexpr int SMEM = STAGES * (A_STAGE + B_STAGE) + 3 * OFF_SLOTS * 4 + 1024 + 256;
   static constexpr int TMEM_COLS = 2 * BN;                    // two accumulator buffers
 };
 
@@ -160,6 +160,10 @@ struct Bars {
 
 struct GParams {
   const int* offsets;       // [E + 1] row offsets of each expert in A / C
+  const int* seg_ends;      // optional [E]: segment e covers rows [offsets[e], seg_ends[e]) - a layout with unused rows
+                            // between segments (fixed-capacity receive buffers of the expert-parallel dispatch)
+  const int* expert_map;    // optional [E]: weights / weight scales of segment e are those of expert expert_map[e]
+                            // (several segments - one per source rank - share one expert)
   const float* a_scale;     // [M_total, K / 128]
   const float* b_scale;     // [E, K / 128, N / 128]
   bf16* c;                  // [M_total, N]
@@ -168,18 +172,18 @@ struct GParams {
 };
 
 // tile id -> (expert, first row, rows, n0); returns false when id is past the end
-__device__ __forceinline__ bool locate(const int* offs, int E, int tiles_n, int bn, int id, int& e, int& m0, int& m_end,
-                                       int& n0) {
+__device__ __forceinline__ bool locate(const int* offs, const int* ends, int E, int tiles_n, int bn, int id, int& e,
+                                       int& m0, int& m_end, int& n0) {
   // Within an expert the row tiles vary fastest: the CTAs running at one time then share a few weight column
   // blocks (each read from HBM once and hit in L2 by the other row tiles) instead of streaming the whole weight
   // matrix once per row tile; the expert's activations (rows x K bytes) stay L2-resident either way.
   for (e = 0; e < E; ++e) {
-    const int rows = offs[e + 1] - offs[e];
+    const int rows = max(ends[e] - offs[e], 0);
     const int tm = (rows + BM - 1) / BM;
     const int t = tm * tiles_n;
     if (id < t) {
       m0 = offs[e] + (id % tm) * BM;
-      m_end = offs[e + 1];
+      m_end = ends[e];
       n0 = (id / tm) * bn;
       return true;
     }
@@ -198,13 +202,19 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE;
   int* sOff = reinterpret_cast<int*>(sB + STAGES * B_STAGE);
-  Bars* bars = reinterpret_cast<Bars*>(sOff + OFF_SLOTS);
+  int* sEnd = sOff + OFF_SLOTS;
+  int* sMap = sEnd + OFF_SLOTS;
+  Bars* bars = reinterpret_cast<Bars*>(sMap + OFF_SLOTS);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = p.N / BN;
   const int KB = p.K / BK;
 
   for (int i = threadIdx.x; i <= p.E; i += Cfg<NWG>::THREADS) sOff[i] = p.offsets[i];
+  for (int i = threadIdx.x; i < p.E; i += Cfg<NWG>::THREADS) {
+    sEnd[i] = p.seg_ends != nullptr ? p.seg_ends[i] : p.offsets[i + 1];
+    sMap[i] = p.expert_map != nullptr ? p.expert_map[i] : i;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&bars->full[s], 1);
@@ -233,7 +243,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       bool ok = true;
       for (int id = blockIdx.x; ok; id += gridDim.x) {
         int e, m0, m_end, n0;
-        if (!locate(sOff, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
+        if (!locate(sOff, sEnd, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(&bars->empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, p.status, 100 + s)) { ok = false; break; }
@@ -241,7 +251,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           tma_load_2d(sA + s * A_STAGE, &tmA, &bars->full[s], kb * BK, m0);            // box {128 k, 128 m}
 #pragma unroll
           for (int g = 0; g < NWG; ++g)                                                  // box {128 k, 128 n, 1}
-            tma_load_3d(sB + s * B_STAGE + g * (SCALE_BLOCK * BK), &tmB, &bars->full[s], kb * BK, n0 + g * SCALE_BLOCK, e);
+            tma_load_3d(sB + s * B_STAGE + g * (SCALE_BLOCK * BK), &tmB, &bars->full[s], kb * BK, n0 + g * SCALE_BLOCK, sMap[e]);
           armed = it + 1;
         }
       }
@@ -257,7 +267,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       bool ok = true;
       for (int id = blockIdx.x; ok; id += gridDim.x) {
         int e, m0, m_end, n0;
-        if (!locate(sOff, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
+        if (!locate(sOff, sEnd, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES, acc = it & 1;
           if (!mbar_wait(&bars->tempty[acc], ((it >> 1) & 1) ^ 1, abort_flag, p.status, 200 + acc)) { ok = false; break; }
@@ -288,14 +298,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     bool ok = true;
     for (int id = blockIdx.x; ok; id += gridDim.x) {
       int e, m0, m_end, n0;
-      if (!locate(sOff, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
+      if (!locate(sOff, sEnd, p.E, tiles_n, BN, id, e, m0, m_end, n0)) break;
       const int row = m0 + tid;
       const bool live = row < m_end;
       float acc[SCALE_BLOCK];
 #pragma unroll
       for (int i = 0; i < SCALE_BLOCK; ++i) acc[i] = 0.f;
       const float* as_row = p.a_scale + static_cast<size_t>(live ? row : m0) * kbn;
-      const float* bs = p.b_scale + (static_cast<size_t>(e) * kbn) * nbn + n0 / 128 + wg;
+      const float* bs = p.b_scale + (static_cast<size_t>(sMap[e]) * kbn) * nbn + n0 / 128 + wg;
       // The scales of block kb + 1 are LOADED here and only multiplied at the top of the next iteration: issue is in
       // order, so using them now would park the warp on the load for a full memory latency every block.
       float a_nx = as_row[0], b_nx = bs[0];
@@ -380,6 +390,27 @@ PD_EXPORT int pd_fp8_quant_128x128_t(const void* w, void* wt, float* scales, int
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }
 
+static int launch_grouped(const CUtensorMap& tmA, const CUtensorMap& tmB, const GParams& p, int N, int max_tiles,
+                          cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(grouped_gemm_fp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(grouped_gemm_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM) != cudaSuccess)
+      return kErrCuda;
+    configured = true;
+  }
+  // max_tiles counts 128 x 128 tiles; the 128 x 256 kernel has half as many
+  const bool wide = (N % Cfg<2>::BN) == 0;
+  const int tiles = wide ? (max_tiles + 1) / 2 : max_tiles;
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (grid < 1) grid = 1;
+  if (wide)
+    grouped_gemm_fp8_kernel<2><<<grid, Cfg<2>::THREADS, Cfg<2>::SMEM, stream>>>(tmA, tmB, p);
+  else
+    grouped_gemm_fp8_kernel<1><<<grid, Cfg<1>::THREADS, Cfg<1>::SMEM, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
+}
+
 // A [M_total, K] e4m3 (rows sorted by expert), a_scale [M_total, K/128]; B [E, N, K] e4m3, b_scale [E, K/128, N/128];
 // offsets [E + 1] int32 (device); C [M_total, N] bf16.  max_tiles: upper bound of sum_e ceil(rows_e / 128) * N / 128
 // used to size the grid (for example ceil(M_total / 128) + E, times N / 128).
@@ -395,22 +426,27 @@ PD_EXPORT int pd_grouped_gemm_fp8(const void* A, const float* a_scale, const voi
   uint32_t box[3] = {BK, SCALE_BLOCK, 1};
   ok &= encode_tmap(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return kErrTensorMap;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(grouped_gemm_fp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(grouped_gemm_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<2>::SMEM) != cudaSuccess)
-      return kErrCuda;
-    configured = true;
-  }
-  GParams p{offsets, a_scale, b_scale, (bf16*)C, E, N, K, ldc, status};
-  // max_tiles counts 128 x 128 tiles; the 128 x 256 kernel has half as many
-  const bool wide = (N % Cfg<2>::BN) == 0;
-  const int tiles = wide ? (max_tiles + 1) / 2 : max_tiles;
-  int grid = tiles < sm_count() ? tiles : sm_count();
-  if (grid < 1) grid = 1;
-  if (wide)
-    grouped_gemm_fp8_kernel<2><<<grid, Cfg<2>::THREADS, Cfg<2>::SMEM, stream>>>(tmA, tmB, p);
-  else
-    grouped_gemm_fp8_kernel<1><<<grid, Cfg<1>::THREADS, Cfg<1>::SMEM, stream>>>(tmA, tmB, p);
-  return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
+  GParams p{offsets, nullptr, nullptr, a_scale, b_scale, (bf16*)C, E, N, K, ldc, status};
+  return launch_grouped(tmA, tmB, p, N, max_tiles, stream);
+}
+
+// Segment form: rows of segment s are [seg_start[s], seg_end[s]) (unused rows may lie between segments) and its
+// weights are those of expert expert_map[s]; n_seg <= 64, E_w = number of weight matrices in B.
+PD_EXPORT int pd_grouped_gemm_fp8_seg(const void* A, const float* a_scale, const void* B, const float* b_scale,
+                                      const int* seg_start, const int* seg_end, const int* expert_map, void* C,
+                                      int M_total, int N, int K, int n_seg, int E_w, int ldc, int max_tiles, int* status,
+                                      cudaStream_t stream) {
+  if (M_total <= 0 || N <= 0 || K <= 0 || n_seg <= 0 || n_seg > MAX_EXPERTS || E_w <= 0 || (N % SCALE_BLOCK) || (K % BK))
+    return kErrBadShape;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C) || (ldc % 8)) return kErrAlignment;
+  CUtensorMap tmA, tmB;
+  bool ok = encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, A, K, M_total, uint64_t(K), BK, BM);
+  uint64_t dims[3] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(E_w)};
+  uint64_t strides[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(K) * N};
+  uint32_t box[3] = {BK, SCALE_BLOCK, 1};
+  ok &= encode_tmap(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return kErrTensorMap;
+  // offsets[n_seg] is never read in this form (the ends come from seg_end)
+  GParams p{seg_start, seg_end, expert_map, a_scale, b_scale, (bf16*)C, n_seg, N, K, ldc, status};
+  return launch_grouped(tmA, tmB, p, N, max_tiles, stream);
 }

@@ -67,6 +67,17 @@ class MoELayer(nn.Layer):
             self.top_k = gate.top_k
         self.gate = gate
 
+    # capacity of the fused exchange per (expert, source rank): ceil(factor * top_k * tokens / experts) rows, or
+    # ``fused_capacity`` rows when set; routed copies beyond it are dropped (GShard capacity semantics)
+    fused_capacity_factor = 1.25
+    fused_capacity = None
+
+    def _use_fused(self, inp):
+        if not self._grouped or self.recompute_interval > 0 or self.world_size < 2:
+            return False
+        from .....parallel.moe_exchange import fused_moe_available
+        return fused_moe_available(inp, self.experts, self.group)
+
     def _experts_forward(self, x, fwd_expert_count):
         if self._grouped:
             return self.experts(x, fwd_expert_count)
@@ -82,6 +93,13 @@ class MoELayer(nn.Layer):
         origin_shape = inp.shape
         inp = inp.reshape([-1, origin_shape[-1]])
         value, gate = self.gate(inp)
+        if self._use_fused(inp):
+            # one autograd function: fp8-quantising dispatch over peer memory, grouped block-scaled GEMMs, weighted
+            # combine; routing metadata stays on the device
+            from .....parallel.moe_exchange import fused_moe_forward
+            y = fused_moe_forward(C._plain(inp), C._plain(value), C._plain(gate), self.experts, self.group,
+                                  capacity_factor=self.fused_capacity_factor, cap=self.fused_capacity)
+            return as_tensor(y).reshape(origin_shape)
         pos, local_count, global_count, fwd_count, fwd_bs = prepare_forward(gate, self.num_expert, self.world_size,
                                                                             self.group)
         topk = gate.shape[1] if gate.dim() > 1 else 1

@@ -134,3 +134,13 @@ def test_auto_parallel_engine_two_ranks_cpu(tmp_path):
         assert r["eval"]["acc"] > 0.7
     assert res[0]["eval"]["loss"] == res[1]["eval"]["loss"]           # averaged over ranks
     assert res[0]["files"] == ["ck_dist0.pdopt", "ck_dist0.pdparams", "ck_dist1.pdopt", "ck_dist1.pdparams"]
+
+
+def test_context_parallel_ulysses_and_ring_attention_cpu():
+    """Sequence split over 2 ranks: all-to-all (Ulysses) and ring attention reproduce full-sequence attention, outputs
+    and q / k / v gradients, causal and not, with grouped-query heads."""
+    res = run_workers("context_parallel.py", 2, timeout=180)
+    for r in res:
+        for k, v in r.items():
+            assert v < 1e-5, (k, v)
+
