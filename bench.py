@@ -250,7 +250,8 @@ def main():
             "metric": "Llama-2 7B TP+SP train tok/s" if args.model == "llama2-7b" else f"{args.model} train tok/s",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights)",
+            "dtype": "bf16", "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights; the same 16 "
+                                     "micro-batches every step, so the loss memorises them and falls towards 0)",
             "impl": "ours", "mode": args.mode,
             "config": {"model": args.model, "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
                        "global_batch": n_mb, "micro_batch": 1, "accumulation": n_mb, "seq_len": seq,
@@ -265,22 +266,29 @@ def main():
         if args.layers:
             out["invalid"] = "debug run with a reduced layer count"
         print(json.dumps(out))
-    used_graph = graph["g"] is not None
-    if used_graph:
-        graph["g"].reset()                # drop the captured work (it references the communicators) before teardown
+    if graph["g"] is not None:
+        graph["g"].reset()                # the captured work references the communicators: it goes first
         graph.update(g=None, loss=None, tok=None)
     torch.cuda.synchronize()
     if world > 1:
+        # Teardown order.  Symmetric-memory blocks keep the group's store and communicator in use through their
+        # rendezvous handles, and slots / graphs keep the blocks alive; left to interpreter exit these objects were
+        # destroyed after the process group, in arbitrary order, and the exit blocked.  So: every rank idle (barrier),
+        # drop graphs, slots and blocks explicitly, then destroy the group.  A timer bounds the teardown in case a
+        # library destructor still waits on a peer that is already gone; the result line is out by then.
         tdist.barrier()
         sys.stdout.flush()
-        # Tearing down communicators whose collectives were captured into a CUDA graph has been seen to block;
-        # all ranks are past the barrier with nothing in flight, so give the teardown a bounded time.
-        import threading
-        t = threading.Thread(target=tdist.destroy_process_group, daemon=True)
-        t.start()
-        t.join(30.0)
-        if t.is_alive() or used_graph:
-            os._exit(0)                   # skip interpreter finalisation as well: nothing is left to flush
+        from paddle_b200.parallel import fused_linear_impl, symm
+        fused_linear_impl._slots.clear()
+        del model, opt
+        symm.release_all()
+        torch.cuda.synchronize()
+        guard = threading.Timer(60.0, lambda: os._exit(0))
+        guard.daemon = True
+        guard.start()
+        tdist.barrier()
+        tdist.destroy_process_group()
+        guard.cancel()
     return 0
 
 

@@ -13,6 +13,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <condition_variable>
@@ -246,4 +247,78 @@ PD_EXPORT int pd_comm_static_check(int kind, int64_t in_numel, int64_t out_numel
     case 3: return (in_numel % world) ? 2 : (in_numel == out_numel ? 0 : 3);        // all_to_all
     default: return 0;
   }
+}
+
+// ------------------------------------------------------------------------------------------- gradient reducer
+// Bookkeeping of the data-parallel gradient reducer (EagerReducer, paddle/fluid/distributed/collective/reducer.cc:482:
+// MarkVarReady :797, MarkGroupReady :944, FinalizeBackward :1040): which bucket a parameter belongs to, how many
+// gradients of each bucket have arrived in the current backward pass, which bucket is complete and may be reduced,
+// and - when backward ends - which buckets never completed (unused parameters).  The tensors themselves stay with the
+// caller; this object only keeps the counters, so the per-gradient hook is one native call.
+namespace {
+struct Reducer {
+  std::vector<int> bucket_of;      // parameter -> bucket
+  std::vector<int> bucket_size;    // parameters per bucket
+  std::vector<int> ready;          // gradients arrived per bucket in this backward
+  std::vector<char> seen;          // parameter arrived in this backward
+  std::vector<char> launched;      // bucket handed out for reduction in this backward
+  bool in_backward = false;
+  std::mutex mu;
+};
+}  // namespace
+
+PD_EXPORT void* pd_reducer_create(const int* bucket_of_param, int n_params, int n_buckets) {
+  auto* r = new Reducer();
+  r->bucket_of.assign(bucket_of_param, bucket_of_param + n_params);
+  r->bucket_size.assign(n_buckets, 0);
+  for (int i = 0; i < n_params; ++i) {
+    if (bucket_of_param[i] < 0 || bucket_of_param[i] >= n_buckets) {
+      delete r;
+      return nullptr;
+    }
+    r->bucket_size[bucket_of_param[i]]++;
+  }
+  r->ready.assign(n_buckets, 0);
+  r->seen.assign(n_params, 0);
+  r->launched.assign(n_buckets, 0);
+  return r;
+}
+PD_EXPORT void pd_reducer_destroy(void* h) { delete static_cast<Reducer*>(h); }
+
+// A gradient arrived.  Returns: bucket index (>= 0) when this arrival completed the bucket, -1 when the bucket is
+// still incomplete, -2 when the parameter was already marked in this backward (a second use without no_sync),
+// -3 for a bad index.  *first_of_backward is set to 1 for the first arrival of a backward pass: the caller queues its
+// end-of-backward callback then (and not when a bucket happens to complete).
+PD_EXPORT int pd_reducer_mark_ready(void* h, int param, int* first_of_backward) {
+  auto* r = static_cast<Reducer*>(h);
+  std::lock_guard<std::mutex> g(r->mu);
+  if (param < 0 || param >= static_cast<int>(r->bucket_of.size())) return -3;
+  *first_of_backward = r->in_backward ? 0 : 1;
+  r->in_backward = true;
+  if (r->seen[param]) return -2;
+  r->seen[param] = 1;
+  const int b = r->bucket_of[param];
+  if (++r->ready[b] == r->bucket_size[b]) {
+    r->launched[b] = 1;
+    return b;
+  }
+  return -1;
+}
+// End of backward: writes the buckets that received some but not all gradients, or none at all, into out (capacity
+// cap) and resets every counter for the next pass.  Returns how many there are.
+PD_EXPORT int pd_reducer_finish(void* h, int* out, int cap) {
+  auto* r = static_cast<Reducer*>(h);
+  std::lock_guard<std::mutex> g(r->mu);
+  int n = 0;
+  for (size_t b = 0; b < r->ready.size(); ++b) {
+    if (!r->launched[b]) {
+      if (n < cap) out[n] = static_cast<int>(b);
+      ++n;
+    }
+  }
+  std::fill(r->ready.begin(), r->ready.end(), 0);
+  std::fill(r->seen.begin(), r->seen.end(), 0);
+  std::fill(r->launched.begin(), r->launched.end(), 0);
+  r->in_backward = false;
+  return n;
 }

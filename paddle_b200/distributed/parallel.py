@@ -128,17 +128,76 @@ class DataParallel(Layer):
             self._buckets.append(b)
             for i in idxs:
                 self._param2bucket[id(params[i])] = bi
+        self._index = {id(p): i for i, p in enumerate(params)}
+        bucket_of = [self._param2bucket[id(p)] for p in params]
+        self._native = None
+        try:
+            import ctypes
+
+            from ..ops import _lib
+            rt = _lib.runtime()
+            rt.pd_reducer_create.restype = ctypes.c_void_p
+            arr = (ctypes.c_int * len(bucket_of))(*bucket_of)
+            h = rt.pd_reducer_create(arr, len(bucket_of), len(self._buckets))
+            if h:
+                self._native = (rt, ctypes.c_void_p(h))
+        except Exception:  # noqa: BLE001 - without the native runtime the same counters are kept in Python
+            self._native = None
+        self._seen = set()
+        self._in_backward = False
         for p in params:
             p.register_post_accumulate_grad_hook(self._make_hook())
+
+    def _mark_ready(self, p):
+        """-> (bucket index | -1 incomplete | -2 duplicate, first arrival of this backward)."""
+        if self._native is not None:
+            import ctypes
+            rt, h = self._native
+            first = ctypes.c_int(0)
+            return rt.pd_reducer_mark_ready(h, self._index[id(p)], ctypes.byref(first)), bool(first.value)
+        first = not self._in_backward
+        self._in_backward = True
+        if id(p) in self._seen:
+            return -2, first
+        self._seen.add(id(p))
+        bi = self._param2bucket[id(p)]
+        b = self._buckets[bi]
+        b["ready"] += 1
+        if b["ready"] == len(b["params"]):
+            b["launched"] = True
+            return bi, first
+        return -1, first
+
+    def _unfinished(self):
+        """Buckets that did not complete in the backward pass that just ended; resets the counters."""
+        if self._native is not None:
+            import ctypes
+            rt, h = self._native
+            out = (ctypes.c_int * len(self._buckets))()
+            n = rt.pd_reducer_finish(h, out, len(self._buckets))
+            return [out[i] for i in range(n)]
+        left = [i for i, b in enumerate(self._buckets) if not b.get("launched")]
+        for b in self._buckets:
+            b["ready"], b["launched"] = 0, False
+        self._seen.clear()
+        self._in_backward = False
+        return left
 
     def _make_hook(self):
         def hook(p):
             if not self._sync:
                 return
-            b = self._buckets[self._param2bucket[id(p)]]
-            b["ready"] += 1
-            if b["ready"] == len(b["params"]):
-                self._launch(b)
+            bi, first = self._mark_ready(p)
+            if first:
+                # the end-of-backward work is queued by the FIRST gradient of the pass, not by the first complete bucket:
+                # a pass in which no bucket completes (an unused parameter in a one-bucket model) must still be finished,
+                # or its stale counts would fire a bucket in the middle of the next pass
+                torch.autograd.Variable._execution_engine.queue_callback(self._finalize)
+            if bi == -2:
+                raise RuntimeError(f"gradient of {getattr(p, 'name', 'a parameter')} was produced twice in one backward "
+                                   "pass; wrap the extra passes in no_sync()")
+            if bi >= 0:
+                self._launch(self._buckets[bi])
         return hook
 
     def _launch(self, b):
@@ -147,10 +206,6 @@ class DataParallel(Layer):
         flat.div_(self._nranks)
         task = C.all_reduce(flat, group=self.group, sync_op=False)
         self._pending.append((task, flat, grads))
-        b["ready"] = 0
-        # the optimizer may run right after backward(): make completion part of the autograd run
-        if len(self._pending) == 1:
-            torch.autograd.Variable._execution_engine.queue_callback(self._finalize)
 
     def _finalize(self):
         for task, flat, grads in self._pending:
@@ -161,22 +216,29 @@ class DataParallel(Layer):
                 g.copy_(flat[off:off + n].view_as(g))
                 off += n
         self._pending.clear()
-        if self.find_unused_parameters or any(b["ready"] for b in self._buckets):
-            # parameters that received no gradient this step: reduce what is there so ranks agree
-            for b in self._buckets:
-                if b["ready"]:
-                    for p in b["params"]:
-                        g = torch.Tensor.grad.__get__(p)
-                        if g is None:
-                            p.grad = torch.zeros_like(p)
-                    b["ready"] = 0
-                    grads = [torch.Tensor.grad.__get__(p) for p in b["params"]]
-                    flat = torch.cat([g.reshape(-1) for g in grads]).div_(self._nranks)
-                    C.all_reduce(flat, group=self.group)
-                    off = 0
-                    for g in grads:
-                        g.copy_(flat[off:off + g.numel()].view_as(g))
-                        off += g.numel()
+        left = self._unfinished()
+        if not left:
+            return
+        if not self.find_unused_parameters:
+            names = [getattr(p, "name", "?") for bi in left for p in self._buckets[bi]["params"]
+                     if torch.Tensor.grad.__get__(p) is None]
+            raise RuntimeError(
+                "some parameters received no gradient in this backward pass, so their buckets were never reduced "
+                f"({', '.join(names[:8])}{' ...' if len(names) > 8 else ''}).  Construct DataParallel with "
+                "find_unused_parameters=True if parts of the model are skipped on purpose.")
+        # parameters without a gradient this step take part with zeros so that every rank issues the same collectives
+        for bi in left:
+            b = self._buckets[bi]
+            for p in b["params"]:
+                if torch.Tensor.grad.__get__(p) is None:
+                    p.grad = torch.zeros_like(p)
+            grads = [torch.Tensor.grad.__get__(p) for p in b["params"]]
+            flat = torch.cat([g.reshape(-1) for g in grads]).div_(self._nranks)
+            C.all_reduce(flat, group=self.group)
+            off = 0
+            for g in grads:
+                g.copy_(flat[off:off + g.numel()].view_as(g))
+                off += g.numel()
 
     def no_sync(self):
         dp = self

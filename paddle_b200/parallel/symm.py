@@ -12,6 +12,7 @@ import torch
 import torch.distributed as tdist
 
 _enabled_groups = set()
+_live_blocks = []          # weak references to every SymmBlock, for release_all()
 
 
 class SymmBlock:
@@ -45,6 +46,17 @@ class SymmBlock:
         self.nbytes = nbytes
         torch.cuda.synchronize()
         tdist.barrier(group=pg, device_ids=[dev.index])
+        import weakref
+        _live_blocks.append(weakref.ref(self))
+
+    def release(self):
+        """Drop the mapping of the peers' memory and the local allocation.  Every rank has to do this before the
+        process group that exchanged the handles is destroyed: the handle object keeps using the group's store and
+        communicator, and tearing it down after them (at interpreter exit, in arbitrary order) can block."""
+        self.handle = None
+        self.local = None
+        self.ptrs = []
+        self.mc_ptr = 0
 
     def view(self, offset: int, shape, dtype):
         n = 1
@@ -55,6 +67,18 @@ class SymmBlock:
 
     def peer_ptrs(self, offset: int):
         return [p + offset for p in self.ptrs]
+
+
+def release_all():
+    """Release every symmetric block of this process (after a device synchronise and a barrier by the caller: no
+    kernel of any rank may still touch them).  Call before ``destroy_process_group``."""
+    import gc
+    for ref in _live_blocks:
+        b = ref()
+        if b is not None:
+            b.release()
+    _live_blocks.clear()
+    gc.collect()
 
 
 def multicast_enabled() -> bool:

@@ -144,3 +144,11 @@ def test_context_parallel_ulysses_and_ring_attention_cpu():
         for k, v in r.items():
             assert v < 1e-5, (k, v)
 
+
+def test_data_parallel_unused_parameter_cpu():
+    """A backward pass in which no bucket completes is still finished: zeros are reduced for the missing gradients when
+    find_unused_parameters is set, an error names the parameters when it is not."""
+    res = run_workers("dp_unused.py", 2, timeout=120)
+    for r in res:
+        assert r["agree"] and r["unused_zero"] and r["expected"] and r["raised"] and r["after_ok"], r
+
