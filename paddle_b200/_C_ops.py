@@ -68,4 +68,9 @@ def __getattr__(name):
     for mod in (_p, _p.nn.functional):
         if hasattr(mod, base):
             return getattr(mod, base)
+    from . import _op_table
+    fn = _op_table.resolve(name)
+    if fn is not None:
+        _REGISTRY[name] = fn
+        return fn
     raise AttributeError(f"_C_ops has no operator {name!r}")

