@@ -34,6 +34,10 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (marks the run invalid)")
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--micro-batches", type=int, default=16)
+    ap.add_argument("--sharding", type=int, default=0, choices=[0, 3],
+                    help="3: sharding stage 3 over all ranks instead of tensor parallelism (parameters, gradients and "
+                         "optimizer state partitioned; every rank feeds its own micro-batches: BASELINE config 3 with "
+                         "--model llama2-13b --micro-batches 8)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay each micro-batch (forward + backward) from a CUDA graph; auto = when --gpus > 1, "
@@ -124,8 +128,11 @@ def main():
     paddle.set_kernel_policy(args.mode)
     paddle.seed(1234)
 
-    tp = world
-    if world > 1:
+    tp = world if not args.sharding else 1
+    if world > 1 and args.sharding:
+        import paddle_b200.distributed as pdist
+        pdist.init_parallel_env()
+    elif world > 1:
         from paddle_b200.distributed import fleet
         strategy = fleet.DistributedStrategy()
         strategy.hybrid_configs = {"dp_degree": 1, "mp_degree": tp, "pp_degree": 1, "sharding_degree": 1}
@@ -139,16 +146,20 @@ def main():
 
     model = LlamaForCausalLM(cfg)
     from paddle_b200.distributed.fleet.utils.mix_precision_utils import enable_main_grad
-    enable_main_grad(model)
+    if not args.sharding:
+        enable_main_grad(model)
     opt = paddle.optimizer.AdamW(learning_rate=1e-5, beta1=0.9, beta2=0.95, epsilon=1e-8, weight_decay=0.1,
                                  parameters=model.parameters(), multi_precision=True,
                                  grad_clip=paddle.nn.ClipGradByGlobalNorm(1.0))
-    if world > 1:
+    if world > 1 and args.sharding:
+        from paddle_b200.distributed.sharding import group_sharded_parallel
+        model, opt, _ = group_sharded_parallel(model, opt, "p_g_os")
+    elif world > 1:
         from paddle_b200.distributed import fleet
         model = fleet.distributed_model(model)
         opt = fleet.distributed_optimizer(opt)
 
-    gen = torch.Generator().manual_seed(4321)           # same token stream on every rank (TP)
+    gen = torch.Generator().manual_seed(4321 + (rank if args.sharding else 0))   # TP: same tokens on every rank
     host_ids = torch.randint(0, cfg.vocab_size, (n_mb, 1, seq + 1), generator=gen, dtype=torch.int64).pin_memory()
     dev_ids = host_ids.cuda()
 
@@ -216,7 +227,7 @@ def main():
         return ms, last
 
     host_issue_ms = [0.0]
-    use_graph = args.graph == "on" or (args.graph == "auto" and world > 1)
+    use_graph = args.graph == "on" or (args.graph == "auto" and world > 1 and not args.sharding)
     if use_graph:
         train_step(False)                # eager once: allocates symmetric buffers, caches, optimizer state
         capture_micro_batch()
@@ -232,7 +243,7 @@ def main():
     from paddle_b200.ops import _lib
     _lib.check_status()
 
-    tokens_per_step = n_mb * seq
+    tokens_per_step = n_mb * seq * (world if args.sharding else 1)
     ms_per_step = ms / args.steps
     value = tokens_per_step / (ms_per_step / 1e3)
 
@@ -249,13 +260,15 @@ def main():
         out = {
             "metric": "Llama-2 7B TP+SP train tok/s" if args.model == "llama2-7b" else f"{args.model} train tok/s",
             "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak" if args.sharding else "strong",
+            "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, N(0,0.02) random-init weights; the same 16 "
                                      "micro-batches every step, so the loss memorises them and falls towards 0)",
             "impl": "ours", "mode": args.mode,
             "config": {"model": args.model, "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
-                       "global_batch": n_mb, "micro_batch": 1, "accumulation": n_mb, "seq_len": seq,
-                       "parallelism": f"tp{tp}+sp" if tp > 1 else "single",
+                       "global_batch": n_mb * (world if args.sharding else 1), "micro_batch": 1, "accumulation": n_mb,
+                       "seq_len": seq,
+                       "parallelism": (f"sharding3x{world}" if args.sharding else (f"tp{tp}+sp" if tp > 1 else "single")),
                        "optimizer": "AdamW fp32 master weights + fp32 main_grad, global-norm clip",
                        "l2": "working set (>= 13 GB of weights per micro-batch) far exceeds the 126 MB L2"},
             "model_tflops_per_gpu": flops / (ms_per_step / 1e3) / 1e12 / world,

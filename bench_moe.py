@@ -16,6 +16,16 @@ import json
 import os
 
 
+class _Only:
+    """A view of some parameters with the ``parameters()`` method that ``enable_main_grad`` walks."""
+
+    def __init__(self, params):
+        self._p = list(params)
+
+    def parameters(self):
+        return self._p
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -26,6 +36,8 @@ def main():
     ap.add_argument("--micro-batches", type=int, default=4)
     ap.add_argument("--experts", default="grouped_fp8", choices=["grouped_fp8", "loop"])
     ap.add_argument("--model", default="mixtral-8x7b", choices=["mixtral-8x7b", "tiny"])
+    ap.add_argument("--no-dense-sharding", dest="dense_sharding", action="store_false",
+                    help="replicate the optimizer state of the dense parameters and all-reduce their gradients")
     args = ap.parse_args()
 
     import torch
@@ -54,10 +66,31 @@ def main():
                                          max_position_embeddings=args.seq_len)
     model = MixtralForCausalLM(cfg, moe_group=group)
     from paddle_b200.distributed.fleet.utils.mix_precision_utils import enable_main_grad
-    enable_main_grad(model)
-    opt = paddle.optimizer.AdamW(learning_rate=1e-5, beta1=0.9, beta2=0.95, epsilon=1e-8, weight_decay=0.1,
-                                 parameters=model.parameters(), multi_precision=True)
     shared = [p for p in model.parameters() if not getattr(p, "is_moe_param", False)]
+    expert_params = [p for p in model.parameters() if getattr(p, "is_moe_param", False)]
+    mk = lambda ps: paddle.optimizer.AdamW(learning_rate=1e-5, beta1=0.9, beta2=0.95, epsilon=1e-8, weight_decay=0.1,   # noqa: E731
+                                           parameters=ps, multi_precision=True)
+    dense_opt = None
+    if world > 1 and args.dense_sharding:
+        # expert parallel + sharding stage 1 for the dense (attention / router / embedding) parameters: they are
+        # replicated, so their optimizer state is split over the ranks and their gradients are reduce-scattered
+        # bucket by bucket under backward (split-parameter sharding optimizer); the experts are local to a rank
+        from paddle_b200.distributed.fleet.meta_optimizers.dygraph_optimizer.dygraph_sharding_optimizer import (
+            DygraphShardingOptimizerV2)
+
+        class _ShardingTopology:
+            def get_sharding_parallel_group(self): return group
+            def get_sharding_parallel_world_size(self): return world
+            def get_sharding_parallel_rank(self): return rank
+            def get_model_parallel_group(self): return None
+            def get_pipe_parallel_group(self): return None
+        enable_main_grad(_Only(expert_params))
+        dense_opt = DygraphShardingOptimizerV2(mk(shared), _ShardingTopology(), {"comm_overlap": True,
+                                                                                  "comm_buffer_size_MB": 256})
+        opt = mk(expert_params)
+    else:
+        enable_main_grad(model)
+        opt = mk(model.parameters())
     seq, n_mb = args.seq_len, args.micro_batches
     gen = torch.Generator().manual_seed(4321 + rank)
     host_ids = torch.randint(0, cfg.vocab_size, (n_mb, 1, seq + 1), generator=gen, dtype=torch.int64).pin_memory()
@@ -69,7 +102,10 @@ def main():
             loss = model(tok[:, :-1], tok[:, 1:]) / n_mb
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
-        if world > 1:                                   # attention / router / embedding weights are replicated
+        if dense_opt is not None:
+            dense_opt.step()
+            dense_opt.clear_grad()
+        elif world > 1:                                 # attention / router / embedding weights are replicated
             for p in shared:
                 g = getattr(p, "main_grad", None)
                 g = g if g is not None else p.grad
@@ -113,8 +149,14 @@ def main():
             "config": {"model": args.model, "layers": cfg.num_hidden_layers,
                        "reduced_depth": cfg.num_hidden_layers < 32 and args.model != "tiny",
                        "experts": args.experts, "global_batch": world * n_mb, "seq_len": seq,
-                       "parallelism": f"ep{world}", "l2": "inputs larger than L2"}}))
+                       "parallelism": f"ep{world}" + ("+sharding1(dense)" if dense_opt is not None else ""), "l2": "inputs larger than L2"}}))
     if world > 1:
+        torch.cuda.synchronize()
+        tdist.barrier()
+        from paddle_b200.parallel import moe_exchange, symm
+        moe_exchange._exchanges.clear()
+        symm.release_all()
+        tdist.barrier()
         tdist.destroy_process_group()
     return 0
 

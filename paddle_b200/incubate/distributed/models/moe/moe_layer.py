@@ -97,8 +97,15 @@ class MoELayer(nn.Layer):
             # one autograd function: fp8-quantising dispatch over peer memory, grouped block-scaled GEMMs, weighted
             # combine; routing metadata stays on the device
             from .....parallel.moe_exchange import fused_moe_forward
+            cap = self.fused_capacity
+            cf = getattr(self.gate, "capacity_factor", None)
+            if cap is None and cf:
+                # a router that already prunes to a per-expert capacity over this rank's tokens: the receive regions are
+                # sized to exactly that, so the exchange itself drops nothing
+                k_ = gate.shape[1] if gate.dim() > 1 else 1
+                cap = int(cf * inp.shape[0] * k_ / (self.num_expert * self.world_size)) + 1
             y = fused_moe_forward(C._plain(inp), C._plain(value), C._plain(gate), self.experts, self.group,
-                                  capacity_factor=self.fused_capacity_factor, cap=self.fused_capacity)
+                                  capacity_factor=self.fused_capacity_factor, cap=cap)
             return as_tensor(y).reshape(origin_shape)
         pos, local_count, global_count, fwd_count, fwd_bs = prepare_forward(gate, self.num_expert, self.world_size,
                                                                             self.group)

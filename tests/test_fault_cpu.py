@@ -285,3 +285,74 @@ def test_weight_grad_store_defers_and_matches_plain_backward():
     WeightGradStore.run(batch)
     for p, g in zip(net.parameters(), ref):
         assert torch.allclose(p.grad, g, atol=1e-6)
+
+
+def test_native_process_group_task_timeout_error_and_abort(tmp_path):
+    """The native process group against stand-in NCCL / CUDA-runtime libraries (host-injected failures, no GPU): a
+    collective completes and its task is forgotten; a stalled one times out within the bound, the failure is published
+    for the peers and the communicator is aborted; an asynchronous communicator error is reported as such; a failing
+    NCCL call surfaces its result code; an aborted group refuses further calls."""
+    import ctypes
+    import os
+    import subprocess
+    import time
+
+    import pytest
+    import torch
+
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "fakes")
+    libs = {}
+    for name in ("fake_nccl", "fake_cudart"):
+        out = str(tmp_path / f"lib{name}.so")
+        subprocess.run(["gcc", "-shared", "-fPIC", "-O1", "-o", out, os.path.join(here, name + ".c")], check=True)
+        libs[name] = out
+    from paddle_b200.distributed import native_pg as N
+    N.load(libs["fake_nccl"], libs["fake_cudart"])
+    fn, fc = ctypes.CDLL(libs["fake_nccl"]), ctypes.CDLL(libs["fake_cudart"])
+
+    class Store(dict):
+        def set(self, k, v): self[k] = v
+        def get(self, k): return self[k]
+        def check(self, keys): return all(k in self for k in keys)
+
+    store = Store()
+    pg = N.NativeProcessGroup(0, 1, device=0, store=store, name="g0")
+    assert "pd/nccl_id/g0" in store and len(store["pd/nccl_id/g0"]) == 128
+    x = torch.arange(8, dtype=torch.float32)
+    out = torch.zeros(8)
+    pg.all_gather(out, x)                                  # sync_op: issued on the comm stream, waited for
+    assert torch.equal(out, x) and pg.inflight() == 0
+    t = pg.all_reduce(x, sync_op=False)
+    assert t.is_completed() and t.wait(timeout=1.0) and pg.inflight() == 0
+    pg.broadcast(x, 0, use_calc_stream=True)
+    # a failing NCCL call is reported with its result code
+    fn.fake_nccl_set(0, 3)
+    with pytest.raises(N.CommError, match="nccl result 3"):
+        pg.all_reduce(x)
+    # asynchronous communicator error while waiting
+    fc.fake_cuda_stall(1)
+    t = pg.all_reduce(x, sync_op=False)
+    assert not t.is_completed()
+    fn.fake_nccl_set(1, 0)
+    with pytest.raises(N.CommError) as e:
+        t.wait(timeout=5.0)
+    assert e.value.kind == "comm_error" and pg.aborted and fn.fake_nccl_aborts() == 1
+    assert b"comm_error" in store["pd/comm_error/g0"]
+    with pytest.raises(N.CommError, match="aborted"):
+        pg.all_reduce(x)
+    pg.destroy()
+    # timeout: bounded, then abort; a second group learns about it from the store before its next call
+    fn.fake_nccl_set(0, 0)
+    store2 = Store()
+    pg2 = N.NativeProcessGroup(0, 1, store=store2, name="g1")
+    t = pg2.reduce_scatter(out, x, sync_op=False)
+    t0 = time.perf_counter()
+    with pytest.raises(N.CommError) as e:
+        t.wait(timeout=0.2)
+    assert e.value.kind == "timeout" and 0.15 < time.perf_counter() - t0 < 2.0 and fn.fake_nccl_aborts() == 2
+    fc.fake_cuda_stall(0)
+    peer = N.NativeProcessGroup(0, 1, store=store2, name="g1", unique_id=store2["pd/nccl_id/g1"])
+    with pytest.raises(N.CommError, match="a peer reported"):
+        peer.all_reduce(x)
+    assert peer.aborted
+    peer.destroy(), pg2.destroy()
