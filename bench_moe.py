@@ -85,8 +85,9 @@ def main():
             def get_model_parallel_group(self): return None
             def get_pipe_parallel_group(self): return None
         enable_main_grad(_Only(expert_params))
-        dense_opt = DygraphShardingOptimizerV2(mk(shared), _ShardingTopology(), {"comm_overlap": True,
-                                                                                  "comm_buffer_size_MB": 256})
+        dense_opt = DygraphShardingOptimizerV2(mk(shared), _ShardingTopology(),
+                                               {"comm_overlap": True, "comm_buffer_size_MB": 256,
+                                                "accumulate_steps": args.micro_batches})
         opt = mk(expert_params)
     else:
         enable_main_grad(model)

@@ -183,6 +183,14 @@ __device__ __forceinline__ void load_b(const CUtensorMap* tm, uint8_t* dst, uint
   }
 }
 
+// Optional phase timestamps of the all-gather GEMM (diagnostics, globaltimer ns): per CTA {start, loads issued,
+// ns spent waiting for arrival flags, epilogue done, push done (communication CTAs)}.  Off unless pd_ag_gemm_trace(1).
+__device__ int g_ag_trace_on = 0;
+__device__ unsigned long long g_ag_trace[256 * 8];
+__device__ __forceinline__ void ag_trace(int slot, unsigned long long v) {
+  if (g_ag_trace_on && blockIdx.x < 256) g_ag_trace[blockIdx.x * 8 + slot] = v;
+}
+
 // ============================================================================================ ag_gemm
 struct AGParams {
   int gathered_b;      // wait_mode 1 only: the gathered (token-major) operand is B instead of A
@@ -297,6 +305,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // warps kept it (and with it every flag) waiting until the whole push was over.
         __syncthreads();
       }
+      if (threadIdx.x == 0) ag_trace(4, globaltimer_ns());
       return;
     }
     if (threadIdx.x != 0) return;
@@ -410,9 +419,11 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  if (threadIdx.x == 0) ag_trace(0, globaltimer_ns());
 
   if (warp == 4) {
     if (lane == 0) {
+      unsigned long long waited = 0;
       prefetch_tmap(&tmA);
       prefetch_tmap(&tmB);
       prefetch_tmap(&tmL);
@@ -439,7 +450,9 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           local_tile = (m0 / rows_per_rank) == rank;
           const int chunk = m0 / sub_rows;      // == src * n_sub + sub-chunk
           if (!local_tile && chunk != last_chunk) {
+            const unsigned long long w0 = g_ag_trace_on ? globaltimer_ns() : 0;
             if (!flag_wait_ge(flags_local + chunk, epoch, wait_ns, status, 600)) { ok = false; *abort_flag = 1; break; }
+            if (g_ag_trace_on) waited += globaltimer_ns() - w0;
             fence_proxy_async_all();
             last_chunk = chunk;
           }
@@ -478,6 +491,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
+      ag_trace(1, globaltimer_ns());
+      ag_trace(2, waited);
       if (!ok)
         for (int i = 0; i < STAGES; ++i)
           if (armed & (1u << i)) mbar_drain(&bars->full[i], (armed_parity >> i) & 1u);
@@ -549,6 +564,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     if (epi_tid == 0) {
       tma_wait_group<0>();
+      ag_trace(3, globaltimer_ns());
       if (alive && p.do_ack) {
         // all staged data of this epoch has been consumed by this CTA: the last CTA acknowledges to every rank
         __threadfence();
@@ -1263,9 +1279,20 @@ PD_EXPORT int pd_gemm_rs_mc(const void* A, const void* B, void* out, int M, int 
 
 // Diagnostics: switch the per-CTA phase timestamps of pd_gemm_rs on / off, and copy them out (256 x 4 values).
 PD_EXPORT int pd_gemm_rs_trace(int on) {
+  void* p = nullptr;
+  if (on && cudaGetSymbolAddress(&p, pd::gc::g_rs_trace) == cudaSuccess) cudaMemset(p, 0, sizeof(unsigned long long) * 256 * 8);
   return cudaMemcpyToSymbol(pd::gc::g_rs_trace_on, &on, sizeof(int)) == cudaSuccess ? 0 : pd::kErrCuda;
 }
 PD_EXPORT int pd_gemm_rs_trace_read(unsigned long long* host_out) {
   return cudaMemcpyFromSymbol(host_out, pd::gc::g_rs_trace, sizeof(unsigned long long) * 256 * 8) == cudaSuccess
+             ? 0 : pd::kErrCuda;
+}
+PD_EXPORT int pd_ag_gemm_trace(int on) {
+  void* p = nullptr;
+  if (on && cudaGetSymbolAddress(&p, pd::gc::g_ag_trace) == cudaSuccess) cudaMemset(p, 0, sizeof(unsigned long long) * 256 * 8);
+  return cudaMemcpyToSymbol(pd::gc::g_ag_trace_on, &on, sizeof(int)) == cudaSuccess ? 0 : pd::kErrCuda;
+}
+PD_EXPORT int pd_ag_gemm_trace_read(unsigned long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, pd::gc::g_ag_trace, sizeof(unsigned long long) * 256 * 8) == cudaSuccess
              ? 0 : pd::kErrCuda;
 }

@@ -45,6 +45,14 @@ inline bool encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, cons
                         CUtensorMapSwizzle swz) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
+  // The encoder is a driver-API call and needs a context bound to THIS thread.  The runtime binds the primary context
+  // lazily, on a thread's first runtime call that needs it; a worker thread (the autograd engine's) whose first CUDA
+  // work is one of these launchers has none yet, and the encoder answers CUDA_ERROR_INVALID_CONTEXT.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   cuuint64_t d[5], s[4];
   cuuint32_t b[5], e[5];
   for (int i = 0; i < rank; ++i) {
@@ -56,6 +64,15 @@ inline bool encode_tmap(CUtensorMap* out, CUtensorMapDataType dt, int rank, cons
   CUresult r = fn(out, dt, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, s, b, e,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {   // say which map was refused: the launcher only returns kErrTensorMap
+    fprintf(stderr, "[pd] cuTensorMapEncodeTiled failed (%d): base %p rank %d dims", static_cast<int>(r), base, rank);
+    for (int i = 0; i < rank; ++i) fprintf(stderr, " %llu", static_cast<unsigned long long>(d[i]));
+    fprintf(stderr, " strides");
+    for (int i = 0; i + 1 < rank; ++i) fprintf(stderr, " %llu", static_cast<unsigned long long>(s[i]));
+    fprintf(stderr, " box");
+    for (int i = 0; i < rank; ++i) fprintf(stderr, " %u", b[i]);
+    fprintf(stderr, "\n");
+  }
   return r == CUDA_SUCCESS;
 }
 

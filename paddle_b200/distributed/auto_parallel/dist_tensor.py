@@ -114,7 +114,7 @@ class _AllToAll(torch.autograd.Function):
         assert x.shape[dst_dim] % n == 0
         ins = [c.contiguous() for c in x.chunk(n, dim=dst_dim)]
         outs = [torch.empty_like(ins[0]) for _ in range(n)]
-        C.alltoall(ins, outs, group=group)
+        C._alltoall_io(ins, outs, group=group)
         return torch.cat([_plain(o) for o in outs], dim=src_dim)
 
     @staticmethod

@@ -304,7 +304,13 @@ def reduce_scatter(tensor, tensor_list, op=ReduceOp.SUM, group=None, sync_op=Tru
     return _finish(w, sync_op, use_calc_stream)
 
 
-def alltoall(in_tensor_list, out_tensor_list, group=None, sync_op=True, use_calc_stream=False):
+def alltoall(out_tensor_list, in_tensor_list, group=None, sync_op=True, use_calc_stream=False):
+    """Tensor i of ``in_tensor_list`` goes to rank i; ``out_tensor_list`` receives one tensor per rank (argument order of
+    python/paddle/distributed/communication/all_to_all.py:26: outputs first)."""
+    return _alltoall_io(in_tensor_list, out_tensor_list, group, sync_op, use_calc_stream)
+
+
+def _alltoall_io(in_tensor_list, out_tensor_list, group=None, sync_op=True, use_calc_stream=False):
     g = _grp(group)
     if g.nranks == 1:
         out_tensor_list.clear()
@@ -335,8 +341,15 @@ def alltoall(in_tensor_list, out_tensor_list, group=None, sync_op=True, use_calc
 all_to_all = alltoall
 
 
-def alltoall_single(in_tensor, out_tensor, in_split_sizes=None, out_split_sizes=None, group=None, sync_op=True,
+def alltoall_single(out_tensor, in_tensor, in_split_sizes=None, out_split_sizes=None, group=None, sync_op=True,
                     use_calc_stream=False):
+    """Rows of ``in_tensor`` are split over the ranks (evenly or by ``in_split_sizes``); ``out_tensor`` receives the
+    pieces in rank order (python/paddle/distributed/communication/all_to_all.py:78: output first)."""
+    return _alltoall_single_io(in_tensor, out_tensor, in_split_sizes, out_split_sizes, group, sync_op, use_calc_stream)
+
+
+def _alltoall_single_io(in_tensor, out_tensor, in_split_sizes=None, out_split_sizes=None, group=None, sync_op=True,
+                        use_calc_stream=False):
     g = _grp(group)
     if g.nranks == 1:
         out_tensor.copy_(in_tensor)
@@ -345,7 +358,7 @@ def alltoall_single(in_tensor, out_tensor, in_split_sizes=None, out_split_sizes=
         n = g.nranks
         ins = list(torch.split(_plain(in_tensor), in_split_sizes or in_tensor.shape[0] // n, 0))
         outs = list(torch.split(_plain(out_tensor), out_split_sizes or out_tensor.shape[0] // n, 0))
-        return alltoall(ins, outs, group, sync_op, use_calc_stream)
+        return _alltoall_io(ins, outs, group, sync_op, use_calc_stream)
     w = tdist.all_to_all_single(_plain(out_tensor), _plain(in_tensor.contiguous()), out_split_sizes, in_split_sizes,
                                 group=g.process_group, async_op=True)
     return _finish(w, sync_op, use_calc_stream)

@@ -40,15 +40,15 @@ def alltoall(out_tensor_or_tensor_list, in_tensor_or_tensor_list, group=None, sy
     _check(sync_op, use_calc_stream)
     import torch
     if isinstance(in_tensor_or_tensor_list, torch.Tensor):
-        return C.alltoall_single(in_tensor_or_tensor_list, out_tensor_or_tensor_list, None, None, group, sync_op,
+        return C._alltoall_single_io(in_tensor_or_tensor_list, out_tensor_or_tensor_list, None, None, group, sync_op,
                                  use_calc_stream)
-    return C.alltoall(in_tensor_or_tensor_list, out_tensor_or_tensor_list, group, sync_op, use_calc_stream)
+    return C._alltoall_io(in_tensor_or_tensor_list, out_tensor_or_tensor_list, group, sync_op, use_calc_stream)
 
 
 def alltoall_single(out_tensor, in_tensor, out_split_sizes=None, in_split_sizes=None, group=None, sync_op=True,
                     use_calc_stream=False):
     _check(sync_op, use_calc_stream)
-    return C.alltoall_single(in_tensor, out_tensor, in_split_sizes, out_split_sizes, group, sync_op, use_calc_stream)
+    return C._alltoall_single_io(in_tensor, out_tensor, in_split_sizes, out_split_sizes, group, sync_op, use_calc_stream)
 
 
 def scatter(tensor, tensor_or_tensor_list=None, src=0, group=None, sync_op=True, use_calc_stream=False):

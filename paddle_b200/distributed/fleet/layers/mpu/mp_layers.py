@@ -52,6 +52,20 @@ class VocabParallelEmbedding(Layer):
                                      vocab_size=self.origin_num_embeddings)
         return mp_ops._mp_allreduce(out, group=self.model_parallel_group)
 
+    def forward_sequence_parallel(self, x):
+        """Embedding of all tokens of ``x`` flattened to ``[T]``, returned as this rank's sequence shard ``[T / n, H]``
+        (what ``ScatterOp.apply(embedding(x).reshape([T, H]))`` gives).  On GPUs with peer-mapped memory one kernel
+        writes every row into the shard of the rank that owns its token; otherwise lookup, all-reduce and slice."""
+        tokens = 1
+        for d in x.shape:
+            tokens *= int(d)
+        if self.is_mp and mp_ops.fused_embedding_available(self.weight, tokens, self.model_parallel_group):
+            return mp_ops.vocab_parallel_embedding_to_sequence_shard(x, self.weight, self.model_parallel_group,
+                                                                     self.vocab_start_index)
+        from ...utils.sequence_parallel_utils import ScatterOp
+        h = self.forward(x)
+        return ScatterOp.apply(h.reshape([tokens, h.shape[-1]]))
+
 
 class ColumnParallelLinear(Layer):
     def __init__(self, in_features, out_features, weight_attr=None, has_bias=None, gather_output=True,

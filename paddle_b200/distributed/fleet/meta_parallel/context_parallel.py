@@ -63,12 +63,12 @@ def _a2a(x, group, scatter_heads):
         # piece p = heads [p*h/n, (p+1)*h/n) of my tokens -> rank p; I receive my head group for every rank's tokens
         send = x.reshape(b, s, n, h // n, d).permute(2, 0, 1, 3, 4).contiguous()      # [n, b, s, h/n, d]
         recv = torch.empty_like(send)
-        C.alltoall_single(send.view(n * b, -1), recv.view(n * b, -1), group=group)
+        C._alltoall_single_io(send.view(n * b, -1), recv.view(n * b, -1), group=group)
         return recv.permute(1, 0, 2, 3, 4).reshape(b, n * s, h // n, d)               # sequence in rank order
     assert s % n == 0
     send = x.reshape(b, n, s // n, h, d).permute(1, 0, 2, 3, 4).contiguous()          # [n, b, s/n, h, d]
     recv = torch.empty_like(send)
-    C.alltoall_single(send.view(n * b, -1), recv.view(n * b, -1), group=group)
+    C._alltoall_single_io(send.view(n * b, -1), recv.view(n * b, -1), group=group)
     return recv.permute(1, 2, 0, 3, 4).reshape(b, s // n, n * h, d)                   # heads in rank order
 
 

@@ -30,7 +30,7 @@ def _exchange(x, send_counts, recv_counts, group, n_local):
     if n == 1:
         out.copy_(x)
     else:
-        C.alltoall_single(x.contiguous(), out, in_splits, out_splits, group=group)
+        C._alltoall_single_io(x.contiguous(), out, in_splits, out_splits, group=group)
     return C._plain(out)
 
 

@@ -56,14 +56,14 @@ def _capacity_limit(topk_idx, num_expert, world_size, capacity, group):
         pos_count = _number_count(topk_idx, num_expert * world_size)
         if world_size > 1:
             glob = torch.empty_like(pos_count)
-            C.alltoall_single(pos_count, glob, group=group)
+            C._alltoall_single_io(pos_count, glob, group=group)
         else:
             glob = pos_count
         # experts of this rank: counts arriving from every worker, clipped in worker order
         allowed = _limit_by_capacity(glob, cap, world_size)
         if world_size > 1:
             back = torch.empty_like(allowed)
-            C.alltoall_single(allowed, back, group=group)
+            C._alltoall_single_io(allowed, back, group=group)
         else:
             back = allowed
         return _prune_gate_by_capacity(topk_idx, back, num_expert, world_size)

@@ -22,7 +22,7 @@ def prepare_forward(gate, num_expert, world_size, moe_group):
         local_expert_count = _number_count(gate, num_expert * world_size)
         if world_size > 1:
             global_expert_count = torch.empty_like(local_expert_count)
-            C.alltoall_single(local_expert_count, global_expert_count, group=moe_group)
+            C._alltoall_single_io(local_expert_count, global_expert_count, group=moe_group)
         else:
             global_expert_count = local_expert_count
         fwd_expert_count = global_expert_count.reshape(world_size, num_expert).sum(0)

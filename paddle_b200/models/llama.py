@@ -186,11 +186,11 @@ class LlamaModel(nn.Layer):
 
     def forward(self, input_ids):
         batch, seq = input_ids.shape
-        h = self.embed_tokens(input_ids).reshape([batch * seq, self.config.hidden_size])
         sp = self.config.tensor_parallel_degree > 1 and self.config.sequence_parallel
         if sp:
-            from ..distributed.fleet.utils.sequence_parallel_utils import ScatterOp
-            h = ScatterOp.apply(h)
+            h = self.embed_tokens.forward_sequence_parallel(input_ids)
+        else:
+            h = self.embed_tokens(input_ids).reshape([batch * seq, self.config.hidden_size])
         residual = None
         for layer in self.layers:
             if self.config.recompute and self.training:

@@ -66,10 +66,16 @@ def bench_gemm(args, timer, hbm, tf):
         a = torch.randn((K, M) if ta else (M, K), device="cuda").to(torch.bfloat16)
         b = torch.randn((N, K) if tb else (K, N), device="cuda").to(torch.bfloat16)
         t = timer(lambda: native.gemm(a, b, ta, tb), args.iters)
+        # the other tile scheme for comparison (default: 256 x 256 per SM pair, cta_group::2)
+        other = "1cta" if native.GEMM_IMPL == "2cta" else "2cta"
+        prev = native.set_gemm_impl(other)
+        t_other = timer(lambda: native.gemm(a, b, ta, tb), args.iters)
+        native.set_gemm_impl(prev)
         A, B = (a.t() if ta else a), (b.t() if tb else b)
         t2 = timer(lambda: torch.matmul(A, B), args.iters) if not args.no_baseline else float("nan")
         fl = 2.0 * M * N * K
-        out.append(dict(op="gemm", name=name, M=M, N=N, K=K, ms=t, tflops=fl / t / 1e9, frac_of_measured=fl / t / 1e9 / tf,
+        out.append(dict(op="gemm", name=name, impl=prev, M=M, N=N, K=K, ms=t, tflops=fl / t / 1e9,
+                        frac_of_measured=fl / t / 1e9 / tf, **{f"{other}_ms": t_other, f"{other}_tflops": fl / t_other / 1e9},
                         lib_ms=t2, lib_tflops=fl / t2 / 1e9))
         print(json.dumps(out[-1]), flush=True)
     return out

@@ -59,10 +59,13 @@ def main():
         out_rs = torch.empty(elems // n, device="cuda", dtype=torch.bfloat16)
         cases = {
             # name: (ours, nccl, bytes on the bus per rank)
-            "all_reduce": (lambda: sc.all_reduce(x, out_ar), lambda: tdist.all_reduce(out_ar), 2 * size * (n - 1) / n),
+            "all_reduce": (lambda: sc._run(0, x, out_ar, size), lambda: tdist.all_reduce(out_ar), 2 * size * (n - 1) / n),
             "reduce_scatter": (lambda: sc.reduce_scatter(rows, out_rs),
                                lambda: tdist.reduce_scatter_tensor(out_rs, rows.reshape(-1)), size * (n - 1) / n),
         }
+        if sc.nvls_available() and size >= 65536:
+            cases["all_reduce_nvls"] = (lambda: sc.all_reduce_nvls(x, out_ar), lambda: tdist.all_reduce(out_ar),
+                                        2 * size * (n - 1) / n)
         if size * n <= (args.max_mb << 20):
             cases["all_gather"] = (lambda: sc.all_gather(x, out_ag), lambda: tdist.all_gather_into_tensor(out_ag, x),
                                    size * (n - 1))

@@ -26,6 +26,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--trace", action="store_true",
+                    help="print the per-CTA phase timestamps of the push reduce-scatter GEMM (GEMM tiles done, arrivals "
+                         "published, first reduce unit, reduction done; microseconds from kernel start)")
     args = ap.parse_args()
 
     import torch.distributed as tdist
@@ -127,6 +130,32 @@ def main():
             key = f"fused_mode{mode}" + (f"_ctas{ctas}" if ctas is not None else "")
             rec[key + "_us"] = t
             rec[key + "_err"] = err
+            if args.trace and ctas is None:
+                import ctypes
+
+                import numpy as np
+                k = _lib.kernels()
+                k.pd_ag_gemm_trace(1)
+                for _ in range(3):
+                    run()
+                torch.cuda.synchronize()
+                tdist.barrier()
+                buf = (ctypes.c_ulonglong * 2048)()
+                k.pd_ag_gemm_trace_read(buf)
+                k.pd_ag_gemm_trace(0)
+                tt = np.array(list(buf), dtype=np.float64).reshape(256, 8)
+                gemm = tt[tt[:, 3] > 0]
+                comm = tt[tt[:, 4] > 0]
+                if gemm.size:
+                    t0 = gemm[:, 0].min()
+                    med = lambda v: [round(float(v.min()), 1), round(float(np.median(v)), 1), round(float(v.max()), 1)]   # noqa: E731
+                    rec[key + "_trace"] = {"gemm_ctas": int(gemm.shape[0]), "comm_ctas": int(comm.shape[0]),
+                                           "loads_issued_us": med((gemm[:, 1] - t0) / 1e3),
+                                           "flag_wait_us": med(gemm[:, 2] / 1e3),
+                                           "epilogue_done_us": med((gemm[:, 3] - t0) / 1e3),
+                                           "push_done_us": med((comm[:, 4] - t0) / 1e3) if comm.size else None}
+                for r_ in range(8 * 256):
+                    buf[r_] = 0
             del pair
         emit(rec)
 
@@ -162,6 +191,29 @@ def main():
             key = ("fused_nvls_red%d" % n_red) if use_mc else "fused_push"
             rec[key + "_us"] = t
             rec[key + "_err"] = err
+            if args.trace and not use_mc:
+                import ctypes
+
+                import numpy as np
+                k = _lib.kernels()
+                k.pd_gemm_rs_trace(1)
+                for _ in range(3):
+                    run()
+                torch.cuda.synchronize()
+                tdist.barrier()
+                buf = (ctypes.c_ulonglong * 2048)()
+                k.pd_gemm_rs_trace_read(buf)
+                k.pd_gemm_rs_trace(0)
+                tt = np.array(list(buf), dtype=np.float64).reshape(256, 8)
+                tt = tt[tt[:, 0] > 0]
+                t0 = tt[:, 0].min()
+                rec["trace_ctas"] = int(tt.shape[0])
+                for nm, col in (("gemm_done", 1), ("signalled", 2), ("first_unit_ready", 4), ("first_unit_reduced", 5),
+                                ("reduced", 3)):
+                    v = (tt[:, col] - t0) / 1e3
+                    v = v[v > 0]
+                    if v.size:
+                        rec[f"trace_{nm}_us"] = [round(float(v.min()), 1), round(float(np.median(v)), 1), round(float(v.max()), 1)]
             del pair
         emit(rec)
     tdist.barrier()

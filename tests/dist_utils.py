@@ -38,8 +38,11 @@ def run_workers(script, nranks, backend="gloo", extra_env=None, timeout=240, arg
     try:
         return _run_workers(script, nranks, backend, extra_env, timeout, args, gpus)
     except AssertionError as e:
-        # another process can grab a rendezvous port between the probe and the workers' bind: try once more
-        if _retry and ("ddress already in use" in str(e) or "EADDRINUSE" in str(e)):
+        # another process can grab a rendezvous port between the probe and the workers' bind
+        # (or a loaded machine resets a connection while the ranks build gloo's full mesh): try once more
+        transient = ("ddress already in use", "EADDRINUSE", "Connection refused", "Connection reset", "connectFullMesh",
+                     "Broken pipe")
+        if _retry and any(t in str(e) for t in transient):
             return _run_workers(script, nranks, backend, extra_env, timeout, args, gpus)
         raise
 

@@ -22,9 +22,9 @@ dist.all_gather(out, x); res["all_gather_into"] = out.numpy()
 rs = paddle.to_tensor(np.zeros(8 // n, np.float32), place=dev)
 dist.reduce_scatter(rs, x); res["reduce_scatter"] = rs.numpy()
 ins = [paddle.to_tensor(np.full(3, rank * 10 + j, np.float32), place=dev) for j in range(n)]
-outs = []; dist.alltoall(ins, outs); res["alltoall"] = np.stack([o.numpy() for o in outs])
+outs = []; dist.alltoall(outs, ins); res["alltoall"] = np.stack([o.numpy() for o in outs])
 a2 = paddle.to_tensor(np.zeros(8, np.float32), place=dev)
-dist.alltoall_single(x, a2); res["alltoall_single"] = a2.numpy()
+dist.alltoall_single(a2, x); res["alltoall_single"] = a2.numpy()
 sc = paddle.to_tensor(np.zeros(4, np.float32), place=dev)
 dist.scatter(sc, [paddle.to_tensor(np.full(4, j + 1, np.float32), place=dev) for j in range(n)] if rank == 0 else None, 0)
 res["scatter"] = sc.numpy()

@@ -24,8 +24,8 @@ def build():
     ex = FP8GroupedExperts(NL, H, I, initializer_range=0.05).to("gpu").to(dtype="bfloat16")
     paddle.seed(9)
     layer = MoELayer(H, ex, gate={"type": "naive", "top_k": 2}, moe_group=group)
-    for p in layer.gate.parameters():
-        p.data = p.data.to("cuda")
+    layer.to("gpu")
+    layer.to(dtype="bfloat16")
     return layer
 
 

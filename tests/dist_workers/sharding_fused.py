@@ -90,6 +90,11 @@ for dtype, numel in ((torch.float32, 1000), (torch.bfloat16, 70001 * 2), (torch.
         rs_ref = torch.empty(numel // n, device="cuda", dtype=dtype)
         dist.reduce_scatter(rs_ref, list(x.chunk(n)), group=g)
         errs.append(float((sc.reduce_scatter(x).float() - rs_ref.float()).abs().max() / rs_ref.float().abs().max()))
+for dtype, rows_each, width in ((torch.bfloat16, 5, 33), (torch.float32, 64, 1024), (torch.uint8, 3, 7)):
+    x = (torch.randn(n * rows_each, width, device="cuda") * 40).to(dtype)
+    a2a_ref = torch.empty_like(x)
+    dist.alltoall_single(a2a_ref, x, group=g)
+    errs.append(float((sc.all_to_all(x).float() - a2a_ref.as_subclass(torch.Tensor).float()).abs().max()))
 res["symm_coll_err"] = max(errs)
 # poisoned receive buffers: every byte a collective reads must have been written by a peer in THIS call, so filling
 # both receive slots with NaN beforehand may not change any result (a read-before-arrival would surface as NaN)
@@ -133,4 +138,87 @@ for _ in range(3):
 res["symm_coll_graph_err"] = max(ge)
 torch.cuda.synchronize()
 _lib.check_status()
+# vocab-parallel cross entropy: the symmetric-memory exchange kernel against the two-all-reduce form, forward and
+# backward, rows not a multiple of the block, ignored labels, two different row counts in turn
+from paddle_b200.distributed.fleet.layers.mpu import mp_ops
+ce_err = []
+for rows in (1000, 4096, 1000):
+    torch.manual_seed(77)                                   # same labels everywhere
+    V = 512
+    labels = torch.randint(0, V * n, (rows,), device="cuda")
+    labels[::17] = -100
+    torch.manual_seed(100 + rank)
+    lg = torch.randn(rows, V, device="cuda").bfloat16()
+    outs = []
+    for fusedce in ("1", "0"):
+        os.environ["PD_FUSED_CE"] = fusedce
+        l = lg.clone().requires_grad_(True)
+        loss = mp_ops._ParallelCE.apply(l, labels, g, -100)
+        loss.sum().backward()
+        outs.append((loss.detach().float(), l.grad.float()))
+    os.environ.pop("PD_FUSED_CE")
+    ce_err.append(float((outs[0][0] - outs[1][0]).abs().max()))
+    ce_err.append(float((outs[0][1] - outs[1][1]).abs().max()))
+res["fused_ce_err"] = max(ce_err)
+torch.cuda.synchronize()
+_lib.check_status()
+# vocabulary-parallel embedding written straight into the sequence shards, against the plain lookup in the full table
+emb_err = []
+for T_tok in (n * 96, n * 1000):
+    Vs, Hh = 256, 512
+    torch.manual_seed(5)
+    full_table = (torch.randn(n * Vs, Hh, device="cuda") * 0.5).bfloat16()
+    ids = torch.randint(0, n * Vs, (T_tok,), device="cuda")
+    wsh = full_table[rank * Vs:(rank + 1) * Vs].clone().requires_grad_(True)
+    shard = mp_ops._VocabEmbedToSeqShard.apply(ids, wsh, g, rank * Vs)
+    rows = T_tok // n
+    ref_t = full_table.clone().float().requires_grad_(True)
+    ref_full = torch.nn.functional.embedding(ids, ref_t)
+    emb_err.append(float((shard.float() - ref_full[rank * rows:(rank + 1) * rows]).abs().max()))
+    torch.manual_seed(6)
+    dy_full = torch.randn(T_tok, Hh, device="cuda").bfloat16()
+    shard.backward(dy_full[rank * rows:(rank + 1) * rows])
+    ref_full.backward(dy_full.float())
+    ref_dw = ref_t.grad[rank * Vs:(rank + 1) * Vs]
+    emb_err.append(float((wsh.grad.float() - ref_dw).abs().max() / ref_dw.abs().max()))
+res["fused_embedding_err"] = max(emb_err)
+torch.cuda.synchronize()
+_lib.check_status()
+# in-switch (NVLS) two-shot all-reduce: sizes that change from call to call (the per-block arrival counts must carry
+# over), a poisoned buffer, and CUDA-graph replay
+res["symm_nvls"] = bool(sc.nvls_available())
+if sc.nvls_available():
+    ne = []
+    for dtype, numel in ((torch.float32, 262144), (torch.bfloat16, 8 * 1000), (torch.bfloat16, 524288),
+                         (torch.float32, 4 * 33333), (torch.bfloat16, 8 * 1000)):
+        x = torch.randn(numel, device="cuda").to(dtype)
+        ref = x.float().clone()
+        dist.all_reduce(ref, group=g)
+        dist.barrier(group=g)
+        torch.cuda.synchronize()
+        sc._nvls_state()["block"].local[: numel * x.element_size()].fill_(0xFF)   # NaN pattern in both dtypes
+        torch.cuda.synchronize()
+        dist.barrier(group=g)
+        got = sc.all_reduce_nvls(x)
+        ne.append(float((got.float() - ref).abs().max() / ref.abs().max()) if not torch.isnan(got.float()).any() else 1e9)
+    res["symm_nvls_err"] = max(ne)
+    xs = torch.randn(1 << 18, device="cuda").bfloat16()
+    outg = torch.empty_like(xs)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        sc.all_reduce_nvls(xs, out=outg)
+    torch.cuda.current_stream().wait_stream(side)
+    graph2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph2):
+        sc.all_reduce_nvls(xs, out=outg)
+    ref = xs.float().clone()
+    dist.all_reduce(ref, group=g)
+    ge = []
+    for _ in range(3):
+        outg.zero_()
+        graph2.replay()
+        ge.append(float((outg.float() - ref).abs().max() / ref.abs().max()))
+    res["symm_nvls_graph_err"] = max(ge)
+    torch.cuda.synchronize()
+    _lib.check_status()
 _common.dump(res)

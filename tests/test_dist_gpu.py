@@ -83,6 +83,10 @@ def test_fused_sharding_kernels():
         assert r["rs_adamw_err"] < 1e-2, r
         assert r["zero3_linear_err"] < 2e-2, r
         assert r["symm_coll_err"] < 1e-2 and r["symm_coll_graph_err"] < 1e-4, r
+        assert r["fused_ce_err"] < 1e-4, r
+        assert r["fused_embedding_err"] < 1e-2, r
+        if r.get("symm_nvls"):
+            assert r["symm_nvls_err"] < 1e-2 and r["symm_nvls_graph_err"] < 1e-2, r
 
 
 def test_fused_moe_dispatch_combine():
