@@ -55,6 +55,9 @@ struct Params {
   const float* lse;     // [B, Hq, Sq] natural log
   const float* delta;   // [B, Hq, Sq]
   int* status;
+  const int4* bounds;   // column-sparse mask, as in the forward kernel: [B, mask_heads, Sk] of {lts, lte, uts, ute}
+  int mask_heads;
+  const int4* tile_bounds;   // [B, mask_heads, ceil(Sk / 128)] of {max lts, min lte, max uts, min ute}
 };
 
 __device__ __forceinline__ bool warp_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
@@ -75,6 +78,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+template <bool kMask>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -102,7 +106,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int first_q = kv0 - causal_off;            // first query row that sees kv row kv0
     t0 = first_q > 0 ? first_q / BQ : 0;
   }
-  const int per_head = n_sub > t0 ? n_sub - t0 : 0;
+  int t1 = n_sub;
+  if (kMask && p.mask_heads != p.Hq) {
+    // query sub-tiles outside [t0, t1) are masked as a whole for every column of this key tile: rows from max lts on
+    // when the lower range is open-ended, rows below min ute when the upper range starts at row 0.  (With one mask per
+    // query head the range would differ between the heads this CTA walks, so it is not narrowed then.)
+    const int mh = p.mask_heads == 1 ? 0 : kv_head;
+    const int4 tb = __ldg(p.tile_bounds + (static_cast<size_t>(batch) * p.mask_heads + mh) * gridDim.x + jb);
+    if (tb.y >= p.Sq) t1 = min(t1, (max(tb.x, 0) + BQ - 1) / BQ);
+    if (tb.z <= 0) t0 = max(t0, min(tb.w, p.Sq) / BQ);
+  }
+  const int per_head = t1 > t0 ? t1 - t0 : 0;
   const int n_it = per_head * group;
 
   if (threadIdx.x == 0) {
@@ -261,6 +275,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_after();
       // visible iff kv <= q + off  <=>  q_local >= kvi - off - q0
       const int first_visible = p.causal ? (kvi - causal_off - q0) : 0;
+      // this thread's key column carries its own masked query-row ranges (made local to the sub-tile here)
+      int4 b4 = make_int4(0, 0, 0, 0);
+      if (kMask && kvi < p.Sk) {
+        const int mh = p.mask_heads == 1 ? 0 : (p.mask_heads == p.Hq ? qh : kv_head);
+        b4 = __ldg(p.bounds + (static_cast<size_t>(batch) * p.mask_heads + mh) * p.Sk + kvi);
+        b4.x -= q0; b4.y -= q0; b4.z -= q0; b4.w -= q0;
+      }
       const uint32_t buf = tmem + lane_base + COL_BUF + b * 128;
       uint32_t s_r[2][32], dp_r[2][32];
       tmem_ld_32x32(buf + OFF_ST, s_r[0]);
@@ -282,7 +303,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float pe = fast_exp2(fmaf(__uint_as_float(s_r[h][c + e]), p.scale_log2, -l2[e]));
-            if (h * 32 + c + e < first_visible) pe = 0.f;
+            const int ql = h * 32 + c + e;
+            if (ql < first_visible || (kMask && ((ql >= b4.x && ql < b4.y) || (ql >= b4.z && ql < b4.w)))) pe = 0.f;
             pv[e] = pe;
             dsv[e] = pe * (__uint_as_float(dp_r[h][c + e]) - dl[e]) * p.scale;
           }
@@ -445,7 +467,8 @@ PD_EXPORT int pd_flash_attn_bwd(const void* d_o, const void* q, const void* k, c
                                 int64_t k_tok, int64_t k_batch, int64_t v_tok, int64_t v_batch, int64_t o_tok,
                                 int64_t o_batch, int64_t do_tok, int64_t do_batch, int64_t dq_tok, int64_t dq_batch,
                                 int64_t dk_tok, int64_t dk_batch, int64_t dv_tok, int64_t dv_batch, float scale, int causal,
-                                int* status, cudaStream_t stream) {
+                                const void* bounds, const void* tile_bounds, int mask_heads, int* status,
+                                cudaStream_t stream) {
   using namespace pd;
   using namespace pd::fab;
   (void)unused;
@@ -469,16 +492,21 @@ PD_EXPORT int pd_flash_attn_bwd(const void* d_o, const void* q, const void* k, c
   if (!ok) return kErrTensorMap;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return kErrCuda;
     configured = true;
   }
   const int64_t rows = static_cast<int64_t>(B) * Sq * Hq;
   delta_kernel<<<static_cast<unsigned>((rows * 32 + 255) / 256), 256, 0, stream>>>(
       (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, B, Sq, Hq, o_tok, o_batch, do_tok, do_batch);
-  Params p{B, Sq, Sk, Hq, Hkv, causal, scale, scale * 1.4426950408889634f, lse, delta, status};
+  if (bounds != nullptr && (mask_heads != 1 && mask_heads != Hq && mask_heads != Hkv)) return kErrBadShape;
+  if (bounds != nullptr && (!aligned16(bounds) || tile_bounds == nullptr || !aligned16(tile_bounds))) return kErrAlignment;
+  Params p{B, Sq, Sk, Hq, Hkv, causal, scale, scale * 1.4426950408889634f, lse, delta, status,
+           static_cast<const int4*>(bounds), mask_heads, static_cast<const int4*>(tile_bounds)};
   dim3 grid((Sk + BKV - 1) / BKV, Hkv, B);
-  flash_bwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmQ, tmDO, tmK, tmV, tmDQ, tmDK, tmDV, p);
+  if (bounds != nullptr) flash_bwd_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmQ, tmDO, tmK, tmV, tmDQ, tmDK, tmDV, p);
+  else flash_bwd_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmQ, tmDO, tmK, tmV, tmDQ, tmDK, tmDV, p);
   int64_t blocks = (rows * 32 + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   dq_convert_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, rows, Sq, Hq, dq_tok,

@@ -38,6 +38,7 @@ struct Barriers {
   uint64_t drain;
   uint32_t tmem_base;
   int abort_flag;
+  int j_lo, j_hi;       // key tiles [j_lo, j_hi) are visited (mask-aware)
 };
 
 struct Params {
@@ -46,6 +47,14 @@ struct Params {
   float scale_log2;   // softmax scale * log2(e)
   float* lse;         // [B, Hq, Sq]
   int* status;
+  // column-sparse mask (flashmask): per key column four query-row bounds {lts, lte, uts, ute}; query row r does not
+  // see column c iff lts <= r < lte or uts <= r < ute.  [B, mask_heads, Sk] with mask_heads 1, Hkv or Hq; null = none.
+  const int4* bounds;
+  int mask_heads;
+  // per 128-column key tile: {max lts, min lte, max uts, min ute} over its columns, [B, mask_heads, ceil(Sk / 128)];
+  // a (query tile, key tile) pair is skipped when one of the two ranges covers every row of the query tile for every
+  // column of the key tile
+  const int4* tile_bounds;
 };
 
 // lane 0 performs the bounded wait, the verdict is shared so that the warp stays convergent for the
@@ -69,6 +78,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+template <bool kMask>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -90,7 +100,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int causal_off = p.Sk - p.Sq;                             // key j visible to query i iff j <= i + off
   int kv_len = p.Sk;
   if (p.causal) kv_len = min(p.Sk, q0 + BQ + causal_off);
-  const int n_kv = kv_len > 0 ? (kv_len + BKV - 1) / BKV : 0;
+  int n_kv = kv_len > 0 ? (kv_len + BKV - 1) / BKV : 0;
+  int jbase = 0;
 
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
@@ -110,10 +121,38 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     fence_mbar_init();
   }
   if (warp == 5) tmem_alloc(&bars->tmem_base, 512);
+  if (kMask && warp == 1) {
+    // first and last key tile that is not masked out as a whole for this query tile
+    const int mh = p.mask_heads == 1 ? 0 : (p.mask_heads == p.Hq ? head : kv_head);
+    const int tiles_k = (p.Sk + BKV - 1) / BKV;
+    const int4* tb = p.tile_bounds + (static_cast<size_t>(batch) * p.mask_heads + mh) * tiles_k;
+    int lo = n_kv, hi = 0;
+    for (int j = lane; j < n_kv; j += 32) {
+      const int4 b = __ldg(tb + j);
+      const bool dead = (b.x <= q0 && b.y >= q0 + BQ) || (b.z <= q0 && b.w >= q0 + BQ);
+      if (!dead) {
+        lo = min(lo, j);
+        hi = max(hi, j + 1);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      lo = min(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+      hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    }
+    if (lane == 0) {
+      bars->j_lo = lo;
+      bars->j_hi = hi;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
+  if (kMask) {
+    jbase = bars->j_lo;
+    n_kv = bars->j_hi > bars->j_lo ? bars->j_hi - bars->j_lo : 0;
+  }
 
   if (warp == 4) {
     // ---------------------------------------------------------------- TMA producer
@@ -130,16 +169,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = (j / KV_STAGES) & 1;
         if (!mbar_wait(&bars->k_empty[s], ph ^ 1, abort_flag, p.status, 100 + s)) { ok = false; break; }
         mbar_expect_tx(&bars->k_full[s], TILE_BYTES);
-        tma_load_4d(sK + s * TILE_BYTES, &tmK, &bars->k_full[s], 0, kv_head, j * BKV, batch);
-        tma_load_4d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &bars->k_full[s], 64, kv_head, j * BKV, batch);
+        tma_load_4d(sK + s * TILE_BYTES, &tmK, &bars->k_full[s], 0, kv_head, (jbase + j) * BKV, batch);
+        tma_load_4d(sK + s * TILE_BYTES + HALF_BYTES, &tmK, &bars->k_full[s], 64, kv_head, (jbase + j) * BKV, batch);
         if (!mbar_wait(&bars->v_empty[s], ph ^ 1, abort_flag, p.status, 110 + s)) {
           mbar_drain(&bars->k_full[s], ph);
           ok = false;
           break;
         }
         mbar_expect_tx(&bars->v_full[s], TILE_BYTES);
-        tma_load_4d(sV + s * TILE_BYTES, &tmV, &bars->v_full[s], 0, kv_head, j * BKV, batch);
-        tma_load_4d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, &bars->v_full[s], 64, kv_head, j * BKV, batch);
+        tma_load_4d(sV + s * TILE_BYTES, &tmV, &bars->v_full[s], 0, kv_head, (jbase + j) * BKV, batch);
+        tma_load_4d(sV + s * TILE_BYTES + HALF_BYTES, &tmV, &bars->v_full[s], 64, kv_head, (jbase + j) * BKV, batch);
       }
       if (!ok || *abort_flag) {
         mbar_drain(&bars->q_full, 0);
@@ -212,8 +251,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t s_tmem = tmem + lane_base + COL_S + (j & 1) * 128;
       const uint32_t p_tmem = tmem + lane_base + COL_P + (j & 1) * 64;
       // highest visible key column (local to this tile) for this row
-      int col_limit = p.Sk - 1 - j * BKV;
-      if (p.causal) col_limit = min(col_limit, qi + causal_off - j * BKV);
+      const int col0 = (jbase + j) * BKV;          // first key column of this tile
+      int col_limit = p.Sk - 1 - col0;
+      if (p.causal) col_limit = min(col_limit, qi + causal_off - col0);
       const bool need_mask = col_limit < BKV - 1;
       // one TMEM read of the whole 128-column row: four loads in flight, one wait
       uint32_t r[4][32];
@@ -226,6 +266,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             if (c * 32 + i > col_limit) r[c][i] = 0xff800000u;   // -inf: contributes exp2(-inf) = 0
+          }
+        }
+      }
+      if (kMask) {
+        // every lane of the warp reads the same address: one broadcast transaction per column
+        const int mh = p.mask_heads == 1 ? 0 : (p.mask_heads == p.Hq ? head : kv_head);
+        const int4* bnd = p.bounds + (static_cast<size_t>(batch) * p.mask_heads + mh) * p.Sk + col0;
+        const int cols = min(BKV, p.Sk - col0);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (c * 32 + i < cols) {
+              const int4 b4 = __ldg(bnd + c * 32 + i);
+              if ((qi >= b4.x && qi < b4.y) || (qi >= b4.z && qi < b4.w)) r[c][i] = 0xff800000u;
+            }
           }
         }
       }
@@ -355,13 +411,17 @@ static bool make_map(CUtensorMap* m, const void* ptr, int B, int S, int H, int64
 }  // namespace pd
 
 // q: [B, Sq, Hq, 128], k/v: [B, Sk, Hkv, 128], o: [B, Sq, Hq, 128] (bf16; strides in elements, head
-// stride must be 128), lse: [B, Hq, Sq] fp32.
+// stride must be 128), lse: [B, Hq, Sq] fp32.  bounds: optional int32 [B, mask_heads, Sk, 4] column-sparse mask
+// (see Params::bounds; python/paddle/nn/functional/flash_attention.py:1299 `flashmask_attention`).
 PD_EXPORT int pd_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq,
                                 int Sk, int Hq, int Hkv, int64_t q_tok, int64_t q_batch, int64_t k_tok,
                                 int64_t k_batch, int64_t v_tok, int64_t v_batch, int64_t o_tok, int64_t o_batch,
-                                float scale, int causal, int* status, cudaStream_t stream) {
+                                float scale, int causal, const void* bounds, const void* tile_bounds, int mask_heads,
+                                int* status, cudaStream_t stream) {
   using namespace pd;
   using namespace pd::fa;
+  if (bounds != nullptr && (mask_heads != 1 && mask_heads != Hq && mask_heads != Hkv)) return kErrBadShape;
+  if (bounds != nullptr && (!aligned16(bounds) || tile_bounds == nullptr || !aligned16(tile_bounds))) return kErrAlignment;
   if (B <= 0 || Sq <= 0 || Sk <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0) return kErrBadShape;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return kErrAlignment;
   if ((q_tok % 8) || (k_tok % 8) || (v_tok % 8) || (o_tok % 8) || (q_batch % 8) || (k_batch % 8) ||
@@ -373,12 +433,15 @@ PD_EXPORT int pd_flash_attn_fwd(const void* q, const void* k, const void* v, voi
     return kErrTensorMap;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return kErrCuda;
     configured = true;
   }
-  Params p{B, Sq, Sk, Hq, Hkv, causal, scale * 1.4426950408889634f, lse, status};
+  Params p{B, Sq, Sk, Hq, Hkv, causal, scale * 1.4426950408889634f, lse, status, static_cast<const int4*>(bounds),
+           mask_heads, static_cast<const int4*>(tile_bounds)};
   dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
-  flash_fwd_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, p);
+  if (bounds != nullptr) flash_fwd_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, p);
+  else flash_fwd_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmQ, tmK, tmV, tmO, p);
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }

@@ -51,6 +51,11 @@ class SymmCollectives:
     def nvls_available(self):
         return self.n > 1 and symm.multicast_enabled() and self.block.mc_ptr != 0
 
+    def _nvls_pays(self, nbytes):
+        """Through the switch every GPU moves about (1 + 1/n) of the vector per direction (its own copy is read over
+        the link as well), a direct exchange 2 (n - 1) / n: the switch only wins from four ranks up."""
+        return self.n >= 4 and nbytes >= self.NVLS_MIN_BYTES and nbytes % 16 == 0 and self.nvls_available()
+
     def all_reduce_nvls(self, x, out=None):
         """Two-shot all-reduce in which the NVSwitch does the additions (multimem.ld_reduce) and the broadcast
         (multimem.st).  bf16 or fp32, byte size a multiple of 16."""
@@ -87,7 +92,7 @@ class SymmCollectives:
         assert x.dtype in (torch.bfloat16, torch.float32)
         out = torch.empty_like(x) if out is None else out
         nbytes = x.numel() * x.element_size()
-        if nbytes >= self.NVLS_MIN_BYTES and nbytes % 16 == 0 and self.nvls_available():
+        if self._nvls_pays(nbytes):
             return self.all_reduce_nvls(x, out)
         return self._run(0, x, out, nbytes)
 

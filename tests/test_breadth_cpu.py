@@ -591,3 +591,44 @@ def test_c_ops_registry_coverage_and_kernel_level_semantics():
     assert _C_ops.shape64(x).numpy().tolist() == [1, 1, 4, 4]
     c = _C_ops.fft_r2c(paddle.to_tensor(np.ones(8, "float32")), [0])
     assert tuple(c.shape) == (5,) and np.allclose(c.numpy()[0], 8.0)
+
+
+def test_flashmask_bounds_normalisation_matches_dense_mask():
+    """The uniform {lts, lte, uts, ute} form the attention kernels consume hides exactly the entries the reference's
+    dense conversion hides, for all four input forms and for sliding windows; the per-tile summary never declares a
+    tile dead that has a visible entry."""
+    import torch
+
+    from paddle_b200.nn.functional.flash_attention import _flashmask_dense, _window_bounds
+    from paddle_b200.ops.attention import normalize_flashmask
+    S = 300
+    g = torch.Generator().manual_seed(3)
+    cols = torch.arange(S, dtype=torch.int32)
+    lts = (cols + torch.randint(1, 90, (S,), generator=g, dtype=torch.int32)).clamp(max=S)
+    lte = (lts + torch.randint(0, 90, (S,), generator=g, dtype=torch.int32)).clamp(max=S)
+    ute = (cols - torch.randint(0, 90, (S,), generator=g, dtype=torch.int32)).clamp(min=0)
+    uts = (ute - torch.randint(0, 60, (S,), generator=g, dtype=torch.int32)).clamp(min=0)
+    cases = [(True, lts.view(1, 1, S, 1)), (True, torch.stack([lts, lte], -1).view(1, 1, S, 2)),
+             (False, torch.stack([lts, ute], -1).view(1, 1, S, 2)),
+             (False, torch.stack([lts, lte, uts, ute], -1).view(1, 1, S, 4)),
+             (True, _window_bounds(None, 17, True, 1, S, S, "cpu")),
+             (False, _window_bounds(None, (9, 30), False, 1, S, S, "cpu"))]
+    rows = torch.arange(S).view(1, 1, S, 1)
+    for causal, idx in cases:
+        dense = _flashmask_dense(idx, S, S, causal, "cpu")
+        b, tb = normalize_flashmask(idx, causal, S)
+        lo, le, us, ue = (b[..., i].unsqueeze(2) for i in range(4))
+        mine = ((rows >= lo) & (rows < le)) | ((rows >= us) & (rows < ue))
+        if causal:
+            mine = mine | (rows < torch.arange(S).view(1, 1, 1, S))
+        assert torch.equal(mine, dense)
+        for t in range(tb.shape[2]):
+            x = tb[0, 0, t]
+            for q0 in range(0, S, 128):
+                dead = (x[0] <= q0 and x[1] >= q0 + 128) or (x[2] <= q0 and x[3] >= q0 + 128)
+                if dead:
+                    assert bool(dense[0, 0, q0:q0 + 128, t * 128:(t + 1) * 128].all())
+    # window semantics: key j is visible to row i iff i - left <= j <= i + right
+    w = _flashmask_dense(_window_bounds(None, (9, 30), False, 1, S, S, "cpu"), S, S, False, "cpu")[0, 0]
+    i, j = torch.meshgrid(torch.arange(S), torch.arange(S), indexing="ij")
+    assert torch.equal(~w, (j >= i - 9) & (j <= i + 30))
