@@ -31,7 +31,20 @@ constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 2 * C_CHUNK_BYTES + 1024 + 256;
 constexpr uint32_t PEER_BIT_MASK = 0xFEFFFFFFu;   // clears the CTA-pair bit of a shared::cluster address -> leader CTA
 
-enum Epi : int { kStoreBf16 = 0, kStoreF32 = 1, kAccumF32 = 2 };
+enum Epi : int { kStoreBf16 = 0, kStoreF32 = 1, kAccumF32 = 2, kBiasAct = 3, kSwiglu = 4 };
+// kBiasAct: C = act(A B + bias) as bf16 (bias bf16 [N] or null; act: 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh),
+// 4 silu) - the reference's fused_gemm_epilogue (paddle/phi/kernels/fusion/gpu/fused_gemm_epilogue_kernel.cu).
+// kSwiglu: the N columns hold (gate, up) pairs interleaved; C [M, N / 2] = silu(gate) * up as bf16, i.e. the first
+// feed-forward GEMM with its activation, without the [M, N] intermediate ever reaching memory.
+__device__ __forceinline__ float apply_act(float x, int act) {
+  switch (act) {
+    case 1: return fmaxf(x, 0.f);
+    case 2: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+    case 3: return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    case 4: return x / (1.f + __expf(-x));
+    default: return x;
+  }
+}
 
 struct Barriers {
   uint64_t full[STAGES];
@@ -127,7 +140,8 @@ __device__ __forceinline__ void load_half(void* dst, const CUtensorMap* tm, uint
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int mn3d, int splits, int* status) {
+                  const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int mn3d, int splits, int* status,
+                  const __nv_bfloat16* bias, int act) {
   extern __shared__ uint8_t smem_raw[];
   // the dynamic shared memory starts at the same offset in both CTAs, so the aligned carve-up is identical in both
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -243,7 +257,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   } else {
     // ------------------------------------------------------------ epilogue (warps 0..3 of each CTA: its 128 rows)
     const int epi_tid = threadIdx.x;
-    constexpr int CW = (EPI == kStoreBf16) ? 64 : 32;
+    constexpr int CW = (EPI == kStoreBf16 || EPI == kBiasAct) ? 64 : (EPI == kSwiglu ? 128 : 32);
     constexpr int NCHUNK = TILE_N / CW;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     int it = 0;
@@ -270,12 +284,43 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         named_bar_sync(1, 128);
         uint8_t* row_ptr = stage + epi_tid * 128;
         const int sw = epi_tid & 7;
-        if (EPI == kStoreBf16) {
+        if (EPI == kSwiglu) {
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_acc + c * CW + h * 32, r);
+            tmem_ld_wait();
+            float o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float g = __uint_as_float(r[2 * i]), u = __uint_as_float(r[2 * i + 1]);
+              o[i] = g / (1.f + __expf(-g)) * u;
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              uint4 v;
+              v.x = pack_bf16x2(o[8 * j + 0], o[8 * j + 1]);
+              v.y = pack_bf16x2(o[8 * j + 2], o[8 * j + 3]);
+              v.z = pack_bf16x2(o[8 * j + 4], o[8 * j + 5]);
+              v.w = pack_bf16x2(o[8 * j + 6], o[8 * j + 7]);
+              *reinterpret_cast<uint4*>(row_ptr + (((h * 2 + j) ^ sw) << 4)) = v;
+            }
+          }
+        } else if (EPI == kStoreBf16 || EPI == kBiasAct) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             uint32_t r[32];
             tmem_ld_32x32(t_acc + c * CW + h * 32, r);
             tmem_ld_wait();
+            if (EPI == kBiasAct) {
+              const int col0 = n0 + c * CW + h * 32;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float x = __uint_as_float(r[i]);
+                if (bias != nullptr && col0 + i < N) x += __bfloat162float(__ldg(bias + col0 + i));
+                r[i] = __float_as_uint(apply_act(x, act));
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint4 v;
@@ -306,6 +351,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
           if (rows_live && n0 + c * CW < N) {
             if (EPI == kAccumF32) tma_reduce_add_2d(&tmC, stage, n0 + c * CW, m0);
+            else if (EPI == kSwiglu) tma_store_2d(&tmC, stage, (n0 + c * CW) / 2, m0);
             else tma_store_2d(&tmC, stage, n0 + c * CW, m0);
           }
           tma_commit_group();
@@ -323,7 +369,8 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 
 template <bool A_MN, bool B_MN, int EPI>
 static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, int M, int N, int K,
-                          int mn3d, int* status, cudaStream_t stream, int max_ctas, int splits) {
+                          int mn3d, int* status, cudaStream_t stream, int max_ctas, int splits,
+                          const __nv_bfloat16* bias = nullptr, int act = 0) {
   auto kfn = gemm2_bf16_kernel<A_MN, B_MN, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -335,7 +382,7 @@ static int launch_variant(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
   if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2;
   if (clusters > tiles) clusters = tiles;
   if (clusters < 1) clusters = 1;
-  kfn<<<clusters * 2, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, M, N, K, mn3d, splits, status);
+  kfn<<<clusters * 2, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmC, M, N, K, mn3d, splits, status, bias, act);
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }
 
@@ -375,5 +422,36 @@ PD_EXPORT int pd_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, in
   PD_GEMM2_CASE(0, 0, 1) PD_GEMM2_CASE(0, 1, 1) PD_GEMM2_CASE(1, 0, 1) PD_GEMM2_CASE(1, 1, 1)
   PD_GEMM2_CASE(0, 0, 2) PD_GEMM2_CASE(0, 1, 2) PD_GEMM2_CASE(1, 0, 2) PD_GEMM2_CASE(1, 1, 2)
 #undef PD_GEMM2_CASE
+  return kErrBadShape;
+}
+
+// C = act(A B + bias) (swiglu = 0; C bf16 [M, N]) or C = silu(gate) * up over interleaved (gate, up) column pairs
+// (swiglu = 1; C bf16 [M, N / 2], N a multiple of 16, bias must be null).  Operand layouts as pd_gemm_bf16_2cta.
+PD_EXPORT int pd_gemm_bf16_2cta_epi(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                    int a_mn_major, int b_mn_major, const void* bias, int act, int swiglu, int* status,
+                                    cudaStream_t stream) {
+  using namespace pd;
+  using namespace pd::gemm2;
+  if (M <= 0 || N <= 0 || K <= 0 || act < 0 || act > 4) return kErrBadShape;
+  if (swiglu && (bias != nullptr || (N % 16))) return kErrBadShape;
+  if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return kErrAlignment;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8)) return kErrAlignment;
+  CUtensorMap tmA, tmB, tmC;
+  bool ok = true;
+  int a3d = 0, b3d = 0;
+  if (!a_mn_major) ok &= encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, A, K, M, uint64_t(lda) * 2, BK, BM);
+  else ok &= encode_tmap_mn(&tmA, A, M, K, uint64_t(lda) * 2, BM / 64, BK, &a3d);
+  if (!b_mn_major) ok &= encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, B, K, N, uint64_t(ldb) * 2, BK, BN_HALF);
+  else ok &= encode_tmap_mn(&tmB, B, N, K, uint64_t(ldb) * 2, BN_HALF / 64, BK, &b3d);
+  ok &= encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, C, swiglu ? N / 2 : N, M, uint64_t(ldc) * 2, 64, BM);
+  if (!ok) return kErrTensorMap;
+  const __nv_bfloat16* bp = static_cast<const __nv_bfloat16*>(bias);
+#define PD_GEMM2_EPI_CASE(AM, BM_)                                                                              \
+  if (a_mn_major == AM && b_mn_major == BM_) {                                                                  \
+    if (swiglu) return launch_variant<AM, BM_, kSwiglu>(tmA, tmB, tmC, M, N, K, a3d | (b3d << 1), status, stream, 0, 1); \
+    return launch_variant<AM, BM_, kBiasAct>(tmA, tmB, tmC, M, N, K, a3d | (b3d << 1), status, stream, 0, 1, bp, act);   \
+  }
+  PD_GEMM2_EPI_CASE(0, 0) PD_GEMM2_EPI_CASE(0, 1) PD_GEMM2_EPI_CASE(1, 0) PD_GEMM2_EPI_CASE(1, 1)
+#undef PD_GEMM2_EPI_CASE
   return kErrBadShape;
 }

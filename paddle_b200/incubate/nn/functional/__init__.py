@@ -104,18 +104,70 @@ def fused_linear(x, weight, bias=None, transpose_weight=False, name=None):
     return fused_matmul_bias(x, weight, bias, False, transpose_weight)
 
 
+def _kernel_ok(t):
+    return isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.bfloat16 and K._POLICY == "fused"
+
+
 def fused_linear_activation(x, y, bias, trans_x=False, trans_y=False, activation=None):
+    """``act(x @ y + bias)`` (fused_matmul_bias.py:113; kernel paddle/phi/kernels/fusion/gpu/fused_gemm_epilogue_kernel.cu).
+    Without autograd the bias and the activation run in the GEMM epilogue; under autograd the pre-activation is needed
+    for the backward pass, so only the bias is fused."""
+    from ....ops import native
+    act = activation if activation not in ("", "none") else None
+    needs_grad = torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in (x, y, bias))
+    if (not needs_grad and _kernel_ok(x) and _kernel_ok(y) and y.dim() == 2 and act in native.ACT_CODES and not trans_x
+            and x.shape[-1] % 8 == 0 and y.shape[0] % 8 == 0 and y.shape[1] % 8 == 0 and y.is_contiguous()
+            and (bias is None or (_kernel_ok(bias) and bias.is_contiguous()))):
+        x2 = x.reshape(-1, x.shape[-1])
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        out = native.gemm_epilogue(x2, y, bias, act, trans_b=bool(trans_y))
+        return as_tensor(out.view(*x.shape[:-1], out.shape[-1]))
     return _act(activation)(fused_matmul_bias(x, y, bias, trans_x, trans_y))
+
+
+def fused_linear_swiglu_interleaved(x, weight_interleaved):
+    """First feed-forward GEMM with its activation: ``weight_interleaved [in, 2F]`` holds the gate and up projections
+    with their columns interleaved (gate_0, up_0, gate_1, up_1, ...: see :func:`interleave_gate_up`); returns
+    ``silu(x @ gate) * (x @ up)`` as ``[..., F]`` from one kernel - the ``[..., 2F]`` product never reaches memory.
+    Inference path (no autograd: the backward pass would need the product)."""
+    from ....ops import native
+    x2 = x.reshape(-1, x.shape[-1])
+    x2 = x2 if x2.is_contiguous() else x2.contiguous()
+    if _kernel_ok(x2) and _kernel_ok(weight_interleaved) and weight_interleaved.shape[1] % 16 == 0:
+        out = native.gemm_epilogue(x2, weight_interleaved, swiglu=True)
+    else:
+        h = torch.matmul(x2, weight_interleaved)
+        out = torch.nn.functional.silu(h[:, 0::2]) * h[:, 1::2]
+    return as_tensor(out.view(*x.shape[:-1], out.shape[-1]))
+
+
+def interleave_gate_up(gate_weight, up_weight):
+    """``[in, F]`` gate and up projection weights as one ``[in, 2F]`` matrix with interleaved columns."""
+    return torch.stack([gate_weight, up_weight], -1).reshape(gate_weight.shape[0], -1).contiguous()
 
 
 def fused_bias_act(x, bias=None, dequant_scales=None, shift=None, smooth=None, act_method="gelu",
                    compute_dtype="default", quant_scale=-1, quant_round_type=0, quant_max_bound=0, quant_min_bound=0):
+    """``act(x + bias)`` in one pass (fused_bias_act.py; kernel paddle/phi/kernels/fusion/gpu/fused_bias_act_kernel.cu).
+    The int8 dequantise / quantise arguments of the reference are not provided."""
+    if dequant_scales is not None or shift is not None or smooth is not None or quant_scale > 0:
+        raise NotImplementedError("fused_bias_act: the int8 (de)quantisation arguments are not provided")
+    from ....ops import native
+    needs_grad = torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in (x, bias))
+    if (not needs_grad and _kernel_ok(x) and x.is_contiguous() and act_method in native.BIAS_ACT_CODES
+            and (x.shape[-1] // (2 if act_method in ("swiglu", "geglu") else 1)) % 8 == 0
+            and (bias is None or (_kernel_ok(bias) and bias.is_contiguous()))):
+        return as_tensor(native.bias_act(x, bias, act_method))
     if bias is not None:
         x = x + bias
     return _act(act_method)(x)
 
 
 def fused_dropout_add(x, y, p=0.5, training=True, mode="upscale_in_train", name=None):
+    """``dropout(x) + y`` (fused_dropout_add.py:30).  On the GPU one Philox kernel does both and the backward pass
+    regenerates the mask from (seed, offset) instead of reading a stored one."""
+    if training and 0.0 < p < 1.0 and K.dropout_add_supported(x, y):
+        return K.dropout_add(x, y, p, mode == "upscale_in_train")[0]
     return F.dropout(x, p, training=training, mode=mode) + y
 
 
@@ -296,8 +348,38 @@ def block_multihead_attention(qkv, key_cache, value_cache, seq_lens_encoder, seq
         return _block_attn_reference(qkv, key_cache, value_cache, lens, block_tables, Hq, Hkv, D, cos, sin,
                                      use_neox_style, scale, block_size, decode=True)
     lens = seq_lens_encoder.reshape([-1]).to(torch.int32)
+    if use_native:
+        return _block_attn_prefill_native(qkv, key_cache, value_cache, lens, block_tables, Hq, Hkv, D, cos, sin,
+                                          use_neox_style, scale, block_size)
     return _block_attn_reference(qkv, key_cache, value_cache, lens, block_tables, Hq, Hkv, D, cos, sin, use_neox_style,
                                  scale, block_size, decode=False)
+
+
+def _block_attn_prefill_native(qkv, kc, vc, lens, tables, Hq, Hkv, D, cos, sin, neox, scale, bs):
+    """Prefill of paged attention without a host loop: positions and page slots of all prompt tokens are computed on
+    the device, the rotated keys / values are scattered into the pages in one indexed store each, and the packed
+    prompts are attended in ONE launch of the flash kernels with a causal document mask (flash_attn_unpadded)."""
+    from ....nn.functional.flash_attention import flash_attn_unpadded
+    dev = qkv.device
+    lens64 = lens.to(torch.int64)
+    cu = torch.zeros(lens64.numel() + 1, dtype=torch.int64, device=dev)
+    cu[1:] = lens64.cumsum(0)
+    total = qkv.shape[0]
+    tok = torch.arange(total, device=dev)
+    seq = torch.searchsorted(cu, tok, right=True) - 1
+    pos = tok - cu[seq]
+    row = qkv.reshape(total, Hq + 2 * Hkv, D)
+    q, k, v = row[:, :Hq], row[:, Hq:Hq + Hkv], row[:, Hq + Hkv:]
+    if cos is not None:
+        c, s_ = cos[pos][:, None, :], sin[pos][:, None, :]
+        q = _rot(q.float(), c, s_, neox).to(qkv.dtype)
+        k = _rot(k.float(), c, s_, neox).to(qkv.dtype)
+    blk = tables.to(torch.int64)[seq, pos // bs]
+    kc[blk, :, pos % bs] = k.to(kc.dtype)
+    vc[blk, :, pos % bs] = v.to(vc.dtype)
+    cu32 = cu.to(torch.int32)
+    out, _ = flash_attn_unpadded(q.contiguous(), k.contiguous(), v.contiguous(), cu32, cu32, 0, 0, scale, causal=True)
+    return as_tensor(out.reshape(total, Hq * D)), qkv, kc, vc
 
 
 def _rot(t, cos, sin, neox):

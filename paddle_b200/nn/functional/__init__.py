@@ -208,6 +208,9 @@ def dropout(x, p=0.5, axis=None, training=True, mode="upscale_in_train", name=No
     if p == 0.0:
         return x
     if axis is None:
+        if 0.0 < p < 1.0 and K.dropout_add_supported(x):
+            # own Philox kernel: keep decisions addressed by the CUDA generator's (seed, offset), regenerated in backward
+            return K.dropout_add(x, None, p, mode == "upscale_in_train")[0]
         y = TF.dropout(x, p, True)
         return y if mode == "upscale_in_train" else y * (1.0 - p)
     axes = [axis] if isinstance(axis, int) else list(axis)

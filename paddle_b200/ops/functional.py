@@ -45,9 +45,12 @@ class _LinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
-        y = native.gemm(x2, weight)
-        if bias is not None:
-            y = y + bias
+        if bias is not None and bias.dtype == torch.bfloat16 and bias.is_contiguous() and weight.shape[1] % 8 == 0:
+            y = native.gemm_epilogue(x2, weight, bias)          # bias added in the GEMM epilogue
+        else:
+            y = native.gemm(x2, weight)
+            if bias is not None:
+                y = y + bias
         ctx.save_for_backward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.x_shape = x.shape
@@ -434,6 +437,49 @@ def embedding(ids, table, padding_idx=None, vocab_start=0, sharded=False):
     ok = (local >= 0) & (local < table.shape[0])
     out = torch.nn.functional.embedding(local.clamp(0, table.shape[0] - 1), table)
     return out * ok.unsqueeze(-1).to(out.dtype)
+
+
+# ------------------------------------------------------------------------------------------- dropout
+def _next_philox(n):
+    """(seed, offset) of the current CUDA generator for a dropout over ``n`` elements; advances the generator, so the
+    saved / restored generator state (RNG tracker, recompute) reproduces the same masks."""
+    gen = torch.cuda.default_generators[torch.cuda.current_device()]
+    seed, offset = gen.initial_seed(), gen.get_offset()
+    gen.set_offset(offset + native.dropout_offset_step(n))
+    return seed, offset
+
+
+class _DropoutAddFn(torch.autograd.Function):
+    """out = dropout(x) [+ y]; backward regenerates the keep decisions from (seed, offset) - no mask is stored
+    (paddle/phi/kernels/fusion/gpu/fused_dropout_add_grad_kernel.cu)."""
+
+    @staticmethod
+    def forward(ctx, x, y, p, upscale, seed, offset):
+        ctx.meta = (p, upscale, seed, offset, y is not None)
+        return native.dropout_add(x, y, p, upscale, seed, offset)
+
+    @staticmethod
+    def backward(ctx, dout):
+        p, upscale, seed, offset, has_y = ctx.meta
+        dout = dout.contiguous()
+        dx = native.dropout_add(dout, None, p, upscale, seed, offset) if ctx.needs_input_grad[0] else None
+        return dx, (dout if has_y else None), None, None, None, None
+
+
+def dropout_add_supported(x, y=None):
+    return (_native_any(x) and x.dtype in (torch.bfloat16, torch.float32) and x.is_contiguous()
+            and (y is None or (y.shape == x.shape and y.dtype == x.dtype and y.is_contiguous()))
+            and not torch.cuda.is_current_stream_capturing())
+
+
+def _native_any(x):
+    return isinstance(x, torch.Tensor) and x.is_cuda and _POLICY == "fused"
+
+
+def dropout_add(x, y, p, upscale=True, seed_offset=None):
+    """``dropout(x) + y`` (``y`` may be None) in one kernel; returns ``(out, (seed, offset))``."""
+    seed, offset = seed_offset if seed_offset is not None else _next_philox(x.numel())
+    return as_tensor(_DropoutAddFn.apply(x, y, float(p), bool(upscale), int(seed), int(offset))), (seed, offset)
 
 
 # ------------------------------------------------------------------------------------------- attention

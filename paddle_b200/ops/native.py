@@ -7,6 +7,8 @@ from __future__ import annotations
 
 import os
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -383,6 +385,90 @@ def adamw_flat(param_bf16, master, grad, m, v, lr, beta1, beta2, eps, coeff, bet
 
 
 # --------------------------------------------------------------------------------------------- decode / inference
+ACT_CODES = {None: 0, "none": 0, "identity": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4, "swish": 4}
+
+
+def gemm_epilogue(a, b, bias=None, act=None, trans_a=False, trans_b=False, swiglu=False, out=None):
+    """``act(op(a) @ op(b) + bias)`` in one kernel (bias bf16 ``[N]``; act in ``ACT_CODES``), or with ``swiglu=True``
+    ``silu(gate) * up`` over the interleaved (gate, up) column pairs of the product, returning ``[M, N / 2]``."""
+    _req(a.dtype == BF16 and b.dtype == BF16 and a.dim() == 2 and b.dim() == 2, "gemm_epilogue: 2-D bf16 operands required")
+    _req(a.stride(1) == 1 and b.stride(1) == 1, "gemm_epilogue: operands need a unit inner stride")
+    M, K = (a.shape[1], a.shape[0]) if trans_a else (a.shape[0], a.shape[1])
+    Kb, N = (b.shape[1], b.shape[0]) if trans_b else (b.shape[0], b.shape[1])
+    _req(K == Kb, f"gemm_epilogue: inner dimensions differ ({K} vs {Kb})")
+    _req(act in ACT_CODES, f"gemm_epilogue: unknown activation {act!r}")
+    if bias is not None:
+        _req(bias.dtype == BF16 and bias.numel() == N and bias.is_contiguous(), "gemm_epilogue: bias must be bf16 [N]")
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=BF16, device=a.device)
+    _req(out.dtype == BF16 and tuple(out.shape) == (M, n_out) and out.stride(1) == 1, "gemm_epilogue: bad `out`")
+    rc = _lib.kernels().pd_gemm_bf16_2cta_epi(
+        ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
+        c_int(out.stride(0)), c_int(1 if trans_a else 0), c_int(0 if trans_b else 1), ptr(bias), c_int(ACT_CODES[act]),
+        c_int(1 if swiglu else 0), ptr(_lib.status_buffer(a.device)), stream())
+    check(rc, "pd_gemm_bf16_2cta_epi")
+    _count()
+    return out
+
+
+def dropout_add(x, y, p, upscale, seed, offset, out=None):
+    """``dropout(x) [+ y]`` with keep decisions from the Philox stream at ``(seed, offset)``."""
+    _req(x.is_contiguous() and x.dtype in (BF16, F32), "dropout_add: contiguous bf16 / fp32 input required")
+    _req(y is None or (y.is_contiguous() and y.dtype == x.dtype and y.shape == x.shape), "dropout_add: bad `y`")
+    out = torch.empty_like(x) if out is None else out
+    rc = _lib.kernels().pd_dropout_add(ptr(x), ptr(y), ptr(out), c_int64(x.numel()), c_int(1 if x.dtype == F32 else 0),
+                                       c_float(p), c_int(1 if upscale else 0), ctypes.c_ulonglong(int(seed) & (2 ** 64 - 1)),
+                                       ctypes.c_ulonglong(int(offset)), stream())
+    check(rc, "pd_dropout_add")
+    _count()
+    return out
+
+
+def dropout_offset_step(n):
+    k = _lib.kernels()
+    k.pd_dropout_offset_step.restype = ctypes.c_longlong
+    return int(k.pd_dropout_offset_step(c_int64(n)))
+
+
+BIAS_ACT_CODES = {None: 0, "none": 0, "identity": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3, "silu": 4, "swish": 4,
+                  "swiglu": 5, "geglu": 6}
+
+
+def bias_act(x, bias, act):
+    """``act(x + bias)`` over the last axis; ``swiglu`` / ``geglu`` halve it (gate half first)."""
+    _req(x.dtype == BF16 and x.is_contiguous(), "bias_act: contiguous bf16 input required")
+    code = BIAS_ACT_CODES[act]
+    cols = x.shape[-1]
+    F_ = cols // 2 if code >= 5 else cols
+    rows = x.numel() // cols
+    _req(bias is None or (bias.dtype == BF16 and bias.numel() == cols and bias.is_contiguous()), "bias_act: bad bias")
+    out = torch.empty((*x.shape[:-1], F_), dtype=BF16, device=x.device)
+    rc = _lib.kernels().pd_bias_act(ptr(x), ptr(bias), ptr(out), c_int64(rows), c_int(F_), c_int(code), stream())
+    check(rc, "pd_bias_act")
+    _count()
+    return out
+
+
+def sample_top_p_top_k(logits, top_p=None, top_k=0, temperature=1.0, seed=0, offset=0, input_is_prob=False):
+    """One token per row from ``softmax(logits / temperature)`` cut to the ``top_k`` most likely tokens and to the
+    nucleus of mass ``top_p`` (fp32 ``[rows]`` or None).  Returns ``(ids int64 [rows], probs fp32 [rows])``."""
+    _req(logits.dim() == 2 and logits.stride(1) == 1 and logits.dtype in (BF16, F32), "sample: [rows, V] bf16 / fp32 required")
+    rows, V = logits.shape
+    ids = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    probs = torch.empty(rows, dtype=F32, device=logits.device)
+    if top_p is not None:
+        top_p = top_p.reshape(-1).to(F32).contiguous()
+        _req(top_p.numel() == rows, "sample: one top_p per row required")
+    rc = _lib.kernels().pd_sample_top_p_top_k(
+        ptr(logits), c_int(1 if logits.dtype == F32 else 0), c_int64(rows), c_int64(logits.stride(0)), c_int(V), ptr(top_p),
+        c_int(int(top_k)), c_float(float(temperature)), c_int(1 if input_is_prob else 0),
+        ctypes.c_ulonglong(int(seed) & (2 ** 64 - 1)), ctypes.c_ulonglong(int(offset)), ptr(ids), ptr(probs), stream())
+    check(rc, "pd_sample_top_p_top_k")
+    _count()
+    return ids, probs
+
+
 def gemm_splitk(a, b, acc_f32, splits=0, trans_b=False):
     """``acc_f32 += a @ op(b)`` with K cut into ``splits`` slices that run on different SMs (skinny decode GEMMs).
     ``splits=0`` picks a count that fills the GPU.  ``acc_f32`` must hold zeros (``splitk_finalize`` re-zeroes it)."""

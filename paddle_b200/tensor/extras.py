@@ -288,6 +288,22 @@ def top_p_sampling(x, ps, threshold=None, topp_seed=None, seed=-1, k=0, mode="tr
     ``top_p_sampling``)."""
     import torch
     from .._core.tensor import as_tensor
+    if (x.is_cuda and x.dim() == 2 and threshold is None and mode == "truncated" and not return_top
+            and x.shape[1] * 4 <= 200 * 1024 and x.dtype in (torch.bfloat16, torch.float32)):
+        # one kernel per call, no sort: bisection on the probability value inside shared memory
+        from ..ops import functional as K
+        from ..ops import native
+        if K.get_kernel_policy() == "fused":
+            xt = x.as_subclass(torch.Tensor)
+            xt = xt if xt.stride(1) == 1 else xt.contiguous()
+            if seed is not None and seed >= 0:
+                sd, off = int(seed), 0
+            else:
+                gen = torch.cuda.default_generators[torch.cuda.current_device()]
+                sd, off = gen.initial_seed(), gen.get_offset()
+                gen.set_offset(off + 4)
+            ids, probs = native.sample_top_p_top_k(xt, ps.as_subclass(torch.Tensor), k or 0, 1.0, sd, off, input_is_prob=True)
+            return as_tensor(probs.to(x.dtype).reshape(-1, 1)), as_tensor(ids.reshape(-1, 1))
     p = x.as_subclass(torch.Tensor).float()
     tp = ps.as_subclass(torch.Tensor).float().reshape(-1, 1)
     sp, si = torch.sort(p, dim=-1, descending=True)

@@ -159,3 +159,75 @@ def test_withheld_signal_returns_status_not_hang():
     ref = (x.float() @ w.float())
     assert (native.gemm(x, w).float() - ref).abs().max() / ref.abs().max() < 1e-2      # the context still works
     _lib.check_status()
+
+
+def test_block_multihead_attention_op_native_vs_reference():
+    """The Paddle-signature paged attention op on its native path (single-launch masked prefill, rope + append +
+    paged decode kernels) against the plain-operator form of the same op."""
+    import paddle_b200 as paddle
+    from paddle_b200.ops import _lib
+    from paddle_b200.ops import functional as K
+    IF = paddle.incubate.nn.functional
+    torch.manual_seed(9)
+    B, Hq, Hkv, D, bs = 3, 8, 2, 128, 64
+    lens = [130, 64, 7]
+    nblk = 4
+    tables = torch.arange(B * nblk, dtype=torch.int32, device="cuda").view(B, nblk)
+    half = D // 2
+    inv = 1.0 / (10000 ** (torch.arange(half, device="cuda").float() / half))
+    ang = torch.arange(512, device="cuda").float()[:, None] * inv[None]
+    rope = torch.stack([ang.cos(), ang.sin()]).view(2, 1, 512, 1, half)
+    qkv = (torch.randn(sum(lens), (Hq + 2 * Hkv) * D, device="cuda") * 0.5).bfloat16()
+    step = (torch.randn(B, (Hq + 2 * Hkv) * D, device="cuda") * 0.5).bfloat16()
+    enc = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    zero = torch.zeros(B, dtype=torch.int32, device="cuda")
+    one = torch.ones(B, dtype=torch.int32, device="cuda")
+    res = {}
+    for policy in ("fused", "baseline"):
+        K.set_kernel_policy(policy)
+        try:
+            kc = torch.zeros(B * nblk, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+            vc = torch.zeros_like(kc)
+            o1, _, kc, vc = IF.block_multihead_attention(qkv, kc, vc, enc, zero, enc, block_tables=tables, rope_emb=rope,
+                                                         use_neox_style=True, block_size=bs)
+            o2, _, kc, vc = IF.block_multihead_attention(step, kc, vc, zero, enc, one, block_tables=tables, rope_emb=rope,
+                                                         use_neox_style=True, block_size=bs)
+            res[policy] = (o1.float(), o2.float(), kc.float().clone(), vc.float().clone())
+        finally:
+            K.set_kernel_policy("fused")
+    _lib.check_status()
+    for a, b in zip(res["fused"], res["baseline"]):
+        assert (a - b).abs().max().item() < 3e-2 * b.abs().max().item() + 1e-2
+
+
+def test_sampling_kernel_distribution_and_cuts():
+    """Sort-free top-p / top-k sampler: drawn tokens stay inside the nucleus a sort would give, frequencies follow the
+    renormalised distribution, and (seed, offset) reproduces the draw."""
+    from paddle_b200.ops import native
+    torch.manual_seed(0)
+    V, rows = 1000, 40000
+    logits = torch.randn(V, device="cuda") * 2.0
+    probs = torch.softmax(logits, -1)
+    sp, si = torch.sort(probs, descending=True)
+    for top_p, top_k in ((0.8, 0), (1.0, 20), (0.6, 5), (1.0, 0)):
+        keep = (torch.cumsum(sp, 0) - sp) < top_p
+        if top_k:
+            keep[top_k:] = False
+        allowed = torch.zeros(V, dtype=torch.bool, device="cuda")
+        allowed[si[keep]] = True
+        want = torch.where(allowed, probs, torch.zeros_like(probs))
+        want = want / want.sum()
+        x = logits.expand(rows, V).contiguous()
+        ids, pr = native.sample_top_p_top_k(x, torch.full((rows,), top_p, device="cuda"), top_k, 1.0, seed=7, offset=0)
+        assert bool(allowed[ids].all())
+        freq = torch.bincount(ids, minlength=V).float() / rows
+        assert (freq - want).abs().max().item() < 0.01
+        assert torch.allclose(pr, probs[ids], rtol=1e-4, atol=1e-6)
+        ids2, _ = native.sample_top_p_top_k(x, torch.full((rows,), top_p, device="cuda"), top_k, 1.0, seed=7, offset=0)
+        assert torch.equal(ids, ids2)
+        ids3, _ = native.sample_top_p_top_k(x, torch.full((rows,), top_p, device="cuda"), top_k, 1.0, seed=7, offset=4)
+        assert not torch.equal(ids, ids3)
+    # bf16 logits of a 32000-token vocabulary, temperature, greedy limit
+    big = (torch.randn(8, 32000, device="cuda") * 3).bfloat16()
+    ids, _ = native.sample_top_p_top_k(big, None, 1, 0.7, seed=1)
+    assert torch.equal(ids, big.float().argmax(-1))

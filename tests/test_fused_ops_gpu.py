@@ -145,3 +145,86 @@ def test_accumulate_and_add():
     assert torch.allclose(acc, 1 + a.float())
     b = torch.randn(100000, device="cuda").to(BF)
     assert torch.allclose(native.add_bf16(a.contiguous(), b).float(), (a.float() + b.float()).to(BF).float())
+
+
+@pytest.mark.parametrize("act", [None, "relu", "gelu", "silu"])
+def test_gemm_bias_activation_epilogue(act):
+    """act(x @ W + b) from the GEMM epilogue against fp32."""
+    import paddle_b200 as paddle
+    from paddle_b200.ops import _lib
+    torch.manual_seed(3)
+    x = (torch.randn(3, 100, 256, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(256, 520, device="cuda") * 0.1).bfloat16()
+    b = torch.randn(520, device="cuda").bfloat16()
+    with torch.no_grad():
+        y = paddle.incubate.nn.functional.fused_linear_activation(x, w, b, activation=act)
+    _lib.check_status()
+    ref = x.float() @ w.float() + b.float()
+    ref = {None: lambda t: t, "relu": torch.relu, "gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu}[act](ref)
+    assert (y.float() - ref).abs().max().item() < 3e-2 * ref.abs().max().item() + 2e-2
+    # training path: bias in the epilogue, gradients through autograd
+    xg, wg, bg = x.clone().requires_grad_(True), w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    out = paddle.nn.functional.linear(xg, wg, bg)
+    out.float().pow(2).sum().backward()
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    (xf @ wf + bf).bfloat16().float().pow(2).sum().backward()
+    for a, r in ((xg.grad, xf.grad), (wg.grad, wf.grad), (bg.grad, bf.grad)):
+        assert (a.float() - r).abs().max().item() < 3e-2 * r.abs().max().item() + 1e-1
+
+
+def test_gemm_swiglu_epilogue():
+    import paddle_b200 as paddle
+    from paddle_b200.ops import _lib
+    IF = paddle.incubate.nn.functional
+    torch.manual_seed(4)
+    x = (torch.randn(300, 512, device="cuda") * 0.5).bfloat16()
+    gate = (torch.randn(512, 1376, device="cuda") * 0.05).bfloat16()
+    up = (torch.randn(512, 1376, device="cuda") * 0.05).bfloat16()
+    y = IF.fused_linear_swiglu_interleaved(x, IF.interleave_gate_up(gate, up))
+    _lib.check_status()
+    ref = torch.nn.functional.silu(x.float() @ gate.float()) * (x.float() @ up.float())
+    assert y.shape == (300, 1376)
+    assert (y.float() - ref).abs().max().item() < 3e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu", "silu", "swiglu", "geglu"])
+def test_bias_act_kernel(act):
+    import paddle_b200 as paddle
+    torch.manual_seed(5)
+    x = torch.randn(7, 33, 512, device="cuda").bfloat16()
+    b = torch.randn(512, device="cuda").bfloat16()
+    with torch.no_grad():
+        y = paddle.incubate.nn.functional.fused_bias_act(x, b, act_method=act)
+    h = x.float() + b.float()
+    if act in ("swiglu", "geglu"):
+        g, u = h.chunk(2, -1)
+        ref = (torch.nn.functional.silu(g) if act == "swiglu" else torch.nn.functional.gelu(g)) * u
+    else:
+        ref = getattr(torch.nn.functional, act)(h)
+    assert y.shape == ref.shape
+    assert (y.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_dropout_add_philox(dtype):
+    """Keep rate, scaling, reproducibility from (seed, offset), backward mask = forward mask, generator advance."""
+    import paddle_b200 as paddle
+    from paddle_b200.ops import functional as K
+    n, p = 1 << 20, 0.3
+    x = torch.ones(n + 5, device="cuda", dtype=dtype).requires_grad_(True)
+    y = torch.full((n + 5,), 2.0, device="cuda", dtype=dtype).requires_grad_(True)
+    out, (seed, off) = K.dropout_add(x, y, p)
+    kept = (out.float() - 2.0) > 0
+    assert abs(kept.float().mean().item() - (1 - p)) < 5e-3
+    assert torch.allclose(out.float()[kept], torch.tensor(2.0 + 1 / (1 - p), device="cuda"), atol=2e-2)
+    out.sum().backward()
+    assert torch.equal(x.grad.float() > 0, kept) and torch.all(y.grad.float() == 1)
+    out2, _ = K.dropout_add(x.detach(), y.detach(), p, seed_offset=(seed, off))
+    assert torch.equal(out2, out.detach())
+    out3 = paddle.incubate.nn.functional.fused_dropout_add(x.detach(), y.detach(), p)      # generator moved on
+    assert not torch.equal(out3, out.detach())
+    paddle.seed(123)
+    a = paddle.nn.functional.dropout(x.detach(), p)
+    paddle.seed(123)
+    b = paddle.nn.functional.dropout(x.detach(), p)
+    assert torch.equal(a, b)

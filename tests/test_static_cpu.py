@@ -238,3 +238,104 @@ def test_transformer_layer_program_matches_eager_at_another_batch_size():
         out = enc(emb(ids)).mean(1)
     got, = static.Executor().run(main, feed={"ids": x}, fetch_list=[out])
     np.testing.assert_allclose(got, ref, rtol=1e-6, atol=1e-7)
+
+
+def test_decomposition_rules_match_composites_eagerly():
+    """Every registered rule equals the composite operator it replaces (values and input gradient)."""
+    import torch
+    import torch.nn.functional as TF
+
+    from paddle_b200.decomposition import get_decomp_rule, registered_ops
+    paddle.disable_static()                 # plain eager comparison; the fixture's teardown tolerates the early switch
+    torch.manual_seed(0)
+    x = torch.randn(6, 10, dtype=torch.float64)
+    t = torch.randn(6, 10, dtype=torch.float64)
+    w, b = torch.randn(10, dtype=torch.float64), torch.randn(10, dtype=torch.float64)
+    cases = {
+        "relu": (TF.relu, (x,), {}), "relu6": (TF.relu6, (x * 4,), {}), "leaky_relu": (TF.leaky_relu, (x, 0.1), {}),
+        "sigmoid": (torch.sigmoid, (x,), {}), "silu": (TF.silu, (x,), {}), "gelu": (TF.gelu, (x,), {}),
+        "hardswish": (TF.hardswish, (x * 3,), {}), "hardsigmoid": (TF.hardsigmoid, (x * 3,), {}),
+        "hardtanh": (TF.hardtanh, (x,), {}), "softplus": (TF.softplus, (x * 10,), {}), "softsign": (TF.softsign, (x,), {}),
+        "mish": (TF.mish, (x,), {}), "elu": (TF.elu, (x,), {}), "selu": (TF.selu, (x,), {}),
+        "softmax": (TF.softmax, (x,), {"dim": 1}), "log_softmax": (TF.log_softmax, (x,), {"dim": 0}),
+        "logsumexp": (torch.logsumexp, (x, 1), {}), "layer_norm": (TF.layer_norm, (x, [10], w, b), {}),
+        "rms_norm": (TF.rms_norm, (x, [10], w, 1e-6), {}),
+        "batch_norm": (TF.batch_norm, (x, w * 0.1, w.abs() + 0.5, w, b), {}),
+        "group_norm": (TF.group_norm, (x.reshape(6, 10, 1), 5, w, b), {}),
+        "instance_norm": (TF.instance_norm, (x.reshape(2, 3, 10),), {}),
+        "normalize": (TF.normalize, (x,), {}), "var": (torch.var, (x, 1), {}), "std": (torch.std, (x, 0), {}),
+        "square": (torch.square, (x,), {}), "linear": (TF.linear, (x, torch.randn(4, 10, dtype=torch.float64), None), {}),
+        "addmm": (torch.addmm, (torch.randn(6, 6, dtype=torch.float64), x, x.t()), {"beta": 0.5, "alpha": 2.0}),
+        "addcmul": (torch.addcmul, (x, t, t), {"value": 0.3}), "addcdiv": (torch.addcdiv, (x, t, t.abs() + 1), {"value": 0.3}),
+        "lerp": (torch.lerp, (x, t, 0.3), {}), "mse_loss": (TF.mse_loss, (x, t), {}), "l1_loss": (TF.l1_loss, (x, t), {}),
+        "smooth_l1_loss": (TF.smooth_l1_loss, (x, t), {}),
+        "binary_cross_entropy_with_logits": (TF.binary_cross_entropy_with_logits, (x, torch.sigmoid(t)), {}),
+        "cross_entropy": (TF.cross_entropy, (x, torch.tensor([1, 2, -100, 0, 9, 3])), {}),
+        "dropout": (TF.dropout, (x, 0.5, False), {}),
+    }
+    untested = set(registered_ops()) - set(cases) - {"swiglu", "squared_l2_norm", "baddbmm"}
+    assert not untested, untested
+    for name, (fn, args, kwargs) in cases.items():
+        a1 = [a.clone().requires_grad_(True) if isinstance(a, torch.Tensor) and a.is_floating_point() and i == 0 else a
+              for i, a in enumerate(args)]
+        a2 = [a.clone().requires_grad_(True) if isinstance(a, torch.Tensor) and a.is_floating_point() and i == 0 else a
+              for i, a in enumerate(args)]
+        want, got = fn(*a1, **kwargs), get_decomp_rule(name)(*a2, **kwargs)
+        assert torch.allclose(want, got, atol=1e-9), name
+        want.sum().backward()
+        got.sum().backward()
+        assert torch.allclose(a1[0].grad, a2[0].grad, atol=1e-9), name
+
+
+def test_decompose_program_to_primitives_and_train():
+    """decompose() rewrites a recorded program into primitive nodes only; outputs, black / white lists and a training
+    step through the decomposed program (append_backward on primitives) are unchanged."""
+    from paddle_b200.decomposition import PRIMITIVES, decompose, is_primitive_program
+
+    def build():
+        main, startup = static.Program(), static.Program()
+        with static.program_guard(main, startup):
+            paddle.seed(5)
+            x = static.data("x", [-1, 16], "float32")
+            lab = static.data("lab", [-1], "int64")
+            fc1 = paddle.nn.Linear(16, 32)
+            fc2 = paddle.nn.Linear(32, 8)
+            h = paddle.nn.functional.gelu(fc1(x))
+            h = paddle.nn.functional.layer_norm(h, [32])
+            logits = fc2(h)
+            prob = paddle.nn.functional.softmax(logits, axis=-1)
+            loss = paddle.nn.functional.cross_entropy(logits, lab)
+        return main, startup, x, lab, prob, loss, [fc1, fc2]
+
+    rng = np.random.RandomState(0)
+    xv, lv = rng.randn(12, 16).astype("float32"), rng.randint(0, 8, (12,)).astype("int64")
+    exe = static.Executor()
+    main, startup, x, lab, prob, loss, _ = build()
+    base = exe.run(main, feed={"x": xv, "lab": lv}, fetch_list=[prob, loss])
+    types_before = {n.type for n in main._nodes}
+    assert {"gelu", "layer_norm", "softmax"} <= types_before
+    decompose(main, [prob, loss], blacklist={"pd_op.softmax"})
+    assert "softmax" in {n.type for n in main._nodes} and "gelu" not in {n.type for n in main._nodes}
+    decompose(main, [prob, loss])
+    assert is_primitive_program(main), sorted({n.type for n in main._nodes} - PRIMITIVES)
+    after = exe.run(main, feed={"x": xv, "lab": lv}, fetch_list=[prob, loss])
+    for a, b in zip(base, after):
+        assert np.allclose(a, b, atol=1e-5)
+    # whitelist
+    main2, _, _, _, prob2, loss2, _ = build()
+    decompose(main2, [prob2], whitelist={"gelu"})
+    t2 = {n.type for n in main2._nodes}
+    assert "gelu" not in t2 and "layer_norm" in t2
+    # training through the decomposed program equals training through the composite one
+    losses = []
+    for dec in (False, True):
+        main3, startup3, _, _, _, loss3, fcs = build()
+        if dec:
+            decompose(main3, [loss3])
+        with static.program_guard(main3, startup3):
+            opt = paddle.optimizer.SGD(learning_rate=0.1, parameters=[p for f in fcs for p in f.parameters()])
+            opt.minimize(loss3)
+        exe.run(startup3)
+        losses.append([float(exe.run(main3, feed={"x": xv, "lab": lv}, fetch_list=[loss3])[0]) for _ in range(4)])
+    assert losses[0][-1] < losses[0][0]
+    assert np.allclose(losses[0], losses[1], atol=1e-5), losses
