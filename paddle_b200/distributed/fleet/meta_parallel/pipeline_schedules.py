@@ -209,11 +209,43 @@ class ScheduleExecutor:
         o.total_loss = None
         act_like = getattr(self, "_act_like", None)
 
-        def need(src, msg, like):
-            while msg not in stash:
+        # Receives are posted ahead of their use (``PD_PP_PREFETCH`` messages per source, default 2; 0 = blocking
+        # receive at the point of use): the order of the messages a peer sends is known from its schedule, so the
+        # transfer of the next activation / gradient runs on the communicator's stream under this stage's compute and
+        # the compute stream only waits for the one it consumes (the reference overlaps its p2p the same way:
+        # pp_utils/p2p_communication.py batched isend / irecv on the comm stream).
+        import collections
+        import os
+        depth = int(os.environ.get("PD_PP_PREFETCH", "2"))
+        posted = {q: collections.deque() for q in incoming}
+        likes = {"act": act_like[:2] if act_like is not None else None, "grad": getattr(self, "_out_like", None)}
+
+        def post(src):
+            from ...._core.dtype import default_device
+            while len(posted[src]) < depth and cursor[src] < len(incoming[src]):
                 nxt = incoming[src][cursor[src]]
+                like = likes[nxt[0]]
+                if like is None:            # shape not known yet (before the first activation went through)
+                    return
+                buf = torch.empty(like[0], dtype=like[1], device=default_device())
+                w = C.irecv(buf, self._global[src], self._chan[(src, self.rank)])
+                posted[src].append((nxt, buf, w))
                 cursor[src] += 1
-                stash[nxt] = self._recv_next(src, nxt, like)
+
+        def need(src, msg, like):
+            likes[msg[0]] = like
+            while msg not in stash:
+                if not posted[src]:
+                    post(src)
+                if posted[src]:
+                    nxt, buf, w = posted[src].popleft()
+                    w.wait()
+                    stash[nxt] = buf
+                else:
+                    nxt = incoming[src][cursor[src]]
+                    cursor[src] += 1
+                    stash[nxt] = self._recv_next(src, nxt, likes[nxt[0]] or like)
+            post(src)
             return stash.pop(msg)
 
         from ....ops.functional import WeightGradStore
@@ -246,6 +278,8 @@ class ScheduleExecutor:
                         self._exchange_meta(out, (r + 1) % P)
                         self._meta_sent = True
                     self._send(out, (r + 1) % P, pending)
+                    if likes["grad"] is None:
+                        likes["grad"] = self._out_like = (list(out.shape), out.dtype)
                 if not forward_only:
                     ins[(c, m)], outs[(c, m)] = x, out
             else:
@@ -260,8 +294,11 @@ class ScheduleExecutor:
                     x.grad = None
                 if kind == "Bx":
                     deferred[(c, m)] = WeightGradStore.pop()
+            for q in posted:                  # keep the receive window full while the next step computes
+                post(q)
         WeightGradStore.split = WeightGradStore.enabled = False
         assert not deferred, "weight gradients left in the store"
+        assert not any(posted.values()), "posted receives left over"
         for w, _ in pending:
             w.wait()
         assert not stash and all(cursor[q] == len(incoming[q]) for q in incoming), "pipeline messages left over"

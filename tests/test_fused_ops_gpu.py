@@ -183,7 +183,7 @@ def test_gemm_swiglu_epilogue():
     y = IF.fused_linear_swiglu_interleaved(x, IF.interleave_gate_up(gate, up))
     _lib.check_status()
     ref = torch.nn.functional.silu(x.float() @ gate.float()) * (x.float() @ up.float())
-    assert y.shape == (300, 1376)
+    assert list(y.shape) == [300, 1376]
     assert (y.float() - ref).abs().max().item() < 3e-2 * ref.abs().max().item() + 1e-2
 
 
@@ -201,7 +201,7 @@ def test_bias_act_kernel(act):
         ref = (torch.nn.functional.silu(g) if act == "swiglu" else torch.nn.functional.gelu(g)) * u
     else:
         ref = getattr(torch.nn.functional, act)(h)
-    assert y.shape == ref.shape
+    assert list(y.shape) == list(ref.shape)
     assert (y.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item() + 1e-2
 
 
