@@ -220,6 +220,10 @@ struct AGParams {
   unsigned long long wait_ns;
 };
 
+struct AckPtrs {
+  unsigned long long p[MAX_RANKS];
+};
+
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -439,6 +443,12 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t ph = 0, armed = 0, armed_parity = 0;
       bool ok = true;
       int last_chunk = -1;
+      // A chunk's arrival is checked once per CTA, not once per tile: the acquire load at system scope plus the proxy
+      // fence cost about a microsecond, and with the tokens as the reduction dimension (weight gradients) a tile walks
+      // every remote chunk, so re-checking stalled the four-stage ring for most of a tile.  Nothing is checked at all
+      // when the matrix was staged by an earlier launch of this stream (skip_push): that launch consumed every chunk.
+      const bool no_wait = p.skip_push != 0;
+      unsigned long long seen = 0;
       for (int t = cta; t < num_tiles && ok; t += nct) {
         int tm, tn;
         if (wait_mode == 0 && nranks > 1) ag_tile(t, tiles_n, tiles_per_src, rank, nranks, tm, tn);
@@ -450,10 +460,13 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           local_tile = (m0 / rows_per_rank) == rank;
           const int chunk = m0 / sub_rows;      // == src * n_sub + sub-chunk
           if (!local_tile && chunk != last_chunk) {
-            const unsigned long long w0 = g_ag_trace_on ? globaltimer_ns() : 0;
-            if (!flag_wait_ge(flags_local + chunk, epoch, wait_ns, status, 600)) { ok = false; *abort_flag = 1; break; }
-            if (g_ag_trace_on) waited += globaltimer_ns() - w0;
-            fence_proxy_async_all();
+            if (!no_wait && !(chunk < 64 && ((seen >> chunk) & 1ull))) {
+              const unsigned long long w0 = g_ag_trace_on ? globaltimer_ns() : 0;
+              if (!flag_wait_ge(flags_local + chunk, epoch, wait_ns, status, 600)) { ok = false; *abort_flag = 1; break; }
+              if (g_ag_trace_on) waited += globaltimer_ns() - w0;
+              fence_proxy_async_all();
+              if (chunk < 64) seen |= 1ull << chunk;
+            }
             last_chunk = chunk;
           }
         }
@@ -465,8 +478,13 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             local_k = ((kb * BK) / rows_per_rank) == rank;
             const int chunk = (kb * BK) / sub_rows;
             if (!local_k && chunk != last_chunk) {
-              if (!flag_wait_ge(flags_local + chunk, epoch, wait_ns, status, 610)) { ok = false; *abort_flag = 1; break; }
-              fence_proxy_async_all();
+              if (!no_wait && !(chunk < 64 && ((seen >> chunk) & 1ull))) {
+                const unsigned long long w0 = g_ag_trace_on ? globaltimer_ns() : 0;
+                if (!flag_wait_ge(flags_local + chunk, epoch, wait_ns, status, 610)) { ok = false; *abort_flag = 1; break; }
+                if (g_ag_trace_on) waited += globaltimer_ns() - w0;
+                fence_proxy_async_all();
+                if (chunk < 64) seen |= 1ull << chunk;
+              }
               last_chunk = chunk;
             }
           }
@@ -1178,6 +1196,30 @@ PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, in
   PD_AG_CASE(1, 1, 0)
 #undef PD_AG_CASE
   return kErrBadShape;
+}
+
+// Acknowledgement on its own: the staged matrix of `epoch` has been consumed by other launches of this stream (a plain
+// GEMM reading the staging buffer), so the peers may overwrite it.  Counts as ONE acknowledging CTA in the slot's
+// cumulative `local_done` bookkeeping (the host advances its base by one).
+namespace pd {
+namespace gc {
+__global__ void ag_ack_kernel(int rank, int nranks, int epoch, AckPtrs ptrs, int* local_done, const int* bias) {
+  const int epoch_v = epoch + (bias != nullptr ? __ldg(bias) : 0);
+  atomicAdd(local_done, 1);
+  __threadfence_system();
+  for (int r = 0; r < nranks; ++r) st_release_sys(reinterpret_cast<int*>(ptrs.p[r]) + rank, epoch_v);
+}
+}  // namespace gc
+}  // namespace pd
+PD_EXPORT int pd_ag_ack(int rank, int nranks, int epoch, const unsigned long long* peer_ack, int* local_done, const int* bias,
+                        cudaStream_t stream) {
+  using namespace pd;
+  using namespace pd::gc;
+  if (nranks < 1 || nranks > MAX_RANKS) return kErrBadShape;
+  AckPtrs ptrs;
+  for (int i = 0; i < MAX_RANKS; ++i) ptrs.p[i] = i < nranks ? peer_ack[i] : 0;
+  ag_ack_kernel<<<1, 1, 0, stream>>>(rank, nranks, epoch, ptrs, local_done, bias);
+  return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }
 
 // GEMM -> reduce-scatter.  A: [M, K] (or [K, M] if a_mn), B as in pd_gemm_bf16, M = nranks * rows_per_rank.

@@ -217,24 +217,41 @@ _COMM_VEC = {2: 8, 4: 16, 8: 28}           # vector stores to every peer (push_m
 _COMM_MC = {2: 8, 4: 16, 8: 16}             # multicast stores (push_mode 2): one store per 16 bytes
 
 
-def _comm_ctas(nranks, tiles, jobs, push, mode=0):
+PUSH_BYTES_PER_US_PER_CTA = 13e3     # measured: one SM sustains 12-15 GB/s of NVLink stores (any push form)
+GEMM_FLOP_PER_US_PER_SM = 8.5e6      # 1-CTA tile loop of the fused kernels under load (~1250 TFLOP/s over 148 SMs)
+
+
+def _comm_ctas(nranks, tiles, jobs, push, mode=0, work=None):
     """CTAs that push the local shard to the peers.  ``PD_AG_COMM_CTAS`` overrides.
 
-    Bulk-copy ring (mode 0): one such CTA keeps about 128 KB in flight, which over NVLink is worth roughly 15 GB/s,
-    so the count grows with the number of peers (measured on 8 GPUs: the qkv all-gather GEMM takes 237 / 158 /
-    133 us with 8 / 16 / 32 of them); on top of the per-degree base, SMs that the GEMM could not use anyway (its
-    tile count does not fill the last wave) are given to the push, up to the number of push jobs.
-    Vector / multicast push (modes 1, 2): every thread of a push CTA copies, a job is 1/PARTS of a chunk.
-    A launch that does not push (second GEMM on staged data) has no communication CTAs at all."""
+    The launch ends at about max(GEMM time on the remaining SMs, push time + a short tail), because tiles are visited
+    in arrival order and only the last chunks' tiles have to wait for the end of the push.  With ``work`` =
+    (M, N, K, bytes this rank must send) the count that balances the two is chosen: a small GEMM behind a full-size
+    gather (the dgrad of a row-parallel layer: 69 GFLOP behind 16 MB on 2 GPUs) needs twice the push CTAs of a large one,
+    or it spends its time waiting for data at 8 x 13 GB/s.  Bounds: the per-degree table value halved from below, the
+    number of push jobs and 64 from above.  Without ``work`` the table value is used (plus, on 4+ ranks, the SMs the
+    GEMM's last wave cannot fill).  A launch that does not push has no communication CTAs at all."""
     if not push:
         return 0
     if "PD_AG_COMM_CTAS" in os.environ:
         return max(1, min(N_COMM, jobs))
     table = (_COMM_BASE, _COMM_VEC, _COMM_MC)[mode]
     base = min(table.get(nranks, 8), max(jobs, 1))
+    sms = _sms()
+    if work is not None and os.environ.get("PD_AG_COMM_MODEL", "1") != "0":
+        M, N, K, send_bytes = work
+        tile_us = 2.0 * BM * BN * K / GEMM_FLOP_PER_US_PER_SM
+        best, best_t = base, None
+        for c in range(max(2, base // 2), min(max(jobs, 1), 64) + 1):
+            waves = -(-tiles // (sms - c))
+            gemm_us = waves * tile_us
+            push_us = send_bytes / (c * PUSH_BYTES_PER_US_PER_CTA) + 8.0 + tile_us
+            t = max(gemm_us, push_us)
+            if best_t is None or t < best_t - 0.5:
+                best, best_t = c, t
+        return best
     if nranks < 4 or mode == 2:
         return base
-    sms = _sms()
     waves = -(-tiles // (sms - base))
     needed = -(-tiles // waves)
     return max(base, min(sms - needed, jobs))
@@ -247,7 +264,9 @@ def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode
         slot.epoch += 1
     tiles = ((M + BM - 1) // BM) * ((N + BN - 1) // BN)
     jobs = (group.nranks - 1) * slot.n_sub if slot.push_mode == 0 else slot.n_sub * slot.parts
-    n_comm = _comm_ctas(group.nranks, tiles, jobs, push, slot.push_mode)
+    shard_bytes = slot.rows * slot.row_elems * 2
+    send_bytes = shard_bytes if slot.push_mode == 2 else shard_bytes * (group.nranks - 1)
+    n_comm = _comm_ctas(group.nranks, tiles, jobs, push, slot.push_mode, (M, N, K, send_bytes))
     gemm_ctas = min(_sms() - n_comm, tiles)
     rc = _lib.kernels().pd_ag_gemm(
         ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)),
@@ -284,9 +303,44 @@ def gemm_rs(slot, group, a, b, out, M, N, K, a_mn, b_mn):
     return out
 
 
+WGRAD_PLAIN = _env_int("PD_WGRAD_PLAIN", 1)
+
+
+def ag_ack(slot, group):
+    """Tell every rank that this rank is done with the matrix staged in ``slot`` for its current epoch."""
+    rc = _lib.kernels().pd_ag_ack(c_int(group.rank), c_int(group.nranks), c_int(slot.epoch - slot.bias_host[0]),
+                                  slot.p_ack, ptr(slot.done), ptr(slot.bias), stream())
+    check(rc, "pd_ag_ack")
+    slot.done_base += 1
+    native._count()
+
+
 def _wgrad(weight, a, b, M, N, K, slot, group, x_shard, push, ack, gathered_b=False):
-    """dW (+)= A^T B with tokens as the reduction dimension; straight into main_grad when present."""
+    """dW (+)= A^T B with tokens as the reduction dimension; straight into main_grad when present.
+
+    When nothing has to be pushed - the gathered operand is still staged from the forward (or the dgrad) launch - the
+    product is an ordinary local GEMM over this GPU's own staging buffer, and the 2-CTA kernel runs it at twice the
+    rate of the flag-driven one (143 vs 281 us for the 7B qkv shape on 2 GPUs); a one-thread launch then acknowledges
+    the epoch to the peers."""
     mg = getattr(weight, "main_grad", None)
+    if not push and WGRAD_PLAIN and native.GEMM_IMPL == "2cta":
+        if slot.push_mode != 2:
+            # the fused kernels read this rank's own rows straight from the shard, and only the multicast push writes
+            # them into the staging buffer as well: complete the staged matrix first (a local copy of 1/n of it)
+            r0 = group.rank * slot.rows
+            slot.stage[r0:r0 + slot.rows].copy_(x_shard.detach().reshape(slot.rows, slot.row_elems))
+        if mg is not None:
+            native.gemm(a, b, trans_a=True, out=mg, accumulate=True)
+        else:
+            dw = native.gemm(a, b, trans_a=True)
+        if ack:
+            ag_ack(slot, group)
+        if mg is not None:
+            hook = getattr(weight, "_main_grad_ready_hook", None)
+            if hook is not None:
+                hook(weight)
+            return None
+        return dw
     if mg is not None:
         ag_gemm(slot, group, x_shard, a, b, mg, M, N, K, 1, 1, 2, 1, push, ack, gathered_b)
         hook = getattr(weight, "_main_grad_ready_hook", None)
