@@ -39,6 +39,9 @@ def parse_args():
                          "optimizer state partitioned; every rank feeds its own micro-batches: BASELINE config 3 with "
                          "--model llama2-13b --micro-batches 8)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--kernel-table", default="",
+                    help="after the timed regions, run one more step under the CUDA activity tracer and write the per-kernel "
+                         "time table to this file (diagnosis; not part of any reported number)")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay each micro-batch (forward + backward) from a CUDA graph; auto = when --gpus > 1, "
                          "where the per-GPU work is small enough for the host to become the limit")
@@ -254,6 +257,24 @@ def main():
         e2e = {"value": tokens_per_step / (e_ms / args.steps / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": int(n_mb * (seq + 1) * 8), "d2h_bytes_per_step": 4,
                "ms_per_step": e_ms / args.steps, "loss": e_loss}
+
+    if args.kernel_table:
+        # diagnosis only, after every timed region: one more step under the CUDA activity tracer, kernel durations
+        # summed per name (durations under a tracer are for comparing shares, never a bench value)
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            train_step(False)
+            torch.cuda.synchronize()
+        if rank == 0:
+            rows = sorted(((k.key, k.count, getattr(k, "device_time_total", 0.0)) for k in prof.key_averages()),
+                          key=lambda r: -r[2])
+            tot = sum(r[2] for r in rows) or 1.0
+            with open(args.kernel_table, "w") as f:
+                f.write(f"# {world} GPU(s), one step ({n_mb} micro-batches), kernel time sum {tot / 1e3:.1f} ms\n")
+                for k, c, t in rows[:40]:
+                    f.write(f"{t / 1e3:9.2f} ms {100 * t / tot:5.1f}% n={c:6d} avg {t / max(c, 1):8.1f} us  {k[:120]}\n")
+        barrier()
 
     if rank == 0:
         flops = cfg.flops_per_token(seq) * tokens_per_step

@@ -965,9 +965,13 @@ gemm_rs_mc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (threadIdx.x == 0 && alive) {
       // every partial tile of this epoch has been read out of every rank's buffer: they may overwrite them
       __threadfence();
+      // the last reducer of THIS launch acknowledges and re-arms the counter (launches on a slot are ordered on one
+      // stream, so the count never mixes two launches and the number of reducers may differ from call to call)
       const int done = atomicAdd(p.local_done, 1) + 1;
-      if (done == p.n_red * epoch_v)
+      if (done == p.n_red) {
+        atomicExch(p.local_done, 0);
         for (int r = 0; r < p.nranks; ++r) st_release_sys(reinterpret_cast<int*>(p.peer_ack[r]) + p.rank, epoch_v);
+      }
     }
     return;
   }
@@ -1204,10 +1208,11 @@ PD_EXPORT int pd_ag_gemm(const void* A, const void* B, void* C, int M, int N, in
 namespace pd {
 namespace gc {
 __global__ void ag_ack_kernel(int rank, int nranks, int epoch, AckPtrs ptrs, int* local_done, const int* bias) {
+  // one lane per peer: the release stores (each of which orders the earlier reads of this GPU before it) go out side
+  // by side instead of one after the other
   const int epoch_v = epoch + (bias != nullptr ? __ldg(bias) : 0);
-  atomicAdd(local_done, 1);
-  __threadfence_system();
-  for (int r = 0; r < nranks; ++r) st_release_sys(reinterpret_cast<int*>(ptrs.p[r]) + rank, epoch_v);
+  if (threadIdx.x == 0) atomicAdd(local_done, 1);
+  if (static_cast<int>(threadIdx.x) < nranks) st_release_sys(reinterpret_cast<int*>(ptrs.p[threadIdx.x]) + rank, epoch_v);
 }
 }  // namespace gc
 }  // namespace pd
@@ -1218,7 +1223,7 @@ PD_EXPORT int pd_ag_ack(int rank, int nranks, int epoch, const unsigned long lon
   if (nranks < 1 || nranks > MAX_RANKS) return kErrBadShape;
   AckPtrs ptrs;
   for (int i = 0; i < MAX_RANKS; ++i) ptrs.p[i] = i < nranks ? peer_ack[i] : 0;
-  ag_ack_kernel<<<1, 1, 0, stream>>>(rank, nranks, epoch, ptrs, local_done, bias);
+  ag_ack_kernel<<<1, 32, 0, stream>>>(rank, nranks, epoch, ptrs, local_done, bias);
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }
 
@@ -1272,7 +1277,7 @@ PD_EXPORT int pd_gemm_rs(const void* A, const void* B, void* out, int M, int N, 
 }
 
 // GEMM -> reduce-scatter over NVLS.  partial_local: this rank's bf16 [M][N] partial buffer inside a symmetric block
-// whose multicast address is mc_partial (the same offset on every rank).  n_red reducer CTAs (constant for a slot).
+// whose multicast address is mc_partial (the same offset on every rank).  n_red reducer CTAs (may differ from call to call).
 PD_EXPORT int pd_gemm_rs_mc(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int a_mn,
                             int b_mn, int rows_per_rank, int rank, int nranks, int epoch, void* partial_local,
                             unsigned long long mc_partial, const unsigned long long* peer_counters,

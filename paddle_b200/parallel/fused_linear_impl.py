@@ -94,9 +94,11 @@ class _RSSlot:
         self.mc_partial = self.block.mc_ptr
         # with a multicast mapping the same block holds this rank's full partial product [nranks * rows, N] and the
         # owner of a slab reads it with multimem.ld_reduce (gemm_rs_mc); the layout has the same size either way
-        # (two ranks: the switch would have to deliver half of the matrix to each rank through latency-bound
-        # ld_reduce loads, and the push form is faster there - 117 against 135 us for the o_proj shape)
-        self.mc = bool(self.mc_partial) and _env_int("PD_RS_MODE", 1 if n >= 4 else 0) == 1
+        # Opt-in (``PD_RS_MODE=1``): measured in isolation the push form is the faster one - o_proj / down shapes of
+        # the 7B model 117 against 135 us on two ranks, 79 / 111 against 113 / 153 us on four - because the reducers
+        # pull through latency-bound ld_reduce loads (a reducer SM sustains a few GB/s of reduced rows) and every
+        # reducer is an SM taken from the GEMM.
+        self.mc = bool(self.mc_partial) and _env_int("PD_RS_MODE", 0) == 1
         self.n_red = _env_int("PD_RS_RED_CTAS", 32)
         self.done = torch.zeros(1, dtype=torch.int32, device=self.block.local.device)
         self.epoch = 0
@@ -283,14 +285,35 @@ def ag_gemm(slot, group, x_shard, a, b, out, M, N, K, a_mn, b_mn, epi, wait_mode
     return out
 
 
+def _red_ctas(default, tiles, K, result_bytes):
+    """Reducer CTAs of the in-switch reduce-scatter GEMM.  Every reducer is an SM the GEMM does not get, and 32 of them
+    can cost the GEMM a whole extra wave (512 tiles: 4 waves on 128 SMs, 5 on 116); too few and the reduction of this
+    rank's slab (one SM pulls ~13 GB/s of reduced rows) outlasts the GEMM.  Picks the count that minimises
+    max(GEMM waves x tile time, reduction time + one tile).  ``PD_RS_RED_CTAS`` fixes it."""
+    if "PD_RS_RED_CTAS" in os.environ:
+        return default
+    sms = _sms()
+    tile_us = 2.0 * BM * BN * K / GEMM_FLOP_PER_US_PER_SM
+    best, best_t = default, None
+    for r in range(8, 49):
+        gemm_us = -(-tiles // (sms - r)) * tile_us
+        red_us = result_bytes / (r * PUSH_BYTES_PER_US_PER_CTA) + tile_us + 8.0
+        t = max(gemm_us, red_us)
+        if best_t is None or t < best_t - 0.5:
+            best, best_t = r, t
+    return best
+
+
 def gemm_rs(slot, group, a, b, out, M, N, K, a_mn, b_mn):
     slot.epoch += 1
     if slot.mc:
+        tiles = ((M + BM - 1) // BM) * ((N + BN - 1) // BN)
+        n_red = _red_ctas(slot.n_red, tiles, K, slot.rows * N * 2)
         rc = _lib.kernels().pd_gemm_rs_mc(
             ptr(a), ptr(b), ptr(out), c_int(M), c_int(N), c_int(K), c_int(a.stride(0)), c_int(b.stride(0)), c_int(a_mn),
             c_int(b_mn), c_int(slot.rows), c_int(group.rank), c_int(group.nranks), c_int(slot.epoch - slot.bias_host[0]),
             ptr(slot.block.local), ctypes.c_ulonglong(slot.mc_partial), slot.p_cnt, slot.p_ack, ptr(slot.done),
-            ptr(slot.bias), c_int(slot.n_red), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
+            ptr(slot.bias), c_int(n_red), c_int(WAIT_MS), ptr(_lib.status_buffer(out.device)), stream())
         check(rc, "pd_gemm_rs_mc")
         native._count()
         return out
