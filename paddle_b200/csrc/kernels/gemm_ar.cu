@@ -10,6 +10,9 @@
 // rank's per-slab counter, waits (bounded) until its own counter shows all ranks' slabs of this epoch, then sums
 // the n partials in fp32 (+ residual) and writes the final bf16 slab.  Transfer of slab t overlaps the MMA of the
 // slabs still in flight on other SMs; there is no separate collective launch and no host synchronisation.
+// In-switch form (multicast mapping available, 4 ranks or more): the slab is stored into this rank's OWN buffer only,
+// the same notices are exchanged, and the reduction is one multimem.ld_reduce per 16 bytes - the NVSwitch adds the
+// n copies - so nothing is pushed n - 1 times and no SM adds partials of other ranks.
 //
 // The epoch lives in device memory (state[0]; the last CTA of a launch advances it), so the kernel can be replayed
 // from a CUDA graph with constant arguments.  Counters grow monotonically (expected = epoch * nranks * ARRIVAL_UNITS, independent of the K split); the two
@@ -48,7 +51,8 @@ template <int B3D>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_ar_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Peers peers,
                const bf16* __restrict__ residual, bf16* __restrict__ out, int M, int N, int K, int ldc, int rank,
-               int nranks, int m_cap, int S, int* state, unsigned long long wait_ns, int* status) {
+               int nranks, int m_cap, int S, int* state, unsigned long long wait_ns, int* status,
+               const bf16* __restrict__ mc_recv) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -167,9 +171,16 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (row < M) {
           const uint4 v = *reinterpret_cast<const uint4*>(sC + row * 256 + ((chunk ^ (row & 15)) << 4));
           const size_t off = slot_off + static_cast<size_t>(row) * N + n0 + chunk * 8;
-          for (int p = 0; p < nranks; ++p) {
-            const int peer = (rank + p) % nranks;                     // spread the first stores over the links
-            *reinterpret_cast<uint4*>(peers.recv[peer] + off) = v;
+          if (mc_recv != nullptr) {
+            // in-switch form: the partial stays in this rank's own buffer, at the same offset on every rank; the
+            // reduction below reads the sum of all ranks' copies through the multicast address
+            *reinterpret_cast<uint4*>(peers.recv[rank] + (static_cast<size_t>(slot) * nranks * S + ks) * m_cap * static_cast<size_t>(N) +
+                                      static_cast<size_t>(row) * N + n0 + chunk * 8) = v;
+          } else {
+            for (int p = 0; p < nranks; ++p) {
+              const int peer = (rank + p) % nranks;                     // spread the first stores over the links
+              *reinterpret_cast<uint4*>(peers.recv[peer] + off) = v;
+            }
           }
         }
       }
@@ -199,8 +210,12 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[e] = 0.f;
           const size_t off = static_cast<size_t>(row) * N + n0 + chunk * 8;
-          for (int p = 0; p < parts; ++p) {
-            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(p) * m_cap * N + off));
+          const int n_add = mc_recv != nullptr ? S : parts;            // the switch has already added the ranks
+          const bf16* src = mc_recv != nullptr
+                                ? mc_recv + static_cast<size_t>(slot) * parts * m_cap * static_cast<size_t>(N) : base;
+          for (int p = 0; p < n_add; ++p) {
+            const bf16* a = src + static_cast<size_t>(p) * m_cap * N + off;
+            const uint4 v = mc_recv != nullptr ? multimem_ld_reduce_bf16x8(a) : __ldcg(reinterpret_cast<const uint4*>(a));
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -249,11 +264,12 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // nranks device pointers (index = rank) into each rank's receive buffer ([2][nranks][m_cap][N] bf16) and counters
 // ([N/128] int32, zero-initialised once); state: 2 local int32 (zero-initialised once).  N % 128 == 0, M <= 128,
 // M <= m_cap, (N / 128) * splits <= number of SMs; the receive buffer holds [2][nranks * splits][m_cap][N] bf16 and
-// every rank must pass the same `splits`.
+// every rank must pass the same `splits`.  mc_recv: multicast address of the receive buffers (0 = push form): each rank
+// then keeps its partial slabs in its own buffer and the reduction reads the cross-rank sum with multimem.ld_reduce.
 PD_EXPORT int pd_gemm_ar(const void* A, const void* B, void* out, const void* residual, int M, int N, int K, int lda,
                          int ldb, int ldc, int rank, int nranks, const unsigned long long* peer_recv,
                          const unsigned long long* peer_cnt, int m_cap, int splits, int* state, int wait_ms, int* status,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, unsigned long long mc_recv) {
   using namespace pd;
   using namespace pd::gar;
   if (M <= 0 || M > BM || M > m_cap || N <= 0 || (N % BN) || K <= 0 || nranks < 1 || nranks > MAX_RANKS)
@@ -291,10 +307,10 @@ PD_EXPORT int pd_gemm_ar(const void* A, const void* B, void* out, const void* re
   if (b3d)
     gemm_ar_kernel<1><<<(N / BN) * splits, NUM_THREADS, SMEM_BYTES, stream>>>(
         tmA, tmB, peers, (const bf16*)residual, (bf16*)out, M, N, K, ldc, rank, nranks, m_cap, splits, state, wait_ns,
-        status);
+        status, reinterpret_cast<const bf16*>(mc_recv));
   else
     gemm_ar_kernel<0><<<(N / BN) * splits, NUM_THREADS, SMEM_BYTES, stream>>>(
         tmA, tmB, peers, (const bf16*)residual, (bf16*)out, M, N, K, ldc, rank, nranks, m_cap, splits, state, wait_ns,
-        status);
+        status, reinterpret_cast<const bf16*>(mc_recv));
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }

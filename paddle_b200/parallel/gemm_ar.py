@@ -42,6 +42,10 @@ class GemmAllReduce:
         vals = self.block.peer_ptrs(self.off_cnt)
         self.p_cnt = U64x8(*(vals + [0] * (8 - len(vals))))
         self.state = torch.zeros(2, dtype=torch.int32, device=self.block.local.device)
+        # in-switch reduction (multimem.ld_reduce over the receive buffers) from 4 ranks up; PD_GEMM_AR_NVLS=0 / 1 forces
+        import os
+        want = os.environ.get("PD_GEMM_AR_NVLS")
+        self.mc_recv = self.block.mc_ptr if (self.block.mc_ptr and (want == "1" or (want is None and n >= 4))) else 0
 
     def __call__(self, x, w, residual=None, out=None):
         M, K = x.shape
@@ -53,7 +57,8 @@ class GemmAllReduce:
         rc = _lib.kernels().pd_gemm_ar(ptr(x), ptr(w), ptr(out), ptr(residual), c_int(M), c_int(self.N), c_int(K),
                                        c_int(x.stride(0)), c_int(w.stride(0)), c_int(out.stride(0)),
                                        c_int(self.group.rank), c_int(self.n), self.p_recv, self.p_cnt, c_int(self.m_cap),
-                                       c_int(splits), ptr(self.state), c_int(WAIT_MS), ptr(_lib.status_buffer(x.device)), stream())
+                                       c_int(splits), ptr(self.state), c_int(WAIT_MS), ptr(_lib.status_buffer(x.device)), stream(),
+                                       ctypes.c_ulonglong(self.mc_recv))
         check(rc, "pd_gemm_ar")
         from ..ops import native
         native._count()

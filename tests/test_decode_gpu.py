@@ -147,7 +147,7 @@ def test_withheld_signal_returns_status_not_hang():
     t0 = time.time()
     rc = _lib.kernels().pd_gemm_ar(ptr(x), ptr(w), ptr(out), ptr(None), c_int(M), c_int(N), c_int(K_), c_int(K_), c_int(N),
                                    c_int(N), c_int(0), c_int(2), p_recv, p_cnt, c_int(M), c_int(1), ptr(state), c_int(200),
-                                   ptr(_lib.status_buffer()), stream())
+                                   ptr(_lib.status_buffer()), stream(), ctypes.c_ulonglong(0))
     assert rc == 0
     torch.cuda.synchronize()
     assert time.time() - t0 < 5.0

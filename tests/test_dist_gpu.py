@@ -8,6 +8,12 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ENV = {"NCCL_NVLS_ENABLE": "0"}
 
 
+def _ranks():
+    """Kernels whose protocol depends on the number of peers run on 4 GPUs when the box has them, else on 2."""
+    import torch
+    return 4 if torch.cuda.device_count() >= 4 else 2
+
+
 def test_collective_api_nccl():
     res = run_workers("collective_api.py", 2, backend="nccl", gpus=True, extra_env=ENV)
     x = [np.arange(8, dtype=np.float32) + 10 * r for r in range(2)]
@@ -22,7 +28,8 @@ def test_collective_api_nccl():
 
 @pytest.mark.parametrize("policy", ["baseline", "fused"])
 def test_llama_tp_sp_parity_gpu(policy):
-    res = run_workers("llama_tp.py", 2, backend="nccl", gpus=True, args=("bfloat16", policy), extra_env=ENV)
+    res = run_workers("llama_tp.py", _ranks() if policy == "fused" else 2, backend="nccl", gpus=True, args=("bfloat16", policy),
+                      extra_env=ENV, timeout=400)
     for r in res:
         assert np.allclose(r["tp"], r["twin"], rtol=3e-2, atol=3e-2), (r["tp"], r["twin"])
         assert r["maxdiff"] < 2e-2, r["maxdiff"]
@@ -48,7 +55,7 @@ def test_fused_ag_gemm_and_gemm_rs(form):
     env = dict(ENV)
     env.update({"ring": {"PD_AG_PUSH_MODE": "0", "PD_RS_MODE": "0"}, "vector": {"PD_AG_PUSH_MODE": "1", "PD_RS_MODE": "0"},
                 "nvls": {"PD_AG_PUSH_MODE": "2", "PD_RS_MODE": "1"}}[form])
-    res = run_workers("fused_comm.py", 2, backend="nccl", gpus=True, extra_env=env)
+    res = run_workers("fused_comm.py", _ranks(), backend="nccl", gpus=True, extra_env=env, timeout=400)
     if form == "nvls" and not res[0]["multicast"]:
         pytest.skip("no NVLink multicast on this box")
     for r in res:
@@ -58,10 +65,13 @@ def test_fused_ag_gemm_and_gemm_rs(form):
             assert v < 3e-2, (k, v)
 
 
-def test_tp_decode_fused_gemm_allreduce():
-    """Fused GEMM->all-reduce kernel (eager and from a CUDA graph) and the TP serving engine against the single-GPU
-    engine."""
-    res = run_workers("decode_tp.py", 2, backend="nccl", gpus=True, extra_env=ENV, timeout=400)
+@pytest.mark.parametrize("form", ["push", "nvls"])
+def test_tp_decode_fused_gemm_allreduce(form):
+    """Fused GEMM->all-reduce kernel (eager and from a CUDA graph; partial slabs pushed to every rank, or kept local and
+    summed by the switch with multimem.ld_reduce) and the TP serving engine against the single-GPU engine."""
+    env = dict(ENV)
+    env["PD_GEMM_AR_NVLS"] = "1" if form == "nvls" else "0"
+    res = run_workers("decode_tp.py", _ranks(), backend="nccl", gpus=True, extra_env=env, timeout=400)
     for r in res:
         assert r["gemm_ar_err"] < 2e-2 and r["gemm_ar_graph_err"] < 2e-2, r
         assert r["fused_uses_fused_ar"] and not r["baseline_uses_fused_ar"]
