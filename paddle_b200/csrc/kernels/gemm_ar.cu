@@ -199,7 +199,59 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bars->verdict = ok;
     }
     named_bar_sync(1, 128);
-    if (bars->verdict != 0 && ks == 0) {
+    if (bars->verdict != 0 && ks == 0 && mc_recv != nullptr) {
+      // in-switch form: a multimem.ld_reduce takes microseconds, so a thread first issues the loads of eight of its rows
+      // (x S K-slices) and only then adds - up to 32 requests in flight per thread instead of one
+      const int half = lane >> 4, chunk = lane & 15;
+      const bf16* src = mc_recv + static_cast<size_t>(slot) * nranks * S * m_cap * static_cast<size_t>(N);
+      constexpr int RB = 8;
+      for (int rb = warp * 2 + half; rb < M; rb += 8 * RB) {
+        uint4 v[RB][MAX_SPLITS];
+#pragma unroll
+        for (int i = 0; i < RB; ++i) {
+          const int row = rb + 8 * i;
+#pragma unroll
+          for (int p = 0; p < MAX_SPLITS; ++p)
+            if (row < M && p < S)
+              v[i][p] = multimem_ld_reduce_bf16x8(src + static_cast<size_t>(p) * m_cap * N + static_cast<size_t>(row) * N + n0 + chunk * 8);
+        }
+#pragma unroll
+        for (int i = 0; i < RB; ++i) {
+          const int row = rb + 8 * i;
+          if (row >= M) continue;
+          float acc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+          for (int p = 0; p < MAX_SPLITS; ++p) {
+            if (p < S) {
+              const uint32_t w[4] = {v[i][p].x, v[i][p].y, v[i][p].z, v[i][p].w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                acc[2 * e] += __uint_as_float(w[e] << 16);
+                acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+              }
+            }
+          }
+          const size_t o = static_cast<size_t>(row) * ldc + n0 + chunk * 8;
+          if (residual != nullptr) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(residual + o);
+            const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              acc[2 * e] += __uint_as_float(w[e] << 16);
+              acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+            }
+          }
+          uint4 ov;
+          ov.x = pack_bf16x2(acc[0], acc[1]);
+          ov.y = pack_bf16x2(acc[2], acc[3]);
+          ov.z = pack_bf16x2(acc[4], acc[5]);
+          ov.w = pack_bf16x2(acc[6], acc[7]);
+          *reinterpret_cast<uint4*>(out + o) = ov;
+        }
+      }
+    } else if (bars->verdict != 0 && ks == 0) {
       const int half = lane >> 4, chunk = lane & 15;
       const int parts = nranks * S;
       const bf16* base = peers.recv[rank] + static_cast<size_t>(slot) * parts * m_cap * static_cast<size_t>(N);
@@ -210,12 +262,8 @@ gemm_ar_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
           for (int e = 0; e < 8; ++e) acc[e] = 0.f;
           const size_t off = static_cast<size_t>(row) * N + n0 + chunk * 8;
-          const int n_add = mc_recv != nullptr ? S : parts;            // the switch has already added the ranks
-          const bf16* src = mc_recv != nullptr
-                                ? mc_recv + static_cast<size_t>(slot) * parts * m_cap * static_cast<size_t>(N) : base;
-          for (int p = 0; p < n_add; ++p) {
-            const bf16* a = src + static_cast<size_t>(p) * m_cap * N + off;
-            const uint4 v = mc_recv != nullptr ? multimem_ld_reduce_bf16x8(a) : __ldcg(reinterpret_cast<const uint4*>(a));
+          for (int p = 0; p < parts; ++p) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(base + static_cast<size_t>(p) * m_cap * N + off));
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
