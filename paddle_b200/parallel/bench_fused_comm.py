@@ -158,6 +158,29 @@ def main():
                     buf[r_] = 0
             del pair
         emit(rec)
+        # weight gradient of the same layer: dW += gather(x)^T dY with the gathered x already staged (no push), once
+        # through the flag-driven all-gather GEMM kernel and once as a plain GEMM over the staging buffer
+        slot = FL._AGSlot(g, rows, H)
+        FL.ag_gemm(slot, g, x, slot.stage, w, y, T, N, H, 0, 1, 0, 0, push=True, ack=False)
+        slot.stage[rank * rows:(rank + 1) * rows].copy_(x)
+        torch.cuda.synchronize()
+        tdist.barrier()
+        dy = (torch.randn(T, N, device="cuda") * 0.05).to(torch.bfloat16)
+        mg = torch.zeros(H, N, device="cuda", dtype=torch.float32)
+        ref_dw = xfull.float().t() @ dy.float()
+        FL.ag_gemm(slot, g, x, slot.stage, dy, mg, H, N, T, 1, 1, 2, 1, False, False, False)
+        err_ag = rel(mg, ref_dw)
+        mg.zero_()
+        native.gemm(slot.stage, dy, trans_a=True, out=mg, accumulate=True)
+        err_plain = rel(mg, ref_dw)
+        wrec = {"op": f"wgrad_{name}", "shape": [H, N, T], "flop": 2.0 * T * H * N,
+                "flag_driven_us": timed(lambda: FL.ag_gemm(slot, g, x, slot.stage, dy, mg, H, N, T, 1, 1, 2, 1, False, False, False)),
+                "flag_driven_err": err_ag,
+                "plain_gemm_on_stage_us": timed(lambda: native.gemm(slot.stage, dy, trans_a=True, out=mg, accumulate=True)),
+                "plain_gemm_on_stage_err": err_plain,
+                "cublas_bf16_out_us": timed(lambda: torch.matmul(xfull.t(), dy))}
+        emit(wrec)
+        del slot
 
     for name, K in row_shapes.items():
         N = H
