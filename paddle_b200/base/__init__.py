@@ -17,3 +17,23 @@ def in_dygraph_mode():
 def is_compiled_with_cuda():
     import torch
     return torch.cuda.is_available()
+
+
+class _Core:
+    """``paddle.base.core``: the names scripts take from the reference's binding module that make sense here."""
+    from ..framework.errors import EnforceNotMet  # noqa: F401
+
+    class EOFException(Exception):
+        """Raised by readers at the end of data (paddle.base.core.EOFException)."""
+
+    @staticmethod
+    def is_compiled_with_cuda():
+        return is_compiled_with_cuda()
+
+    @staticmethod
+    def get_cuda_device_count():
+        import torch
+        return torch.cuda.device_count()
+
+
+core = _Core()

@@ -17,7 +17,9 @@
 // dQ^T over dP^T.  Sub-tiles alternate between A and B, so GEMMs (1),(2) of sub-tile t+1 run on the tensor cores
 // while the softmax warps work on sub-tile t, and GEMMs (3)-(5) of t overlap the softmax of t+1.  The per-column
 // LSE / Delta values are staged in shared memory once per sub-tile and read as broadcasts.
-// Warps: 0-3 softmax (+ final dK/dV store), 4-7 dQ drain, 8 TMA producer, 9 MMA issuer.
+// Warps: 0-3 softmax of query columns 0-31 (+ per-column statistics, final dK/dV store), 10-13 softmax of query columns
+// 32-63 (the element-wise work needs no exchange between the halves: the log-sum-exp is an input), 4-7 dQ drain, 8 TMA
+// producer, 9 MMA issuer.
 #include <math.h>
 
 #include "host_utils.h"
@@ -34,7 +36,7 @@ constexpr int Q_HALF = Q_TILE / 2;
 constexpr int STAGES = 3;
 constexpr int DS_BYTES = BKV * BQ * 2;        // 16 KB
 constexpr int DQ_STAGE_BYTES = BQ * D * 4;    // 32 KB fp32 [64 q][128 d]
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 448;
 constexpr int STATS_BYTES = 2 * 128 * 4;         // [2][lse2 x64 | delta x64]
 constexpr int SMEM_BYTES = 2 * KV_TILE + STAGES * 2 * Q_TILE + 2 * DS_BYTES + DQ_STAGE_BYTES + STATS_BYTES + 1024 + 256;
 constexpr uint32_t COL_DK = 0, COL_DV = 128, COL_BUF = 256;
@@ -127,7 +129,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars->st_full[b], 1);
-      mbar_init(&bars->pds_full[b], 128);
+      mbar_init(&bars->pds_full[b], 256);
       mbar_init(&bars->dq_full[b], 1);
       mbar_init(&bars->dq_empty[b], 128);
     }
@@ -245,11 +247,13 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp < 4) {
-    // ---------------------------------------------------------------- softmax warps: thread = kv row
-    const int row = threadIdx.x;
+  } else if (warp < 4 || warp >= 10) {
+    // ---------------------------------------------------------------- softmax warps: thread = kv row x column half
+    // a warp may touch the TMEM lanes of its own quarter (warp index mod 4) only
+    const int h = warp < 4 ? 0 : 1;                                 // query columns [32 h, 32 h + 32) of the sub-tile
+    const int row = (warp & 3) * 32 + lane;
     const int kvi = kv0 + row;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int sw = row & 7;
     bool ok = true;
     auto load_stat = [&](int it) -> float {
@@ -261,16 +265,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (row < 64) v = in ? v * 1.4426950408889634f : INFINITY;         // +inf -> p = 0 for padded rows
       return v;
     };
-    float next_stat = n_it > 0 ? load_stat(0) : 0.f;
+    float next_stat = (n_it > 0 && h == 0) ? load_stat(0) : 0.f;
     for (int it = 0; it < n_it; ++it) {
       const int qh = kv_head * group + it / per_head;
       const int q0 = (t0 + it % per_head) * BQ;
       const int b = it & 1;
       // per-column statistics of this sub-tile -> shared memory (threads 0-63: LSE in log2 units, 64-127: Delta).
       // The value was fetched one iteration ahead, so the global-memory latency never sits in front of the barrier.
-      stats[b * 128 + row] = next_stat;
-      if (it + 1 < n_it) next_stat = load_stat(it + 1);
-      named_bar_sync(1, 128);
+      if (h == 0) {
+        stats[b * 128 + row] = next_stat;
+        if (it + 1 < n_it) next_stat = load_stat(it + 1);
+      }
+      named_bar_sync(1, 256);
       if (!warp_mbar_wait(&bars->st_full[b], (it >> 1) & 1, abort_flag, p.status, 300 + b)) { ok = false; break; }
       tc_fence_after();
       // visible iff kv <= q + off  <=>  q_local >= kvi - off - q0
@@ -283,16 +289,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         b4.x -= q0; b4.y -= q0; b4.z -= q0; b4.w -= q0;
       }
       const uint32_t buf = tmem + lane_base + COL_BUF + b * 128;
-      uint32_t s_r[2][32], dp_r[2][32];
-      tmem_ld_32x32(buf + OFF_ST, s_r[0]);
-      tmem_ld_32x32(buf + OFF_ST + 32, s_r[1]);
-      tmem_ld_32x32(buf + OFF_DPT, dp_r[0]);
-      tmem_ld_32x32(buf + OFF_DPT + 32, dp_r[1]);
-      tmem_ld_wait();                                   // everything is in registers: the buffer may be overwritten
+      uint32_t s_r[32], dp_r[32];
+      tmem_ld_32x32(buf + OFF_ST + h * 32, s_r);
+      tmem_ld_32x32(buf + OFF_DPT + h * 32, dp_r);
+      tmem_ld_wait();
+      // P^T / dS^T go over S^T, and one half's outputs land on the columns the OTHER half reads its S^T from: nobody
+      // writes before both halves hold their inputs in registers
+      tc_fence_before();
+      named_bar_sync(4, 256);
+      tc_fence_after();
       const float* st = stats + b * 128;
       uint8_t* row_ptr = sDS + b * DS_BYTES + row * 128;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
+      {
         uint32_t pk_p[16], pk_ds[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 4) {
@@ -302,11 +310,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           float pv[4], dsv[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            float pe = fast_exp2(fmaf(__uint_as_float(s_r[h][c + e]), p.scale_log2, -l2[e]));
+            float pe = fast_exp2(fmaf(__uint_as_float(s_r[c + e]), p.scale_log2, -l2[e]));
             const int ql = h * 32 + c + e;
             if (ql < first_visible || (kMask && ((ql >= b4.x && ql < b4.y) || (ql >= b4.z && ql < b4.w)))) pe = 0.f;
             pv[e] = pe;
-            dsv[e] = pe * (__uint_as_float(dp_r[h][c + e]) - dl[e]) * p.scale;
+            dsv[e] = pe * (__uint_as_float(dp_r[c + e]) - dl[e]) * p.scale;
           }
           pk_p[c >> 1] = pack_bf16x2(pv[0], pv[1]);
           pk_p[(c >> 1) + 1] = pack_bf16x2(pv[2], pv[3]);
@@ -325,10 +333,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       mbar_arrive(&bars->pds_full[b]);
     }
-    // ---- final: dK, dV (fp32 in TMEM) -> bf16 -> swizzled staging (Q/dO ring is idle now) -> TMA store
-    if (ok && n_it > 0) ok = warp_mbar_wait(&bars->dkv_full, 0, abort_flag, p.status, 310);
-    named_bar_sync(1, 128);
-    if (ok) {
+    // ---- final (first softmax warpgroup): dK, dV (fp32 in TMEM) -> bf16 -> swizzled staging (Q/dO ring is idle now)
+    // -> TMA store
+    if (h == 0 && ok && n_it > 0) ok = warp_mbar_wait(&bars->dkv_full, 0, abort_flag, p.status, 310);
+    if (h == 0) named_bar_sync(3, 128);
+    if (h == 0 && ok) {
       tc_fence_after();
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
@@ -357,8 +366,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       fence_proxy_async_smem();
     }
-    named_bar_sync(1, 128);
-    if (ok && threadIdx.x == 0) {
+    if (h == 0) named_bar_sync(3, 128);
+    if (h == 0 && ok && threadIdx.x == 0) {
       tma_store_4d(&tmDK, sQ, 0, kv_head, kv0, batch);
       tma_store_4d(&tmDK, sQ + KV_HALF, 64, kv_head, kv0, batch);
       tma_store_4d(&tmDV, sQ + KV_TILE, 0, kv_head, kv0, batch);

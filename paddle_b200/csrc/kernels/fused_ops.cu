@@ -699,6 +699,24 @@ using namespace pd::ew;
 
 #define PD_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda)
 
+#ifdef PD_DEBUG_BOUNDS
+#include "sm100_prims.cuh"
+// First recorded violation of the debug-bounds build over all kernel files: {kind, x, y, block, thread, 0, 0, 0};
+// kind 0 = none.  Reading clears the records.
+PD_EXPORT int pd_debug_bounds_read(int* out8) {
+  int first[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  pd::PdBoundsReaders& readers = pd::pd_bounds_readers();
+  for (int k = 0; k < readers.n; ++k) {
+    int rec[8];
+    if (readers.fn[k](rec) != 0) return kErrCuda;
+    if (first[0] == 0 && rec[0] != 0)
+      for (int i = 0; i < 8; ++i) first[i] = rec[i];
+  }
+  for (int i = 0; i < 8; ++i) out8[i] = first[i];
+  return kLaunchOk;
+}
+#endif
+
 // w_is_f32: weight dtype (0 = bf16, 1 = fp32).  residual / residual_out / inv_rms may be null.
 PD_EXPORT int pd_rms_norm_fwd(const void* x, const void* residual, const void* w, int w_is_f32, void* y,
                               void* residual_out, float* inv_rms, int64_t rows, int H, float eps,

@@ -64,8 +64,9 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS) sample_kernel(const T* __restrict__ logits, int64_t ld, int V,
                                                          const float* __restrict__ top_p, int top_k, float inv_temp,
                                                          int input_is_prob, unsigned long long seed,
-                                                         unsigned long long offset, long long* __restrict__ out_id,
-                                                         float* __restrict__ out_prob) {
+                                                         unsigned long long offset,
+                                                         const long long* __restrict__ draw_counter,
+                                                         long long* __restrict__ out_id, float* __restrict__ out_prob) {
   extern __shared__ float prob[];           // V probabilities
   __shared__ float red[WARPS + 2];
   __shared__ float warp_tot[WARPS];
@@ -124,6 +125,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const T* __restrict__ l
   for (int i = threadIdx.x; i < V; i += THREADS) kept += prob[i] >= thr ? prob[i] : 0.f;
   kept = block_sum(kept, red);
   curandStatePhilox4_32_10_t st;
+  // a device-resident draw counter lets a captured launch (CUDA graph) draw fresh numbers at every replay
+  if (draw_counter != nullptr) offset += static_cast<unsigned long long>(*draw_counter) * 4ull;
   curand_init(seed, static_cast<unsigned long long>(row), offset, &st);
   const float target = curand_uniform(&st) * kept;      // (0, kept]
   if (threadIdx.x == 0) pick = -1;
@@ -175,9 +178,11 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(const T* __restrict__ l
 // logits: [rows, V] (row stride ld elements) bf16 (is_f32 = 0) or fp32; input_is_prob = 1 when they already are
 // probabilities.  top_p: fp32 [rows] or null (= 1); top_k <= 0: no count limit.  out_id: int64 [rows]; out_prob: fp32
 // [rows] or null (probability of the drawn token before renormalisation).  V * 4 bytes must fit in shared memory.
+// draw_counter: optional device int64; the Philox offset used is offset + 4 * (*draw_counter).
 PD_EXPORT int pd_sample_top_p_top_k(const void* logits, int is_f32, int64_t rows, int64_t ld, int V, const float* top_p,
                                     int top_k, float temperature, int input_is_prob, unsigned long long seed,
-                                    unsigned long long offset, long long* out_id, float* out_prob, cudaStream_t stream) {
+                                    unsigned long long offset, long long* out_id, float* out_prob, cudaStream_t stream,
+                                    const long long* draw_counter) {
   using namespace pd;
   using namespace pd::smp;
   if (rows <= 0 || V <= 0 || temperature <= 0.f) return kErrBadShape;
@@ -193,10 +198,11 @@ PD_EXPORT int pd_sample_top_p_top_k(const void* logits, int is_f32, int64_t rows
   }
   if (is_f32)
     sample_kernel<float><<<static_cast<unsigned>(rows), THREADS, smem, stream>>>(
-        static_cast<const float*>(logits), ld, V, top_p, top_k, 1.f / temperature, input_is_prob, seed, offset, out_id, out_prob);
+        static_cast<const float*>(logits), ld, V, top_p, top_k, 1.f / temperature, input_is_prob, seed, offset, draw_counter, out_id,
+        out_prob);
   else
     sample_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), THREADS, smem, stream>>>(
-        static_cast<const __nv_bfloat16*>(logits), ld, V, top_p, top_k, 1.f / temperature, input_is_prob, seed, offset, out_id,
-        out_prob);
+        static_cast<const __nv_bfloat16*>(logits), ld, V, top_p, top_k, 1.f / temperature, input_is_prob, seed, offset, draw_counter,
+        out_id, out_prob);
   return cudaGetLastError() == cudaSuccess ? kLaunchOk : kErrCuda;
 }

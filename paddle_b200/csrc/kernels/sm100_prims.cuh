@@ -181,9 +181,56 @@ __device__ __forceinline__ void st_v4(void* p, const uint4& v) {
   asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// ---------------------------------------------------------------- PD_DEBUG_BOUNDS
+// A build with -DPD_DEBUG_BOUNDS (`python -m paddle_b200.ops.build --debug-bounds`, library libpd_kernels_dbg.so,
+// loaded when PD_DEBUG_BOUNDS=1) checks every TMA / bulk copy before it is issued: the innermost coordinate of a tiled
+// copy must be a multiple of four elements (necessary for the 16-byte start rule with 32-bit elements, and for 16-bit
+// elements with the even tile origins all kernels here use), stores and reductions must not start at a negative
+// coordinate, untiled bulk copies need 16-byte aligned addresses and sizes.  A copy that fails its check is NOT issued
+// - an unaligned start is an illegal instruction that costs the context - and the first violation is recorded
+// ({kind, x, y, blockIdx.x, threadIdx.x}; read with pd_debug_bounds_read); the consumer's bounded wait then reports
+// the missing data through the status word.  The release build compiles the checks away.
+#ifdef PD_DEBUG_BOUNDS
+// one record per translation unit (device code is linked per file); every file registers a reader for its own
+static __device__ int g_pd_bounds[8];
+typedef int (*pd_bounds_reader_t)(int*);
+struct PdBoundsReaders {
+  pd_bounds_reader_t fn[64];
+  int n;
+  int push_back(pd_bounds_reader_t f) {
+    if (n < 64) fn[n++] = f;
+    return 0;
+  }
+};
+inline PdBoundsReaders& pd_bounds_readers() {
+  static PdBoundsReaders readers = {{nullptr}, 0};
+  return readers;
+}
+static int pd_bounds_read_this_file(int* out8) {
+  const int zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(out8, g_pd_bounds, sizeof(zero)) != cudaSuccess) return -1;
+  return cudaMemcpyToSymbol(g_pd_bounds, zero, sizeof(zero)) == cudaSuccess ? 0 : -1;
+}
+static const int pd_bounds_registered = pd_bounds_readers().push_back(&pd_bounds_read_this_file);
+__device__ __forceinline__ bool pd_bounds_ok(bool ok, int kind, int x, int y) {
+  if (!ok && atomicCAS(&g_pd_bounds[0], 0, kind) == 0) {
+    g_pd_bounds[1] = x;
+    g_pd_bounds[2] = y;
+    g_pd_bounds[3] = static_cast<int>(blockIdx.x);
+    g_pd_bounds[4] = static_cast<int>(threadIdx.x);
+  }
+  return ok;
+}
+#define PD_BOUNDS_CHECK(cond, kind, x, y) \
+  if (!pd_bounds_ok((cond), (kind), (x), (y))) return
+#else
+#define PD_BOUNDS_CHECK(cond, kind, x, y)
+#endif
+
 // ---------------------------------------------------------------- TMA (no cluster multicast anywhere)
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar,
                                             int x, int y) {
+  PD_BOUNDS_CHECK((x & 3) == 0, 1, x, y);
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
@@ -192,6 +239,7 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
 }
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar,
                                             int x, int y, int z) {
+  PD_BOUNDS_CHECK((x & 3) == 0, 2, x, y);
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(smem_dst)),
@@ -200,6 +248,7 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* t
 }
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar,
                                             int x, int y, int z, int w) {
+  PD_BOUNDS_CHECK((x & 3) == 0, 3, x, y);
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(smem_dst)),
@@ -208,18 +257,21 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* t
 }
 // Untiled bulk copies (addresses 16-byte aligned, size a multiple of 16 bytes).  No multicast.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  PD_BOUNDS_CHECK(((reinterpret_cast<uintptr_t>(gmem_src) | smem_u32(smem_dst) | bytes) & 15u) == 0, 31, static_cast<int>(bytes), 0);
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(smem_dst)),
                "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
 __device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  PD_BOUNDS_CHECK(((reinterpret_cast<uintptr_t>(gmem_dst) | smem_u32(smem_src) | bytes) & 15u) == 0, 32, static_cast<int>(bytes), 0);
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
                "r"(smem_u32(smem_src)), "r"(bytes)
                : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int x,
                                              int y) {
+  PD_BOUNDS_CHECK((x & 3) == 0 && x >= 0 && y >= 0, 11, x, y);
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::
                    "l"(reinterpret_cast<uint64_t>(tmap)),
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
@@ -227,6 +279,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void
 }
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, const void* smem_src, int x,
                                              int y, int z) {
+  PD_BOUNDS_CHECK((x & 3) == 0 && x >= 0 && y >= 0, 12, x, y);
   asm volatile(
       "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
           reinterpret_cast<uint64_t>(tmap)),
@@ -235,6 +288,7 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* tmap, const void
 }
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* tmap, const void* smem_src, int x,
                                              int y, int z, int w) {
+  PD_BOUNDS_CHECK((x & 3) == 0 && x >= 0 && y >= 0, 13, x, y);
   asm volatile(
       "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::
           "l"(reinterpret_cast<uint64_t>(tmap)),
@@ -243,6 +297,7 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* tmap, const void
 }
 __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, const void* smem_src,
                                                   int x, int y) {
+  PD_BOUNDS_CHECK((x & 3) == 0 && x >= 0 && y >= 0, 21, x, y);
   asm volatile(
       "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::
           "l"(reinterpret_cast<uint64_t>(tmap)),
@@ -251,6 +306,7 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* tmap, const
 }
 __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* tmap, const void* smem_src,
                                                   int x, int y, int z, int w) {
+  PD_BOUNDS_CHECK((x & 3) == 0 && x >= 0 && y >= 0, 23, x, y);
   asm volatile(
       "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::
           "l"(reinterpret_cast<uint64_t>(tmap)),

@@ -106,6 +106,25 @@ class LlamaForCausalLMInference(nn.Layer):
         best = vals.argmax(0, keepdim=True)
         return idxs.gather(0, best)[0]
 
+    def _pick(self, logits):
+        """Next token per sequence: greedy, or one draw from the top-k / nucleus of softmax(logits / temperature)
+        when sampling is configured (`generate(do_sample=True, ...)`).  Under tensor parallelism the vocabulary
+        shards are gathered first; every rank draws with the same seed and counter, hence the same token."""
+        cfg = getattr(self, "_sampling", None)
+        if cfg is None:
+            return self._argmax(logits)
+        from ..ops import native
+        if self.tp_group is not None:
+            from ..distributed import collective as C
+            parts = torch.empty((self.nranks, *logits.shape), dtype=logits.dtype, device=logits.device)
+            C.all_gather_into_tensor(parts, logits.contiguous(), group=self.tp_group)
+            logits = parts.permute(1, 0, 2).reshape(logits.shape[0], -1).contiguous()
+        top_p, top_k, temperature, seed = cfg
+        tp = self._top_p_buf[:logits.shape[0]]
+        ids, _ = native.sample_top_p_top_k(logits, tp, top_k, temperature, seed, 0, draw_counter=self._draws)
+        self._draws += 1                      # device-side: a replayed graph advances it as well
+        return ids
+
     @torch.no_grad()
     def prefill(self, input_ids):
         """input_ids [B, S] (equal lengths).  Returns the first generated token per sequence [B]."""
@@ -117,21 +136,39 @@ class LlamaForCausalLMInference(nn.Layer):
         h = self.transformer.prefill_paged(x, kv, self._cos[:S].contiguous(), self._sin[:S].contiguous(), B, S)
         last = h.view(B, S, -1)[:, -1].contiguous()
         kv.seq_lens[:B] = S
-        return self._argmax(self._logits(last))
+        return self._pick(self._logits(last))
 
     def _decode_step(self, B):
         kv = self._kv
         x = torch.nn.functional.embedding(self._tokens[:B], self.embed_tokens.weight.detach())
         h = self.transformer.decode_paged(x, kv, self._cos64, self._sin64)
-        nxt = self._argmax(self._logits(h))
+        nxt = self._pick(self._logits(h))
         self._tokens[:B].copy_(nxt)
         kv.seq_lens[:B] += 1
 
     @torch.no_grad()
-    def generate(self, input_ids, max_new_tokens, use_cuda_graph=True, timings=None):
-        """Greedy decoding.  Returns int64 tokens [B, max_new_tokens]; ``timings`` (a dict) receives ``ttft_ms`` and
-        ``decode_ms`` measured with CUDA events."""
+    def generate(self, input_ids, max_new_tokens, use_cuda_graph=True, timings=None, do_sample=False, top_p=1.0,
+                 top_k=0, temperature=1.0, seed=0):
+        """Greedy decoding, or with ``do_sample`` top-k / nucleus sampling on the device (one sort-free kernel per
+        step, Philox stream addressed by ``seed`` and a device-resident draw counter, so the captured decode step draws
+        fresh numbers at every replay).  Returns int64 tokens [B, max_new_tokens]; ``timings`` (a dict) receives
+        ``ttft_ms`` and ``decode_ms`` measured with CUDA events."""
         B, S = input_ids.shape
+        sampling = (float(top_p), int(top_k), float(temperature), int(seed)) if do_sample else None
+        if sampling != getattr(self, "_sampling", None):
+            self._graph = None                # the captured step has the old choice baked in
+        self._sampling = sampling
+        if sampling is not None:
+            dev = input_ids.device
+            # the captured step holds on to these buffers: allocate once, reset in place
+            if getattr(self, "_draws", None) is None:
+                self._draws = torch.zeros(1, dtype=torch.int64, device=dev)
+            else:
+                self._draws.zero_()
+            if getattr(self, "_top_p_buf", None) is None or self._top_p_buf.numel() < B:
+                self._top_p_buf = torch.empty(max(B, 64), dtype=torch.float32, device=dev)
+                self._graph = None
+            self._top_p_buf.fill_(float(top_p))
         kv = self._kv
         kv.reset()
         for b in range(B):
@@ -149,12 +186,15 @@ class LlamaForCausalLMInference(nn.Layer):
             if self._graph is None or self._graph_batch != B:
                 # warm-up on a side stream (lazy initialisation), rewind the state, then capture
                 lens0, tok0 = kv.seq_lens.clone(), self._tokens.clone()
+                draws0 = self._draws.clone() if sampling is not None else None
                 side = torch.cuda.Stream()
                 side.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(side):
                     self._decode_step(B)
                 torch.cuda.current_stream().wait_stream(side)
                 kv.seq_lens.copy_(lens0), self._tokens.copy_(tok0)
+                if draws0 is not None:
+                    self._draws.copy_(draws0)             # the warm-up step drew once
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self._decode_step(B)

@@ -23,8 +23,14 @@ class NativeLibraryError(RuntimeError):
     pass
 
 
-class KernelStatusError(RuntimeError):
-    """A kernel gave up on a bounded wait (or rejected its arguments) and wrote a status word."""
+def _timeout_base():
+    from ..framework.errors import ExecutionTimeoutError
+    return ExecutionTimeoutError
+
+
+class KernelStatusError(_timeout_base()):
+    """A kernel gave up on a bounded wait (or rejected its arguments) and wrote a status word.  An
+    ``ExecutionTimeoutError`` (error code 8), hence a ``RuntimeError``."""
 
 
 def _load(name: str, builder: str):
@@ -49,8 +55,30 @@ def kernels() -> ctypes.CDLL:
     if _kernels is None:
         with _lock:
             if _kernels is None:
-                _kernels = _load("libpd_kernels.so", "build_kernels")
+                if os.environ.get("PD_DEBUG_BOUNDS") == "1":
+                    # checked build: every TMA / bulk copy is validated before it is issued (sm100_prims.cuh)
+                    path = os.path.join(_LIB_DIR, "libpd_kernels_dbg.so")
+                    if not os.path.exists(path):
+                        from . import build as _build
+                        _build.build_kernels(debug_bounds=True)
+                    _kernels = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+                else:
+                    _kernels = _load("libpd_kernels.so", "build_kernels")
     return _kernels
+
+
+def debug_bounds_violation():
+    """First violation recorded by the ``PD_DEBUG_BOUNDS=1`` build since the last call, as a dict, or None."""
+    k = kernels()
+    if not hasattr(k, "pd_debug_bounds_read"):
+        raise RuntimeError("the loaded kernel library is not the debug-bounds build (set PD_DEBUG_BOUNDS=1)")
+    rec = (ctypes.c_int * 8)()
+    check(k.pd_debug_bounds_read(rec), "pd_debug_bounds_read")
+    if rec[0] == 0:
+        return None
+    kinds = {1: "tma_load_2d", 2: "tma_load_3d", 3: "tma_load_4d", 11: "tma_store_2d", 12: "tma_store_3d",
+             13: "tma_store_4d", 21: "tma_reduce_add_2d", 23: "tma_reduce_add_4d", 31: "bulk_load", 32: "bulk_store"}
+    return {"copy": kinds.get(rec[0], rec[0]), "x": rec[1], "y": rec[2], "block": rec[3], "thread": rec[4]}
 
 
 def runtime() -> ctypes.CDLL:
@@ -92,8 +120,13 @@ _LAUNCH_ERRORS = {
 
 
 def check(rc: int, what: str):
+    """Turn a launcher return code into a typed error (``framework/errors.py``): bad shape / alignment ->
+    InvalidArgumentError (a ValueError), beyond the supported size -> OutOfRangeError, tensor-map or CUDA launch failure
+    -> ExternalError; all of them are RuntimeErrors as well."""
     if rc != 0:
-        raise RuntimeError(f"{what}: native launcher returned {rc} ({_LAUNCH_ERRORS.get(rc, 'unknown')})")
+        from ..framework import errors
+        cls = errors.LAUNCH_ERROR_CLASSES.get(rc, errors.LaunchExternal)
+        raise cls(f"{what}: native launcher returned {rc} ({_LAUNCH_ERRORS.get(rc, 'unknown')})")
 
 
 # One 4-int status word per device: {code, block, site, detail}; written by kernels whose bounded

@@ -55,10 +55,14 @@ def _compile_one(cmd, src, obj, log_path):
     return obj
 
 
-def build_kernels(verbose: bool = False, force: bool = False) -> str:
-    """Compile every ``csrc/kernels/*.cu`` for sm_100a and link ``libpd_kernels.so``."""
+def build_kernels(verbose: bool = False, force: bool = False, debug_bounds: bool = False) -> str:
+    """Compile every ``csrc/kernels/*.cu`` for sm_100a and link ``libpd_kernels.so``.  ``debug_bounds`` builds
+    ``libpd_kernels_dbg.so`` with ``-DPD_DEBUG_BOUNDS`` instead (coordinate / alignment checks in front of every TMA and
+    bulk copy, see ``sm100_prims.cuh``); ``ops._lib`` loads it when ``PD_DEBUG_BOUNDS=1``."""
     kdir = os.path.join(CSRC, "kernels")
     os.makedirs(OBJ_DIR, exist_ok=True)
+    if debug_bounds:
+        return _build_kernels_variant(kdir, "libpd_kernels_dbg.so", "dbg_", ["-DPD_DEBUG_BOUNDS"], verbose, force)
     out = os.path.join(LIB_DIR, "libpd_kernels.so")
     srcs = sorted(f for f in os.listdir(kdir) if f.endswith(".cu"))
     hdr_t = _newest_header(kdir)
@@ -82,6 +86,33 @@ def build_kernels(verbose: bool = False, force: bool = False) -> str:
     if jobs or not os.path.exists(out):
         cmd = [nvcc, "-shared", "-o", out, *objs, "-lcudart", "-gencode", "arch=compute_100a,code=sm_100a"]
         p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode != 0:
+            raise RuntimeError("link failed:\n" + p.stdout + p.stderr)
+    return out
+
+
+def _build_kernels_variant(kdir, lib_name, obj_prefix, extra_flags, verbose, force):
+    out = os.path.join(LIB_DIR, lib_name)
+    srcs = sorted(f for f in os.listdir(kdir) if f.endswith(".cu"))
+    hdr_t = _newest_header(kdir)
+    nvcc = _nvcc()
+    jobs, objs = [], []
+    for s in srcs:
+        src = os.path.join(kdir, s)
+        obj = os.path.join(OBJ_DIR, obj_prefix + s[:-3] + ".o")
+        objs.append(obj)
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), hdr_t):
+            continue
+        jobs.append(([nvcc, *NVCC_FLAGS, *extra_flags, "-I", kdir, "-c", src, "-o", obj], src, obj, obj + ".log"))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for fut in [ex.submit(_compile_one, *j) for j in jobs]:
+                o = fut.result()
+                if verbose:
+                    print("compiled", os.path.basename(o), file=sys.stderr)
+    if jobs or not os.path.exists(out):
+        p = subprocess.run([nvcc, "-shared", "-o", out, *objs, "-lcudart", "-gencode", "arch=compute_100a,code=sm_100a"],
+                           capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError("link failed:\n" + p.stdout + p.stderr)
     return out
@@ -152,6 +183,9 @@ def build_all(verbose: bool = False, force: bool = False):
 
 
 if __name__ == "__main__":
-    k, r = build_all(verbose=True, force="--force" in sys.argv)
-    print(k)
-    print(r)
+    if "--debug-bounds" in sys.argv:
+        print(build_kernels(verbose=True, force="--force" in sys.argv, debug_bounds=True))
+    else:
+        k, r = build_all(verbose=True, force="--force" in sys.argv)
+        print(k)
+        print(r)

@@ -450,12 +450,13 @@ def bias_act(x, bias, act):
     return out
 
 
-def sample_top_p_top_k(logits, top_p=None, top_k=0, temperature=1.0, seed=0, offset=0, input_is_prob=False):
+def sample_top_p_top_k(logits, top_p=None, top_k=0, temperature=1.0, seed=0, offset=0, input_is_prob=False,
+                       draw_counter=None, out=None):
     """One token per row from ``softmax(logits / temperature)`` cut to the ``top_k`` most likely tokens and to the
     nucleus of mass ``top_p`` (fp32 ``[rows]`` or None).  Returns ``(ids int64 [rows], probs fp32 [rows])``."""
     _req(logits.dim() == 2 and logits.stride(1) == 1 and logits.dtype in (BF16, F32), "sample: [rows, V] bf16 / fp32 required")
     rows, V = logits.shape
-    ids = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    ids = torch.empty(rows, dtype=torch.int64, device=logits.device) if out is None else out
     probs = torch.empty(rows, dtype=F32, device=logits.device)
     if top_p is not None:
         top_p = top_p.reshape(-1).to(F32).contiguous()
@@ -463,7 +464,8 @@ def sample_top_p_top_k(logits, top_p=None, top_k=0, temperature=1.0, seed=0, off
     rc = _lib.kernels().pd_sample_top_p_top_k(
         ptr(logits), c_int(1 if logits.dtype == F32 else 0), c_int64(rows), c_int64(logits.stride(0)), c_int(V), ptr(top_p),
         c_int(int(top_k)), c_float(float(temperature)), c_int(1 if input_is_prob else 0),
-        ctypes.c_ulonglong(int(seed) & (2 ** 64 - 1)), ctypes.c_ulonglong(int(offset)), ptr(ids), ptr(probs), stream())
+        ctypes.c_ulonglong(int(seed) & (2 ** 64 - 1)), ctypes.c_ulonglong(int(offset)), ptr(ids), ptr(probs), stream(),
+        ptr(draw_counter))
     check(rc, "pd_sample_top_p_top_k")
     _count()
     return ids, probs

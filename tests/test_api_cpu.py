@@ -216,3 +216,33 @@ def test_tensor_semantics_table():
     paddle.seed(1)
     assert paddle.rand([3]).tolist() == r1
     assert paddle.matmul(paddle.ones([2, 2], "bfloat16"), paddle.ones([2, 2], "bfloat16")).dtype == paddle.bfloat16
+
+
+def test_typed_errors_follow_the_reference_mapping():
+    """Error codes map onto the built-in exception classes the reference raises for them, share EnforceNotMet as base,
+    and the native launcher codes arrive as typed errors that are still RuntimeErrors."""
+    import pytest
+
+    import paddle_b200 as paddle
+    from paddle_b200.framework import errors
+    from paddle_b200.ops import _lib
+    pairs = {errors.InvalidArgumentError: ValueError, errors.OutOfRangeError: IndexError,
+             errors.ResourceExhaustedError: MemoryError, errors.UnimplementedError: NotImplementedError,
+             errors.FatalError: SystemError, errors.ExternalError: OSError, errors.InvalidTypeError: TypeError,
+             errors.NotFoundError: RuntimeError, errors.ExecutionTimeoutError: RuntimeError}
+    for cls, builtin in pairs.items():
+        assert issubclass(cls, builtin) and issubclass(cls, errors.EnforceNotMet)
+        assert errors.BY_CODE[cls.code] is cls
+    assert paddle.base.core.EnforceNotMet is errors.EnforceNotMet
+    with pytest.raises(ValueError, match=r"\(InvalidArgumentError\).*bad shape"):
+        _lib.check(-1, "pd_some_kernel")
+    with pytest.raises(RuntimeError):
+        _lib.check(-2, "pd_some_kernel")
+    with pytest.raises(IndexError):
+        _lib.check(-5, "pd_some_kernel")
+    with pytest.raises(OSError):
+        _lib.check(-4, "pd_some_kernel")
+    assert issubclass(_lib.KernelStatusError, errors.ExecutionTimeoutError)
+    with pytest.raises(errors.PreconditionNotMetError):
+        errors.enforce(False, message="state")
+    errors.enforce(True)

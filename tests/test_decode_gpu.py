@@ -121,6 +121,18 @@ def test_paged_engine_matches_training_forward():
             agree += int(((row.argmax(-1) == toks[:, t]) & clear).sum())
             total += int(clear.sum())
         assert total > 0 and agree == total, (graph, agree, total)
+    # sampling on the device: reproducible per seed, eager and graph replays draw the same sequence (the draw counter
+    # lives on the device), a different seed gives another one, top_k = 1 is greedy
+    greedy = infer.generate(ids, NEW, use_cuda_graph=True)
+    s_eager = infer.generate(ids, NEW, use_cuda_graph=False, do_sample=True, top_p=0.9, temperature=5.0, seed=11)
+    s_graph = infer.generate(ids, NEW, use_cuda_graph=True, do_sample=True, top_p=0.9, temperature=5.0, seed=11)
+    s_other = infer.generate(ids, NEW, use_cuda_graph=True, do_sample=True, top_p=0.9, temperature=5.0, seed=12)
+    s_k1 = infer.generate(ids, NEW, use_cuda_graph=True, do_sample=True, top_k=1, seed=5)
+    assert torch.equal(s_eager, s_graph)
+    assert not torch.equal(s_graph, s_other)
+    assert not torch.equal(s_graph, greedy)
+    assert torch.equal(s_k1, greedy)
+    assert torch.equal(infer.generate(ids, NEW, use_cuda_graph=True), greedy)       # back to greedy re-captures
 
 
 def test_withheld_signal_returns_status_not_hang():

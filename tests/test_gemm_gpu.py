@@ -68,3 +68,40 @@ def test_gemm_large_and_deterministic():
     assert torch.allclose(o1[:256].float(), ref, rtol=2e-2, atol=1.0)
     ref2 = a[-128:].float() @ b.float()
     assert torch.allclose(o1[-128:].float(), ref2, rtol=2e-2, atol=1.0)
+
+
+def test_debug_bounds_build_runs_clean():
+    """The -DPD_DEBUG_BOUNDS build of the kernels (every TMA / bulk copy checked before it is issued) computes the same
+    results and records no violation for GEMM (all layouts, accumulate), attention forward / backward and RMSNorm."""
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import math, torch
+from paddle_b200.ops import _lib, native, attention
+assert hasattr(_lib.kernels(), "pd_debug_bounds_read")
+torch.manual_seed(0)
+a = torch.randn(300, 520, device="cuda").bfloat16(); b = torch.randn(520, 264, device="cuda").bfloat16()
+for impl in ("2cta", "1cta"):
+    native.set_gemm_impl(impl)
+    y = native.gemm(a, b)
+    assert (y.float() - a.float() @ b.float()).abs().max() < 0.5
+    acc = torch.zeros(520, 264, device="cuda")
+    x2 = torch.randn(300, 264, device="cuda").bfloat16()
+    native.gemm(a, x2, trans_a=True, out=acc, accumulate=True)
+    assert (acc - a.float().t() @ x2.float()).abs().max() < 0.5
+q = torch.randn(1, 300, 2, 128, device="cuda").bfloat16().requires_grad_(True)
+k = torch.randn(1, 300, 2, 128, device="cuda").bfloat16().requires_grad_(True)
+v = torch.randn(1, 300, 2, 128, device="cuda").bfloat16().requires_grad_(True)
+o = attention.flash_attn_func(q, k, v, True, 1 / math.sqrt(128))
+o.backward(torch.randn_like(o))
+w = torch.ones(512, device="cuda").bfloat16()
+native.rms_norm_fwd(torch.randn(64, 512, device="cuda").bfloat16(), w, 1e-6)
+torch.cuda.synchronize()
+_lib.check_status()
+assert _lib.debug_bounds_violation() is None
+print("CLEAN")
+"""
+    env = dict(os.environ, PD_DEBUG_BOUNDS="1", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0 and "CLEAN" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
