@@ -329,24 +329,35 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int jobs = npeers * n_sub;                 // the local shard is read in place by the GEMM
     const int my_jobs = static_cast<int>(blockIdx.x) < jobs ? (jobs - static_cast<int>(blockIdx.x) + p.n_comm - 1) / p.n_comm : 0;
     const uint32_t row_bytes = static_cast<uint32_t>(p.row_elems) * 2;
-    const int rows_per_piece = row_bytes >= PIECE_MAX ? 1 : PIECE_MAX / row_bytes;
-    const int ppj = (p.sub_rows + rows_per_piece - 1) / rows_per_piece;     // pieces per job
+    // A piece is either several whole rows (rows of up to PIECE_MAX bytes) or one PIECE_MAX-byte segment of a row
+    // (wider rows, e.g. a gathered weight of 12288+ columns: a whole row would overrun its ring slot).
+    const int segs = (row_bytes + PIECE_MAX - 1) / PIECE_MAX;               // segments per row
+    const int rows_per_piece = segs > 1 ? 1 : PIECE_MAX / row_bytes;
+    const int ppj = segs > 1 ? p.sub_rows * segs : (p.sub_rows + rows_per_piece - 1) / rows_per_piece;   // pieces per job
     const int total = my_jobs * ppj;
-    auto piece_info = [&](int q, int& peer, int& c, int& row0, uint32_t& bytes) {
+    auto piece_info = [&](int q, int& peer, int& c, int& row0, uint32_t& bytes, uint32_t& col_off) {
       const int j = static_cast<int>(blockIdx.x) + (q / ppj) * p.n_comm;
       c = j / npeers;
       peer = (p.rank + 1 + j % npeers) % p.nranks;
-      row0 = (q % ppj) * rows_per_piece;
-      const int nrows = min(rows_per_piece, p.sub_rows - row0);
-      bytes = static_cast<uint32_t>(nrows) * row_bytes;
+      if (segs > 1) {
+        const int idx = q % ppj;
+        row0 = idx / segs;
+        col_off = static_cast<uint32_t>(idx % segs) * PIECE_MAX;
+        bytes = min(static_cast<uint32_t>(PIECE_MAX), row_bytes - col_off);
+      } else {
+        row0 = (q % ppj) * rows_per_piece;
+        col_off = 0;
+        const int nrows = min(rows_per_piece, p.sub_rows - row0);
+        bytes = static_cast<uint32_t>(nrows) * row_bytes;
+      }
     };
     auto issue_load = [&](int q) {
       int peer, c, row0;
-      uint32_t bytes;
-      piece_info(q, peer, c, row0, bytes);
+      uint32_t bytes, col_off;
+      piece_info(q, peer, c, row0, bytes, col_off);
       const int slot = q % RING;
       const uint8_t* src = static_cast<const uint8_t*>(p.x_shard) +
-                           (static_cast<size_t>(c) * p.sub_rows + row0) * row_bytes;
+                           (static_cast<size_t>(c) * p.sub_rows + row0) * row_bytes + col_off;
       mbar_expect_tx(&ring_bar[slot], bytes);
       bulk_load(smem + slot * PIECE_MAX, src, bytes, &ring_bar[slot]);
     };
@@ -361,8 +372,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         issue_load(q + LOOKAHEAD);
       }
       int peer, c, row0;
-      uint32_t bytes;
-      piece_info(q, peer, c, row0, bytes);
+      uint32_t bytes, col_off;
+      piece_info(q, peer, c, row0, bytes, col_off);
       if (!(checked & (1u << peer))) {
         // the peer must have finished reading what the previous epoch put into this slot
         if (!flag_wait_ge(ack_local + peer, epoch_v - 1, p.wait_ns, p.status, 500 + peer)) { ok = false; break; }
@@ -371,7 +382,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int slot = q % RING;
       if (!mbar_wait(&ring_bar[slot], (q / RING) & 1, &dummy_abort, p.status, 510)) { ok = false; break; }
       uint8_t* dst = reinterpret_cast<uint8_t*>(p.peer_stage[peer]) +
-                     ((static_cast<size_t>(p.rank) * n_sub + c) * p.sub_rows + row0) * row_bytes;
+                     ((static_cast<size_t>(p.rank) * n_sub + c) * p.sub_rows + row0) * row_bytes + col_off;
       bulk_store(dst, smem + slot * PIECE_MAX, bytes);
       tma_commit_group();
       // A chunk's flag is raised FLAG_LAG pieces after its last store was issued: by then waiting for "all but

@@ -51,12 +51,13 @@ _lib.check_status()
 
 # ---- stage-3 linear with the gather fused into the GEMM
 torch.manual_seed(3)                 # same full tensors on every rank
-K, N, M = 256 * n, 512, 384
-w_full = (torch.randn(K, N, device="cuda") * 0.05).bfloat16()
-x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16().requires_grad_(True)
-w_shard = w_full[rank * (K // n):(rank + 1) * (K // n)].clone().requires_grad_(True)
 errs = []
-for it in range(3):
+# second shape: rows of 16400 bytes, wider than one 16 KB piece of the bulk-copy ring (a row then travels in segments)
+for (K, N, M), reps in (((256 * n, 512, 384), 3), ((128 * n, 8200, 256), 2)):
+  w_full = (torch.randn(K, N, device="cuda") * 0.05).bfloat16()
+  x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+  w_shard = w_full[rank * (K // n):(rank + 1) * (K // n)].clone().requires_grad_(True)
+  for it in range(reps):
     y = zero3_linear(x, w_shard, g)
     dy = (torch.randn(M, N, device="cuda") * 0.1).bfloat16()
     y.backward(dy)
