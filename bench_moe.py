@@ -36,9 +36,14 @@ def main():
     ap.add_argument("--micro-batches", type=int, default=4)
     ap.add_argument("--experts", default="grouped_fp8", choices=["grouped_fp8", "loop"])
     ap.add_argument("--model", default="mixtral-8x7b", choices=["mixtral-8x7b", "tiny"])
+    ap.add_argument("--nccl-exchange", action="store_true",
+                    help="comparison arm: dispatch / combine through NCCL all-to-all (global_scatter / global_gather) instead "
+                         "of the fused fp8 exchange over peer memory")
     ap.add_argument("--no-dense-sharding", dest="dense_sharding", action="store_false",
                     help="replicate the optimizer state of the dense parameters and all-reduce their gradients")
     args = ap.parse_args()
+    if args.nccl_exchange:
+        os.environ["PD_FUSED_MOE"] = "0"
 
     import torch
     import torch.distributed as tdist
@@ -150,7 +155,9 @@ def main():
             "config": {"model": args.model, "layers": cfg.num_hidden_layers,
                        "reduced_depth": cfg.num_hidden_layers < 32 and args.model != "tiny",
                        "experts": args.experts, "global_batch": world * n_mb, "seq_len": seq,
-                       "parallelism": f"ep{world}" + ("+sharding1(dense)" if dense_opt is not None else ""), "l2": "inputs larger than L2"}}))
+                       "parallelism": f"ep{world}" + ("+sharding1(dense)" if dense_opt is not None else ""),
+                       "exchange": "nccl all-to-all" if args.nccl_exchange else "fused fp8 dispatch / combine over peer memory",
+                       "l2": "inputs larger than L2"}}))
     if world > 1:
         torch.cuda.synchronize()
         tdist.barrier()

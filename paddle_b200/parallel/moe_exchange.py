@@ -233,6 +233,9 @@ def fused_moe_available(x, experts, group) -> bool:
     """GPU, bf16, stacked (grouped) fp8 experts, a group of up to 8 ranks with symmetric memory."""
     if not (x.is_cuda and x.dtype == torch.bfloat16 and getattr(experts, "grouped", False)):
         return False
+    import os
+    if os.environ.get("PD_FUSED_MOE", "1") == "0":          # comparison arm: NCCL all-to-all dispatch / combine
+        return False
     if group is None or group.nranks > 8 or not symm.supported():
         return False
     from ..ops import functional as K
