@@ -121,6 +121,16 @@ class RowParallelLinear(Layer):
     def forward(self, x):
         if not self.input_is_parallel and self.is_mp:
             x = mp_ops._c_split(x, group=self.model_parallel_group)
+        if self.is_mp and torch.is_tensor(x) and x.is_cuda:
+            # training-size inputs on GPUs: the reduction runs from inside the GEMM (GEMM -> reduce-scatter kernel) and
+            # an all-gather of the reduced slabs completes the all-reduce
+            from .....ops import functional as K
+            from .....parallel import fused_linear_impl as FL
+            x2 = x.reshape([-1, x.shape[-1]])
+            if K.get_kernel_policy() == "fused" and FL.linear_all_reduce_ok(x2, self.weight, self.model_parallel_group):
+                out = FL.linear_all_reduce(x2, self.weight, self.model_parallel_group)
+                out = out.reshape([*x.shape[:-1], out.shape[-1]])
+                return out + self.bias if self.bias is not None else out
         out = F.linear(x, self.weight)
         if self.is_mp:
             out = mp_ops._mp_allreduce(out, group=self.model_parallel_group)

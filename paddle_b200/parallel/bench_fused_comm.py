@@ -6,7 +6,8 @@
 
 Shapes are the Llama-2 7B tensor-parallel linears at degree N (qkv / gate_up: column parallel, all-gather in front;
 o_proj / down: row parallel, reduce-scatter behind).  Times are CUDA events on the launching stream after warm-up,
-max over ranks.  ``--sweep`` also times every push form (bulk ring / vector stores / multicast) with several push-CTA
+max over ranks.  ``--extra`` adds the decode GEMM->all-reduce, the gradient-bucket reduce-scatter (+AdamW) and the stage-3 linear against
+their unfused sequences.  ``--sweep`` also times every push form (bulk ring / vector stores / multicast) with several push-CTA
 counts and the NVLS reduce-scatter with several reducer counts.  Rank 0 prints one JSON object per line.
 """
 from __future__ import annotations
@@ -26,6 +27,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--extra", action="store_true",
+                    help="also time the decode GEMM->all-reduce, the bucket reduce-scatter (+AdamW) and the stage-3 linear")
     ap.add_argument("--trace", action="store_true",
                     help="print the per-CTA phase timestamps of the push reduce-scatter GEMM (GEMM tiles done, arrivals "
                          "published, first reduce unit, reduction done; microseconds from kernel start)")
@@ -239,10 +242,119 @@ def main():
                         rec[f"trace_{nm}_us"] = [round(float(v.min()), 1), round(float(np.median(v)), 1), round(float(v.max()), 1)]
             del pair
         emit(rec)
+    if args.extra:
+        _extra(args, g, n, rank, timed, rel, emit)
     tdist.barrier()
     torch.cuda.synchronize()
     sys.stdout.flush()
     os._exit(0)
+
+
+def _extra(args, g, n, rank, timed, rel, emit):
+    """The other fused compute + collective kernels against their unfused sequences:
+    decode GEMM -> all-reduce (13B row-parallel projections, 64 tokens), reduce-scatter (+ AdamW) of a gradient bucket,
+    and the stage-3 linear (weight gather fused into forward / dgrad GEMMs, dW through GEMM -> reduce-scatter)."""
+    import torch.distributed as tdist
+
+    from paddle_b200.ops import native
+    from paddle_b200.parallel.gemm_ar import GemmAllReduce
+    from paddle_b200.parallel.rs_adamw import FusedRSAdamW
+    from paddle_b200.parallel.zero3_linear import zero3_linear
+
+    pg = g.process_group
+    # ---- GEMM -> all-reduce, decode shapes of Llama-2 13B (hidden 5120, ffn 13824), batch 64
+    M, Hd = 64, 5120
+    for name, Kfull in (("out_proj", 5120), ("ffn2", 13824)):
+        K = Kfull // n // 64 * 64
+        x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+        w = (torch.randn(K, Hd, device="cuda") * 0.05).bfloat16()
+        res = torch.randn(M, Hd, device="cuda").bfloat16()
+        ref = x.float() @ w.float()
+        tdist.all_reduce(ref, group=pg)
+        ref = ref + res.float()
+        rec = {"op": f"gemm_ar_{name}", "shape": [M, K, Hd], "bytes_weights": K * Hd * 2,
+               "hbm_bound_us": K * Hd * 2 / 6546.6e3}
+        forms = [("push", "0")] + ([("nvls", "1")] if n >= 2 else [])
+        for form, env in forms:
+            os.environ["PD_GEMM_AR_NVLS"] = env
+            op = GemmAllReduce(g, Hd, m_cap=M)
+            os.environ.pop("PD_GEMM_AR_NVLS")
+            if form == "nvls" and not op.mc_recv:
+                continue
+            out = op(x, w, res)
+            torch.cuda.synchronize()
+            rec[f"fused_{form}_err"] = rel(out, ref)
+            rec[f"fused_{form}_us"] = timed(lambda: op(x, w, res))
+
+        def unfused():
+            y = torch.matmul(x, w)
+            tdist.all_reduce(y, group=pg)
+            return y + res
+        rec["unfused_us"] = timed(unfused)
+        emit(rec)
+
+    # ---- reduce-scatter of an fp32 gradient bucket (+ AdamW on the owned slice)
+    shard = (64 << 20) // 4 // n                     # a 64 MB bucket
+    grad = torch.randn(n * shard, device="cuda")
+    outg = torch.empty(shard, device="cuda")
+    master = torch.randn(shard, device="cuda")
+    m_, v_ = torch.zeros(shard, device="cuda"), torch.zeros(shard, device="cuda")
+    pshard = master.bfloat16()
+    fused = FusedRSAdamW(g, shard)
+    refg = torch.empty(shard, device="cuda")
+    tdist.reduce_scatter_tensor(refg, grad, group=pg)
+    fused.reduce(grad, outg)
+    torch.cuda.synchronize()
+    rec = {"op": "rs_bucket_64MB", "bytes": n * shard * 4, "link_bound_us": (n - 1) * shard * 4 / 770e3,
+           "fused_reduce_err": rel(outg, refg), "fused_reduce_us": timed(lambda: fused.reduce(grad, outg)),
+           "nccl_rs_us": timed(lambda: tdist.reduce_scatter_tensor(refg, grad, group=pg)),
+           "fused_rs_adamw_us": timed(lambda: fused.step(grad, master, m_, v_, pshard, 1e-4, 0.9, 0.95, 1e-8, 0.01, 0.9, 0.95))}
+
+    def unfused_opt():
+        tdist.reduce_scatter_tensor(refg, grad, group=pg)
+        native.adamw_flat(pshard, master, refg, m_, v_, 1e-4, 0.9, 0.95, 1e-8, 0.01, 0.9, 0.95)
+    rec["nccl_rs_plus_adamw_us"] = timed(unfused_opt)
+    emit(rec)
+
+    # ---- stage-3 linear: tokens 4096, weight [4096, 12288] (7B qkv) stored as row slices
+    T, K, N = args.tokens, args.hidden, 3 * args.hidden
+    torch.manual_seed(11)
+    w_full = (torch.randn(K, N, device="cuda") * 0.05).bfloat16()
+    w_shard = w_full[rank * (K // n):(rank + 1) * (K // n)].clone().requires_grad_(True)
+    x = (torch.randn(T, K, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    dy = (torch.randn(T, N, device="cuda") * 0.05).bfloat16()
+    y = zero3_linear(x, w_shard, g)
+    rec = {"op": "zero3_linear_qkv", "shape": [T, K, N], "fwd_err": rel(y, x.detach().float() @ w_full.float()),
+           "flop_fwd": 2.0 * T * K * N, "gather_bytes": (n - 1) * (K // n) * N * 2}
+
+    def fused_fb():
+        yy = zero3_linear(x, w_shard, g)
+        yy.backward(dy)
+        x.grad = None
+        w_shard.grad = None
+
+    def unfused_fb():
+        full = torch.empty(K, N, device="cuda", dtype=torch.bfloat16)
+        tdist.all_gather_into_tensor(full, w_shard.detach(), group=pg)
+        torch.matmul(x.detach(), full)
+        full2 = torch.empty_like(full)
+        tdist.all_gather_into_tensor(full2, w_shard.detach(), group=pg)            # stage 3 re-gathers for backward
+        torch.matmul(dy, full2.t())
+        dwf = torch.matmul(x.detach().t(), dy)
+        dws = torch.empty(K // n, N, device="cuda", dtype=torch.bfloat16)
+        tdist.reduce_scatter_tensor(dws, dwf, group=pg)
+    with torch.no_grad():
+        rec["fused_fwd_us"] = timed(lambda: zero3_linear(x.detach(), w_shard.detach(), g))
+
+        def unfused_fwd():
+            full = torch.empty(K, N, device="cuda", dtype=torch.bfloat16)
+            tdist.all_gather_into_tensor(full, w_shard.detach(), group=pg)
+            torch.matmul(x.detach(), full)
+        rec["unfused_fwd_us"] = timed(unfused_fwd)
+    rec["fused_fwd_bwd_us"] = timed(fused_fb)
+    rec["unfused_fwd_bwd_us"] = timed(unfused_fb)
+    rec["compute_bound_fwd_bwd_us"] = 3 * rec["flop_fwd"] / 1644e6
+    emit(rec)
 
 
 if __name__ == "__main__":

@@ -463,6 +463,61 @@ class _LinearReduceScatter(torch.autograd.Function):
         return dx, dw, None
 
 
+class _LinearAllReduce(torch.autograd.Function):
+    """y[T, out] = all_reduce(x[T, in/n] @ W[in/n, out]) for a row-parallel layer WITHOUT sequence parallelism
+    (python/paddle/distributed/fleet/layers/mpu/mp_layers.py:715-732: matmul, then mp_allreduce).  Two-shot form: the
+    GEMM -> reduce-scatter kernel leaves every rank with the reduced rows it owns (partial tiles travel from inside the
+    GEMM's epilogue), and an all-gather of those slabs completes the all-reduce, so the reduction traffic overlaps the
+    GEMM and only the gather - half of an all-reduce's bytes - runs behind it.  Backward needs no communication: dY is
+    replicated, dX = dY W^T and dW = X^T dY are local GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight, group):
+        x = x.contiguous()
+        T, K = x.shape
+        n = group.nranks
+        rows, N = T // n, weight.shape[1]
+        slot = _slot("rs", group, rows, N)
+        y = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+        mine = y[group.rank * rows:(group.rank + 1) * rows]
+        gemm_rs(slot, group, x, weight, mine, T, N, K, 0, 1)
+        import torch.distributed as tdist
+        tdist.all_gather_into_tensor(y, mine, group=group.process_group)
+        ctx.save_for_backward(x, weight)
+        ctx.weight_ref = weight
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = native.gemm(dy, weight, trans_b=True)
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.weight_ref, "main_grad", None)
+            if mg is not None:
+                native.gemm(x, dy, trans_a=True, out=mg, accumulate=True)
+                hook = getattr(ctx.weight_ref, "_main_grad_ready_hook", None)
+                if hook is not None:
+                    hook(ctx.weight_ref)
+            else:
+                dw = native.gemm(x, dy, trans_a=True)
+        return dx, dw, None
+
+
+def linear_all_reduce_ok(x2d, weight, group):
+    """Shapes the fused row-parallel all-reduce takes: bf16 on the GPU, tokens divisible into 128-row slabs per rank,
+    16-byte rows."""
+    return (x2d.is_cuda and x2d.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and group is not None
+            and group.nranks in (2, 4, 8) and symm.supported() and x2d.shape[0] % (group.nranks * SUB_ROWS) == 0
+            and x2d.shape[1] % 8 == 0 and weight.shape[1] % 8 == 0 and os.environ.get("PD_FUSED_ROW_AR", "1") != "0")
+
+
+def linear_all_reduce(x, weight, group):
+    return as_tensor(_LinearAllReduce.apply(x, weight, group))
+
+
 def _shapes_ok(tokens_local_rows):
     return _ag_ok(tokens_local_rows)
 

@@ -60,6 +60,22 @@ for it in range(3):
     res["errs"][f"rs_y_{it}"] = rel(y2, ref_y2)
     res["errs"][f"rs_dx_{it}"] = rel(x2.grad, dyf @ w2.detach().float().t())
     res["errs"][f"rs_dw_{it}"] = rel(w2.grad, x2.detach().float().t() @ dyf)
+# ---- row-parallel layer without sequence parallelism: GEMM -> reduce-scatter kernel + gather = all-reduce, through the
+# public layer (RowParallelLinear with input_is_parallel), forward and backward against fp32
+from paddle_b200.distributed.fleet.layers.mpu.mp_layers import RowParallelLinear
+layer = RowParallelLinear(F * n, H, has_bias=False, input_is_parallel=True)
+layer.to(dtype="bfloat16")
+xr = (torch.randn(2, T // 2, F, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+wr = layer.weight
+assert FL.linear_all_reduce_ok(xr.reshape(-1, F), wr, g)
+yr = layer(xr)
+dyr = (torch.randn(2, T // 2, H, generator=torch.Generator(device="cuda").manual_seed(5), device="cuda") * 0.1).to(torch.bfloat16)
+yr.backward(dyr)
+fullr = xr.detach().float().reshape(-1, F) @ wr.detach().float()
+dist.all_reduce(fullr, group=g)
+res["errs"]["row_ar_y"] = rel(yr.reshape(-1, H), fullr)
+res["errs"]["row_ar_dx"] = rel(xr.grad.reshape(-1, F), dyr.float().reshape(-1, H) @ wr.detach().float().t())
+res["errs"]["row_ar_dw"] = rel(wr.grad, xr.detach().float().reshape(-1, F).t() @ dyr.float().reshape(-1, H))
 _lib.check_status()
 
 
