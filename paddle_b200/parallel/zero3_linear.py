@@ -94,10 +94,10 @@ class _WeightPrefetcher:
             self._issue(key)
         buf, ready = self.pending.pop(key)
         torch.cuda.current_stream().wait_event(ready)
-        if self.frozen and key in self.pos:
-            nxt = self.order[(self.pos[key] + 1) % len(self.order)]
-            if nxt != key:
-                self._issue(nxt)
+        # no wrap-around: between the last linear of one pass and the first of the next lie the backward pass and the
+        # optimizer update of the slices, so the first layer of a pass gathers on demand
+        if self.frozen and key in self.pos and self.pos[key] + 1 < len(self.order):
+            self._issue(self.order[self.pos[key] + 1])
         return buf
 
     def give_back(self, buf):
