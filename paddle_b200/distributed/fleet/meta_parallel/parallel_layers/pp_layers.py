@@ -98,13 +98,15 @@ class PipelineLayerChunk(Layer):
 
 class PipelineLayer(Layer):
     def __init__(self, layers, num_stages=None, topology=None, loss_fn=None, seg_method="uniform", recompute_interval=0,
-                 recompute_ctx=None, num_virtual_pipeline_stages=None):
+                 recompute_ctx=None, num_virtual_pipeline_stages=None, virtual_placement="interleaved"):
         super().__init__()
         from ... import fleet
         self._layers_desc = list(layers)
         self._loss_fn = loss_fn
         self._recompute_interval = recompute_interval
         self._num_virtual = num_virtual_pipeline_stages or 1
+        assert virtual_placement in ("interleaved", "zigzag")
+        self._virtual_placement = virtual_placement
         hcg = fleet.get_hybrid_communicate_group() if topology is None else None
         if hcg is not None:
             self._num_stages = hcg.get_pipe_parallel_world_size()
@@ -126,7 +128,11 @@ class PipelineLayer(Layer):
         self.run_function = []
         if self._num_virtual > 1:
             for chunk in range(self._num_virtual):
-                part = chunk * self._num_stages + self._stage_id
+                # interleaved: chunk c of stage r is segment c * P + r; zigzag (zero-bubble V schedules): odd chunks
+                # run down the ranks, so with two chunks stage r holds segments r and 2P - 1 - r
+                pos = self._stage_id if (virtual_placement == "interleaved" or chunk % 2 == 0) \
+                    else self._num_stages - 1 - self._stage_id
+                part = chunk * self._num_stages + pos
                 lo, hi = self.segment_parts[part], self.segment_parts[part + 1]
                 ch = PipelineLayerChunk()
                 for f in self._build(lo, hi):
@@ -200,7 +206,10 @@ class PipelineLayer(Layer):
     def get_stage_from_index(self, layer_idx):
         for part in range(len(self.segment_parts) - 1):
             if self.segment_parts[part] <= layer_idx < self.segment_parts[part + 1]:
-                return part % self._num_stages
+                chunk, pos = divmod(part, self._num_stages)
+                if self._virtual_placement == "zigzag" and chunk % 2 == 1:
+                    return self._num_stages - 1 - pos
+                return pos
         raise IndexError(layer_idx)
 
     def get_num_virtual_stages(self):

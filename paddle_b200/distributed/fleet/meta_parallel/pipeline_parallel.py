@@ -253,16 +253,25 @@ class PipelineParallel(MetaParallelBase):
             self._layers.allreduce_shared_weight_gradients()
         return self._broadcast_final_loss()
 
+    def _loss_stage(self):
+        """Pipeline stage that holds the last virtual stage (and so the loss): the last one, except under a zigzag
+        placement with an even number of chunks, where the model ends on the first stage."""
+        ex = getattr(self, "_executor", None)
+        if ex is not None:
+            return ex.place.owner(ex.P * ex.V - 1)[0]
+        return self.num_stages - 1
+
     def _broadcast_final_loss(self):
         g = self._hcg.get_pipe_parallel_group()
         from ...._core.dtype import default_device
-        if self.is_last_stage:
+        holder = self._loss_stage()
+        if self.stage_id == holder:
             loss = self.total_loss.float().reshape(1).clone()
             if self._delay_scale_loss:
                 loss = loss / self.accumulate_steps
         else:
             loss = torch.zeros(1, dtype=torch.float32, device=default_device())
-        last = self._hcg.get_rank_from_stage(self.num_stages - 1)
+        last = self._hcg.get_rank_from_stage(holder)
         C.broadcast(loss, last, g)
         return as_tensor(loss.reshape([]))
 

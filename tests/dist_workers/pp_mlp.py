@@ -1,6 +1,7 @@
 """Pipeline parallel vs single-rank twin (pattern of test/collective/fleet/hybrid_parallel_pp_layer.py and
 hybrid_parallel_shared_weight.py): the same stack of layers, built from one seed, trained for three steps
-with 1F1B (argv[1] == "1f1b"), interleaved virtual stages ("vpp") or the zero-bubble H1 order ("zbh1"); dumps per-step losses of
+with 1F1B (argv[1] == "1f1b"), interleaved virtual stages ("vpp"), the zero-bubble H1 order ("zbh1") or the zero-bubble V
+schedule over a zigzag placement ("zbvpp"); dumps per-step losses of
 both and the final parameters of this stage next to the twin's."""
 import os
 import sys
@@ -22,6 +23,8 @@ strategy.hybrid_configs = {"dp_degree": 1, "mp_degree": 1, "pp_degree": n}
 strategy.pipeline_configs = {"accumulate_steps": ACC, "micro_batch_size": MB}
 if mode == "zbh1":          # zero-bubble H1: weight gradients of the first backwards are postponed to the end
     strategy.pipeline_configs["schedule_mode"] = "ZBH1"
+if mode == "zbvpp":         # zero-bubble V: two chunks per rank in zigzag placement, Bx / W split
+    strategy.pipeline_configs["schedule_mode"] = "ZBVPP"
 fleet.init(is_collective=True, strategy=strategy)
 rank = dist.get_rank()
 
@@ -53,7 +56,8 @@ def loss_fn(logits, labels):
 
 
 descs = [SharedLayerDesc("emb", Emb)] + [LayerDesc(Block) for _ in range(6)] + [SharedLayerDesc("emb", Emb, forward_func=head)]
-V = 2 if mode == "vpp" else None
+V = 2 if mode in ("vpp", "zbvpp") else None
+placement = "zigzag" if mode == "zbvpp" else "interleaved"
 paddle.seed(11)
 # twin: all layers on this rank, built in description order from the same seed
 twin_layers = []
@@ -65,13 +69,13 @@ for d in descs:
         twin_layers.append((shared[d.layer_name], d.forward_func))
     else:
         twin_layers.append((d.build_layer(), None))
-pipe = PipelineLayer(descs, loss_fn=loss_fn, num_virtual_pipeline_stages=V)
+pipe = PipelineLayer(descs, loss_fn=loss_fn, num_virtual_pipeline_stages=V, virtual_placement=placement)
 # copy the twin's weights into the stage-local layers
 parts = pipe.segment_parts
 with torch.no_grad():
     if V:
         for c, chunk in enumerate(pipe.get_model_chunks()):
-            lo = parts[c * n + rank]
+            lo = parts[c * n + (rank if (placement == "interleaved" or c % 2 == 0) else n - 1 - rank)]
             for i, f in enumerate(chunk.run_function):
                 src = twin_layers[lo + i][0]
                 if isinstance(f, nn.Layer):

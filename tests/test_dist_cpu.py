@@ -61,7 +61,7 @@ def test_mp2_sharding2_split_param_clip_parity_cpu():
         assert r["opt_keys_ok"] and r["moment_shape_ok"] and r["n_buckets"] > 1
 
 
-@pytest.mark.parametrize("mode", ["1f1b", "vpp", "zbh1"])
+@pytest.mark.parametrize("mode", ["1f1b", "vpp", "zbh1", "zbvpp"])
 def test_pipeline_parallel_parity_cpu(mode):
     """2 pipeline stages (1F1B, and 2 virtual chunks per stage over the ring) with a weight tied between the
     first and the last layer: losses and updated weights equal the single-process twin."""

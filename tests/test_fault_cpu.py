@@ -356,3 +356,31 @@ def test_native_process_group_task_timeout_error_and_abort(tmp_path):
         peer.all_reduce(x)
     assert peer.aborted
     peer.destroy(), pg2.destroy()
+
+
+def test_zero_bubble_v_schedule_properties():
+    """The zero-bubble V schedule: valid for every (P, M) tried (no deadlock, every Bx has its W), every rank runs
+    each of its 2 M forwards / input-gradient halves / weight-gradient halves exactly once, its makespan stays within
+    P + 3 units of the bubble-free 6 M and below interleaved 1F1B with the same two chunks, and the placement is the V."""
+    from paddle_b200.distributed.fleet.meta_parallel import pipeline_schedules as S
+    place = S.Placement(4, 2, "zigzag")
+    assert [place.vs(0, r) for r in range(4)] == [0, 1, 2, 3] and [place.vs(1, r) for r in range(4)] == [7, 6, 5, 4]
+    assert all(place.owner(place.vs(c, r)) == (r, c) for c in range(2) for r in range(4))
+    for P, M in ((2, 2), (2, 4), (3, 6), (4, 4), (4, 8), (8, 8), (8, 16)):
+        span = S.validate(S.zero_bubble_v, P, 2, M)
+        assert span <= 6 * M + P + 3, (P, M, span)
+        assert span < S.validate(S.interleaved_1f1b, P, 2, M) if M % P == 0 else True
+        for r in range(P):
+            steps = S.zero_bubble_v(P, 2, M, r)
+            for kind in ("F", "Bx", "W"):
+                got = sorted((c, m) for k, c, m in steps if k == kind)
+                assert got == sorted((c, m) for c in range(2) for m in range(M)), (P, M, r, kind)
+            # memory: bounded independently of M - at most 3 P chunk activations alive on a rank (first-chunk forwards
+            # stop at 2 P, second-chunk forwards are never held back)
+            alive = peak = 0
+            for k, _, _ in steps:
+                alive += 1 if k == "F" else (-1 if k == "W" else 0)
+                peak = max(peak, alive)
+            assert peak <= 3 * P, (P, M, r, peak)
+    with pytest.raises(ValueError):
+        S.zero_bubble_v(4, 3, 8, 0)
