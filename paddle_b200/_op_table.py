@@ -696,6 +696,11 @@ def resolve(name):
     g = globals()
     if name in g and callable(g[name]) and not name.startswith("_"):
         return g[name]
+    if not name.startswith("_"):
+        from . import _op_table_more
+        fn = getattr(_op_table_more, name, None)
+        if callable(fn) and getattr(fn, "__module__", "") == _op_table_more.__name__:
+            return fn
     path = ALIASES.get(name)
     if path is not None:
         mod, _, attr = path.rpartition(".")

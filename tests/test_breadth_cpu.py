@@ -557,8 +557,8 @@ def test_c_ops_registry_coverage_and_kernel_level_semantics():
             (not_built if getattr(f, "not_built", None) else built).append(n)
         except AttributeError:
             missing.append(n)
-    assert len(built) >= 0.77 * len(names), (len(built), len(names))
-    assert len(missing) <= 0.09 * len(names), missing
+    assert len(built) >= 0.84 * len(names), (len(built), len(names))
+    assert len(missing) <= 0.02 * len(names), missing
     with pytest.raises(NotImplementedError, match="XPU"):
         _C_ops.fc_xpu()
     # functional AdamW against the closed form (adamw_kernel.cu: decoupled decay, bias correction from the beta powers)
@@ -632,3 +632,59 @@ def test_flashmask_bounds_normalisation_matches_dense_mask():
     w = _flashmask_dense(_window_bounds(None, (9, 30), False, 1, S, S, "cpu"), S, S, False, "cpu")[0, 0]
     i, j = torch.meshgrid(torch.arange(S), torch.arange(S), indexing="ij")
     assert torch.equal(~w, (j >= i - 9) & (j <= i + 30))
+
+
+def test_c_ops_quantisation_optimizer_and_misc_kernel_ops():
+    """Kernel-level operators of the third registry tier against their defining formulas."""
+    import math
+
+    import torch
+
+    from paddle_b200 import _C_ops
+    torch.manual_seed(0)
+    x = torch.randn(5, 7)
+    q, s = _C_ops.fake_quantize_abs_max(x, 8, 1)
+    assert float(s) == float(x.abs().max()) and float(q.abs().max()) == 127.0
+    assert torch.allclose(q * s / 127, x, atol=float(s) / 127)
+    qd, sc = _C_ops.fake_channel_wise_quantize_dequantize_abs_max(x, 8, 1, 0)
+    assert torch.allclose(sc, x.abs().amax(1)) and torch.allclose(qd, x, atol=float(x.abs().max()) / 127)
+    assert torch.allclose(_C_ops.fake_dequantize_max_abs(q, s, 127.0), q * s / 127)
+    _, ms, st, ac = _C_ops.fake_quantize_moving_average_abs_max(x, torch.ones(1), torch.zeros(1), torch.zeros(1), 0.9)
+    assert torch.allclose(ms, x.abs().max().reshape(1)) and float(st) == 1.0 and torch.allclose(ac, x.abs().max().reshape(1))
+    # optimizers: one step against the closed forms
+    g = torch.tensor([0.1, -0.2, 0.3])
+    p, d, y = torch.ones(3), torch.zeros(3), torch.zeros(3)
+    _C_ops.asgd_(p, g, torch.tensor(0.5), d, y, torch.tensor(2.0))
+    assert torch.allclose(p, 1 - 0.25 * g) and torch.allclose(d, g) and torch.allclose(y, g)
+    p, prev, lr = torch.ones(3), torch.tensor([0.1, 0.2, -0.3]), torch.full((3,), 0.01)
+    _C_ops.rprop_(p, g, prev, lr, None, torch.tensor([1e-5, 50.0]), torch.tensor([0.5, 1.2]))
+    assert torch.allclose(lr, torch.tensor([0.012, 0.005, 0.005]))
+    assert torch.allclose(p, torch.tensor([1 - 0.012, 1.0, 1.0])) and torch.allclose(prev, torch.tensor([0.1, 0.0, 0.0]))
+    p = torch.ones(3)
+    m1, m2, b1p, b2p, rho = torch.zeros(3), torch.zeros(3), torch.ones(1), torch.ones(1), torch.zeros(1)
+    _C_ops.radam_(p, g, torch.tensor(0.1), b1p, b2p, rho, m1, m2)
+    assert torch.allclose(p, 1 - 0.1 * g, atol=1e-6) and abs(float(rho) - 1.0) < 1e-3     # rho_1 = 1: not yet rectified
+    newp, newm = _C_ops.decayed_adagrad(torch.ones(3), g, torch.zeros(3), torch.tensor([0.1]), 0.95, 1e-6)
+    assert torch.allclose(newm, 0.05 * g * g) and torch.allclose(newp, 1 - 0.1 * g / (newm.sqrt() + 1e-6))
+    # assorted
+    dist, cnt = _C_ops.edit_distance(torch.tensor([[1, 2, 3, 4], [5, 6, 0, 0]]), torch.tensor([[1, 3, 4, 0], [7, 6, 5, 0]]),
+                                     torch.tensor([4, 2]), torch.tensor([3, 3]))
+    assert dist.reshape(-1).tolist() == [1.0, 2.0] and int(cnt) == 2
+    boxes = torch.tensor([[[-5.0, 3.0, 120.0, 70.0]]])
+    assert _C_ops.box_clip(boxes, torch.tensor([[60.0, 100.0, 1.0]])).reshape(-1).tolist() == [0.0, 3.0, 99.0, 59.0]
+    h, xin, w = torch.randn(2, 4), torch.randn(2, 12), torch.randn(4, 12)
+    gate, rh, nh = _C_ops.gru_unit(xin, h, w)
+    u = torch.sigmoid(xin[:, :4] + h @ w[:, :4])
+    r = torch.sigmoid(xin[:, 4:8] + h @ w[:, 4:8])
+    c = torch.tanh(xin[:, 8:] + (r * h) @ w[:, 8:])
+    assert torch.allclose(nh, (1 - u) * h + u * c, atol=1e-6) and torch.allclose(rh, r * h)
+    outs, flat = _C_ops.coalesce_tensor([torch.ones(3), torch.full((2, 2), 2.0)], copy_data=True)
+    assert float(outs[0].sum()) == 3.0 and float(outs[1].sum()) == 8.0 and outs[1].data_ptr() == flat[64:].data_ptr()
+    rows, vals = _C_ops.merge_selected_rows((torch.tensor([3, 1, 3]), torch.tensor([[1.0], [2.0], [5.0]])))
+    assert rows.tolist() == [1, 3] and vals.reshape(-1).tolist() == [2.0, 6.0]
+    o, inter = _C_ops.fused_elemwise_activation(torch.tensor([1.0, -2.0]), torch.tensor([0.5, 0.5]), ["relu", "elementwise_add"])
+    assert o.tolist() == [1.5, 0.0] and inter.tolist() == [1.5, -1.5]
+    pe = _C_ops.add_position_encoding(torch.zeros(1, 3, 4), 1.0, 1.0)
+    assert torch.allclose(pe[0, :, 0], torch.sin(torch.arange(3.0))) and torch.allclose(pe[0, :, 2], torch.cos(torch.arange(3.0)))
+    idx, dd = _C_ops.bipartite_match(torch.tensor([[0.9, 0.2], [0.3, 0.8], [0.1, 0.7]]))
+    assert idx.reshape(-1).tolist() == [0, 1] and torch.allclose(dd.reshape(-1), torch.tensor([0.9, 0.8]))
