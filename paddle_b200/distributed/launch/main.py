@@ -49,6 +49,7 @@ def parse_args(argv=None):
     p.add_argument("--host", default=env.get("POD_IP", "127.0.0.1"))
     p.add_argument("--backend", default=env.get("PADDLE_DISTRI_BACKEND"))
     p.add_argument("--poll_interval", type=float, default=0.5)
+    p.add_argument("--auto_tuner_json", default=None, help="search hybrid-parallel configurations described by this JSON / YAML file")
     p.add_argument("training_script")
     p.add_argument("training_script_args", nargs=argparse.REMAINDER)
     return p.parse_args(argv)
@@ -240,6 +241,12 @@ class CollectiveController:
 
 def launch(argv=None):
     args = parse_args(argv)
+    if args.auto_tuner_json:
+        from .auto_tune import run_auto_tuner
+        code = run_auto_tuner(args)
+        if code:
+            sys.exit(code)
+        return
     ctl = CollectiveController(args)
 
     def on_signal(signum, frame):
