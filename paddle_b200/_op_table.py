@@ -697,10 +697,11 @@ def resolve(name):
     if name in g and callable(g[name]) and not name.startswith("_"):
         return g[name]
     if not name.startswith("_"):
-        from . import _op_table_more
-        fn = getattr(_op_table_more, name, None)
-        if callable(fn) and getattr(fn, "__module__", "") == _op_table_more.__name__:
-            return fn
+        from . import _op_table_more, _op_table_seq
+        for tier in (_op_table_more, _op_table_seq):
+            fn = getattr(tier, name, None)
+            if callable(fn) and getattr(fn, "__module__", "") == tier.__name__:
+                return fn
     path = ALIASES.get(name)
     if path is not None:
         mod, _, attr = path.rpartition(".")

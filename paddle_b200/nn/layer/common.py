@@ -773,9 +773,37 @@ class _RNNBase(Layer):
         self._names = [n for n, _ in self._impl.named_parameters()]
 
     def forward(self, inputs, initial_states=None, sequence_length=None):
+        if sequence_length is not None:
+            return self._forward_lengths(inputs, initial_states, sequence_length)
         params = {n: self._parameters[n] for n in self._names}
         out, st = torch.func.functional_call(self._impl, params, (inputs, initial_states))
         return out, st
+
+    def _forward_lengths(self, inputs, initial_states, sequence_length):
+        """Padded steps leave the state untouched and give zero output (python/paddle/nn/layer/rnn.py:1560-1640):
+        the stepped form of the ``rnn`` operator."""
+        from ..._op_table_seq import rnn
+        impl = self._impl
+        dirs = 2 if impl.bidirectional else 1
+        x = inputs if not impl.batch_first else inputs.transpose([1, 0, 2])
+        B = x.shape[1]
+        mode = {"LSTM": "LSTM", "GRU": "GRU", "RNN": "RNN_TANH" if getattr(impl, "nonlinearity", "tanh") == "tanh" else "RNN_RELU"}[self._mode]
+        if initial_states is None:
+            z = torch.zeros(impl.num_layers * dirs, B, impl.hidden_size, dtype=x.dtype, device=x.device)
+            initial_states = (z, z.clone()) if mode == "LSTM" else z
+        states = list(initial_states) if isinstance(initial_states, (list, tuple)) else [initial_states]
+        sfx = [""] + (["_reverse"] if dirs == 2 else [])
+        mats, biases = [], []
+        for layer in range(impl.num_layers):
+            for s in sfx:
+                mats += [self._parameters[f"weight_ih_l{layer}{s}"], self._parameters[f"weight_hh_l{layer}{s}"]]
+                if impl.bias:
+                    biases += [self._parameters[f"bias_ih_l{layer}{s}"], self._parameters[f"bias_hh_l{layer}{s}"]]
+        out, _, final, _ = rnn(x, states, mats + biases, sequence_length, None, impl.dropout, impl.bidirectional, impl.input_size,
+                               impl.hidden_size, impl.num_layers, mode, 0, not self.training)
+        if impl.batch_first:
+            out = out.transpose([1, 0, 2])
+        return out, (tuple(final) if mode == "LSTM" else final[0])
 
 
 class LSTM(_RNNBase):
