@@ -157,9 +157,29 @@ class DataLoader:
 
     def __iter__(self):
         from .._core.dtype import default_device
+        from ..profiler.timer import benchmark
+        from ..profiler.utils import RecordEvent, in_profiler_mode
+        from ..profiler.profiler_statistic import TracerEventType
         dev = default_device()
-        for batch in self._loader:
-            yield _move(batch, dev)
+        bench = benchmark()
+        bench.check_if_need_record(self)
+        it = iter(self._loader)
+        while True:
+            # reader cost of the throughput timer, and a Dataloader range in a running profile
+            bench.before_reader()
+            rng = RecordEvent("Dataloader#next", TracerEventType.Dataloader) if in_profiler_mode() else None
+            if rng is not None:
+                rng.begin()
+            try:
+                batch = next(it)
+            except StopIteration:
+                return
+            finally:
+                if rng is not None:
+                    rng.end()
+            batch = _move(batch, dev)
+            bench.after_reader()
+            yield batch
 
     def __len__(self):
         return len(self._loader)
