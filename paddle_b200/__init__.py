@@ -207,6 +207,10 @@ _LAZY_SUBMODULES = {
 }
 
 
+# flags given as FLAGS_<name> environment variables act like set_flags at import
+from .framework import flags as _flags_mod  # noqa: E402
+_flags_mod._apply_env_effects()
+
 def __getattr__(name):
     if name in _LAZY_SUBMODULES:
         import importlib

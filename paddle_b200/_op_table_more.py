@@ -457,8 +457,14 @@ def data(name, shape, dtype="float32", place=None):
     return static.data(name, shape, dtype)
 
 
-def accuracy_check(x, y, fn_name="", rtol=1e-5, atol=1e-8, equal_nan=False):
-    """Raises when ``x`` and ``y`` differ beyond the tolerances; returns a boolean tensor otherwise."""
+def accuracy_check(x, y, fn_name="", rtol=None, atol=None, equal_nan=False):
+    """Raises when ``x`` and ``y`` differ beyond the tolerances; returns a boolean tensor otherwise.  Tolerances left
+    unset come from ``FLAGS_accuracy_check_{atol,rtol}_{fp32,fp16,bf16}`` by the dtype of ``x``."""
+    if rtol is None or atol is None:
+        from .framework.flags import flag
+        kind = {torch.float16: "fp16", torch.bfloat16: "bf16"}.get(_t(x).dtype, "fp32")
+        rtol = flag(f"accuracy_check_rtol_{kind}") if rtol is None else rtol
+        atol = flag(f"accuracy_check_atol_{kind}") if atol is None else atol
     ok = torch.allclose(_t(x).float(), _t(y).float(), rtol=rtol, atol=atol, equal_nan=equal_nan)
     if not ok:
         diff = (_t(x).float() - _t(y).float()).abs().max().item()

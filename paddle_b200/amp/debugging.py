@@ -27,11 +27,28 @@ def check_numerics(tensor, op_type="", var_name="", debug_mode=DebugMode.CHECK_N
 
 
 class _NanInfMode(TorchDispatchMode):
+    """Checks every operator output.  ``CHECK_NAN_INF_AND_ABORT`` raises at the first NaN / Inf; the other modes print
+    one line per offending operator and go on; ``checked_op_list`` / ``skipped_op_list`` filter by operator name."""
+
+    def __init__(self, config=None):
+        super().__init__()
+        self.debug_mode = getattr(config, "debug_mode", DebugMode.CHECK_NAN_INF_AND_ABORT)
+        self.checked = set(getattr(config, "checked_op_list", None) or [])
+        self.skipped = set(getattr(config, "skipped_op_list", None) or [])
+        self.found = []
+
     def __torch_dispatch__(self, func, types, args=(), kwargs=None):
         out = func(*args, **(kwargs or {}))
+        name = str(getattr(func, "overloadpacket", func)).split(".")[-1]
+        if (self.checked and name not in self.checked) or name in self.skipped:
+            return out
         for o in (out if isinstance(out, (tuple, list)) else (out,)):
             if isinstance(o, torch.Tensor) and o.is_floating_point() and o.numel() and not bool(torch.isfinite(o).all()):
-                raise RuntimeError(f"nan/inf produced by {func}")
+                if self.debug_mode == DebugMode.CHECK_NAN_INF_AND_ABORT:
+                    raise RuntimeError(f"nan/inf produced by {func}")
+                n_nan, n_inf = int(torch.isnan(o).sum()), int(torch.isinf(o).sum())
+                self.found.append((name, n_nan, n_inf))
+                print(f"[tensor checker] {func}: {n_nan} nan, {n_inf} inf in an output of shape {list(o.shape)}")
         return out
 
 
@@ -52,7 +69,10 @@ _modes = {}
 
 
 def enable_tensor_checker(checker_config=None):
-    m = _NanInfMode()
+    if checker_config is not None and not getattr(checker_config, "enable", True):
+        return
+    disable_tensor_checker()
+    m = _NanInfMode(checker_config)
     m.__enter__()
     _modes["nan"] = m
 
@@ -67,6 +87,8 @@ class TensorCheckerConfig:
     def __init__(self, enable=True, debug_mode=DebugMode.CHECK_NAN_INF_AND_ABORT, output_dir=None,
                  checked_op_list=None, skipped_op_list=None, debug_step=None, stack_height_limit=1):
         self.enable, self.debug_mode = enable, debug_mode
+        self.output_dir, self.checked_op_list, self.skipped_op_list = output_dir, checked_op_list, skipped_op_list
+        self.debug_step, self.stack_height_limit = debug_step, stack_height_limit
 
 
 def enable_operator_stats_collection():

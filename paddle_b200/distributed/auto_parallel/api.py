@@ -321,7 +321,8 @@ def moe_sub_mesh_tensors(dist_tensor, global_mesh=None, local_mesh_dim=-1, globa
 
 def in_auto_parallel_align_mode():
     import os
-    return os.environ.get("FLAGS_enable_auto_parallel_align_mode", "0").lower() in ("1", "true")
+    from ...framework.flags import flag
+    return bool(flag("enable_auto_parallel_align_mode"))
 
 
 class FusePasses:

@@ -5,6 +5,7 @@ from ..pipeline_parallel import P2pHelper, SendRecvMeta  # noqa: F401
 import torch
 
 from .... import collective as _C
+from .....framework.flags import flag as _flag
 
 _hcg = None
 _enable_partial_send_recv = True
@@ -54,9 +55,11 @@ def batch_send_recv_on_calc_stream(p2p_op_list):
     ranks that send to each other cannot deadlock; with ``FLAGS_pp_check_naninf`` set, tensors to send are checked
     for inf / nan first (p2p_communication.py:286)."""
     import os
+
+from .....framework.flags import flag as _flag
     if not p2p_op_list:
         return
-    if os.getenv("FLAGS_pp_check_naninf", "0").lower() in ("1", "true", "yes"):
+    if _flag("pp_check_naninf"):
         for o in p2p_op_list:
             if o.is_send and o.tensor.is_floating_point() and not bool(torch.isfinite(o.tensor).all()):
                 raise ValueError(f"Tensor contains inf or nan values at rank {_C.get_rank()}")

@@ -75,6 +75,11 @@ def init_parallel_env(backend=None):
     world = tdist.get_world_size()
     g = C.Group(tdist.get_rank(), 0, list(range(world)), tdist.group.WORLD, name="_default_pg")
     C._set_default_group(g)
+    from ..framework.flags import flag
+    if flag("enable_async_trace"):
+        from . import watchdog
+        if not watchdog.enabled():
+            watchdog.start(timeout_s=env.pg_timeout / 1000.0)
     return g
 
 

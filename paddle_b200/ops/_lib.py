@@ -94,6 +94,10 @@ def runtime() -> ctypes.CDLL:
                     _runtime = _load(f"libpd_runtime_{san}.so", "build_runtime")
                 else:
                     _runtime = _load("libpd_runtime.so", "build_runtime")
+                _runtime.pd_flag_set.argtypes = [ctypes.c_char_p, ctypes.c_char_p]
+                _runtime.pd_flag_set.restype = None
+                from ..framework import flags as _flags
+                _flags.sync_native()
     return _runtime
 
 
@@ -127,6 +131,15 @@ def check(rc: int, what: str):
         from ..framework import errors
         cls = errors.LAUNCH_ERROR_CLASSES.get(rc, errors.LaunchExternal)
         raise cls(f"{what}: native launcher returned {rc} ({_LAUNCH_ERRORS.get(rc, 'unknown')})")
+    if _sync_launches[0]:
+        # FLAGS_benchmark / FLAGS_check_kernel_launch: wait for the kernel and surface its status word at the call site
+        if torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+            torch.cuda.synchronize()
+            check_status()
+
+
+# switched by framework.flags when FLAGS_benchmark or FLAGS_check_kernel_launch changes
+_sync_launches = [False]
 
 
 # One 4-int status word per device: {code, block, site, detail}; written by kernels whose bounded

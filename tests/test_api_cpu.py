@@ -246,3 +246,75 @@ def test_typed_errors_follow_the_reference_mapping():
     with pytest.raises(errors.PreconditionNotMetError):
         errors.enforce(False, message="state")
     errors.enforce(True)
+
+
+def test_flag_registry_covers_the_reference_and_effects_apply(tmp_path):
+    """Every flag the reference exports is registered with a type, a kind and a note; ``set_flags`` converts and
+    checks types, runs the effect handlers and mirrors values into the native runtime."""
+    import re
+    import subprocess
+    import sys
+
+    import torch
+
+    from paddle_b200.framework import flags as F
+    info = F.flag_info()
+    assert len(info) >= 185 and all(v["kind"] in ("effect", "read", "inert") for v in info.values())
+    assert all(v["note"] for v in info.values() if v["kind"] == "inert")
+    ref = "/root/reference/paddle/common/flags.cc"
+    if os.path.exists(ref):
+        names = set(re.findall(r"PHI_DEFINE_EXPORTED_\w+\(\s*(?://[^\n]*\n\s*)?(\w+)\s*,", open(ref).read()))
+        assert len(names) > 150 and not {n for n in names if "FLAGS_" + n not in info}
+    # conversion and type checks
+    paddle.set_flags({"FLAGS_cudnn_exhaustive_search": "true", "paddle_num_threads": 2, "FLAGS_fraction_of_gpu_memory_to_use": 1})
+    assert torch.backends.cudnn.benchmark is True and torch.get_num_threads() == 2
+    assert paddle.get_flags("FLAGS_fraction_of_gpu_memory_to_use")["FLAGS_fraction_of_gpu_memory_to_use"] == 1.0
+    paddle.set_flags({"FLAGS_cudnn_exhaustive_search": False})
+    with pytest.raises(TypeError):
+        paddle.set_flags({"FLAGS_paddle_num_threads": 1.5})
+    with pytest.raises(TypeError):
+        paddle.set_flags({"FLAGS_check_nan_inf": "yes" and [1]})
+    # tensor checker level: 1 = report and continue
+    paddle.set_flags({"FLAGS_check_nan_inf_level": 1, "FLAGS_check_nan_inf": True})
+    try:
+        out = paddle.to_tensor([1.0, 0.0]) / paddle.to_tensor([0.0, 0.0])
+        assert not bool(torch.isfinite(out).all())
+    finally:
+        paddle.set_flags({"FLAGS_check_nan_inf": False, "FLAGS_check_nan_inf_level": 0})
+    paddle.set_flags({"FLAGS_check_nan_inf": True})
+    try:
+        with pytest.raises(RuntimeError, match="nan/inf"):
+            paddle.to_tensor([1.0]) / paddle.to_tensor([0.0])
+    finally:
+        paddle.set_flags({"FLAGS_check_nan_inf": False})
+    # accuracy_check reads its default tolerances from the flags
+    from paddle_b200 import _C_ops
+    a = paddle.ones([4])
+    with pytest.raises(AssertionError):
+        _C_ops.accuracy_check(a, a + 1e-4, "f")
+    paddle.set_flags({"FLAGS_accuracy_check_atol_fp32": 1e-3})
+    try:
+        assert bool(_C_ops.accuracy_check(a, a + 1e-4, "f"))
+    finally:
+        paddle.set_flags({"FLAGS_accuracy_check_atol_fp32": 1e-6})
+    # native mirror
+    from paddle_b200.ops import _lib
+    import ctypes
+    rt = _lib.runtime()
+    paddle.set_flags({"FLAGS_async_trace_count": 9})
+    buf = ctypes.create_string_buffer(32)
+    assert rt.pd_flag_get(b"FLAGS_async_trace_count", buf, 32) == 1 and buf.value == b"9"
+    paddle.set_flags({"FLAGS_async_trace_count": 5})
+    # the API tracer through FLAGS_trace_api, and flags from the environment acting at import
+    apis = tmp_path / "apis.txt"
+    apis.write_text("paddle.nn.functional.relu\n")
+    paddle.set_flags({"FLAGS_trace_api": f"{apis},{tmp_path / 'trace.txt'}"})
+    try:
+        paddle.nn.functional.relu(paddle.to_tensor([-1.0, 1.0]))
+    finally:
+        paddle.set_flags({"FLAGS_trace_api": ""})
+    assert "relu(" in (tmp_path / "trace.txt").read_text()
+    code = "import torch, paddle_b200; print(torch.backends.cudnn.deterministic, paddle_b200.get_flags('FLAGS_use_autotune'))"
+    env = dict(os.environ, FLAGS_cudnn_deterministic="1", FLAGS_use_autotune="true", PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120).stdout
+    assert out.strip() == "True {'FLAGS_use_autotune': True}"
