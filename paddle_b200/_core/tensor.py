@@ -227,11 +227,11 @@ class Tensor(torch.Tensor):
     def split(self, num_or_sections, axis=0, dim=None):
         axis = axis if dim is None else dim
         if isinstance(num_or_sections, int):
-            n = torch.Tensor.size(self, axis)
+            n = self.shape[axis]                       # the global size for a distributed tensor
             return list(torch.Tensor.split(self, n // num_or_sections, axis))
         secs = list(num_or_sections)
         if -1 in secs:
-            n = torch.Tensor.size(self, axis)
+            n = self.shape[axis]
             secs[secs.index(-1)] = n - (sum(secs) + 1)
         return list(torch.Tensor.split(self, secs, axis))
 

@@ -585,7 +585,195 @@ def _dispatch(func, args, kwargs):
     if name in ("__getitem__", "__setitem__", "__repr__", "__str__", "item", "tolist", "numpy", "__bool__", "__float__",
                 "__int__", "allclose", "equal"):
         return _fallback(func, args, kwargs, mesh) if name == "__getitem__" else _run_on_full(func, args, kwargs, mesh)
+    out = _rule_dispatch(name, func, args, kwargs, mesh)
+    if out is not NotImplemented:
+        return out
     return _fallback(func, args, kwargs, mesh)
+
+
+# --------------------------------------------------------------------------- operators driven by the SPMD rule registry
+def _spec_of(t, mesh):
+    from .spmd_rules import DistTensorSpec
+    if not is_dist(t):
+        return DistTensorSpec(list(t.shape), [-1] * t.dim())
+    dm = [-1] * len(t.shape)
+    for a, p in enumerate(t._dist_placements):
+        if p.is_shard():
+            dm[p.dim] = a
+    return DistTensorSpec(list(t.shape), dm)
+
+
+def _placements_of(sp, mesh):
+    pl = [Replicate()] * mesh.ndim
+    for d, a in enumerate(sp.dims_mapping):
+        if a != -1:
+            pl[a] = Shard(d)
+    for a in sp.partial_dims:
+        pl[a] = Partial()
+    return pl
+
+
+def _by_rule(rule_name, tensors, attrs, mesh, call, list_input=False, rule_kwargs=None):
+    """Run ``call(local tensors)`` with the inputs re-sharded as the rule ``rule_name`` asks and wrap the result(s) with the
+    placements it infers.  ``tensors``: the tensor inputs in the rule's order (``None`` entries are passed through)."""
+    from .spmd_rules import get_phi_spmd_rule
+    rep = [Replicate()] * mesh.ndim
+    dts = []
+    for t in tensors:
+        if t is None:
+            dts.append(None)
+            continue
+        d = t if is_dist(t) else DistTensor.wrap(_plain(t), mesh, rep)
+        if any(p.is_partial() for p in d._dist_placements):
+            d = reshard(d, mesh, [Replicate() if p.is_partial() else p for p in d._dist_placements])
+        dts.append(d)
+    specs = [None if d is None else _spec_of(d, mesh) for d in dts]
+    rule = get_phi_spmd_rule(rule_name)
+    new_in, outs = rule.infer_forward(specs, *attrs, **(rule_kwargs or {})) if list_input else \
+        rule.infer_forward(*specs, *attrs, **(rule_kwargs or {}))
+    if list_input:
+        new_in = new_in[0]
+    flat_outs = outs[0] if (outs and isinstance(outs[0], list)) else outs
+    ref_pl = _placements_of(flat_outs[0], mesh) if flat_outs else rep
+    it = iter(new_in)
+    locals_ = []
+    for d in dts:
+        if d is None:
+            locals_.append(None)
+            continue
+        want = _placements_of(next(it), mesh)
+        d = reshard(d, mesh, want)
+        locals_.append(_guard_replicated_inputs(local_of(d), mesh, want, ref_pl))
+    with torch._C.DisableTorchFunctionSubclass():
+        out = call(locals_)
+    if isinstance(out, (tuple, list)):
+        pls = [_placements_of(o, mesh) for o in flat_outs]
+        pls += [pls[-1] if pls else rep] * (len(out) - len(pls))
+        return type(out)(DistTensor.wrap(o, mesh, pl) if isinstance(o, torch.Tensor) else o for o, pl in zip(out, pls))
+    return DistTensor.wrap(out, mesh, ref_pl)
+
+
+def _arg(args, kwargs, pos, name, default=None):
+    if name in kwargs:
+        return kwargs[name]
+    return args[pos] if len(args) > pos else default
+
+
+def _rule_dispatch(name, func, args, kwargs, mesh):
+    """Operators whose sharded dims pass through untouched: the rule decides which dims must be gathered first, the local
+    call then takes the same arguments as the global one.  Returns NotImplemented when the operator is not covered."""
+    if name in ("cat", "concat", "concatenate", "stack") and isinstance(args[0], (list, tuple)):
+        xs = list(args[0])
+        dim = _arg(args, kwargs, 1, "dim", kwargs.get("axis", 0))
+        kw = {k: v for k, v in kwargs.items() if k not in ("dim", "axis")}
+        return _by_rule("stack" if name == "stack" else "concat", xs, (dim,), mesh, lambda ls: func(ls, dim, **kw), list_input=True)
+    x = args[0] if args else None
+    if not is_dist(x):
+        return NotImplemented
+    nd = len(x.shape)
+    if name in ("split", "chunk", "tensor_split", "split_with_sizes"):
+        arg = _arg(args, kwargs, 1, "split_size_or_sections", kwargs.get("chunks", kwargs.get("split_size", kwargs.get("split_sizes"))))
+        dim = _arg(args, kwargs, 2, "dim", 0)
+        size = x.shape[dim]
+        if name == "chunk" or name == "tensor_split":
+            step = -(-size // arg)
+            sections = [min(step, size - i) for i in range(0, size, step)]
+        else:
+            sections = list(arg) if isinstance(arg, (list, tuple)) else [min(arg, size - i) for i in range(0, size, arg)]
+        return _by_rule("split", [x], (sections, dim), mesh, lambda ls: tuple(torch.split(ls[0], sections, dim)))
+    if name == "unbind":
+        dim = _arg(args, kwargs, 1, "dim", 0)
+        return _by_rule("unbind", [x], (dim,), mesh, lambda ls: tuple(torch.unbind(ls[0], dim)))
+    if name == "squeeze":
+        dim = _arg(args, kwargs, 1, "dim", None)
+        return _by_rule("squeeze", [x], (dim if dim is None else (list(dim) if isinstance(dim, (list, tuple)) else [dim]),), mesh,
+                        lambda ls: func(ls[0]) if dim is None else func(ls[0], dim))
+    if name == "unsqueeze":
+        dim = _arg(args, kwargs, 1, "dim")
+        return _by_rule("unsqueeze", [x], ([dim],), mesh, lambda ls: func(ls[0], dim))
+    if name in ("cumsum", "cumprod", "logcumsumexp"):
+        dim = _arg(args, kwargs, 1, "dim", -1)
+        kw = {k: v for k, v in kwargs.items() if k != "dim"}
+        return _by_rule("cumsum", [x], (dim,), mesh, lambda ls: func(ls[0], dim, **kw))
+    if name in ("argmax", "argmin"):
+        dim = _arg(args, kwargs, 1, "dim", None)
+        keep = _arg(args, kwargs, 2, "keepdim", False)
+        return _by_rule("argmax", [x], (dim, keep, dim is None), mesh, lambda ls: func(ls[0], dim, keep))
+    if name in ("max", "min", "amax", "amin", "prod", "all", "any", "logsumexp") and (len(args) > 1 or "dim" in kwargs) \
+            and not isinstance(_arg(args, kwargs, 1, "dim"), torch.Tensor):
+        dim = _arg(args, kwargs, 1, "dim")
+        keep = _arg(args, kwargs, 2, "keepdim", False)
+        # the local call must see the whole reduced dim: use the non-partial form of the rule
+        return _by_rule("logsumexp", [x], (dim, keep), mesh, lambda ls: func(ls[0], dim, keep))
+    if name == "one_hot":
+        n = _arg(args, kwargs, 1, "num_classes", -1)
+        if n is None or n < 0:
+            return NotImplemented
+        return _by_rule("one_hot", [x], (n,), mesh, lambda ls: func(ls[0], n))
+    if name in ("triu", "tril"):
+        diag = _arg(args, kwargs, 1, "diagonal", 0)
+        return _by_rule("triu", [x], (diag,), mesh, lambda ls: func(ls[0], diag))
+    if name in ("tile", "repeat"):
+        reps = list(args[1]) if (len(args) > 1 and isinstance(args[1], (list, tuple, torch.Size))) else list(args[1:]) or list(kwargs.get("dims", ()))
+        return _by_rule("tile", [x], (reps,), mesh, lambda ls: ls[0].repeat(*([1] * (nd - len(reps)) + reps)) if len(reps) < nd else ls[0].repeat(*reps))
+    if name in ("expand", "broadcast_to", "expand_as"):
+        if name == "expand_as":
+            other = args[1]
+            tgt = list(other.shape)
+        else:
+            tgt = list(args[1]) if (len(args) > 1 and isinstance(args[1], (list, tuple, torch.Size))) else list(args[1:]) or list(kwargs.get("size", ()))
+        off = len(tgt) - nd
+        tgt = [x.shape[i - off] if (s == -1 and i >= off) else s for i, s in enumerate(tgt)]
+
+        def call(ls):
+            loc = list(tgt)
+            for i, s in enumerate(ls[0].shape):            # dims that are carried over keep their local size
+                if x.shape[i] != 1 or tgt[off + i] == 1:
+                    loc[off + i] = s
+            return ls[0].expand(loc)
+        return _by_rule("expand_as", [x], (None, tgt), mesh, call)
+    if name == "pad":
+        pads = list(_arg(args, kwargs, 1, "pad"))
+        kw = {k: v for k, v in kwargs.items() if k != "pad"}
+        rest = args[2:]
+        # torch lists pads from the last dim backwards; the rule takes (before, after) per dim from dim 0
+        per_dim = [0] * (2 * nd)
+        for i in range(len(pads) // 2):
+            d = nd - 1 - i
+            per_dim[2 * d], per_dim[2 * d + 1] = pads[2 * i], pads[2 * i + 1]
+        return _by_rule("pad", [x], (per_dim,), mesh, lambda ls: func(ls[0], pads, *rest, **kw))
+    if name == "index_select":
+        dim, index = args[1], args[2]
+        return _by_rule("gather", [x, index], (dim,), mesh, lambda ls: func(ls[0], dim, ls[1]))
+    if name == "scaled_dot_product_attention" and len(args) >= 3:
+        q, k, v = args[:3]
+        mask = _arg(args, kwargs, 3, "attn_mask", None)
+        kw = {kk: vv for kk, vv in kwargs.items() if kk != "attn_mask"}
+        # torch layout is [batch, heads, seq, head_dim]; the rule speaks [batch, seq, heads, head_dim]
+        from .spmd_rules import DistTensorSpec, get_phi_spmd_rule
+        rep = [Replicate()] * mesh.ndim
+        ds = [t if is_dist(t) else DistTensor.wrap(_plain(t), mesh, rep) for t in (q, k, v)]
+        ds = [reshard(d, mesh, [Replicate() if p.is_partial() else p for p in d._dist_placements]) for d in ds]
+        sw = lambda sp: DistTensorSpec([sp.shape[0], sp.shape[2], sp.shape[1], sp.shape[3]],     # noqa: E731
+                                       [sp.dims_mapping[0], sp.dims_mapping[2], sp.dims_mapping[1], sp.dims_mapping[3]])
+        new_in, outs = get_phi_spmd_rule("flash_attention").infer_forward(*[sw(_spec_of(d, mesh)) for d in ds])
+        out_pl = _placements_of(sw(outs[0]), mesh)
+        ls = []
+        for d, sp in zip(ds, new_in):
+            want = _placements_of(sw(sp), mesh)
+            ls.append(_guard_replicated_inputs(local_of(reshard(d, mesh, want)), mesh, want, out_pl))
+        m_local = None
+        if mask is not None:
+            md = mask if is_dist(mask) else DistTensor.wrap(_plain(mask), mesh, rep)
+            want = [Replicate()] * mesh.ndim
+            for a, p in enumerate(out_pl):              # the mask follows the batch / head split where it has those dims
+                if p.is_shard() and p.dim < 2 and len(md.shape) == 4 and md.shape[p.dim] != 1:
+                    want[a] = Shard(p.dim)
+            m_local = local_of(reshard(md, mesh, want))
+        with torch._C.DisableTorchFunctionSubclass():
+            out = func(ls[0], ls[1], ls[2], m_local, *args[4:], **kw) if mask is not None or len(args) > 3 else func(ls[0], ls[1], ls[2], **kw)
+        return DistTensor.wrap(out, mesh, out_pl)
+    return NotImplemented
 
 
 def _run_on_full(func, args, kwargs, mesh):

@@ -115,6 +115,17 @@ def test_auto_parallel_reshard_spmd_checkpoint_cpu():
         assert r["ckpt_meta"] == ("paddle.distributed.checkpoint.metadata", ["opt.m", "w"], 2, 1, ("opt", "m"))
 
 
+def test_spmd_rule_driven_operators_cpu():
+    """Operators dispatched through the SPMD rule registry (concat / stack / split / unbind / squeeze / cumsum / argmax /
+    triu / tile / expand / one_hot / index_select / pad / attention) on a 2-rank mesh: placements, values and gradients
+    against the dense computation."""
+    res = run_workers("spmd_ops.py", 2, timeout=180)
+    for r in res:
+        assert r.pop("split_n") == 3 and r.pop("sdpa_placement") == "[Shard(dim=1)]"
+        bad = {k: v for k, v in r.items() if v is not True}
+        assert not bad, bad
+
+
 def test_moe_expert_parallel_parity_cpu():
     """2 ranks x 2 local experts, uneven token counts: outputs, input gradients and expert gradients equal the
     dense evaluation of all four experts."""
