@@ -64,6 +64,14 @@ def __getattr__(name):
     if name in _REGISTRY:
         return _REGISTRY[name]
     import paddle_b200 as _p
+    # kernel-level definitions of the later registry tiers follow the operator's own signature and output order,
+    # which can differ from the same-named Python API (edit_distance, accuracy_check ...): they win
+    from . import _op_table_more, _op_table_seq
+    for tier in (_op_table_more, _op_table_seq):
+        fn = getattr(tier, name, None)
+        if callable(fn) and getattr(fn, "__module__", "") == tier.__name__ and not name.startswith("_"):
+            _REGISTRY[name] = fn
+            return fn
     base = name[:-1] if name.endswith("_") else name
     for mod in (_p, _p.nn.functional):
         if hasattr(mod, base):

@@ -118,6 +118,13 @@ for _n in ("create_parameter", "histogram_bin_edges", "matrix_transpose", "reduc
         setattr(Tensor, _n, _v)
 del _n, _v
 
+from .tensor import semantics as _semantics  # noqa: E402
+_semantics.install(globals())
+
+
+def is_compiled_with_ipu():
+    return False
+
 
 def is_compiled_with_cuda():
     return True
@@ -183,8 +190,8 @@ def get_cudnn_version():
 
 
 def set_printoptions(precision=None, threshold=None, edgeitems=None, sci_mode=None, linewidth=None):
-    _torch.set_printoptions(precision=precision, threshold=threshold, edgeitems=edgeitems, sci_mode=sci_mode,
-                            linewidth=linewidth)
+    from .tensor.to_string import set_printoptions as _set
+    _set(precision, threshold, edgeitems, sci_mode, linewidth)
 
 
 def set_grad_enabled_ctx(mode):

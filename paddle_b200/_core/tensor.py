@@ -33,10 +33,14 @@ class Tensor(torch.Tensor):
     # ---- identity / meta
     @property
     def stop_gradient(self) -> bool:
-        return not self.requires_grad
+        return not (self.requires_grad or getattr(self, "_int_wants_grad", False))
 
     @stop_gradient.setter
     def stop_gradient(self, v: bool):
+        if not (self.dtype.is_floating_point or self.dtype.is_complex):
+            # integer tensors carry the flag (the reference allows it) but never take part in autograd
+            self._int_wants_grad = not v
+            return
         if self.is_leaf or not v:
             self.requires_grad_(not v)
         # a non-leaf cannot be switched off in place; Paddle users then call detach()
@@ -92,7 +96,7 @@ class Tensor(torch.Tensor):
         t = self.detach()
         if t.dtype == torch.bfloat16:
             return t.float().cpu().numpy()
-        return torch.Tensor.numpy(t.cpu())
+        return torch.Tensor.numpy(t.cpu().resolve_conj().resolve_neg())
 
     def astype(self, dtype):
         return self.to(_dt.to_torch(dtype))
@@ -135,6 +139,9 @@ class Tensor(torch.Tensor):
         torch.Tensor.grad.__set__(self, v)
 
     def backward(self, grad_tensor=None, retain_graph=False):
+        """A non-scalar tensor starts its backward pass from a gradient of ones (the reference's rule)."""
+        if grad_tensor is None and self.dim() > 0 and self.numel() != 1:
+            grad_tensor = torch.ones_like(self.detach().as_subclass(torch.Tensor))
         torch.Tensor.backward(self, gradient=grad_tensor, retain_graph=retain_graph)
 
     def clear_gradient(self, set_to_zero=True):
@@ -363,12 +370,8 @@ class Tensor(torch.Tensor):
         return r
 
     def __repr__(self):
-        try:
-            body = torch.Tensor.__repr__(self.detach().as_subclass(torch.Tensor))
-        except Exception:  # noqa: BLE001
-            body = "<unprintable>"
-        return (f"Tensor(shape={self.shape}, dtype={_dt.to_name(self.dtype)}, place={self.device}, "
-                f"stop_gradient={self.stop_gradient},\n       {body})")
+        from ..tensor.to_string import to_string
+        return to_string(self)
 
     __str__ = __repr__
 
@@ -450,6 +453,10 @@ def as_tensor(t: torch.Tensor) -> Tensor:
     return t.as_subclass(Tensor)
 
 
+Tensor.__module__ = "paddle"          # type(t) prints as <class 'paddle.Tensor'>; the alias package resolves the name
+Tensor.__qualname__ = "Tensor"
+
+
 def to_tensor(data, dtype=None, place=None, stop_gradient=True):
     """``paddle.to_tensor`` (python/paddle/tensor/creation.py)."""
     td = _dt.to_torch(dtype) if dtype is not None else None
@@ -465,6 +472,9 @@ def to_tensor(data, dtype=None, place=None, stop_gradient=True):
         if td is None:
             if arr.dtype == np.float64 and not isinstance(data, np.ndarray):
                 td = _dt.get_default_dtype()
+            elif arr.dtype == np.complex128 and not isinstance(data, np.ndarray):
+                # Python complex numbers follow the default float dtype: complex64 unless the default is float64
+                td = torch.complex128 if _dt.get_default_dtype() == torch.float64 else torch.complex64
             elif arr.dtype == np.uint16:  # bf16 bit pattern as stored by paddle.save
                 t = torch.from_numpy(arr.view(np.int16).copy()).view(torch.bfloat16)
                 t = t.to(dev or _dt.default_device())
@@ -477,5 +487,5 @@ def to_tensor(data, dtype=None, place=None, stop_gradient=True):
         t = t.to(dev or _dt.default_device())
     r = as_tensor(t)
     if not stop_gradient:
-        r.requires_grad_(True)
+        r.stop_gradient = False
     return r

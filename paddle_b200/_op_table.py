@@ -654,21 +654,24 @@ def fill_diagonal_tensor(x, y, offset=0, dim1=0, dim2=1):
 
 
 def frame(x, frame_length, hop_length, axis=-1):
+    """axis -1: [..., frame_length, n]; axis 0: [n, frame_length, ...] (also for 1-D input)."""
     t = _t(x)
-    if axis in (-1, t.dim() - 1):
-        return _wrap(t.unfold(-1, int(frame_length), int(hop_length)).transpose(-1, -2))      # [..., frame_length, n]
-    return _wrap(t.unfold(0, int(frame_length), int(hop_length)).movedim(-1, 1))              # [n, frame_length, ...]
+    if axis != 0 and axis in (-1, t.dim() - 1):
+        return _wrap(t.unfold(-1, int(frame_length), int(hop_length)).transpose(-1, -2))
+    return _wrap(t.unfold(0, int(frame_length), int(hop_length)).movedim(-1, 1))
 
 
 def overlap_add(x, hop_length, axis=-1):
+    """Inverse layout of ``frame``: axis -1 takes [..., frame_length, n], axis 0 takes [n, frame_length, ...]."""
     t = _t(x)
-    if axis not in (-1, t.dim() - 1):
+    last = axis != 0 and axis in (-1, t.dim() - 1)
+    if not last:
         t = t.movedim(0, -1).movedim(0, -1)            # [n, frame_length, ...] -> [..., frame_length, n]
     fl, n = t.shape[-2], t.shape[-1]
     out = torch.zeros(*t.shape[:-2], (n - 1) * int(hop_length) + fl, dtype=t.dtype, device=t.device)
     for i in range(n):
         out[..., i * int(hop_length):i * int(hop_length) + fl] += t[..., i]
-    return _wrap(out if axis in (-1, _t(x).dim() - 1) else out.movedim(-1, 0))
+    return _wrap(out if last else out.movedim(-1, 0))
 
 
 def merged_adam_(param, grad, learning_rate, moment1, moment2, moment2_max, beta1_pow, beta2_pow, master_param=None,

@@ -251,7 +251,8 @@ def average_accumulates_(param, in_sum_1, in_sum_2, in_sum_3, in_num_accumulates
 
 # ------------------------------------------------------------------------------------------------ assorted
 def edit_distance(hyps, refs, hypslength=None, refslength=None, normalized=False):
-    """Levenshtein distance per row of two padded int matrices -> (distances [B, 1] fp32, sequence count [1])."""
+    """Levenshtein distance per row of two padded int matrices -> (sequence count [1] int64, distances [B, 1] fp32), the
+    output order of the operator's definition."""
     h, r = _t(hyps), _t(refs)
     B = h.shape[0]
     hl = _t(hypslength).reshape(-1).tolist() if hypslength is not None else [h.shape[1]] * B
@@ -267,7 +268,7 @@ def edit_distance(hyps, refs, hypslength=None, refslength=None, normalized=False
             prev = cur
         d = float(prev[-1])
         out[b, 0] = d / max(len(c), 1) if normalized else d
-    return _wrap(out.to(h.device)), _wrap(torch.tensor([B], dtype=torch.int64, device=h.device))
+    return _wrap(torch.tensor([B], dtype=torch.int64, device=h.device)), _wrap(out.to(h.device))
 
 
 def box_clip(input, im_info):

@@ -55,10 +55,17 @@ def _wrap(o):
 
 
 def backward(tensors, grad_tensors=None, retain_graph=False):
+    """Backward from several tensors at once; a missing (or ``None``) initial gradient is ones of the tensor's shape."""
     tensors = [tensors] if isinstance(tensors, torch.Tensor) else list(tensors)
-    if grad_tensors is not None and isinstance(grad_tensors, torch.Tensor):
+    if grad_tensors is None:
+        grad_tensors = [None] * len(tensors)
+    elif isinstance(grad_tensors, torch.Tensor):
         grad_tensors = [grad_tensors]
-    torch.autograd.backward(tensors, grad_tensors, retain_graph=retain_graph)
+    grad_tensors = list(grad_tensors)
+    if len(grad_tensors) != len(tensors):
+        raise ValueError("The length of grad_tensors must be equal to tensors")
+    grads = [torch.ones_like(t.detach().as_subclass(torch.Tensor)) if g is None else g for t, g in zip(tensors, grad_tensors)]
+    torch.autograd.backward(tensors, grads, retain_graph=retain_graph)
 
 
 def grad(outputs, inputs, grad_outputs=None, retain_graph=None, create_graph=False, only_inputs=True,
@@ -76,20 +83,68 @@ class saved_tensors_hooks(torch.autograd.graph.saved_tensors_hooks):
     pass
 
 
+def _jac_one(y, x, batch_axis, create_graph=False):
+    """d y / d x as [M, N] (``batch_axis=None``) or [B, M, N] (``batch_axis=0``: sample b of y depends on sample b of x
+    only); inputs y does not depend on give zeros."""
+    if batch_axis is None:
+        flat = y.reshape(-1)
+        rows = []
+        for i in range(flat.numel()):
+            g = torch.autograd.grad(flat[i], x, retain_graph=True, create_graph=create_graph, allow_unused=True)[0]
+            rows.append(torch.zeros_like(x).reshape(-1) if g is None else g.reshape(-1))
+        return torch.stack(rows) if rows else x.new_zeros(0, x.numel())
+    if batch_axis != 0:
+        raise ValueError("batch_axis should be None or 0")
+    B = y.shape[0]
+    yf = y.reshape(B, -1)
+    cols = []
+    for m in range(yf.shape[1]):
+        g = torch.autograd.grad(yf[:, m].sum(), x, retain_graph=True, create_graph=create_graph, allow_unused=True)[0]
+        cols.append(torch.zeros_like(x).reshape(B, -1) if g is None else g.reshape(B, -1))
+    return torch.stack(cols, 1)
+
+
 def jacobian(ys, xs, batch_axis=None):
+    """Jacobian of ``ys`` with respect to ``xs`` (python/paddle/autograd/autograd.py ``jacobian``): a tensor for tensor
+    arguments, a tuple over ``xs`` (nested in a tuple over ``ys``) when either is a sequence; flattened to [M, N], or
+    [B, M, N] with ``batch_axis=0``.  A callable ``ys`` is evaluated at ``xs`` first."""
     if callable(ys):
-        return torch.autograd.functional.jacobian(ys, xs)
-    flat = ys.reshape(-1)
-    rows = [torch.autograd.grad(flat[i], xs, retain_graph=True, allow_unused=True)[0].reshape(-1) for i in range(flat.numel())]
-    return as_tensor(torch.stack(rows))
+        args = xs if isinstance(xs, (list, tuple)) else (xs,)
+        ys = ys(*args)
+    many_y, many_x = isinstance(ys, (list, tuple)), isinstance(xs, (list, tuple))
+    out = tuple(tuple(as_tensor(_jac_one(y, x, batch_axis)) for x in (xs if many_x else [xs])) for y in (ys if many_y else [ys]))
+    if not many_x:
+        out = tuple(r[0] for r in out)
+    return out if many_y else out[0]
 
 
 def hessian(ys, xs, batch_axis=None):
+    """Second derivatives of a scalar ``ys`` (one scalar per sample with ``batch_axis=0``): [N, N] for one input, a
+    tuple of tuples ``H[i][j] = d2 y / d x_i d x_j`` for several."""
     if callable(ys):
-        return torch.autograd.functional.hessian(ys, xs)
-    g = torch.autograd.grad(ys, xs, create_graph=True)[0].reshape(-1)
-    rows = [torch.autograd.grad(g[i], xs, retain_graph=True)[0].reshape(-1) for i in range(g.numel())]
-    return as_tensor(torch.stack(rows))
+        args = xs if isinstance(xs, (list, tuple)) else (xs,)
+        ys = ys(*args)
+    many_x = isinstance(xs, (list, tuple))
+    xlist = list(xs) if many_x else [xs]
+    if batch_axis is None and ys.numel() != 1:
+        raise ValueError("hessian needs a scalar ys (or batch_axis=0 with one scalar per sample)")
+    firsts = []
+    for x in xlist:
+        target = ys.sum() if batch_axis == 0 else ys.reshape(())
+        g = torch.autograd.grad(target, x, create_graph=True, allow_unused=True)[0]
+        firsts.append(torch.zeros_like(x) if g is None else g)
+    rows = []
+    for gi, xi in zip(firsts, xlist):
+        row = []
+        for xj in xlist:
+            if not gi.requires_grad:
+                n_i = xi.numel() if batch_axis is None else xi[0].numel()
+                n_j = xj.numel() if batch_axis is None else xj[0].numel()
+                row.append(as_tensor(xi.new_zeros((n_i, n_j) if batch_axis is None else (xi.shape[0], n_i, n_j))))
+            else:
+                row.append(as_tensor(_jac_one(gi if batch_axis is None else gi.reshape(gi.shape[0], -1), xj, batch_axis)))
+        rows.append(tuple(row))
+    return tuple(rows) if many_x else rows[0][0]
 
 
 no_grad = torch.no_grad

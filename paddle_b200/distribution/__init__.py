@@ -81,9 +81,13 @@ def _make(name, torch_cls, argmap, base=Distribution):
         vals = dict(zip(names, args))
         vals.update(kwargs)
         self._params = vals
-        self._d = torch_cls(**{argmap[k]: _t(v) for k, v in vals.items() if v is not None})
+        int_args = {"dim", "total_count"} if torch_cls in (D.LKJCholesky, D.Multinomial) else set()
+        conv = {argmap[k]: (int(v) if k in int_args and not isinstance(v, torch.Tensor) else
+                            (int(v.item()) if k in int_args and v.numel() == 1 else _t(v)))
+                for k, v in vals.items() if v is not None}
+        self._d = torch_cls(**conv, validate_args=False)
         for k, v in vals.items():
-            if not hasattr(type(self), k):
+            if not hasattr(type(self), k) or k == "probs":       # the parameter shadows the ``probs(value)`` method alias
                 setattr(self, k, as_tensor(_t(v)) if isinstance(_t(v), torch.Tensor) else v)
     return type(name, (base,), {"__init__": __init__})
 
@@ -110,6 +114,63 @@ MultivariateNormal = _make("MultivariateNormal", D.MultivariateNormal,
 Poisson = _make("Poisson", D.Poisson, {"rate": "rate"})
 StudentT = _make("StudentT", D.StudentT, {"df": "df", "loc": "loc", "scale": "scale"})
 LKJCholesky = _make("LKJCholesky", D.LKJCholesky, {"dim": "dim", "concentration": "concentration"})
+
+
+class _GeometricMixin:
+    """Number of failures before the first success, k = 0, 1, 2, ... (python/paddle/distribution/geometric.py)."""
+
+    def pmf(self, k):
+        p = _t(self.probs)
+        return as_tensor(torch.pow(1.0 - p, _t(k)) * p)
+
+    def log_pmf(self, k):
+        return as_tensor(torch.log(_t(self.pmf(k))))
+
+    def cdf(self, k):
+        p = _t(self.probs)
+        return as_tensor(1.0 - torch.pow(1.0 - p, _t(k) + 1))
+
+    def rsample(self, shape=()):
+        p = _t(self.probs)
+        u = torch.rand(tuple(shape) + tuple(p.shape), dtype=p.dtype).clamp_min(torch.finfo(p.dtype).tiny)
+        return as_tensor(torch.floor(torch.log(u) / torch.log1p(-p)))
+
+    def sample(self, shape=()):
+        with torch.no_grad():
+            return self.rsample(shape)
+
+    def entropy(self):
+        p = _t(self.probs)
+        return as_tensor(-((1.0 - p) * torch.log(1.0 - p) + p * torch.log(p)) / p)
+
+    def kl_divergence(self, other):
+        p, q = _t(self.probs), _t(other.probs)
+        return as_tensor(p * torch.log(p / q) + (1.0 - p) * torch.log((1.0 - p) / (1.0 - q)))
+
+
+Geometric = type("Geometric", (_GeometricMixin, Geometric), {})
+
+
+def _bernoulli_cdf(self, value):
+    """0 below 0, 1 - p on [0, 1), 1 from 1 on."""
+    v, p = _t(value), _t(self.probs)
+    v, p = torch.broadcast_tensors(v, p)
+    return as_tensor(torch.where(v < 0, torch.zeros_like(p), torch.where(v < 1, 1 - p, torch.ones_like(p))))
+
+
+Bernoulli.cdf = _bernoulli_cdf
+
+
+def _poisson_entropy(self):
+    """Sum of -p log p over the support up to rate + 30 sqrt(rate) (the tail beyond is below float precision)."""
+    rate = _t(self.rate)
+    hi = int(torch.ceil(rate.max() + 30 * torch.sqrt(rate.max())).item()) + 1
+    values = torch.arange(hi, dtype=rate.dtype).reshape((-1,) + (1,) * rate.dim())
+    lp = self._d.log_prob(values)
+    return as_tensor(-(lp.exp() * lp).sum(0) * (rate != 0).to(rate.dtype))
+
+
+Poisson.entropy = _poisson_entropy
 
 
 class Categorical(Distribution):
@@ -211,3 +272,10 @@ def kl_divergence(p, q):
         if isinstance(p, cp) and isinstance(q, cq):
             return fn(p, q)
     return as_tensor(D.kl_divergence(p._d, q._d))
+
+
+from .._core.submodule_alias import alias_submodules as _alias  # noqa: E402
+_alias(__name__, ("bernoulli", "beta", "binomial", "categorical", "cauchy", "chi2", "continuous_bernoulli", "dirichlet", "distribution",
+                  "exponential", "exponential_family", "gamma", "geometric", "gumbel", "independent", "kl", "laplace", "lkj_cholesky",
+                  "lognormal", "multinomial", "multivariate_normal", "normal", "poisson", "student_t", "transform", "transformed_distribution",
+                  "uniform", "variable"))

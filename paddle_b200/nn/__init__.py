@@ -8,3 +8,8 @@ from . import utils  # noqa: F401
 from .layer.extras import *  # noqa: E402,F401,F403
 from .layer.extras import (AdaptiveLogSoftmaxWithLoss, BeamSearchDecoder, BiRNN, Bilinear, GRUCell, HSigmoidLoss, LSTMCell,  # noqa: E402,F401
                            ParameterDict, RNN, RNNCellBase, SimpleRNNCell, SpectralNorm, dynamic_decode)
+
+
+from .._core.submodule_alias import alias_submodules as _alias  # noqa: E402
+_alias(__name__, ("loss", "activation", "conv", "norm", "pooling", "rnn", "transformer", "vision", "container", "distance", "common"))
+_alias(__name__ + ".layer", ("loss", "activation", "conv", "norm", "pooling", "rnn", "transformer", "vision", "container", "distance"))

@@ -248,12 +248,17 @@ def cross_entropy(input, label, weight=None, ignore_index=-100, reduction="mean"
         input = input.movedim(axis, -1)
         if soft_label:
             label = label.movedim(axis, -1)
+    if label_smoothing > 0.0 and label.is_floating_point() and label.dim() == input.dim() and label.shape[-1] == input.shape[-1]:
+        # one-hot (float) labels under label smoothing are smoothed and treated as soft labels
+        label = label * (1 - label_smoothing) + label_smoothing / input.shape[-1]
+        soft_label, label_smoothing = True, 0.0
     if soft_label or not use_softmax or label_smoothing > 0.0 or weight is not None:
-        logp = TF.log_softmax(input.float(), -1) if use_softmax else torch.log(input.float())
+        wide = input if input.dtype == torch.float64 else input.float()
+        logp = TF.log_softmax(wide, -1) if use_softmax else torch.log(wide)
         if not soft_label:
             lab = label.squeeze(-1) if label.dim() == input.dim() else label
             if label_smoothing > 0.0:
-                oh = TF.one_hot(lab.clamp(min=0), input.shape[-1]).float()
+                oh = TF.one_hot(lab.clamp(min=0).long(), input.shape[-1]).to(logp.dtype)
                 oh = oh * (1 - label_smoothing) + label_smoothing / input.shape[-1]
                 loss = -(oh * logp).sum(-1)
                 loss = torch.where(lab == ignore_index, torch.zeros_like(loss), loss)
@@ -267,7 +272,9 @@ def cross_entropy(input, label, weight=None, ignore_index=-100, reduction="mean"
                 valid = (lab != ignore_index).sum().clamp(min=1)
                 return loss.sum() / valid
             return _reduce(loss, reduction)
-        loss = -(label.float() * logp).sum(-1)
+        loss = -(label.to(logp.dtype) * logp).sum(-1)
+        if weight is not None:
+            loss = loss * (label.to(logp.dtype) * weight.to(logp.dtype)).sum(-1)
         return _reduce(loss, reduction)
     lab = label.squeeze(-1) if label.dim() == input.dim() else label
     loss = K.softmax_cross_entropy(input, lab, ignore_index)
@@ -290,7 +297,10 @@ def softmax_with_cross_entropy(logits, label, soft_label=False, ignore_index=-10
 
 
 def nll_loss(input, label, weight=None, ignore_index=-100, reduction="mean", name=None):
-    return TF.nll_loss(input, label.long(), weight, ignore_index=ignore_index, reduction=reduction)
+    label = label.long()
+    if input.dim() == 2 and label.dim() == 2 and label.shape[1] == 1:
+        label = label.reshape(-1)                      # [N, 1] class ids are taken as [N]
+    return TF.nll_loss(input, label, weight, ignore_index=ignore_index, reduction=reduction)
 
 
 def mse_loss(input, label, reduction="mean", name=None):
@@ -461,12 +471,15 @@ def adaptive_max_pool2d(x, output_size, return_mask=False, name=None):
     return TF.adaptive_max_pool2d(x, output_size, return_mask)
 
 
-def pad(x, pad, mode="constant", value=0.0, data_format="NCHW", pad_from_left_axis=True, name=None):
+def pad(x, pad, mode="constant", value=0.0, data_format=None, pad_from_left_axis=True, name=None):
     pad = [int(p) for p in (pad.tolist() if isinstance(pad, torch.Tensor) else pad)]
     nd = x.dim()
-    if len(pad) == 2 * nd:  # per-axis pairs from the first axis: torch wants last axis first
+    if data_format is None:
+        data_format = {3: "NCL", 4: "NCHW", 5: "NCDHW"}.get(nd, "NCHW")
+    if len(pad) == 2 * nd and mode == "constant":
+        # per-axis pairs; from the first axis by default (torch wants the last axis first), from the last one otherwise
         pairs = [pad[2 * i:2 * i + 2] for i in range(nd)]
-        flat = [v for pr in reversed(pairs) for v in pr]
+        flat = [v for pr in reversed(pairs) for v in pr] if pad_from_left_axis else list(pad)
         return TF.pad(x, flat, mode=mode, value=value) if mode == "constant" else TF.pad(x, flat, mode=mode)
     cl = data_format in ("NHWC", "NLC", "NDHWC")
     if cl:
@@ -543,3 +556,13 @@ def temporal_shift(x, seg_num, shift_ratio=0.25, name=None, data_format="NCHW"):
 
 from .extras import *  # noqa: E402,F401,F403
 from .extras import (elu_, hardtanh_, leaky_relu_, softmax_, tanh_, thresholded_relu_)  # noqa: E402,F401
+
+
+from ..._core.submodule_alias import alias_submodules as _alias  # noqa: E402
+_alias(__name__, ("loss", "activation", "common", "conv", "distance", "extension", "input", "norm", "pooling", "sparse_attention", "vision"))
+# ``F.flash_attention`` is a module in the reference and a function here: the function carries the module's names
+for _n in ("flash_attention", "flash_attn_unpadded", "flashmask_attention", "scaled_dot_product_attention", "flash_attn_qkvpacked",
+           "flash_attn_varlen_qkvpacked", "flash_attn_varlen_func", "flash_attention_with_sparse_mask", "sdp_kernel", "calc_reduced_attention_scores"):
+    if _n in globals():
+        setattr(flash_attention, _n, globals()[_n])
+del _n

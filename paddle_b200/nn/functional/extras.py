@@ -145,6 +145,8 @@ def hsigmoid_loss(input, label, num_classes, weight, bias=None, path_table=None,
                 nodes.append(code // 2 - 1)
                 codes.append(float(code % 2))
                 code //= 2
+        keep = [j for j, nd_ in enumerate(nodes) if 0 <= nd_ < w.shape[0]]     # a label beyond num_classes walks off the tree
+        nodes, codes = [nodes[j] for j in keep], [codes[j] for j in keep]
         n = torch.tensor(nodes, dtype=torch.long)
         logit = w[n] @ x[i] + (_p(bias).reshape(-1)[n] if bias is not None else 0)
         losses.append(TF.binary_cross_entropy_with_logits(logit, torch.tensor(codes, dtype=x.dtype), reduction="sum"))
@@ -166,7 +168,7 @@ def margin_cross_entropy(logits, label, margin1=1.0, margin2=0.5, margin3=0.0, s
 
 def rnnt_loss(input, label, input_lengths, label_lengths, blank=0, fastemit_lambda=0.001, reduction="mean", name=None):
     """RNN-T loss by the forward algorithm in log space (input: [B, T, U+1, V] un-normalised logits)."""
-    lp = torch.log_softmax(_p(input).float(), -1)
+    lp = torch.log_softmax(_p(input) if _p(input).dtype == torch.float64 else _p(input).float(), -1)
     B = lp.shape[0]
     losses = []
     for b in range(B):
@@ -285,3 +287,27 @@ def flash_attn_varlen_qkvpacked(qkv, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, m
                                False, training=training)
         outs.append(_p(o)[0])
     return as_tensor(torch.cat(outs, 0)), None
+
+
+def edit_distance(input, label, normalized=True, ignored_tokens=None, input_length=None, label_length=None):
+    """Levenshtein distance between rows of two padded id matrices (python/paddle/nn/functional/loss.py ``edit_distance``):
+    ``ignored_tokens`` are dropped from both first; ``normalized`` divides by the label length.
+    -> (number of sequences [1] int64, distances [batch, 1] float32): the operator's output order, which is what the
+    reference returns in dynamic mode."""
+    a, b = _p(input).long(), _p(label).long()
+    la = _p(input_length).reshape(-1).tolist() if input_length is not None else [a.shape[1]] * a.shape[0]
+    lb = _p(label_length).reshape(-1).tolist() if label_length is not None else [b.shape[1]] * b.shape[0]
+    drop = set(int(t) for t in (ignored_tokens or []))
+    out = []
+    for i in range(a.shape[0]):
+        h = [t for t in a[i, :int(la[i])].tolist() if t not in drop]
+        r = [t for t in b[i, :int(lb[i])].tolist() if t not in drop]
+        prev = list(range(len(r) + 1))
+        for x in range(1, len(h) + 1):
+            cur = [x] + [0] * len(r)
+            for y in range(1, len(r) + 1):
+                cur[y] = min(prev[y] + 1, cur[y - 1] + 1, prev[y - 1] + (h[x - 1] != r[y - 1]))
+            prev = cur
+        d = float(prev[len(r)])
+        out.append(d / max(len(r), 1) if normalized else d)
+    return as_tensor(torch.tensor([a.shape[0]], dtype=torch.int64)), as_tensor(torch.tensor(out, dtype=torch.float32).reshape(-1, 1))

@@ -29,8 +29,8 @@ def _fn_layer(name, fn, arg_names, defaults=()):
         vals.update(kwargs)
         self._kw = vals
 
-    def forward(self, *inputs):
-        return fn(*inputs, **self._kw)
+    def forward(self, *inputs, **named_inputs):
+        return fn(*inputs, **named_inputs, **self._kw)
     return type(name, (Layer,), {"__init__": __init__, "forward": forward})
 
 
@@ -178,6 +178,25 @@ class AdaptiveLogSoftmaxWithLoss(Layer):
 
     def forward(self, input, label):
         return FX.adaptive_log_softmax_with_loss(input, label, self.head_weight, self.tail_weights, self.cutoffs, self.head_bias)
+
+    def log_prob(self, input):
+        """Log-probabilities of all ``n_classes`` classes, [batch, n_classes]: head classes directly, tail classes as
+        cluster log-probability plus the log-probability inside the cluster."""
+        x = _p(input)
+        head = x @ _p(self.head_weight)
+        if self.head_bias is not None:
+            head = head + _p(self.head_bias)
+        head_lp = torch.log_softmax(head, 1)
+        short = self.cutoffs[0]
+        parts = [head_lp[:, :short]]
+        for i, (w1, w2) in enumerate(self.tail_weights):
+            lp = torch.log_softmax((x @ _p(w1)) @ _p(w2), 1)
+            parts.append(head_lp[:, short + i:short + i + 1] + lp)
+        return as_tensor(torch.cat(parts, 1))
+
+    def predict(self, input):
+        """The most likely class per row."""
+        return as_tensor(torch.argmax(_p(self.log_prob(input)), 1))
 
 
 class SpectralNorm(Layer):

@@ -194,7 +194,7 @@ class Layer:
         return list(super().__dir__()) + list(self._parameters) + list(self._sub_layers) + list(self._buffers)
 
     # ------------------------------------------------------------------ traversal
-    def named_sublayers(self, prefix="", include_self=False, layers_set=None) -> Iterator:
+    def named_sublayers(self, prefix="", include_self=False, layers_set=None, remove_duplicate=True) -> Iterator:
         layers_set = set() if layers_set is None else layers_set
         if include_self and id(self) not in layers_set:
             layers_set.add(id(self))
@@ -337,6 +337,8 @@ class Layer:
                     continue
                 new = fn(p.data)
                 if new is not p.data:
+                    if p.requires_grad and not (new.is_floating_point() or new.is_complex()):
+                        p.requires_grad_(False)           # integer parameters cannot take gradients
                     p.data = new
                 if p.grad is not None:
                     p.grad = fn(p.grad)

@@ -126,7 +126,7 @@ class Adamax(Optimizer):
     def __init__(self, learning_rate=0.001, beta1=0.9, beta2=0.999, epsilon=1e-8, parameters=None, weight_decay=None,
                  grad_clip=None, name=None, multi_precision=False):
         super().__init__(learning_rate, parameters, weight_decay, grad_clip, name, multi_precision)
-        self._beta1, self._beta2, self._epsilon = beta1, beta2, epsilon
+        self._beta1, self._beta2, self._epsilon = float(beta1), float(beta2), float(epsilon)
 
     def _create_accumulators(self, params):
         for p in params:

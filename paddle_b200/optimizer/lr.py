@@ -266,3 +266,51 @@ class ReduceOnPlateau(LRScheduler):
 
     def get_lr(self):
         return self.last_lr
+
+
+# ------------------------------------------------------------------------------------------- functional (legacy) forms
+# python/paddle/optimizer/lr.py:2697-3190: the functions of the older API return scheduler objects in dynamic mode;
+# ``step()`` advances them once per optimizer update.
+def noam_decay(d_model, warmup_steps, learning_rate=1.0):
+    return NoamDecay(d_model, warmup_steps, learning_rate)
+
+
+def exponential_decay(learning_rate, decay_steps, decay_rate, staircase=False):
+    """learning_rate * decay_rate ^ (step / decay_steps); ``staircase`` floors the exponent."""
+    def f(step):
+        e = step / decay_steps
+        return decay_rate ** (math.floor(e) if staircase else e)
+    return LambdaDecay(learning_rate, f)
+
+
+def natural_exp_decay(learning_rate, decay_steps, decay_rate, staircase=False):
+    """learning_rate * exp(-decay_rate * step / decay_steps)."""
+    def f(step):
+        e = step / decay_steps
+        return math.exp(-decay_rate * (math.floor(e) if staircase else e))
+    return LambdaDecay(learning_rate, f)
+
+
+def inverse_time_decay(learning_rate, decay_steps, decay_rate, staircase=False):
+    """learning_rate / (1 + decay_rate * step / decay_steps)."""
+    def f(step):
+        e = step / decay_steps
+        return 1.0 / (1.0 + decay_rate * (math.floor(e) if staircase else e))
+    return LambdaDecay(learning_rate, f)
+
+
+def polynomial_decay(learning_rate, decay_steps, end_learning_rate=0.0001, power=1.0, cycle=False):
+    return PolynomialDecay(learning_rate, decay_steps, end_learning_rate, power, cycle)
+
+
+def piecewise_decay(boundaries, values):
+    return PiecewiseDecay(boundaries, values)
+
+
+def cosine_decay(learning_rate, step_each_epoch, epochs):
+    """learning_rate * 0.5 * (cos(epoch * pi / epochs) + 1) with epoch = floor(step / step_each_epoch)."""
+    return LambdaDecay(learning_rate, lambda step: 0.5 * (math.cos(math.floor(step / step_each_epoch) * math.pi / epochs) + 1))
+
+
+def linear_lr_warmup(learning_rate, warmup_steps, start_lr, end_lr):
+    return LinearWarmup(learning_rate, warmup_steps, start_lr, end_lr)

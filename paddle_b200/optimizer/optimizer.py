@@ -168,9 +168,31 @@ class Optimizer:
         if _sg.recording():
             from ..static import _static_minimize
             return _static_minimize(self, loss, parameters, no_grad_set)
-        loss.backward()
+        # dynamic mode: the caller has already run ``loss.backward()``; minimize applies the gradients that exist
+        # (python/paddle/optimizer/optimizer.py ``minimize`` -> ``backward`` collects ``param.grad`` in dygraph)
+        params_grads = self.backward(loss, parameters=parameters, no_grad_set=no_grad_set)
+        if not params_grads and loss is not None and getattr(loss, "grad_fn", None) is not None:
+            loss.backward()
         self.step()
-        return None, None
+        return None, params_grads
+
+    def backward(self, loss=None, startup_program=None, parameters=None, no_grad_set=None, callbacks=None):
+        """(parameter, gradient) pairs of the parameters that have a gradient (dynamic mode: the gradients computed by the
+        caller's ``loss.backward()``)."""
+        skip = set(id(p) for p in (no_grad_set or []))
+        plist = parameters if parameters is not None else self._parameter_list
+        flat = []
+        for p in plist:
+            flat += list(p["params"]) if isinstance(p, dict) else [p]
+        return [(p, p.grad) for p in flat if p.grad is not None and id(p) not in skip and not p.stop_gradient]
+
+    def apply_gradients(self, params_grads):
+        """Update the given parameters with the given gradients."""
+        for p, g in params_grads:
+            if g is not None and p.grad is not g:
+                p.grad = g if isinstance(g, torch.Tensor) else torch.as_tensor(g)
+        self.step()
+        return []
 
     def clear_grad(self, set_to_zero=True):
         for p in self._parameter_list:

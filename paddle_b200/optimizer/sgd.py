@@ -118,7 +118,7 @@ class Lamb(Optimizer):
     def __init__(self, learning_rate=0.001, lamb_weight_decay=0.01, beta1=0.9, beta2=0.999, epsilon=1e-6,
                  parameters=None, grad_clip=None, exclude_from_weight_decay_fn=None, multi_precision=False, name=None):
         super().__init__(learning_rate, parameters, None, grad_clip, name, multi_precision)
-        self._wd, self._beta1, self._beta2, self._epsilon = lamb_weight_decay, beta1, beta2, epsilon
+        self._wd, self._beta1, self._beta2, self._epsilon = float(lamb_weight_decay), float(beta1), float(beta2), float(epsilon)
         self._exclude = exclude_from_weight_decay_fn
 
     def _create_accumulators(self, params):

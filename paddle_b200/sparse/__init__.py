@@ -22,7 +22,7 @@ def sparse_coo_tensor(indices, values, shape=None, dtype=None, place=None, stop_
     if dtype is not None:
         from .._core import dtype as _dt
         v = v.to(_dt.to_torch(dtype))
-    t = torch.sparse_coo_tensor(i, v, size=tuple(shape) if shape is not None else None)
+    t = torch.sparse_coo_tensor(i, v, size=tuple(shape)) if shape is not None else torch.sparse_coo_tensor(i, v)
     t.requires_grad_(not stop_gradient and t.is_floating_point())
     return t
 

@@ -269,14 +269,21 @@ def batch(reader, batch_size, drop_last=False):
 class iinfo:
     def __init__(self, dtype):
         i = torch.iinfo(_dt.to_torch(dtype))
-        self.min, self.max, self.bits, self.dtype = i.min, i.max, i.bits, str(dtype)
+        self.min, self.max, self.bits, self.dtype = i.min, i.max, i.bits, _dt.to_name(_dt.to_torch(dtype))
+
+    def __repr__(self):
+        return f"paddle.iinfo(min={self.min}, max={self.max}, bits={self.bits}, dtype={self.dtype})"
 
 
 class finfo:
     def __init__(self, dtype):
         f = torch.finfo(_dt.to_torch(dtype))
         self.min, self.max, self.eps, self.tiny, self.resolution, self.bits = f.min, f.max, f.eps, f.tiny, f.resolution, f.bits
-        self.smallest_normal, self.dtype = f.smallest_normal, str(dtype)
+        self.smallest_normal, self.dtype = f.smallest_normal, _dt.to_name(_dt.to_torch(dtype))
+
+    def __repr__(self):
+        return (f"paddle.finfo(min={self.min}, max={self.max}, eps={self.eps}, resolution={self.resolution}, "
+                f"smallest_normal={self.smallest_normal}, tiny={self.tiny}, bits={self.bits}, dtype={self.dtype})")
 
 
 pstring, raw = "pstring", "raw"

@@ -522,3 +522,8 @@ class RandomErasing(BaseTransform):
                     return erase(img, i, j, h, w, v, self.inplace)
                 return erase(img, i, j, h, w, 0 if self.value == "random" else v, self.inplace)
         return img
+
+
+# ``paddle.vision.transforms.functional`` is a module of its own in the reference
+from .._core.submodule_alias import alias_submodules as _alias  # noqa: E402
+_alias(__name__, ("functional", "transforms"))

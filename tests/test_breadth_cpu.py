@@ -667,7 +667,7 @@ def test_c_ops_quantisation_optimizer_and_misc_kernel_ops():
     newp, newm = _C_ops.decayed_adagrad(torch.ones(3), g, torch.zeros(3), torch.tensor([0.1]), 0.95, 1e-6)
     assert torch.allclose(newm, 0.05 * g * g) and torch.allclose(newp, 1 - 0.1 * g / (newm.sqrt() + 1e-6))
     # assorted
-    dist, cnt = _C_ops.edit_distance(torch.tensor([[1, 2, 3, 4], [5, 6, 0, 0]]), torch.tensor([[1, 3, 4, 0], [7, 6, 5, 0]]),
+    cnt, dist = _C_ops.edit_distance(torch.tensor([[1, 2, 3, 4], [5, 6, 0, 0]]), torch.tensor([[1, 3, 4, 0], [7, 6, 5, 0]]),
                                      torch.tensor([4, 2]), torch.tensor([3, 3]))
     assert dist.reshape(-1).tolist() == [1.0, 2.0] and int(cnt) == 2
     boxes = torch.tensor([[[-5.0, 3.0, 120.0, 70.0]]])
