@@ -16,14 +16,95 @@ def _p(x):
 class functional:
     @staticmethod
     def get_window(window, win_length, fftbins=True, dtype="float64"):
-        name = window if isinstance(window, str) else window[0]
-        fn = {"hann": torch.hann_window, "hamming": torch.hamming_window, "blackman": torch.blackman_window,
-              "bartlett": torch.bartlett_window, "kaiser": torch.kaiser_window}.get(name)
-        if name in ("rect", "boxcar", "ones"):
-            return as_tensor(torch.ones(win_length, dtype=torch.float64))
-        if fn is None:
-            raise ValueError(f"unknown window {name}")
-        return as_tensor(fn(win_length, periodic=fftbins, dtype=torch.float64))
+        """Window by name, or ``(name, parameter...)`` for the parametrised ones (python/paddle/audio/functional/
+        window.py ``get_window``): hamming, hann, gaussian (std), general_gaussian (power, width), exponential (tau),
+        triang, bohman, blackman, cosine, tukey (alpha), taylor (nbar, sll), bartlett, kaiser (beta), nuttall;
+        ``fftbins`` gives the periodic form used with an FFT."""
+        from .._core import dtype as _dt
+        args = ()
+        if isinstance(window, (tuple, list)):
+            window, args = window[0], tuple(window[1:])
+        if not isinstance(window, str):
+            raise ValueError(f"The window must be a str or a tuple of (str, parameters), got {type(window)}")
+        if window in ("gaussian", "exponential", "kaiser") and not args:
+            raise ValueError(f"The '{window}' window needs one or more parameters -- pass a tuple.")
+        n = int(win_length)
+        m = n + 1 if fftbins else n                      # periodic form: one extra point, last one dropped
+        k = torch.arange(m, dtype=torch.float64)
+
+        def cos_sum(coeffs):
+            w = torch.zeros(m, dtype=torch.float64)
+            for i, a in enumerate(coeffs):
+                w = w + ((-1) ** i) * a * torch.cos(2 * math.pi * i * k / max(m - 1, 1))
+            return w
+        c = (m - 1) / 2.0
+        if window in ("rect", "boxcar", "ones"):
+            w = torch.ones(m, dtype=torch.float64)
+        elif window == "hann":
+            w = cos_sum([0.5, 0.5])
+        elif window == "hamming":
+            w = cos_sum([0.54, 0.46])
+        elif window == "blackman":
+            w = cos_sum([0.42, 0.5, 0.08])
+        elif window == "nuttall":
+            w = cos_sum([0.3635819, 0.4891775, 0.1365995, 0.0106411])
+        elif window == "bartlett":
+            w = 1.0 - torch.abs(2.0 * k / max(m - 1, 1) - 1.0)
+        elif window == "triang":
+            kk = torch.arange(1, (m + 1) // 2 + 1, dtype=torch.float64)
+            half = (2 * kk - 1.0) / m if m % 2 == 0 else 2 * kk / (m + 1.0)
+            w = torch.cat([half, half.flip(0)]) if m % 2 == 0 else torch.cat([half, half[:-1].flip(0)])
+        elif window == "cosine":
+            w = torch.sin(math.pi / m * (k + 0.5))
+        elif window == "bohman":
+            fac = torch.abs(torch.linspace(-1, 1, m, dtype=torch.float64)[1:-1])
+            mid = (1 - fac) * torch.cos(math.pi * fac) + 1.0 / math.pi * torch.sin(math.pi * fac)
+            w = torch.cat([torch.zeros(1, dtype=torch.float64), mid, torch.zeros(1, dtype=torch.float64)])
+        elif window == "gaussian":
+            w = torch.exp(-0.5 * ((k - c) / float(args[0])) ** 2)
+        elif window == "general_gaussian":
+            p_, sig = (float(args[0]), float(args[1])) if len(args) >= 2 else (1.0, float(args[0]) if args else 1.0)
+            w = torch.exp(-0.5 * torch.abs((k - c) / sig) ** (2 * p_))
+        elif window == "exponential":
+            tau = float(args[0])
+            w = torch.exp(-torch.abs(k - c) / tau)
+        elif window == "kaiser":
+            beta = float(args[0])
+            w = torch.special.i0(beta * torch.sqrt((1 - ((k - c) / c) ** 2).clamp(min=0))) / torch.special.i0(torch.tensor(beta, dtype=torch.float64))
+        elif window == "tukey":
+            alpha = float(args[0]) if args else 0.5
+            if alpha <= 0:
+                w = torch.ones(m, dtype=torch.float64)
+            elif alpha >= 1:
+                w = cos_sum([0.5, 0.5])
+            else:
+                width = int(math.floor(alpha * (m - 1) / 2.0))
+                n1, n3 = k[:width + 1], k[m - width - 1:]
+                w1 = 0.5 * (1 + torch.cos(math.pi * (-1 + 2.0 * n1 / alpha / (m - 1))))
+                w3 = 0.5 * (1 + torch.cos(math.pi * (-2.0 / alpha + 1 + 2.0 * n3 / alpha / (m - 1))))
+                w = torch.cat([w1, torch.ones(m - 2 * (width + 1), dtype=torch.float64), w3])
+        elif window == "taylor":
+            nbar, sll = (int(args[0]) if args else 4), (float(args[1]) if len(args) > 1 else 30.0)
+            B = 10 ** (sll / 20)
+            A = math.acosh(B) / math.pi
+            s2 = nbar ** 2 / (A ** 2 + (nbar - 0.5) ** 2)
+            ma = torch.arange(1, nbar, dtype=torch.float64)
+            Fm = torch.empty(nbar - 1, dtype=torch.float64)
+            signs = torch.ones(nbar - 1, dtype=torch.float64)
+            signs[1::2] = -1
+            m2 = ma * ma
+            for mi in range(len(ma)):
+                numer = signs[mi] * torch.prod(1 - m2[mi] / s2 / (A ** 2 + (ma - 0.5) ** 2))
+                denom = 2 * torch.prod(1 - m2[mi] / m2[:mi]) * torch.prod(1 - m2[mi] / m2[mi + 1:])
+                Fm[mi] = numer / denom
+            def W(nn):
+                return 1 + 2 * torch.matmul(Fm.unsqueeze(0), torch.cos(2 * math.pi * ma.unsqueeze(1) * (nn - m / 2.0 + 0.5) / m))
+            w = W(k).reshape(-1)
+            w = w / W(torch.tensor([(m - 1) / 2.0], dtype=torch.float64)).reshape(-1)
+        else:
+            raise ValueError(f"Unknown window type: {window}")
+        w = w[:n] if fftbins else w
+        return as_tensor(w.to(_dt.to_torch(dtype)))
 
     @staticmethod
     def hz_to_mel(freq, htk=False):

@@ -75,6 +75,18 @@ def init_parallel_env(backend=None):
     world = tdist.get_world_size()
     g = C.Group(tdist.get_rank(), 0, list(range(world)), tdist.group.WORLD, name="_default_pg")
     C._set_default_group(g)
+    if backend == "gloo":
+        # gloo keeps worker threads per group; leaving the interpreter with them alive ends some runs with
+        # "terminate called without an active exception", so the groups are taken down at exit
+        import atexit
+
+        def _shutdown():
+            try:
+                if tdist.is_initialized():
+                    tdist.destroy_process_group()
+            except Exception:  # noqa: BLE001 - never turn a clean exit into a failure
+                pass
+        atexit.register(_shutdown)
     from ..framework.flags import flag
     if flag("enable_async_trace"):
         from . import watchdog

@@ -53,10 +53,8 @@ def summary_string(model, input_size=None, dtypes=None, input=None):
         elif isinstance(dtypes, str):
             dtypes = [dtypes] * len(sizes)
         args = [paddle.zeros(s, dtype=d) if "float" in str(d) else paddle.zeros(s, dtype=d) for s, d in zip(sizes, dtypes)]
-    elif isinstance(input, dict):
-        args = None
     else:
-        args = list(input) if isinstance(input, (list, tuple)) else [input]
+        args = [input]               # a given input is passed as ONE argument, whatever its type (tensor, list, dict)
     rows = OrderedDict()
     hooks = []
 
@@ -73,7 +71,7 @@ def summary_string(model, input_size=None, dtypes=None, input=None):
     model.eval()
     try:
         with torch.no_grad():
-            model(**input) if isinstance(input, dict) else model(*args)
+            model(*args)
     finally:
         for h in hooks:
             h.remove()
@@ -88,7 +86,16 @@ def summary_string(model, input_size=None, dtypes=None, input=None):
     for k, r in rows.items():
         out.append(f"{k:<{w[0]}}{str(r['input_shape'])[:w[1] - 1]:<{w[1]}}{str(r['output_shape'])[:w[2] - 1]:<{w[2]}}{r['nb_params']:>{w[3]},d}")
         total_out += _numel_of(r["output_shape"])
-    in_numel = sum(int(torch.Tensor.numel(a)) for a in (args or []) if isinstance(a, torch.Tensor))
+    def _leaves(o):
+        if isinstance(o, torch.Tensor):
+            yield o
+        elif isinstance(o, (list, tuple)):
+            for v in o:
+                yield from _leaves(v)
+        elif isinstance(o, dict):
+            for v in o.values():
+                yield from _leaves(v)
+    in_numel = sum(int(torch.Tensor.numel(a)) for a in _leaves(args))
     mb = lambda n: n * 4 / 1024 ** 2
     out += ["=" * sum(w), f"Total params: {total:,d}", f"Trainable params: {trainable:,d}", f"Non-trainable params: {total - trainable:,d}", line,
             f"Input size (MB): {mb(in_numel):.2f}", f"Forward/backward pass size (MB): {mb(2 * total_out):.2f}", f"Params size (MB): {mb(total):.2f}",

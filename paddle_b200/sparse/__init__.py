@@ -13,7 +13,11 @@ __all__ = ["sparse_coo_tensor", "sparse_csr_tensor", "sin", "tan", "asin", "atan
            "isnan", "slice", "pca_lowrank", "mask_as"]
 
 
+from .tensor import SparseTensor, api as _api, unwrap as _unwrap, wrap as _wrap  # noqa: E402
+
+
 def _p(x):
+    x = _unwrap(x)
     return x.as_subclass(torch.Tensor) if isinstance(x, torch.Tensor) else torch.as_tensor(x)
 
 
@@ -103,8 +107,14 @@ def transpose(x, perm, name=None):
 
 def sum(x, axis=None, dtype=None, keepdim=False, name=None):
     d = x.to_dense()
-    out = d.sum() if axis is None else d.sum(axis, keepdim=keepdim)
-    return out.to_sparse_coo() if out.dim() > 0 else as_tensor(out)
+    if dtype is not None:
+        from .._core import dtype as _dt
+        d = d.to(_dt.to_torch(dtype))
+    if axis is None:                                  # the total comes back as a sparse tensor of shape [1]
+        out = d.sum().reshape([1] * d.dim() if keepdim else [1])
+    else:
+        out = d.sum(axis, keepdim=keepdim)
+    return out.to_sparse_csr() if (x.layout == torch.sparse_csr and out.dim() == 2) else out.to_sparse_coo()
 
 
 def coalesce(x, name=None):
@@ -134,3 +144,11 @@ def mask_as(x, mask, name=None):
 
 def pca_lowrank(x, q=None, center=True, niter=2, name=None):
     return tuple(as_tensor(t) for t in torch.pca_lowrank(x.to_dense(), q, center, niter))
+
+
+# every public operator takes and returns SparseTensor (dense results come back as package tensors)
+for _n in list(__all__):
+    if callable(globals().get(_n)) and _n != "is_same_shape":
+        globals()[_n] = _api(globals()[_n])
+is_same_shape = (lambda f: lambda x, y: f(_unwrap(x), _unwrap(y)))(is_same_shape)
+del _n

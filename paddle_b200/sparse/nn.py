@@ -248,11 +248,22 @@ import types as _types  # noqa: E402
 
 def _namespace_module(ns, name):
     m = _types.ModuleType(name)
+    from .tensor import api
     for k, v in vars(ns).items():
         if not k.startswith("__"):
-            setattr(m, k, v.__func__ if isinstance(v, staticmethod) else v)
+            f = v.__func__ if isinstance(v, staticmethod) else v
+            setattr(m, k, api(f) if callable(f) else f)       # take and return SparseTensor
     _sys.modules[name] = m
     return m
 
 
 functional = _namespace_module(functional, __name__ + ".functional")
+
+
+# layers take and return SparseTensor
+from .tensor import api as _api  # noqa: E402
+for _cls in (ReLU, ReLU6, LeakyReLU, Softmax, BatchNorm, SyncBatchNorm, Conv3D, SubmConv3D, Conv2D, SubmConv2D, MaxPool3D):
+    if "forward" in vars(_cls):
+        _cls.forward = _api(_cls.forward)
+_SparseConv.forward = _api(_SparseConv.forward)
+del _cls

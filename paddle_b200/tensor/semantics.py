@@ -551,12 +551,14 @@ def _field(self, which):
 def _to_sparse_coo(self, sparse_dim=None):
     """COO form with the first ``sparse_dim`` dims indexed (all dims by default)."""
     plain = self.detach().as_subclass(torch.Tensor) if not self.requires_grad else self.as_subclass(torch.Tensor)
-    return plain.to_sparse(sparse_dim if sparse_dim is not None else plain.dim())
+    from ..sparse.tensor import SparseTensor
+    return SparseTensor(plain.to_sparse(sparse_dim if sparse_dim is not None else plain.dim()))
 
 
 def _to_sparse_csr(self):
+    from ..sparse.tensor import SparseTensor
     plain = self.detach().as_subclass(torch.Tensor) if not self.requires_grad else self.as_subclass(torch.Tensor)
-    return plain.to_sparse_csr()
+    return SparseTensor(plain.to_sparse_csr())
 
 
 def _reshape_method(self, *shape, **kw):

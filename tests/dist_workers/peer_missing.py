@@ -15,7 +15,7 @@ g = dist.new_group([0, 1], timeout=datetime.timedelta(seconds=3))
 x = torch.ones(4)
 dist.all_reduce(x, group=g)           # one healthy collective first
 if rank == 1:
-    _common.dump({"left": True})
+    _common.dump({"left": True}, teardown=False)
     sys.exit(0)
 t0 = time.time()
 err = None
@@ -23,4 +23,4 @@ try:
     dist.all_reduce(x, group=g)
 except Exception as e:  # noqa: BLE001
     err = type(e).__name__ + ": " + str(e)[:120]
-_common.dump({"elapsed": time.time() - t0, "error": err, "first": x.tolist()})
+_common.dump({"elapsed": time.time() - t0, "error": err, "first": x.tolist()}, teardown=False)
