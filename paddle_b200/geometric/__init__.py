@@ -41,7 +41,10 @@ def _combine(a, b, op):
 
 def send_ue_recv(x, y, src_index, dst_index, message_op="add", reduce_op="sum", out_size=None, name=None):
     x, y = _p(x), _p(y)
-    msg = _combine(x[_p(src_index).long()], y, message_op)
+    gathered = x[_p(src_index).long()]
+    if y.dim() < gathered.dim():                      # one value per edge: broadcast over the feature dims
+        y = y.reshape(list(y.shape) + [1] * (gathered.dim() - y.dim()))
+    msg = _combine(gathered, y, message_op)
     n = int(out_size) if out_size is not None else x.shape[0]
     return as_tensor(_reduce(msg, dst_index, n, reduce_op))
 
@@ -88,10 +91,23 @@ def reindex_graph(x, neighbors, count, value_buffer=None, index_buffer=None, nam
 
 
 def reindex_heter_graph(x, neighbors, count, value_buffer=None, index_buffer=None, name=None):
-    nb = torch.cat([_p(n).long() for n in neighbors])
-    src, _, out = reindex_graph(x, nb, torch.cat([_p(c).long() for c in count]))
-    dst = torch.cat([torch.repeat_interleave(torch.arange(_p(x).numel()), _p(c).long()) for c in count])
-    return src, as_tensor(dst), out
+    """Several edge types over the same centre nodes ``x``: ``neighbors[i]`` / ``count[i]`` list the neighbours of each
+    centre node under type i.  Ids are renumbered in one space: the centre nodes first, then every new neighbour in order
+    of first appearance over the types.  -> (reindexed sources of all types concatenated, their destination = index
+    of the centre node, the node list)."""
+    centres = _p(x).long().tolist()
+    ids = {v: i for i, v in enumerate(centres)}
+    nodes = list(centres)
+    src, dst = [], []
+    for nb, c in zip(neighbors, count):
+        for v in _p(nb).long().tolist():
+            if v not in ids:
+                ids[v] = len(nodes)
+                nodes.append(v)
+            src.append(ids[v])
+        dst.append(torch.repeat_interleave(torch.arange(len(centres)), _p(c).long()))
+    return (as_tensor(torch.tensor(src, dtype=torch.int64)), as_tensor(torch.cat(dst) if dst else torch.zeros(0, dtype=torch.int64)),
+            as_tensor(torch.tensor(nodes, dtype=torch.int64)))
 
 
 def sample_neighbors(row, colptr, input_nodes, sample_size=-1, eids=None, return_eids=False, perm_buffer=None, name=None):
