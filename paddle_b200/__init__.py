@@ -198,11 +198,23 @@ def set_grad_enabled_ctx(mode):
     return _torch.set_grad_enabled(mode)
 
 
+_lazy_depth = [0]
+
+
+def _lazy_init_active():
+    return _lazy_depth[0] > 0
+
+
 class LazyGuard:
+    """Layers built inside the guard get parameters whose initial values are not computed until
+    ``param.initialize()`` is called (python/paddle/nn/initializer/lazy_init.py)."""
+
     def __enter__(self):
+        _lazy_depth[0] += 1
         return self
 
     def __exit__(self, *a):
+        _lazy_depth[0] -= 1
         return False
 
 

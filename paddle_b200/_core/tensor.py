@@ -391,6 +391,14 @@ class Tensor(torch.Tensor):
 class EagerParamBase(Tensor):
     """Trainable parameter (python/paddle/base/framework.py ``EagerParamBase``)."""
 
+    def initialize(self):
+        """Run the initializer that ``paddle.LazyGuard`` deferred (no effect on an initialised parameter)."""
+        init = self.__dict__.pop("_deferred_init", None)
+        if init is not None:
+            with torch.no_grad():
+                init(self)
+        return self
+
     @staticmethod
     def __new__(cls, data, trainable=True, name=None):
         t = torch.Tensor._make_subclass(cls, data.detach(), trainable)

@@ -86,7 +86,12 @@ def reindex_graph(x, neighbors, count, value_buffer=None, index_buffer=None, nam
             first[v] = len(uniq)
             uniq.append(v)
     src = torch.tensor([first[v] for v in neighbors.tolist()], dtype=torch.int64)
-    dst = torch.repeat_interleave(torch.arange(x.numel()), count)
+    n = x.numel()
+    if count.numel() != n and n and count.numel() % n == 0:
+        # several edge types in one call: neighbours and counts of the types are concatenated
+        dst = torch.cat([torch.repeat_interleave(torch.arange(n), count[i * n:(i + 1) * n]) for i in range(count.numel() // n)])
+    else:
+        dst = torch.repeat_interleave(torch.arange(n), count)
     return as_tensor(src), as_tensor(dst), as_tensor(torch.tensor(uniq, dtype=torch.int64))
 
 

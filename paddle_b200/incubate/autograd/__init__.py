@@ -131,3 +131,7 @@ class Hessian(Jacobian):
             self._mat = torch.cat(parts, -1)
         else:
             self._mat = torch.cat([j.reshape(j.shape[0], -1) for j in jac], -1)
+
+
+from ..._core.submodule_alias import alias_submodules as _alias  # noqa: E402
+_alias(__name__, ("functional", "primapi", "utils"))

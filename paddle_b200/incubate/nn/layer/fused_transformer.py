@@ -43,6 +43,35 @@ class FusedDropoutAdd(Layer):
         return IF.fused_dropout_add(x, y, self.p, self.training, self.mode)
 
 
+class FusedDropout(Layer):
+    """Dropout that may share one keep decision along some axes (python/paddle/incubate/nn/layer/fused_dropout_nd.py):
+    with ``axis`` given the mask has size 1 on every other axis and is broadcast, so whole slices are dropped."""
+
+    def __init__(self, p=0.5, axis=None, mode="upscale_in_train", name=None):
+        super().__init__()
+        if not isinstance(p, (float, int)) or p < 0 or p > 1:
+            raise ValueError("p argument should be a number between 0 and 1")
+        if mode not in ("downscale_in_infer", "upscale_in_train"):
+            raise ValueError("mode argument should be 'downscale_in_infer' or 'upscale_in_train'")
+        if axis is not None and not isinstance(axis, (int, list, tuple)):
+            raise TypeError("datatype of axis argument should be int or list")
+        self.p, self.axis, self.mode = float(p), axis, mode
+
+    def forward(self, x):
+        import torch
+        if not self.training or self.p == 0.0:
+            return x if self.mode == "upscale_in_train" or not self.training and self.p == 0 else x * (1.0 - self.p) \
+                if self.mode == "downscale_in_infer" and not self.training else x
+        if self.p == 1.0:
+            return x * 0
+        shape = list(x.shape)
+        if self.axis is not None:
+            axes = [self.axis] if isinstance(self.axis, int) else list(self.axis)
+            shape = [s if i in [a % len(shape) for a in axes] else 1 for i, s in enumerate(shape)]
+        keep = (torch.rand(shape, device=x.device) >= self.p).to(x.dtype)
+        return x * keep / (1.0 - self.p) if self.mode == "upscale_in_train" else x * keep
+
+
 class FusedBiasDropoutResidualLayerNorm(Layer):
     def __init__(self, embed_dim, dropout_rate=0.5, weight_attr=None, bias_attr=None, epsilon=1e-5, name=None):
         super().__init__()

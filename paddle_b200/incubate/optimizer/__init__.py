@@ -30,7 +30,10 @@ class LookAhead:
                     p.copy_(slow)
 
     def minimize(self, loss, startup_program=None, parameters=None, no_grad_set=None):
-        loss.backward()
+        """Dynamic mode: the caller ran ``loss.backward()``; apply the gradients that exist (run it when none do)."""
+        has_grads = any(p.grad is not None for p in self.inner_optimizer._parameter_list)
+        if not has_grads and getattr(loss, "grad_fn", None) is not None:
+            loss.backward()
         self.step()
         return None, None
 
@@ -69,6 +72,15 @@ class ModelAverage:
 
     def minimize(self, loss, *a, **k):
         self.step()
+
+    def clear_grad(self, set_to_zero=True):
+        """Gradients belong to the inner optimizer's parameters; cleared here for loops that drive both optimizers."""
+        for p in self._params:
+            if p.grad is not None:
+                if set_to_zero:
+                    p.grad.zero_()
+                else:
+                    p.grad = None
 
     def apply(self, executor=None, need_restore=True):
         ma = self

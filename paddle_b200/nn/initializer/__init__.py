@@ -133,7 +133,9 @@ class Assign(Initializer):
     def __call__(self, param, block=None):
         v = self.value if isinstance(self.value, torch.Tensor) else torch.as_tensor(np.asarray(self.value))
         with torch.no_grad():
-            param.copy_(v.to(param.dtype).reshape(param.shape))
+            v = v.to(param.dtype)
+            # a value with fewer elements than the parameter is broadcast (Assign(np.array([2, 2])) fills a 2 x 2 weight)
+            param.copy_(v.reshape(param.shape) if v.numel() == param.numel() else torch.broadcast_to(v, param.shape))
         return param
 
 

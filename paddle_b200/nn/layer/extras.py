@@ -418,7 +418,8 @@ def dynamic_decode(decoder, inits=None, max_step_num=None, output_time_major=Fal
                    is_test=False, return_length=False, **kwargs):
     inputs, states, finished = decoder.initialize(inits)
     outputs, step = [], 0
-    while not bool(finished.all()) and (max_step_num is None or step < max_step_num):
+    # steps 0 .. max_step_num inclusive, as the reference's loop (``step_idx > max_step_num`` ends it)
+    while not bool(finished.all()) and (max_step_num is None or step <= max_step_num):
         out, states, inputs, finished = decoder.step(step, inputs, states, **kwargs)
         outputs.append(out)
         step += 1

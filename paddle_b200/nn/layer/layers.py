@@ -117,6 +117,12 @@ class Layer:
         init = attr.initializer or default_initializer or _global_initializer(is_bias)
         if init is None:
             init = Constant(0.0) if is_bias else XavierUniform()
+        from ... import _lazy_init_active
+        if _lazy_init_active():
+            # under ``paddle.LazyGuard`` the values are not computed yet: ``param.initialize()`` runs the initializer
+            # (the storage is reserved but untouched, so no pages are committed until then)
+            p._deferred_init = init
+            return p
         with torch.no_grad():
             init(p)
         return p
