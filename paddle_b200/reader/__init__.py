@@ -137,3 +137,8 @@ def multiprocess_reader(readers, use_pipe=True, queue_size=1000):
             else:
                 yield s
     return reader
+
+
+# the functions live in ``paddle.reader.decorator`` in the reference
+from .._core.submodule_alias import alias_submodules as _alias  # noqa: E402
+_alias(__name__, ("decorator",))

@@ -295,8 +295,95 @@ def yolo_box(x, img_size, anchors, class_num, conf_thresh, downsample_ratio, cli
     return as_tensor(boxes.reshape(N, -1, 4)), as_tensor(scores.reshape(N, -1, class_num))
 
 
-def yolo_loss(*a, **k):
-    raise NotImplementedError("yolo_loss (YOLOv3 training loss) is not provided; compose it from yolo_box and the losses in paddle.nn")
+def _sce(x, label):
+    """Sigmoid cross entropy on a logit, log(1 + e^x) - x * label (softplus keeps it stable and smooth at 0)."""
+    return torch.nn.functional.softplus(x) - x * label
+
+
+def yolo_loss(x, gt_box, gt_label, anchors, anchor_mask, class_num, ignore_thresh, downsample_ratio, gt_score=None,
+              use_label_smooth=True, name=None, scale_x_y=1.0):
+    """YOLOv3 training loss of one detection head (python/paddle/vision/ops.py ``yolo_loss``; kernel
+    paddle/phi/kernels/cpu/yolo_loss_kernel.cc).  ``x`` [N, len(anchor_mask) * (5 + class_num), H, W] raw head output;
+    ``gt_box`` [N, B, 4] normalised (cx, cy, w, h), rows with w or h <= 0 are padding; ``gt_label`` [N, B].  Per image:
+
+    * every prediction whose decoded box overlaps some ground truth by more than ``ignore_thresh`` is left out of the
+      objectness loss unless it is a positive;
+    * every ground truth picks, among ALL anchors, the one whose shape fits best; when that anchor belongs to this head
+      (``anchor_mask``) the cell holding the box centre becomes a positive: sigmoid cross entropy on the centre offsets,
+      L1 on the log sizes, both weighted by ``(2 - w * h) * score``; class sigmoid cross entropy (smoothed targets
+      ``1 - 1 / class_num`` / ``1 / class_num`` with ``use_label_smooth``) weighted by ``score``; objectness target
+      ``score`` (``gt_score``, 1 by default);
+    * all other kept predictions have objectness target 0.
+    -> loss [N]."""
+    xt = _p(x)
+    xt = xt if xt.dtype == torch.float64 else xt.float()
+    gb, gl = _p(gt_box).to(xt.dtype), _p(gt_label).long()
+    N, _, H, W = xt.shape
+    an_num, mask_num = len(anchors) // 2, len(anchor_mask)
+    B = gb.shape[1]
+    gs = _p(gt_score).to(xt.dtype) if gt_score is not None else torch.ones(N, B, dtype=xt.dtype)
+    input_size = downsample_ratio * H
+    v = xt.reshape(N, mask_num, 5 + class_num, H, W)
+    bias = -0.5 * (scale_x_y - 1.0)
+    pos, neg = (1.0 - 1.0 / class_num, 1.0 / class_num) if use_label_smooth else (1.0, 0.0)
+    aw_all = torch.tensor(anchors[0::2], dtype=xt.dtype)
+    ah_all = torch.tensor(anchors[1::2], dtype=xt.dtype)
+    # decoded prediction boxes (no gradient: they only decide which predictions are ignored)
+    with torch.no_grad():
+        gx = torch.arange(W, dtype=xt.dtype).reshape(1, 1, 1, W)
+        gy = torch.arange(H, dtype=xt.dtype).reshape(1, 1, H, 1)
+        maw = aw_all[list(anchor_mask)].reshape(1, mask_num, 1, 1)
+        mah = ah_all[list(anchor_mask)].reshape(1, mask_num, 1, 1)
+        px = (gx + torch.sigmoid(v[:, :, 0]) * scale_x_y + bias) / W
+        py = (gy + torch.sigmoid(v[:, :, 1]) * scale_x_y + bias) / H
+        pw = torch.exp(v[:, :, 2]) * maw / input_size
+        ph = torch.exp(v[:, :, 3]) * mah / input_size
+        valid = (gb[..., 2] > 0) & (gb[..., 3] > 0)                                   # [N, B]
+
+        def iou_cxcywh(ax, ay, aw_, ah_, bx, by, bw, bh):
+            l = torch.maximum(ax - aw_ / 2, bx - bw / 2)
+            r = torch.minimum(ax + aw_ / 2, bx + bw / 2)
+            t = torch.maximum(ay - ah_ / 2, by - bh / 2)
+            b = torch.minimum(ay + ah_ / 2, by + bh / 2)
+            inter = (r - l).clamp(min=0) * (b - t).clamp(min=0)
+            return inter / (aw_ * ah_ + bw * bh - inter).clamp(min=1e-10)
+        e = lambda t: t.unsqueeze(-1)                                                  # noqa: E731
+        g = lambda t: t.reshape(N, 1, 1, 1, B)                                         # noqa: E731
+        ious = iou_cxcywh(e(px), e(py), e(pw), e(ph), g(gb[..., 0]), g(gb[..., 1]), g(gb[..., 2]), g(gb[..., 3]))
+        ious = torch.where(valid.reshape(N, 1, 1, 1, B), ious, torch.zeros_like(ious))
+        obj_mask = torch.where(ious.max(-1).values > ignore_thresh, -torch.ones_like(px), torch.zeros_like(px))   # [N, A, H, W]
+    loss = xt.new_zeros(N)
+    for i in range(N):
+        for t in range(B):
+            if not bool(valid[i, t]):
+                continue
+            bx, by, bw, bh = (float(c) for c in gb[i, t])
+            gi, gj = int(bx * W), int(by * H)
+            # best anchor by shape overlap (both boxes centred at the origin)
+            iw = torch.minimum(aw_all / input_size, torch.tensor(bw, dtype=xt.dtype))
+            ih = torch.minimum(ah_all / input_size, torch.tensor(bh, dtype=xt.dtype))
+            inter = iw * ih
+            shape_iou = inter / (aw_all * ah_all / input_size ** 2 + bw * bh - inter)
+            best_n = int(torch.argmax(shape_iou))
+            if best_n not in list(anchor_mask):
+                continue
+            a = list(anchor_mask).index(best_n)
+            score = gs[i, t]
+            tx, ty = bx * W - gi, by * H - gj
+            tw = math.log(bw * input_size / anchors[2 * best_n])
+            th = math.log(bh * input_size / anchors[2 * best_n + 1])
+            scale = (2.0 - bw * bh) * score
+            cell = v[i, a, :, gj, gi]
+            loss[i] = loss[i] + (_sce(cell[0], tx) + _sce(cell[1], ty) + (cell[2] - tw).abs() + (cell[3] - th).abs()) * scale
+            obj_mask[i, a, gj, gi] = score
+            target = torch.full((class_num,), neg, dtype=xt.dtype)
+            target[int(gl[i, t])] = pos
+            loss[i] = loss[i] + (_sce(cell[5:], target) * score).sum()
+    obj_logit = v[:, :, 4]
+    pos_part = torch.where(obj_mask > 1e-6, _sce(obj_logit, torch.ones_like(obj_logit)) * obj_mask, torch.zeros_like(obj_logit))
+    neg_part = torch.where((obj_mask <= 1e-6) & (obj_mask > -0.5), _sce(obj_logit, torch.zeros_like(obj_logit)), torch.zeros_like(obj_logit))
+    loss = loss + (pos_part + neg_part).sum((1, 2, 3))
+    return as_tensor(loss.to(_p(x).dtype))
 
 
 def matrix_nms(bboxes, scores, score_threshold, post_threshold, nms_top_k, keep_top_k, use_gaussian=False,

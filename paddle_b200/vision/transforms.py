@@ -103,16 +103,62 @@ def to_grayscale(img, num_output_channels=1):
         else back(g.expand(3, -1, -1)) if num_output_channels == 3 else np.asarray(g[0].round().clamp(0, 255).to(torch.uint8))
 
 
+def _is_pil_image(img):
+    try:
+        from PIL import Image
+    except ImportError:
+        return False
+    return isinstance(img, Image.Image)
+
+
+def _is_numpy_image(img):
+    return isinstance(img, np.ndarray) and img.ndim in (2, 3)
+
+
+def _is_tensor_image(img):
+    return isinstance(img, torch.Tensor)
+
+
 class BaseTransform:
+    """Base of the transforms (python/paddle/vision/transforms/transforms.py ``BaseTransform``).  ``keys`` names what each
+    element of a tuple input is (``"image"``, ``"coords"``, ``"boxes"``, ``"mask"``; ``None`` entries pass through) and
+    every element goes to ``_apply_<key>``.  ``_get_params(inputs)`` is evaluated once per call into ``self.params`` so
+    that random decisions are shared by all elements."""
+
     def __init__(self, keys=None):
-        self.keys = keys
+        if keys is None:
+            keys = ("image",)
+        elif not isinstance(keys, (list, tuple)):
+            raise ValueError(f"keys should be a list or tuple, but got {type(keys)}")
+        for k in keys:
+            if k is not None and not hasattr(self, f"_apply_{k}") and k not in ("image", "coords", "boxes", "mask"):
+                raise NotImplementedError(f"{k} is unsupported data structure")
+        self.keys = tuple(keys)
+        self.params = None
+
+    def _get_params(self, inputs):
+        return None
 
     def __call__(self, inputs):
-        if isinstance(inputs, tuple) and self.keys:
-            return tuple(self._apply_image(x) if k == "image" else x for x, k in zip(inputs, self.keys))
-        return self._apply_image(inputs)
+        is_seq = isinstance(inputs, (tuple, list))
+        seq = tuple(inputs) if is_seq else (inputs,)
+        self.params = self._get_params(seq)
+        out = []
+        for i, x in enumerate(seq):
+            key = self.keys[i] if i < len(self.keys) else None
+            fn = getattr(self, f"_apply_{key}", None) if key is not None else None
+            out.append(fn(x) if fn is not None else x)
+        if not is_seq:
+            return out[0]
+        return tuple(out) if isinstance(inputs, tuple) else out
 
     def _apply_image(self, img):
+        raise NotImplementedError
+
+    def _apply_boxes(self, boxes):
+        raise NotImplementedError
+
+    def _apply_mask(self, mask):
         raise NotImplementedError
 
 

@@ -123,9 +123,24 @@ def outputs_match(want, got, rtol=2e-3, atol=2e-5):
     return _skeleton(want) == _skeleton(got)
 
 
+def _reset_global_state(paddle_module):
+    """Examples switch global modes (grad mode, default dtype, print options, device, lazy init) and do not always
+    switch them back; every block starts from the defaults."""
+    import torch
+    torch.set_grad_enabled(True)
+    try:
+        paddle_module.set_default_dtype("float32")
+        paddle_module.set_printoptions(precision=8, threshold=1000, edgeitems=3, linewidth=80, sci_mode=False)
+        paddle_module.set_device("cpu")
+        paddle_module.disable_static()
+    except Exception:  # noqa: BLE001
+        pass
+
+
 def run_block(examples, paddle_module, timeout_s=20, check_values=True):
     """-> ("pass" | "fail" | "error" | "timeout", detail)."""
     ns = {"paddle": paddle_module, "__name__": "__main__"}
+    _reset_global_state(paddle_module)
 
     def on_alarm(signum, frame):
         raise _Timeout()

@@ -787,3 +787,50 @@ def test_c_ops_recurrent_and_detection_ops():
     b = torch.roll(a, shifts=1, dims=3)                       # b[..., x] = a[..., x - 1]
     out = _C_ops.correlation(a, b, 2, 1, 2, 1, 1)
     assert torch.allclose(out[0, 13, :, :5], (a * a).mean(1)[0, :, :5], atol=1e-6)             # displacement (0, +1)
+
+
+def test_yolo_loss_hand_computed_and_asp_utilities():
+    """YOLOv3 head loss on a case worked out by hand (zero logits: every sigmoid cross entropy is log 2), and the n:m
+    sparsity helpers with the reference's conventions (``n`` zeros out of ``m``)."""
+    import math
+
+    import numpy as np
+    import torch
+
+    import paddle_b200 as paddle
+    from paddle_b200.incubate import asp
+    x = paddle.zeros([1, 7, 2, 2])
+    x.stop_gradient = False
+    gt = paddle.to_tensor(np.array([[[0.25, 0.25, 0.5, 0.5], [0, 0, 0, 0]]], "float32"))
+    lab = paddle.to_tensor(np.array([[1, 0]], "int32"))
+    loss = paddle.vision.ops.yolo_loss(x, gt, lab, [32, 32], [0], 2, 0.7, 32, use_label_smooth=False)
+    # location 2 * log2 * (2 - 0.25), sizes 0, classes 2 * log2, objectness: 1 positive + 3 negatives
+    assert abs(float(loss) - 9.5 * math.log(2)) < 1e-5
+    loss.sum().backward()
+    g = x.grad.numpy()[0]
+    # d/dlogit of the cross entropy is sigmoid - target: objectness -0.5 / +0.5, classes +0.5 / -0.5, centre offsets 0
+    assert abs(g[4, 0, 0] + 0.5) < 1e-6 and abs(g[4, 1, 1] - 0.5) < 1e-6 and abs(g[6, 0, 0] + 0.5) < 1e-6 and abs(g[5, 0, 0] - 0.5) < 1e-6
+    assert abs(g[0, 0, 0]) < 1e-6 and g[5, 1, 1] == 0
+    smooth = paddle.vision.ops.yolo_loss(paddle.zeros([1, 7, 2, 2]), gt, lab, [32, 32], [0], 2, 0.7, 32, use_label_smooth=True)
+    assert abs(float(smooth) - 9.5 * math.log(2)) < 1e-5          # zero logits: the target does not change log 2
+    other_head = paddle.vision.ops.yolo_loss(paddle.zeros([1, 7, 2, 2]), gt, lab, [8, 8, 32, 32], [0], 2, 0.7, 32)
+    assert abs(float(other_head) - 4 * math.log(2)) < 1e-5        # best anchor belongs to another head: four negatives
+    ignored = paddle.vision.ops.yolo_loss(paddle.zeros([1, 7, 2, 2]), gt, lab, [31, 31, 32, 32], [0], 2, 0.7, 32)
+    assert abs(float(ignored) - 3 * math.log(2)) < 1e-5           # the cell whose box overlaps the ground truth is left out
+    # n:m helpers: n ZEROS in every group of m
+    mat = np.array([[1.0, -4.0, 2.0, 3.0, 9.0, 0.5, 0.1, 8.0]])
+    m1 = asp.get_mask_1d(mat, 1, 4)
+    assert m1.tolist() == [[0, 1, 1, 1, 1, 1, 0, 1]] and asp.check_mask_1d(mat * m1, 1, 4) and not asp.check_mask_1d(mat, 1, 4)
+    m2 = asp.get_mask_1d(mat, 3, 4)
+    assert m2.tolist() == [[0, 1, 0, 0, 1, 0, 0, 0]]
+    blk = np.array([[9, 8, 3, 7], [9, 2, 1, 10], [5, 1, 3, 6], [2, 4, 6, 1]], "float64")
+    greedy, best = asp.get_mask_2d_greedy(blk, 2, 4), asp.get_mask_2d_best(blk, 2, 4)
+    assert greedy.tolist() == [[1, 1, 0, 0], [1, 0, 0, 1], [0, 0, 1, 1], [0, 1, 1, 0]]
+    assert asp.check_mask_2d(greedy, 2, 4) and asp.check_mask_2d(best, 2, 4)
+    assert (blk * best).sum() >= (blk * greedy).sum() == 55.0
+    blk2 = np.array([[2, 8, 9, 9], [9, 1, 3, 9], [5, 6, 3, 9], [2, 4, 6, 9]], "float64")      # here greedy is not optimal
+    assert (blk2 * asp.get_mask_2d_greedy(blk2, 2, 4)).sum() == 56.0 and (blk2 * asp.get_mask_2d_best(blk2, 2, 4)).sum() == 61.0
+    assert asp.CheckMethod.get_checking_method(asp.MaskAlgo.MASK_2D_BEST) == asp.CheckMethod.CHECK_2D
+    t = paddle.randn([8, 16])
+    mask = asp.create_mask(t, asp.MaskAlgo.MASK_1D, 2, 4)
+    assert asp.check_sparsity(torch.as_tensor(t) * mask, asp.CheckMethod.CHECK_1D, 2, 4) and abs(float(mask.mean()) - 0.5) < 1e-6

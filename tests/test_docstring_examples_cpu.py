@@ -21,6 +21,12 @@ GROUPS = {
     "nn_layer": (["nn/layer/*.py"], 164, 4),
     "optimizer_autograd_amp": (["optimizer/*.py", "autograd/*.py", "amp/*.py", "metric/*.py", "framework/*.py", "fft.py", "signal.py",
                                 "regularizer.py", "io/dataloader/*.py"], 143, 4),
+    "sparse_quant_init": (["sparse/*.py", "sparse/nn/functional/*.py", "sparse/nn/layer/*.py", "quantization/*.py", "nn/initializer/*.py",
+                          "nn/utils/*.py", "nn/clip.py", "nn/decode.py"], 82, 8),
+    "incubate_vision_hapi_misc": (["incubate/asp/*.py", "incubate/optimizer/*.py", "incubate/autograd/*.py", "incubate/nn/layer/*.py",
+                                  "incubate/tensor/*.py", "incubate/operators/*.py", "reader/*.py", "hapi/*.py", "vision/ops.py",
+                                  "vision/transforms/*.py", "base/dygraph/base.py", "utils/*.py", "device/__init__.py", "profiler/*.py"],
+                                 118, 16),
     "distribution_audio_geometric_text": (["distribution/*.py", "audio/*/*.py", "geometric/*.py", "geometric/*/*.py", "text/*.py"], 86, 8),
 }
 
