@@ -624,3 +624,8 @@ def load_inference_model(path_prefix, executor=None, **kw):  # noqa: F811
 
 
 from . import nn  # noqa: E402,F401
+
+
+from .._core.submodule_alias import alias_submodules as _alias  # noqa: E402
+_alias(__name__, ("io", "input", "log_helper", "pir_io"))
+_alias(__name__ + ".nn", ("common", "control_flow", "loss", "metric", "sequence_lod", "static_pylayer"))

@@ -165,7 +165,10 @@ class Block:
 
     def create_var(self, name=None, shape=None, dtype="float32", persistable=False, **kw):
         from . import create_global_var
-        return create_global_var(shape or [1], 0.0, dtype, persistable, name=name)
+        declared = list(shape or [1])
+        v = create_global_var([1 if (d is None or d < 0) else int(d) for d in declared], 0.0, dtype, persistable, name=name)
+        v._declared_shape = [(-1 if d is None else int(d)) for d in declared]      # unknown extents are recorded as given
+        return v
 
 
 ALL_PROGRAMS = weakref.WeakSet()

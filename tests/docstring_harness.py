@@ -59,14 +59,16 @@ def extract_blocks(path):
     return out
 
 
-def classify_skip(examples):
+def classify_skip(examples, allow=()):
+    """Why a block is not run, or None.  ``allow`` lists categories to run anyway (``"static"``)."""
     text = "\n".join(e.source for e in examples)
     for d in _SKIP_DIRECTIVES:
         if d in text:
             return "directive"
     if "paddle.distributed" in text or "fleet" in text or "dist." in text:
         return "distributed"
-    if "paddle.static" in text or "enable_static" in text or "static." in text or "paddle.base" in text or "fluid" in text:
+    if "static" not in allow and ("paddle.static" in text or "enable_static" in text or "static." in text or "paddle.base" in text
+                                  or "fluid" in text):
         return "static"
     if "cuda" in text or "gpu" in text.lower() and "place" in text.lower():
         return "gpu"
@@ -179,13 +181,13 @@ def run_block(examples, paddle_module, timeout_s=20, check_values=True):
         signal.signal(signal.SIGALRM, old)
 
 
-def run_file(path, paddle_module, only=None):
+def run_file(path, paddle_module, only=None, allow=()):
     """-> {"pass": [...], "fail": [(name, detail)], "error": [...], "skip": [(name, why)]}."""
     res = {"pass": [], "fail": [], "error": [], "timeout": [], "skip": []}
     for name, examples in extract_blocks(path):
         if only and not any(o in name for o in only):
             continue
-        why = classify_skip(examples)
+        why = classify_skip(examples, allow)
         if why:
             res["skip"].append((name, why))
             continue
