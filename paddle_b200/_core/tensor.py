@@ -27,7 +27,15 @@ class _Size(int):
         return self._shape if dim is None else self._shape[dim]
 
 
-class Tensor(torch.Tensor):
+class _TensorMeta(type(torch.Tensor)):
+    """``type(t)`` prints as the reference's ``<class 'paddle.Tensor'>``; the class keeps its real module so that pickles
+    (data-loader workers, checkpoints) resolve it without the ``paddle`` alias package."""
+
+    def __repr__(cls):
+        return "<class 'paddle.Tensor'>" if cls.__name__ == "Tensor" else super().__repr__()
+
+
+class Tensor(torch.Tensor, metaclass=_TensorMeta):
     """Dense tensor with PaddlePaddle's Python surface."""
 
     # ---- identity / meta
@@ -460,9 +468,6 @@ def as_tensor(t: torch.Tensor) -> Tensor:
         return t
     return t.as_subclass(Tensor)
 
-
-Tensor.__module__ = "paddle"          # type(t) prints as <class 'paddle.Tensor'>; the alias package resolves the name
-Tensor.__qualname__ = "Tensor"
 
 
 def to_tensor(data, dtype=None, place=None, stop_gradient=True):

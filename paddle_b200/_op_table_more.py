@@ -507,7 +507,7 @@ def bipartite_match(dist_mat, match_type="bipartite", dist_threshold=0.5):
         work[r, :] = -1
         work[:, c] = -1
     if match_type == "per_prediction":
-        best, arg = d.max(0)
+        best, arg = torch.max(d, 0)
         extra = (idx[0] < 0) & (best >= dist_threshold)
         idx[0, extra] = arg[extra].to(torch.int32)
         dist[0, extra] = best[extra]

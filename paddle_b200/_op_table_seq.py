@@ -347,7 +347,7 @@ def yolo_box_post(boxes0, boxes1, boxes2, image_shape, image_scale, anchors0, an
             x2, y2 = (cx + bw / 2).clamp(max=pic_w - 1), (cy + bh / 2).clamp(max=pic_h - 1)
             o = obj[a, gy, gx]
             probs = v[a, 5:, gy, gx] * o.unsqueeze(-1)
-            best_p, best_c = probs.max(-1)
+            best_p, best_c = torch.max(probs, -1)
             best_c = torch.where(best_p > 0, best_c, torch.full_like(best_c, -1))
             dets.append(torch.stack([best_c.float(), o, x1, y1, x2, y2, best_p], 1))
         if not dets:

@@ -93,7 +93,7 @@ class LlamaForCausalLMInference(nn.Layer):
 
     def _argmax(self, logits):
         """Greedy token from vocabulary-sharded logits."""
-        val, idx = logits.float().max(-1)
+        val, idx = torch.max(logits.float(), -1)
         if self.tp_group is None:
             return idx
         from ..distributed import collective as C

@@ -397,7 +397,7 @@ def sequence_pool(input, pool_type, is_test=False, pad_value=0.0):
     if pt == "sqrt":
         return as_tensor(x.sum(1) / (x.shape[1] ** 0.5))
     if pt == "max":
-        return as_tensor(x.max(1).values)
+        return as_tensor(torch.max(x, 1).values)
     if pt == "first":
         return as_tensor(x[:, 0])
     if pt == "last":

@@ -157,6 +157,14 @@ def _tie_mask_grad_reduce(x, axis, keepdim, largest, even):
     """max / min style reduction; ``even`` splits the gradient between tied extrema (amax / amin), otherwise the
     gradient goes to every tied element in full (max / min of the reference)."""
     x = _t(x)
+    if not (x.requires_grad and torch.is_grad_enabled()):
+        # no gradient to shape: straight to torch (also covers bool / integer inputs)
+        if axis is None or (isinstance(axis, (list, tuple)) and len(axis) == 0):
+            out = torch.max(x) if largest else torch.min(x)
+            return out.reshape([1] * x.dim()) if keepdim else out
+        if isinstance(axis, torch.Tensor):
+            axis = axis.tolist()
+        return (torch.amax if largest else torch.amin)(x, axis if isinstance(axis, int) else tuple(axis), keepdim=keepdim)
     ax = _axes(axis, x.dim())
     dims = list(range(x.dim())) if ax is None else (ax if isinstance(ax, list) else [ax])
     dims = list(dims) or list(range(x.dim()))
@@ -292,7 +300,10 @@ def reshape(x, shape, name=None):
     if isinstance(shape, torch.Tensor):
         shape = shape.tolist()
     shape = [int(s.item()) if isinstance(s, torch.Tensor) else int(s) for s in shape]
-    shape = [x.shape[i] if (s == 0 and i < x.dim()) else s for i, s in enumerate(shape)]
+    if 0 in shape and x.numel() > 0:
+        # with elements present a literal 0 could never be a valid extent: it copies the input's dim (the reference's
+        # rule); an empty input keeps torch's reading of 0 as an empty extent
+        shape = [x.shape[i] if (s == 0 and i < x.dim()) else s for i, s in enumerate(shape)]
     return torch.reshape(x, shape)
 
 
@@ -566,6 +577,12 @@ def _reshape_method(self, *shape, **kw):
         shape = (kw["shape"],)
     if len(shape) == 1 and isinstance(shape[0], (list, tuple, torch.Size, torch.Tensor)):
         shape = shape[0]
+    if not isinstance(shape, torch.Tensor):
+        try:
+            if 0 not in shape:                                       # the common case goes straight to torch
+                return torch.Tensor.reshape(self, tuple(shape))
+        except (TypeError, RuntimeError):
+            pass
     return reshape(self, list(shape) if not isinstance(shape, torch.Tensor) else shape)
 
 

@@ -26,12 +26,12 @@ def viterbi_decode(potentials, transition_params, lengths, include_bos_eos_tag=T
         back = []
         for t in range(1, L):
             m = alpha[:, None] + trans
-            best, idx = m.max(0)
+            best, idx = torch.max(m, 0)
             alpha = best + pot[b, t]
             back.append(idx)
         if include_bos_eos_tag:
             alpha = alpha + trans[:, N - 1]
-        s, last = alpha.max(0)
+        s, last = torch.max(alpha, 0)
         path = [int(last)]
         for idx in reversed(back):
             path.append(int(idx[path[-1]]))

@@ -348,7 +348,7 @@ def adjust_saturation(img, saturation_factor):
 
 def _rgb_to_hsv(t):
     r, g, b = t
-    mx, mn = t.max(0).values, t.min(0).values
+    mx, mn = torch.max(t, 0).values, torch.min(t, 0).values
     d = mx - mn
     s = torch.where(mx > 0, d / mx.clamp_min(1e-12), torch.zeros_like(mx))
     dz = d.clamp_min(1e-12)
