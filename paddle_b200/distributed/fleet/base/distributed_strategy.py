@@ -76,7 +76,24 @@ class DistributedStrategy:
                        "without_graph_optimization": True, "heter_ccl_mode": False, "a_sync": False,
                        "sync_nccl_allreduce": True, "nccl_comm_num": 1, "fuse_grad_merge": False,
                        "fuse_grad_size_in_num": 8, "last_comm_group_size_MB": 1.0, "gradient_scale_configs":
-                       {"scale_strategy": "avg"}}
+                       {"scale_strategy": "avg"},
+                       # switches of the reference's static-graph meta optimizers: kept so that strategy files load and
+                       # round-trip; the dynamic-graph engine of this framework reads the hybrid / amp / recompute /
+                       # sharding entries above
+                       "adaptive_localsgd": False, "fp16_allreduce": False, "sync_batch_norm": False,
+                       "use_hierarchical_allreduce": False, "hierarchical_allreduce_inter_nranks": 1, "asp": False,
+                       "qat": False, "_calc_comm_same_stream": False, "cudnn_exhaustive_search": False,
+                       "conv_workspace_size_limit": 512, "cudnn_batchnorm_spatial_persistent": False,
+                       "fuse_grad_size_in_TFLOPS": 50.0, "auto": False, "semi_auto": False, "auto_search": False,
+                       "split_data": True, "elastic": False,
+                       "lars_configs": {"lars_coeff": 0.001, "lars_weight_decay": 0.0005, "epsilon": 0.0,
+                                        "exclude_from_weight_decay": []},
+                       "lamb_configs": {"lamb_weight_decay": 0.01, "exclude_from_weight_decay": []},
+                       "dgc_configs": {"rampup_begin_step": 0, "rampup_step": 1, "sparsity": [0.999]},
+                       "localsgd_configs": {"k_steps": 1, "begin_step": 1},
+                       "adaptive_localsgd_configs": {"init_k_steps": 1, "begin_step": 1},
+                       "qat_configs": {"channel_wise_abs_max": True, "weight_bits": 8, "activation_bits": 8,
+                                       "not_quant_pattern": [], "algo": None}}
 
     hybrid_configs = property(lambda self: self._hybrid, lambda self, v: self._hybrid.assign(v))
     amp_configs = property(lambda self: self._amp_configs, lambda self, v: self._amp_configs.assign(v))
@@ -96,6 +113,13 @@ class DistributedStrategy:
 
     def __setattr__(self, k, v):
         if k in self.__dict__["_flags"]:
+            cur = self.__dict__["_flags"][k]
+            if isinstance(cur, dict) and isinstance(v, dict) and k.endswith("_configs") and k != "gradient_scale_configs":
+                unknown = set(v) - set(cur)
+                if unknown:
+                    raise ValueError(f"{k}: unknown keys {sorted(unknown)}")
+                cur.update(v)                      # partial assignment keeps the other defaults, as in the reference
+                return
             self.__dict__["_flags"][k] = v
             return
         prop = getattr(type(self), k, None)

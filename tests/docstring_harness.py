@@ -65,7 +65,7 @@ def classify_skip(examples, allow=()):
     for d in _SKIP_DIRECTIVES:
         if d in text:
             return "directive"
-    if "paddle.distributed" in text or "fleet" in text or "dist." in text:
+    if "distributed" not in allow and ("paddle.distributed" in text or "fleet" in text or "dist." in text):
         return "distributed"
     if "static" not in allow and ("paddle.static" in text or "enable_static" in text or "static." in text or "paddle.base" in text
                                   or "fluid" in text):
