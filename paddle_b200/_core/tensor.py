@@ -129,9 +129,24 @@ class Tensor(torch.Tensor, metaclass=_TensorMeta):
         return torch.Tensor.tolist(self)
 
     def item(self, *idx):
+        """Python scalar of a one-element tensor; ``item(i)`` reads element ``i`` of the flattened tensor and
+        ``item(i, j, ...)`` the element at that index."""
+        plain = self.detach().as_subclass(torch.Tensor)
+        if len(idx) == 1 and plain.dim() != 1:
+            return plain.reshape(-1)[int(idx[0])].item()
         if idx:
-            return torch.Tensor.item(self[idx])
-        return torch.Tensor.item(self)
+            return plain[tuple(int(i) for i in idx)].item()
+        return plain.item()
+
+    @property
+    def inplace_version(self):
+        """How many in-place operations have written this tensor."""
+        return self._version
+
+    def _md5sum(self):
+        """MD5 of the tensor's bytes (debugging aid to compare tensors across runs)."""
+        import hashlib
+        return hashlib.md5(self.detach().cpu().contiguous().as_subclass(torch.Tensor).numpy().tobytes()).hexdigest()
 
     def element_size(self):
         return torch.Tensor.element_size(self)

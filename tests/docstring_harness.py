@@ -53,8 +53,9 @@ def extract_blocks(path):
                             continue
                         if ex:
                             out.append((f"{name}#{ci}" if ci else name, ex))
-                if isinstance(child, ast.ClassDef):
-                    visit(child, name + ".")
+                # methods of classes, and functions defined inside functions (the reference patches Tensor methods
+                # from inside ``monkey_patch_tensor``)
+                visit(child, name + ".")
     visit(tree, "")
     return out
 

@@ -25,8 +25,8 @@ GROUPS = {
                           "nn/utils/*.py", "nn/clip.py", "nn/decode.py"], 82, 8),
     "incubate_vision_hapi_misc": (["incubate/asp/*.py", "incubate/optimizer/*.py", "incubate/autograd/*.py", "incubate/nn/layer/*.py",
                                   "incubate/tensor/*.py", "incubate/operators/*.py", "reader/*.py", "hapi/*.py", "vision/ops.py",
-                                  "vision/transforms/*.py", "base/dygraph/base.py", "utils/*.py", "device/__init__.py", "profiler/*.py"],
-                                 118, 16),
+                                  "vision/transforms/*.py", "base/dygraph/base.py", "base/dygraph/tensor_patch_methods.py", "utils/*.py", "device/__init__.py", "profiler/*.py"],
+                                 130, 16),
     # single-process examples of the distributed package (strategy objects, meshes, role makers)
     "distributed_single_process": (["distributed/fleet/base/distributed_strategy.py", "distributed/auto_parallel/process_mesh.py",
                                    "distributed/fleet/base/role_maker.py"], 47, 6, ("distributed",)),
