@@ -97,6 +97,23 @@ class Fleet:
     def barrier_worker(self):
         C.barrier()
 
+    def all_reduce(self, input, mode="sum"):
+        """Reduce a Python number / array over all workers (``sum``, ``mean`` or ``max``); returns a numpy array, the
+        input itself with a single worker (python/paddle/distributed/fleet/fleet.py ``all_reduce``)."""
+        import numpy as np
+        if mode not in ("sum", "mean", "max"):
+            raise ValueError(f"mode should be sum, mean or max, got {mode!r}")
+        arr = np.asarray(input)
+        if not C.is_initialized() or C.get_world_size() == 1:
+            return arr
+        t = torch.as_tensor(arr.astype("float64") if arr.dtype.kind in "iu" and mode == "mean" else arr)
+        on_gpu = (C._get_default_group().backend or "").lower() == "nccl"
+        t = t.to(torch.device("cuda", torch.cuda.current_device()) if on_gpu else torch.device("cpu"))
+        C.all_reduce(t, C.ReduceOp.MAX if mode == "max" else C.ReduceOp.SUM)
+        if mode == "mean":
+            t = t / C.get_world_size()
+        return t.cpu().numpy()
+
     def init_worker(self):
         pass
 
