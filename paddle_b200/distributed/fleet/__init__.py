@@ -45,4 +45,6 @@ def __getattr__(name):
     if name == "auto":
         from .. import auto_parallel
         return auto_parallel
+    if not name.startswith("_") and hasattr(_fleet, name):
+        return getattr(_fleet, name)               # every public method of the Fleet singleton is a module function
     raise AttributeError(name)
