@@ -36,7 +36,7 @@ def parse_args():
     ap.add_argument("--micro-batches", type=int, default=16)
     ap.add_argument("--sharding", type=int, default=0, choices=[0, 3],
                     help="3: sharding stage 3 over all ranks instead of tensor parallelism (parameters, gradients and "
-                         "optimizer state partitioned; every rank feeds its own micro-batches: BASELINE config 3 with "
+                         "optimizer state partitioned; every rank feeds its own micro-batches: the 13B stage-3 configuration is "
                          "--model llama2-13b --micro-batches 8)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--kernel-table", default="",

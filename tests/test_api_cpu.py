@@ -261,7 +261,9 @@ def test_flag_registry_covers_the_reference_and_effects_apply(tmp_path):
     info = F.flag_info()
     assert len(info) >= 185 and all(v["kind"] in ("effect", "read", "inert") for v in info.values())
     assert all(v["note"] for v in info.values() if v["kind"] == "inert")
-    ref = "/root/reference/paddle/common/flags.cc"
+    ref_root = os.environ.get("PADDLE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                                                                       "reference")
+    ref = os.path.join(ref_root, "paddle", "common", "flags.cc")
     if os.path.exists(ref):
         names = set(re.findall(r"PHI_DEFINE_EXPORTED_\w+\(\s*(?://[^\n]*\n\s*)?(\w+)\s*,", open(ref).read()))
         assert len(names) > 150 and not {n for n in names if "FLAGS_" + n not in info}

@@ -11,7 +11,9 @@ import os
 
 import pytest
 
-REF = "/root/reference/python/paddle"
+# the reference's source tree: $PADDLE_REFERENCE_ROOT, else a directory named ``reference`` beside this repository
+_ROOT = os.environ.get("PADDLE_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+REF = os.path.join(_ROOT, "python", "paddle")
 pytestmark = pytest.mark.skipif(not os.path.isdir(REF), reason="the reference source tree is not present")
 
 GROUPS = {
