@@ -8,6 +8,9 @@ import time
 
 import torch
 
+from . import analytic  # noqa: E402,F401
+from .analytic import Cluster, estimate_step_time, rank_configs  # noqa: E402,F401
+
 __all__ = ["CostModel"]
 
 

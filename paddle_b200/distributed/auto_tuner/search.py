@@ -50,6 +50,11 @@ class GridSearch(SearchAlgo):
     def __init__(self, tuner_cfg):
         super().__init__(tuner_cfg)
         self.all_tasks = search_all(tuner_cfg)
+        algo = tuner_cfg.get("search_algo", {})
+        if isinstance(algo, dict) and algo.get("sort") == "estimated":
+            # try first what the analytic cost model expects to be fastest; what it expects not to fit is left out
+            from .utils import sort_by_estimated_time
+            self.all_tasks = sort_by_estimated_time(self.all_tasks, tuner_cfg)
 
     def search_once(self, history_cfgs):
         return self._next(history_cfgs)

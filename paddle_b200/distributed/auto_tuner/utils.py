@@ -386,4 +386,13 @@ def sort_by_special(cfgs, tuner_cfg):
     ``performance``, the default)."""
     algo = tuner_cfg.get("search_algo", {})
     how = algo.get("sort", "performance") if isinstance(algo, dict) else "performance"
+    if how == "estimated":
+        return sort_by_estimated_time(cfgs, tuner_cfg)
     return sorted(cfgs, key=memory_sort if how == "memory" else performance_sort)
+
+
+def sort_by_estimated_time(cfgs, tuner_cfg):
+    """Order by the analytic step-time estimate of ``paddle.cost_model.analytic`` (fastest first); configurations the
+    estimate puts above the memory limit are dropped.  Needs the model description in ``tuner_cfg["model_cfg"]``."""
+    from ...cost_model.analytic import rank_configs
+    return rank_configs(tuner_cfg["model_cfg"], cfgs, memory_limit_gb=tuner_cfg.get("max_mem_usage"))

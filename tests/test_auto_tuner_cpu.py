@@ -244,3 +244,38 @@ def test_launcher_auto_tuner_mode(tmp_path):
     assert (best["dp_degree"], best["mp_degree"], best["micro_batch_size"]) == (2, 1, 2) and best["ips"] == pytest.approx(200.0)
     rows, _ = at.HistoryRecorder({}).load_history(str(tmp_path / "log" / "tune_history.csv"))
     assert any(h.get("error_info") == "OOM" for h in rows) and len(rows) >= 3
+
+
+def test_analytic_cost_model_against_measured_steps_and_tuner_order():
+    """The analytic step-time model reproduces the throughputs measured for this repository on B200 (tensor parallel
+    Llama-2 7B on 1 / 2 / 4 / 8 GPUs, 13B and 7B with sharding stage 3) within 15 %, behaves monotonically, and drives
+    the tuner's trial order."""
+    from paddle_b200.cost_model import analytic as A
+    m7 = dict(hidden_size=4096, num_layers=32, vocab_size=32000, seq_length=4096, global_batch_size=16, intermediate_size=11008,
+              num_attention_heads=32)
+    m13 = dict(hidden_size=5120, num_layers=40, vocab_size=32000, seq_length=4096, global_batch_size=32, intermediate_size=13824,
+               num_attention_heads=40)
+    measured = {1: 23.0e3, 2: 39.6e3, 4: 68.9e3, 8: 94.7e3}                       # tokens / s, bench.py on B200
+    for n, want in measured.items():
+        est = A.estimate_step_time(m7, dict(dp_degree=1, mp_degree=n, pp_degree=1, sharding_degree=1, micro_batch_size=1))
+        assert abs(est.tokens_per_second / want - 1) < 0.15, (n, est.tokens_per_second, want)
+    z3 = A.estimate_step_time(m13, dict(mp_degree=1, pp_degree=1, sharding_degree=4, sharding_stage=3, micro_batch_size=1))
+    assert abs(z3.tokens_per_second / 38.5e3 - 1) < 0.15 and z3.parts["data_parallel"] > 0.3
+    z3b = A.estimate_step_time(m7, dict(mp_degree=1, sharding_degree=2, sharding_stage=3, micro_batch_size=1, global_batch_size=32))
+    assert abs(z3b.tokens_per_second / 33.9e3 - 1) < 0.15
+    # qualitative behaviour
+    e1 = A.estimate_step_time(m7, dict(mp_degree=8, micro_batch_size=1))
+    e2 = A.estimate_step_time(m7, dict(mp_degree=8, micro_batch_size=1, use_recompute=True))
+    assert e2.seconds > e1.seconds and e2.memory_gb < e1.memory_gb
+    pp = A.estimate_step_time(m7, dict(pp_degree=4, mp_degree=2, micro_batch_size=1))
+    vpp = A.estimate_step_time(m7, dict(pp_degree=4, mp_degree=2, micro_batch_size=1, vpp_degree=2))
+    assert pp.parts["pipeline_bubble"] > vpp.parts["pipeline_bubble"] > 0
+    assert A.all_reduce_time(1e9, 8) < A.all_reduce_time(1e9, 2) * 1.2 and A.all_reduce_time(1e9, 16) > 5 * A.all_reduce_time(1e9, 8)
+    assert A.matmul_time(4096, 4096, 4096) < A.matmul_time(4096, 4096, 8192) and A.attention_time(1, 4096, 32, 128, backward=True) > \
+        A.attention_time(1, 4096, 32, 128)
+    assert not A.estimate_step_time(dict(m13, num_layers=80, hidden_size=8192, intermediate_size=28672), dict(micro_batch_size=1)).fits()
+    # the tuner tries the estimated-fastest configuration first and skips what cannot fit
+    t = at.AutoTuner(_cfg(model_cfg=dict(m7, global_batch_size=64), search_algo={"name": "grid", "sort": "estimated"}, task_limit=5))
+    first = t.search_once()
+    assert first["estimated_tokens_per_second"] == max(c["estimated_tokens_per_second"] for c in t.candidates)
+    assert all(c["estimated_memory_usage"] <= 180 / 1.0737 + 1 for c in t.candidates) and first["mp_degree"] == 1
