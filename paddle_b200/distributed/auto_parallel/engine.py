@@ -51,6 +51,7 @@ class Engine:
         self._merge_k, self._merge_avg, self._merge_i = 1, True, 0
         self._scaler = None
         self.history = None
+        self._plan = self._program = None
         self._rank = C.get_rank() if C.is_initialized() else 0
         self._world = C.get_world_size() if C.is_initialized() else 1
 
@@ -301,31 +302,87 @@ class Engine:
         if load_optimizer and self._optimizer is not None and os.path.exists(opt_path):
             self._optimizer.set_state_dict(framework_io.load(opt_path))
 
-    def cost(self, inputs_spec=None, labels_spec=None, mode=None):
-        """(estimated step time in ms, estimated peak memory in bytes) from parameter and activation sizes: a rough
-        roofline (2 x parameters x tokens FLOPs forward, x3 for training) in place of the reference's op-level cost
-        model; ``None`` where no input shape is known."""
+    def plan(self, inputs_spec=None, labels_spec=None, n_devices=None, mode=None, cluster=None, memory_limit=None,
+             batch_size=None):
+        """Record the forward (and the loss) of the model on example tensors of the given specs, search the data / tensor
+        parallel plans of the recorded program for ``n_devices`` devices (default: the cluster's, else the job's) and
+        keep the best one: ``engine.main_program`` is the recorded program, ``plan.param_specs()`` the parameter
+        layouts, ``plan.apply(model)`` shards the parameters accordingly.  Unknown (-1 / None) dims take
+        ``batch_size`` (default 1)."""
+        import paddle_b200 as paddle
+        from ...static import graph as G
+        from .static.cluster import Cluster, get_default_cluster
+        from .static.planner import Planner
         mode = mode or self._mode
+        ins = _as_list(inputs_spec) or self._inputs_spec or []
+        labs = _as_list(labels_spec) or self._labels_spec or []
+        if not ins:
+            raise ValueError("plan() needs inputs_spec (shapes and dtypes of the model's inputs)")
+        if cluster is None:
+            cluster = self._cluster if isinstance(self._cluster, Cluster) else None
+        if cluster is None:
+            cluster = get_default_cluster(device_count=n_devices or (self._world if self._world > 1 else None))
+        was_static = not paddle.in_dynamic_mode()
+        paddle.enable_static()
+        prog = paddle.static.Program()
+        try:
+            with paddle.static.program_guard(prog, paddle.static.Program()):
+                def holder(sp, i, kind):
+                    shape = [int(batch_size or 1) if d in (None, -1) else int(d) for d in sp.shape]
+                    return paddle.static.data(sp.name or f"{kind}{i}", shape, sp.dtype)
+                xs = [holder(sp, i, "input") for i, sp in enumerate(ins)]
+                ys = [holder(sp, i, "label") for i, sp in enumerate(labs)]
+                out = self._model(*xs)
+                if self._loss is not None and ys and mode != "predict":
+                    outs = out if isinstance(out, (list, tuple)) else [out]
+                    self._loss(*outs, *ys)
+        finally:
+            if not was_static:
+                paddle.disable_static()
+        self._program = prog
+        planner = Planner(prog, cluster, n_devices=n_devices, mode="train" if mode == "train" else "predict",
+                          memory_limit=memory_limit)
+        self._plan = planner.plan()
+        self._planner = planner
+        return self._plan
+
+    def cost(self, inputs_spec=None, labels_spec=None, mode=None):
+        """(estimated step time in ms, estimated peak memory in bytes).  With input specs the model is recorded, planned
+        and priced operator by operator (``plan``); without them only the memory of parameters and optimizer state is
+        known and the time is ``None``."""
+        mode = mode or self._mode
+        specs = _as_list(inputs_spec) or self._inputs_spec or []
+        if specs and self._model is not None:
+            try:
+                plan = self.plan(specs, _as_list(labels_spec) or self._labels_spec, mode=mode)
+                return plan.cost.time * 1e3, plan.cost.memory
+            except Exception as e:                                  # a model that cannot be recorded: fall back to the rough figure
+                import warnings
+                warnings.warn(f"Engine.cost: the model could not be planned ({type(e).__name__}: {e}); using the parameter-count estimate")
         n_param = sum(int(np.prod(p.shape)) for p in self._model.parameters())
         bytes_per = 2 if any(p.dtype in (torch.bfloat16, torch.float16) for p in self._model.parameters()) else 4
         state = n_param * (bytes_per + (12 if mode == "train" else 0))
-        specs = _as_list(inputs_spec) or self._inputs_spec or []
         if not specs:
             return None, state
         tokens = int(np.prod([abs(int(s)) for s in specs[0].shape if s not in (None, -1)][:-1] or [1]))
         flops = 2.0 * n_param * tokens * (3 if mode == "train" else 1)
-        peak = 1.4e15 if bytes_per == 2 else 7e13
+        peak = 1.3e15 if bytes_per == 2 else 7e13
         return flops / peak * 1e3, state
 
     # ------------------------------------------------------------------ introspection
     @property
     def main_program(self):
-        return None
+        return self._program
 
     startup_program = serial_main_program = serial_startup_program = main_program
 
     def get_dist_main_program(self, mode=None):
-        return None
+        """The partition of the planned program for this rank (a list of operators and collectives); ``None`` before
+        ``plan``."""
+        if self._plan is None:
+            return None
+        from .static.partitioner import Partitioner
+        return Partitioner(self._plan.dist_context, self._rank).partition()
 
     get_dist_startup_program = get_serial_main_program = get_serial_startup_program = get_dist_main_program
 

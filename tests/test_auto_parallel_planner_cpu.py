@@ -1,0 +1,233 @@
+"""Planner over recorded programs: cluster description, completion through the SPMD rules, cost estimate, plan search,
+partition, and a one-process simulation of all ranks that checks the completed program against the serial one."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import paddle_b200 as paddle
+import paddle_b200.nn as nn
+import paddle_b200.nn.functional as F
+from paddle_b200.distributed.auto_parallel.static import (Cluster, Completer, CostEstimator, Partitioner, Planner,
+                                                           get_default_cluster, group_ranks)
+from paddle_b200.distributed.auto_parallel.static.cost import (AllgatherOpCost, AllreduceSumOpCost, CommContext,
+                                                                MatmulV2OpCost, build_comm_desc)
+from paddle_b200.distributed.auto_parallel.static.simulate import Simulator
+
+
+@pytest.fixture(autouse=True)
+def _dynamic_mode_after():
+    yield
+    paddle.disable_static()
+    CommContext.reset()
+
+
+def _record_block(B=8, S=16, H=64, heads=4, ffn=256, with_loss=False, V=96):
+    paddle.seed(3)
+    paddle.enable_static()
+    main = paddle.static.Program()
+    with paddle.static.program_guard(main, paddle.static.Program()):
+        x = paddle.static.data("x", [B, S, H], "float32")
+        ln = nn.LayerNorm(H)
+        qkv, proj = nn.Linear(H, 3 * H), nn.Linear(H, H)
+        up, down = nn.Linear(H, ffn), nn.Linear(ffn, H)
+        h = ln(x)
+        t = qkv(h).reshape([B, S, heads, 3 * H // heads]).transpose([0, 2, 1, 3])
+        q, k, v = t[:, :, :, :H // heads], t[:, :, :, H // heads:2 * H // heads], t[:, :, :, 2 * H // heads:]
+        a = F.softmax(paddle.matmul(q, k, transpose_y=True) * 0.25, -1)
+        o = paddle.matmul(a, v).transpose([0, 2, 1, 3]).reshape([B, S, H])
+        y = x + proj(o)
+        out = y + down(F.gelu(up(y)))
+        total = out.sum()
+        extra = {}
+        if with_loss:
+            lab = paddle.static.data("lab", [B, S], "int64")
+            head = nn.Linear(H, V)
+            extra["loss"] = F.cross_entropy(head(out).reshape([-1, V]), lab.reshape([-1]))
+            extra["head"] = head
+    paddle.disable_static()
+    layers = dict(ln=ln, qkv=qkv, proj=proj, up=up, down=down, **extra)
+    return main, layers, out, total
+
+
+def test_cluster_description_round_trip(tmp_path):
+    c = Cluster()
+    path = tmp_path / "cluster.json"
+    c.gen_default_config_cluster(node_count=2, device_count=4, cluster_path=str(path))
+    assert len(c.get_all_devices("GPU")) == 8 and c.get_num_machines() == 2
+    assert not c.cross_machine([0, 1, 2, 3]) and c.cross_machine([3, 4])
+    assert c.get_beta(0, 1) < c.get_beta(0, 4)                     # the switch inside a machine beats the network
+    assert c.get_all_devices("GPU")[0].memory == 180 and c.get_all_devices("GPU")[0].model == "B200"
+    again = Cluster()
+    again.build_from_file(str(path))
+    assert json.dumps(again.to_json(), sort_keys=True) == json.dumps(c.to_json(), sort_keys=True)
+    d = get_default_cluster({"cluster": {"num_nodes": 1, "num_gpus": 2, "gpu_model": "H100", "gpu_memory": 80}})
+    assert [g.model for g in d.get_all_devices("GPU")] == ["H100", "H100"]
+    with pytest.raises(ValueError):
+        get_default_cluster({"cluster": {"num_nodes": 1}})
+
+
+def test_comm_costs_follow_alpha_beta_and_group_size():
+    c = Cluster()
+    c.gen_default_config_cluster(device_count=8)
+    ctx = CommContext(c)
+    n = 256 << 20
+    ar8 = AllreduceSumOpCost(comm_context=ctx, nbytes=n, group_ranks=list(range(8))).time
+    ar2 = AllreduceSumOpCost(comm_context=ctx, nbytes=n, group_ranks=[0, 1]).time
+    ag8 = AllgatherOpCost(comm_context=ctx, nbytes=n, group_ranks=list(range(8))).time
+    bus = 2 * 7 / 8 * n / ar8
+    assert 0.6e12 < bus < 0.8e12                                    # the measured 8-rank bus bandwidth is 0.72 TB/s
+    assert ag8 == pytest.approx(ar8 / 2, rel=0.05)
+    assert ar2 > 0 and (2 * 1 / 2 * n / ar2) < bus                  # two ranks do not reach the 8-rank rate
+    desc = build_comm_desc("c_allreduce_sum", [0, 1, 2, 3], "float32", [1024, 1024])
+    assert AllreduceSumOpCost(op_desc=desc, comm_context=ctx).comm_count == 4 << 20
+    assert AllreduceSumOpCost(comm_context=ctx, nbytes=n, group_ranks=[0]).time == 0.0
+    mm = MatmulV2OpCost(op_desc={"flops": 2 * 8192 ** 3, "bytes": 3 * 2 * 8192 ** 2, "dtype_bytes": 2}, cluster=c)
+    assert 0.8e-3 < mm.time < 1.2e-3                                # 1.1 PFLOP at about 1.2 PFLOP/s
+
+
+def test_completion_derives_the_tensor_parallel_block():
+    main, L, out, total = _record_block()
+    comp = Completer(main, [2, 4], ["dp", "mp"])
+    comp.annotate("x", [0, -1, -1])
+    comp.annotate(L["qkv"].weight, [-1, 1]).annotate(L["up"].weight, [-1, 1])
+    ctx = comp.complete_forward_annotation()
+    spec = lambda t: ctx.get_tensor_dist_attr(t).dims_mapping      # noqa: E731
+    assert spec(L["qkv"].bias) == [1] and spec(L["up"].bias) == [1]
+    assert spec(L["proj"].weight) == [1, -1] and spec(L["down"].weight) == [1, -1]      # row splits were adopted
+    assert spec(L["ln"].weight) == [-1]
+    assert spec(out) == [0, -1, -1]
+    kinds = [(st.kind, st.mesh_axis) for op in ctx.dist_ops for rs in op.reshards for st in rs.steps]
+    assert kinds.count(("all_reduce", 1)) == 2                      # after the two row-parallel products
+    assert ("all_gather", 1) not in kinds and ("all_to_all", 1) not in kinds
+    col_ops = [op for op in ctx.dist_ops if op.kind == "matmul" and op.backward_comm]
+    assert len(col_ops) == 2 and all(st.kind == "all_reduce" and st.mesh_axis == 1 for op in col_ops for st in op.backward_comm)
+    sync = {tuple(ctx.shapes[s]): axes for op in ctx.dist_ops for s, axes in op.grad_sync.items()}
+    assert sync[(64, 192)] == [0] and sync[(64,)] == [0]            # data-parallel gradient sums
+    attn = [op for op in ctx.dist_ops if op.kind == "softmax"][0]
+    assert attn.in_specs[0].dims_mapping == [0, 1, -1, -1]          # heads carry the tensor axis
+    with pytest.raises(ValueError):
+        comp.annotate("x", [0, 1])
+    with pytest.raises(ValueError):
+        Completer(main, [3, 1]).annotate("x", [0, -1, -1])          # 8 is not divisible by 3
+
+
+@pytest.mark.parametrize("mesh", [[2, 4], [1, 4], [4, 1], [2, 2]])
+def test_simulated_ranks_reproduce_the_serial_program(mesh):
+    main, L, out, total = _record_block()
+    x = torch.randn(8, 16, 64)
+    want_out, want_total = main._execute({"x": x}, [out, total])
+    comp = Completer(main, mesh, ["dp", "mp"])
+    if mesh[0] > 1:
+        comp.annotate("x", [0, -1, -1])
+    if mesh[1] > 1:
+        comp.annotate(L["qkv"].weight, [-1, 1]).annotate(L["up"].weight, [-1, 1])
+    ctx = comp.complete_forward_annotation()
+    got_out, got_total = Simulator(ctx).run({"x": x}, [out, total])
+    np.testing.assert_allclose(got_out.numpy(), np.asarray(want_out), rtol=2e-4, atol=2e-5)
+    np.testing.assert_allclose(float(got_total), float(want_total), rtol=1e-4)
+
+
+def test_simulation_of_awkward_annotations_still_matches():
+    """Annotations that force gathers, an all-to-all and a reduce-scatter (sequence split into a column-parallel product,
+    an intermediate pinned to another dim) still give the serial result."""
+    main, L, out, total = _record_block()
+    x = torch.randn(8, 16, 64)
+    want_out, = main._execute({"x": x}, [out])
+    comp = Completer(main, [2, 4], ["dp", "mp"])
+    comp.annotate("x", [0, 1, -1])                                  # sequence split over the tensor axis
+    comp.annotate(L["up"].weight, [-1, 1])
+    comp.annotate(out, [-1, 0, 1])
+    ctx = comp.complete_forward_annotation()
+    kinds = {st.kind for op in ctx.dist_ops for rs in op.reshards + op.out_reshards for st in rs.steps}
+    print(sorted(kinds))
+    assert "all_gather" in kinds and len(kinds) >= 3
+    got, = Simulator(ctx).run({"x": x}, [out])
+    np.testing.assert_allclose(got.numpy(), np.asarray(want_out), rtol=2e-4, atol=2e-5)
+
+
+def test_partition_lists_local_shapes_and_groups():
+    main, L, out, total = _record_block()
+    comp = Completer(main, [2, 4], ["dp", "mp"])
+    comp.annotate("x", [0, -1, -1]).annotate(L["qkv"].weight, [-1, 1]).annotate(L["up"].weight, [-1, 1])
+    ctx = comp.complete_forward_annotation()
+    part = Partitioner(ctx, rank_id=5)
+    nodes = part.partition()
+    comm = [n for n in nodes if n.is_comm]
+    assert {n.type for n in comm} >= {"c_allreduce_sum"}
+    assert all(n.group_ranks == [4, 5, 6, 7] for n in comm if n.type == "c_allreduce_sum" and n.nbytes > 64)
+    shapes = {tuple(t.shape): s for t, s in part.local_param_shapes().items()}
+    assert shapes[(64, 192)] == [64, 48] and shapes[(256, 64)] == [64, 64] and shapes[(64, 64)] == [16, 64]
+    from paddle_b200.distributed.auto_parallel.static.completion import _slot_of
+    assert part.local_slice(_slot_of(main, L["qkv"].weight)) == [(0, 64), (48, 96)]
+    assert group_ranks(5, 0, [2, 4]) == [1, 5]
+    first = [n for n in nodes if n.type == "layer_norm"][0]
+    assert first.inputs[0][1] == [4, 16, 64]
+    assert "c_allreduce_sum" in part.to_string()
+
+
+def test_cost_estimate_and_plan_search():
+    main, L, out, total = _record_block(B=8, S=64, H=256, heads=8, ffn=1024, with_loss=True, V=512)
+    cluster = Cluster()
+    cluster.gen_default_config_cluster(device_count=8)
+    refined = Planner(main, cluster)
+    refined_best = refined.plan()
+    planner = Planner(main, cluster, refine=False)
+    best = planner.plan()
+    assert refined_best.cost.time <= best.cost.time * 1.0001         # dropping column splits never makes the plan slower
+    by = {(tuple(t["mesh"]), t["strategy"]): t for t in planner.trials}
+    assert (8, 1) in {m for m, _ in by} and (1, 8) in {m for m, _ in by}
+    assert best.cost.time == min(t["time"] for t in planner.trials if t["fits"])
+    dp, mp = by[((8, 1), "dp")], by[((1, 8), "mp")]
+    assert dp["parts"]["grad_sync"] > 0 and mp["parts"]["grad_sync"] == 0
+    assert mp["parts"]["param_bytes"] < dp["parts"]["param_bytes"] / 4          # the weights are split eight ways
+    assert mp["parts"]["comm"] > dp["parts"]["comm"]
+    # the vocabulary-parallel loss: the class dim of the logits stays split in the tensor-parallel plan
+    full = Planner(main, cluster, mesh_candidates=[(1, 8)], strategies=("mp+vocab",), refine=False).plan()
+    loss_op = [op for op in full.dist_context.dist_ops if op.kind == "loss"][0]
+    assert loss_op.in_specs[0].dims_mapping == [-1, 1] and not loss_op.reshards
+    assert full.placements(L["head"].weight)[1].is_shard() and full.placements(L["ln"].weight)[1].is_replicated()
+    # a memory limit below the data-parallel plan's need moves the choice to a plan that splits the weights
+    limit = int(dp["memory"] * 0.9)
+    small = [t for t in planner.trials if t["memory"] <= limit]
+    if small:
+        chosen = Planner(main, cluster, memory_limit=limit, refine=False).plan()
+        assert chosen.mesh_shape[1] > 1 and chosen.cost.memory <= limit
+    with pytest.raises(RuntimeError):
+        Planner(main, cluster, memory_limit=1024).plan()
+    est = CostEstimator(best.dist_context, cluster)
+    est.estimate_cost()
+    assert "total" in est.pretty_print_cost()
+    inference = CostEstimator(best.dist_context, cluster, mode="predict").estimate_cost()
+    assert inference.time < best.cost.time and inference.memory < best.cost.memory
+
+
+def test_engine_plans_and_prices_a_model():
+    from paddle_b200.distributed.auto_parallel import Engine
+    from paddle_b200.static import InputSpec
+
+    class MLP(nn.Layer):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b, self.norm = nn.Linear(128, 512), nn.Linear(512, 128), nn.LayerNorm(128)
+
+        def forward(self, x):
+            return self.b(F.relu(self.a(self.norm(x))))
+
+    paddle.seed(0)
+    model = MLP()
+    engine = Engine(model, nn.MSELoss(), paddle.optimizer.AdamW(parameters=model.parameters()))
+    assert engine.main_program is None and engine.get_dist_main_program() is None
+    plan = engine.plan([InputSpec([64, 128], "float32", "x")], [InputSpec([64, 128], "float32", "y")], n_devices=4)
+    assert paddle.in_dynamic_mode()
+    assert engine.main_program is not None and len(engine.main_program._nodes) >= 6
+    assert np.prod(plan.mesh_shape) == 4 and plan.cost.time > 0
+    specs = {tuple(t.shape): m for t, m in plan.param_specs().items()}
+    assert set(specs) == {(128, 512), (512,), (512, 128), (128,)}
+    assert any(n.type == "matmul" for n in engine.get_dist_main_program())
+    ms, mem = engine.cost([InputSpec([64, 128], "float32", "x")], [InputSpec([64, 128], "float32", "y")])
+    assert ms > 0 and mem > 4 * sum(int(np.prod(p.shape)) for p in model.parameters())
+    # the model still runs as before
+    y = model(paddle.randn([4, 128]))
+    assert list(y.shape) == [4, 128]

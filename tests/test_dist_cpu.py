@@ -126,6 +126,17 @@ def test_spmd_rule_driven_operators_cpu():
         assert not bad, bad
 
 
+def test_planned_model_runs_sharded_cpu():
+    """The planner's tensor-parallel plan for an MLP, applied to the live model on 2 ranks: column / row splits as
+    planned, outputs and all gradients equal the serial run."""
+    res = run_workers("planned_mlp.py", 2, timeout=180)
+    for r in res:
+        assert r["specs"]["a.weight"] == [-1, 1] and r["specs"]["b.weight"] == [1, -1] and r["specs"]["a.bias"] == [1]
+        assert r["local_a"] == [32, 32]
+        assert r["out_ok"] is True
+        assert all(r["grads_ok"].values()), r["grads_ok"]
+
+
 def test_moe_expert_parallel_parity_cpu():
     """2 ranks x 2 local experts, uneven token counts: outputs, input gradients and expert gradients equal the
     dense evaluation of all four experts."""
