@@ -136,6 +136,9 @@ class Completer:
         self.program = program
         self._annotated = {}
         self.pre_op_hook = None              # called as hook(completer, node) before an operator is inferred
+        self.prefer_scatter = {}             # mesh axis -> tensor dim: a partial sum entering an element-wise operator is
+        #                                      reduce-scattered along that dim instead of all-reduced (sequence parallel)
+        self._cur_elementwise = False
         self._collect_vars()
 
     dist_context = property(lambda self: self.ctx)
@@ -221,6 +224,7 @@ class Completer:
         name = node.name.rstrip("_") if not node.name.startswith("__") else node.name
         refs = _refs((node.args, node.kwargs))
         slots = [r.slot for r in refs]
+        self._cur_elementwise = name in _ELEMENTWISE
         specs = [self._strip(self._spec(s)) for s in slots]
         out_shapes = [self.ctx.shapes[s] for s in node.out_slots]
         R = get_phi_spmd_rule
@@ -234,6 +238,14 @@ class Completer:
                 x, w = specs[0], specs[1]
                 b = specs[2] if len(specs) > 2 else None
                 order = [0, 1, 2][:len(specs)]
+            w_slot = slots[order[1]]
+            if w_slot in self._annotated:
+                # a fixed weight layout wins over a derived activation layout: an activation split over the same mesh axis
+                # on another dim (sequence parallel in front of a column-parallel product) is gathered first
+                taken = {m for m in w.dims_mapping if m != -1}
+                k_axis = w.dims_mapping[-1 if name == "linear" else -2] if w.ndim >= 2 else -1
+                x = x.with_mapping([-1 if (m in taken and not (d == x.ndim - 1 and m == k_axis)) else m
+                                    for d, m in enumerate(x.dims_mapping)])
             new_in, outs = R("matmul").infer_forward(x, w, False, name == "linear")
             new = [None] * len(specs)
             new[order[0]], new[order[1]] = new_in[0], new_in[1]
@@ -336,9 +348,15 @@ class Completer:
         return "other", ([sp.with_mapping([-1] * sp.ndim) for sp in specs],
                          [DistTensorSpec(sh, [-1] * len(sh)) for sh in out_shapes]), slots, {}
 
-    @staticmethod
-    def _strip(sp):
-        return sp
+    def _strip(self, sp):
+        if not (sp.partial_dims and self.prefer_scatter and self._cur_elementwise):
+            return sp
+        m = list(sp.dims_mapping)
+        for a in sp.partial_dims:
+            d = self.prefer_scatter.get(a)
+            if d is not None and d < sp.ndim and a not in m and m[d] == -1 and sp.shape[d] % self.ctx.mesh_shape[a] == 0:
+                m[d] = a
+        return DistTensorSpec(sp.shape, m, sp.partial_dims)
 
     def _perm(self, node, name, nd):
         if name == "permute":

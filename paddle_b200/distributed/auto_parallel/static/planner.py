@@ -12,6 +12,10 @@ memory:
   partial sum that is all-reduced where a consumer needs the whole value; a projection that feeds a cross entropy keeps
   the class dim split (the vocabulary-parallel loss).
 * ``mp+vocab``: embedding tables are split by rows (vocabulary) as well.
+* ``mp+sp``: like ``mp``, and the sequence dim (dim 1) of the data is split over the tensor axis too, so that everything
+  between the parallel products - normalisation, residual adds, dropout - works on a sequence slice: completion puts an
+  all-gather in front of each column-parallel product and turns the all-reduce behind each row-parallel one into a
+  reduce-scatter (Megatron sequence parallelism).
 
 A column split is dropped again when it makes the plan slower than leaving that weight whole (a greedy pass over the
 candidates, costliest re-shards first), so a weight whose output is needed whole right away stays replicated."""
@@ -86,7 +90,7 @@ def _factorisations(n):
 
 class Planner:
     def __init__(self, program, cluster=None, n_devices=None, mode="train", memory_limit=None, batch_dim=0,
-                 mesh_candidates=None, strategies=("dp", "mp", "mp+vocab"), refine=True):
+                 mesh_candidates=None, strategies=("dp", "mp", "mp+vocab", "mp+sp"), refine=True, seq_dim=1):
         from .cluster import get_default_cluster
         self.program, self.mode = program, mode
         if cluster is None:
@@ -95,26 +99,29 @@ class Planner:
         self.n_devices = n_devices or len(cluster.get_all_devices("GPU"))
         gpus = cluster.get_all_devices("GPU")
         self.memory_limit = memory_limit if memory_limit is not None else (gpus[0].memory * 1e9 * 0.92 if gpus else float("inf"))
-        self.batch_dim = batch_dim
+        self.batch_dim, self.seq_dim = batch_dim, seq_dim
         self.mesh_candidates = mesh_candidates or _factorisations(self.n_devices)
         self.strategies, self.refine = tuple(strategies), refine
         self.trials = []
 
     # ---------------------------------------------------------------- annotation strategies
-    def _data_annotations(self, comp, dp):
+    def _data_annotations(self, comp, dp, sp=1):
         out = {}
-        if dp <= 1:
-            return out
         for name, s in comp.ctx.placeholders.items():
             shp = comp.ctx.shapes[s]
-            if len(shp) > self.batch_dim and shp[self.batch_dim] % dp == 0:
-                m = [-1] * len(shp)
+            m = [-1] * len(shp)
+            if dp > 1 and len(shp) > self.batch_dim and shp[self.batch_dim] % dp == 0:
                 m[self.batch_dim] = 0
+            if sp > 1 and len(shp) > self.seq_dim and shp[self.seq_dim] % sp == 0:
+                m[self.seq_dim] = 1
+            if any(v != -1 for v in m):
                 out[s] = m
         return out
 
     def _evaluate(self, mesh, annotations, strategy):
         comp = Completer(self.program, list(mesh), ["dp", "mp"])
+        if strategy.endswith("+sp"):
+            comp.prefer_scatter = {1: self.seq_dim}
         for s, m in annotations.items():
             comp.annotate(s, m)
         ctx = comp.complete_forward_annotation()
@@ -122,7 +129,7 @@ class Planner:
         cost = est.estimate_cost()
         return Plan(list(mesh), ["dp", "mp"], strategy, dict(annotations), cost, dict(est.parts), ctx), est
 
-    def _column_candidates(self, mesh, annotations, vocab):
+    def _column_candidates(self, mesh, annotations, vocab, seq_parallel=False):
         """One completion pass that adds a column split to every weight whose activation input does not carry the tensor
         axis yet, at the moment the operator is reached (-> all annotations, the slots that were added)."""
         from .completion import _refs
@@ -148,7 +155,8 @@ class Planner:
                     c._annotated[w_slot] = [1, -1]
                     added.append(w_slot)
                 return
-            if 1 in c._spec(x_slot).dims_mapping or len(w_shape) < 2:
+            xm = c._spec(x_slot).dims_mapping
+            if len(w_shape) < 2 or not xm or xm[-1] == 1 or (1 in xm and not seq_parallel):
                 return
             out_dim = 0 if name in ("linear", "conv2d") else len(w_shape) - 1
             if w_shape[out_dim] % mp == 0 and w_shape[out_dim] >= mp:
@@ -157,6 +165,8 @@ class Planner:
                 c._annotated[w_slot] = m
                 added.append(w_slot)
         comp.pre_op_hook = hook
+        if seq_parallel:
+            comp.prefer_scatter = {1: self.seq_dim}
         comp.complete_forward_annotation()
         return dict(comp._annotated), added
 
@@ -168,7 +178,7 @@ class Planner:
             dp, mp = mesh
             probe = Completer(self.program, list(mesh), ["dp", "mp"])
             data = self._data_annotations(probe, dp)
-            if dp > 1 and not data:
+            if dp > 1 and not any(0 in m for m in data.values()):
                 continue                                            # nothing to split the batch of
             for strategy in self.strategies:
                 if strategy != "dp" and mp == 1:
@@ -178,12 +188,16 @@ class Planner:
                 ann = dict(data)
                 added = []
                 if strategy != "dp":
-                    ann, added = self._column_candidates(mesh, data, vocab=strategy.endswith("vocab"))
+                    sp = strategy.endswith("+sp")
+                    base = self._data_annotations(probe, dp, mp) if sp else data
+                    if sp and base == data:
+                        continue                                    # no sequence dim to split
+                    ann, added = self._column_candidates(mesh, base, vocab=strategy.endswith("vocab"), seq_parallel=sp)
                     if not added:
                         continue
                 plan, est = self._evaluate(mesh, ann, strategy)
                 if self.refine and added:
-                    plan = self._refine(mesh, plan, added, data, strategy)
+                    plan = self._refine(mesh, plan, added, base if strategy != "dp" else data, strategy)
                 fits = plan.cost.memory <= self.memory_limit
                 self.trials.append({"mesh": list(mesh), "strategy": strategy, "time": plan.cost.time, "memory": plan.cost.memory,
                                     "fits": fits, "parts": plan.parts})

@@ -34,7 +34,8 @@ class Simulator:
         for r in range(self.n):
             self.state[r][slot] = self._cut(full, spec, r).clone()
 
-    def _apply_step(self, slot, st, cur_map, dst):
+    def _apply_step(self, vals, st, cur_map, dst):
+        """One collective over the per-rank list ``vals`` (in place); ``cur_map`` follows the layout."""
         a = st.mesh_axis
         done = set()
         for r in range(self.n):
@@ -42,37 +43,39 @@ class Simulator:
                 continue
             grp = group_ranks(r, a, self.ms)
             done.update(grp)
-            parts = [self.state[g][slot] for g in grp]
+            parts = [vals[g] for g in grp]
             if st.kind == "all_reduce":
                 tot = sum(parts)
-                for g in grp:
-                    self.state[g][slot] = tot.clone()
+                new = [tot.clone() for _ in grp]
             elif st.kind == "all_gather":
-                d = cur_map.index(a)
-                tot = torch.cat(parts, d)
-                for g in grp:
-                    self.state[g][slot] = tot.clone()
+                tot = torch.cat(parts, cur_map.index(a))
+                new = [tot.clone() for _ in grp]
             elif st.kind == "reduce_scatter":
-                tot = sum(parts)
-                d = dst.dims_mapping.index(a)
-                for i, g in enumerate(grp):
-                    self.state[g][slot] = tot.chunk(len(grp), d)[i].clone()
+                new = [c.clone() for c in sum(parts).chunk(len(grp), dst.dims_mapping.index(a))]
             elif st.kind == "slice":
                 d = dst.dims_mapping.index(a)
-                for i, g in enumerate(grp):
-                    self.state[g][slot] = self.state[g][slot].chunk(len(grp), d)[i].clone()
+                new = [vals[g].chunk(len(grp), d)[i].clone() for i, g in enumerate(grp)]
             elif st.kind == "all_to_all":
-                ds, dd = cur_map.index(a), dst.dims_mapping.index(a)
-                tot = torch.cat(parts, ds)
-                for i, g in enumerate(grp):
-                    self.state[g][slot] = tot.chunk(len(grp), dd)[i].clone()
-        if st.kind in ("all_gather",):
+                tot = torch.cat(parts, cur_map.index(a))
+                new = [c.clone() for c in tot.chunk(len(grp), dst.dims_mapping.index(a))]
+            else:
+                raise ValueError(st.kind)
+            for g, v in zip(grp, new):
+                vals[g] = v
+        if st.kind == "all_gather":
             cur_map[cur_map.index(a)] = -1
         elif st.kind in ("reduce_scatter", "slice"):
             cur_map[dst.dims_mapping.index(a)] = a
         elif st.kind == "all_to_all":
             cur_map[cur_map.index(a)] = -1
             cur_map[dst.dims_mapping.index(a)] = a
+
+    def _resharded(self, rs):
+        vals = [self.state[r][rs.slot] for r in range(self.n)]
+        cur = list(rs.src.dims_mapping)
+        for st in rs.steps:
+            self._apply_step(vals, st, cur, rs.dst)
+        return vals
 
     # ---------------------------------------------------------------- run
     def run(self, feed, fetch):
@@ -82,12 +85,7 @@ class Simulator:
         from .completion import _slot_of
         ctx = self.ctx
         prog = ctx.program
-        first_spec = {}
-        for op in ctx.dist_ops:
-            for rs in op.reshards:
-                first_spec.setdefault(rs.slot, rs.src)
-            for s, sp in zip(op.in_slots, op.in_specs):
-                first_spec.setdefault(s, sp)
+        first_spec = {s: sp for s, sp in ctx.tensor_specs.items() if not sp.partial_dims}
         for name, s in ctx.placeholders.items():
             if s in first_spec:
                 self._place(s, torch.as_tensor(feed[name]), first_spec[s])
@@ -95,19 +93,35 @@ class Simulator:
             if s in first_spec:
                 self._place(s, t.detach(), first_spec[s])
         for op in ctx.dist_ops:
-            if op.kind in ("loss", "embedding", "attention", "other"):
+            if op.kind == "other" and any(m != -1 for sp in op.in_specs for m in sp.dims_mapping):
                 raise NotImplementedError(f"the simulator has no local form of {op.name}")
-            for rs in op.reshards:
-                cur = list(rs.src.dims_mapping)
-                for st in rs.steps:
-                    self._apply_step(rs.slot, st, cur, rs.dst)
+            local = {rs.slot: self._resharded(rs) for rs in op.reshards}      # what THIS operator sees; the variable stays
             node = op.node
             name = node.name
             for r in range(self.n):
-                res = lambda a: self.state[r][a.slot] if isinstance(a, _Ref) else a      # noqa: E731,B023
+                res = lambda a: (local[a.slot][r] if a.slot in local else self.state[r][a.slot]) if isinstance(a, _Ref) else a   # noqa: E731,B023,E501
                 args = list(pytree.tree_map(res, node.args))
                 kwargs = pytree.tree_map(res, node.kwargs)
                 lo = [ctx.local_shape(s, sp) for s, sp in zip(op.out_slots, op.out_specs)]
+                if op.kind == "embedding" and op.in_specs[1].dims_mapping[0] != -1:
+                    # rows of the table are split: look up what this rank owns, zeros elsewhere (the output is partial)
+                    a = op.in_specs[1].dims_mapping[0]
+                    rows = args[1].shape[0]
+                    ids = args[0] - _coords(r, self.ms)[a] * rows
+                    own = (ids >= 0) & (ids < rows)
+                    with torch.no_grad():
+                        out = node.func(ids.clamp(0, rows - 1), *args[1:], **kwargs) * own.unsqueeze(-1)
+                    self.state[r][op.out_slots[0]] = out
+                    continue
+                if op.kind == "loss" and any(m != -1 and sh > 1 and i == (1 if op.in_specs[0].ndim > 1 else 0)
+                                             for i, (m, sh) in enumerate(zip(op.in_specs[0].dims_mapping, op.in_specs[0].shape))):
+                    # the class dim is split: the operator reduces over that mesh axis inside; here the pieces of the
+                    # group are put together and every rank of the group computes the same loss
+                    cd = 1 if op.in_specs[0].ndim > 1 else 0
+                    a = op.in_specs[0].dims_mapping[cd]
+                    slot = op.in_slots[0]
+                    src = local[slot] if slot in local else [self.state[g][slot] for g in range(self.n)]
+                    args[0] = torch.cat([src[g] for g in group_ranks(r, a, self.ms)], cd)
                 if name in ("reshape", "view", "_unsafe_view"):
                     args = [args[0], lo[0]]
                 elif name == "mean" and op.out_specs[0].partial_dims:
@@ -122,9 +136,8 @@ class Simulator:
                 for s, o in zip(op.out_slots, leaves):
                     self.state[r][s] = o
             for rs in op.out_reshards:
-                cur = list(rs.src.dims_mapping)
-                for st in rs.steps:
-                    self._apply_step(rs.slot, st, cur, rs.dst)
+                for r, v in enumerate(self._resharded(rs)):
+                    self.state[r][rs.slot] = v
         outs = []
         for v in fetch:
             s = _slot_of(prog, v)
