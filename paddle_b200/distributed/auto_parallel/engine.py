@@ -340,8 +340,11 @@ class Engine:
             if not was_static:
                 paddle.disable_static()
         self._program = prog
+        amp_dtype = None
+        if self._strategy.amp.enable:
+            amp_dtype = torch.float16 if str(self._strategy.amp.get("dtype", "float16")) == "float16" else torch.bfloat16
         planner = Planner(prog, cluster, n_devices=n_devices, mode="train" if mode == "train" else "predict",
-                          memory_limit=memory_limit)
+                          memory_limit=memory_limit, assume_dtype=amp_dtype)
         self._plan = planner.plan()
         self._planner = planner
         return self._plan

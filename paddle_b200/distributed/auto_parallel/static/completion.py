@@ -131,9 +131,12 @@ def _arg(node, pos, name, default=None):
 
 
 class Completer:
-    def __init__(self, program, mesh_shape, dim_names=None):
+    def __init__(self, program, mesh_shape, dim_names=None, assume_dtype=None):
+        """``assume_dtype``: price floating-point variables as this dtype (a program recorded in float32 that will run
+        under automatic mixed precision in bfloat16)."""
         self.ctx = DistContext(program, mesh_shape, dim_names)
         self.program = program
+        self._assume_dtype = assume_dtype
         self._annotated = {}
         self.pre_op_hook = None              # called as hook(completer, node) before an operator is inferred
         self.prefer_scatter = {}             # mesh axis -> tensor dim: a partial sum entering an element-wise operator is
@@ -157,6 +160,10 @@ class Completer:
         for name, (s, t) in p._placeholders.items():
             c.placeholders[name] = s
             c.shapes[s], c.dtypes[s] = list(t.shape), t.dtype
+        if self._assume_dtype is not None:
+            for s, d in c.dtypes.items():
+                if d.is_floating_point:
+                    c.dtypes[s] = self._assume_dtype
 
     def annotate(self, var, dims_mapping):
         """Fix the sharding of a variable (a program variable, its name, or its slot number)."""

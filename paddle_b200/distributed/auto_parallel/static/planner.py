@@ -90,7 +90,7 @@ def _factorisations(n):
 
 class Planner:
     def __init__(self, program, cluster=None, n_devices=None, mode="train", memory_limit=None, batch_dim=0,
-                 mesh_candidates=None, strategies=("dp", "mp", "mp+vocab", "mp+sp"), refine=True, seq_dim=1):
+                 mesh_candidates=None, strategies=("dp", "mp", "mp+vocab", "mp+sp"), refine=True, seq_dim=1, assume_dtype=None):
         from .cluster import get_default_cluster
         self.program, self.mode = program, mode
         if cluster is None:
@@ -100,6 +100,7 @@ class Planner:
         gpus = cluster.get_all_devices("GPU")
         self.memory_limit = memory_limit if memory_limit is not None else (gpus[0].memory * 1e9 * 0.92 if gpus else float("inf"))
         self.batch_dim, self.seq_dim = batch_dim, seq_dim
+        self.assume_dtype = assume_dtype
         self.mesh_candidates = mesh_candidates or _factorisations(self.n_devices)
         self.strategies, self.refine = tuple(strategies), refine
         self.trials = []
@@ -119,7 +120,7 @@ class Planner:
         return out
 
     def _evaluate(self, mesh, annotations, strategy):
-        comp = Completer(self.program, list(mesh), ["dp", "mp"])
+        comp = Completer(self.program, list(mesh), ["dp", "mp"], assume_dtype=self.assume_dtype)
         if strategy.endswith("+sp"):
             comp.prefer_scatter = {1: self.seq_dim}
         for s, m in annotations.items():
@@ -135,7 +136,7 @@ class Planner:
         from .completion import _refs
         mp = mesh[1]
         added = []
-        comp = Completer(self.program, list(mesh), ["dp", "mp"])
+        comp = Completer(self.program, list(mesh), ["dp", "mp"], assume_dtype=self.assume_dtype)
         for s, m in annotations.items():
             comp.annotate(s, m)
 
@@ -176,7 +177,7 @@ class Planner:
         self.trials = []
         for mesh in self.mesh_candidates:
             dp, mp = mesh
-            probe = Completer(self.program, list(mesh), ["dp", "mp"])
+            probe = Completer(self.program, list(mesh), ["dp", "mp"], assume_dtype=self.assume_dtype)
             data = self._data_annotations(probe, dp)
             if dp > 1 and not any(0 in m for m in data.values()):
                 continue                                            # nothing to split the batch of
