@@ -130,6 +130,15 @@ def _arg(node, pos, name, default=None):
     return node.args[pos] if len(node.args) > pos else default
 
 
+def _flat(nodes):
+    """Recompute / mixed-precision segments made by the program passes are planned node by node."""
+    for n in nodes:
+        if getattr(n, "mode", None) in ("recompute", "autocast") and hasattr(n, "nodes"):
+            yield from _flat(n.nodes)
+        else:
+            yield n
+
+
 class Completer:
     def __init__(self, program, mesh_shape, dim_names=None, assume_dtype=None):
         """``assume_dtype``: price floating-point variables as this dtype (a program recorded in float32 that will run
@@ -392,7 +401,7 @@ class Completer:
         ctx.dist_ops = []
         ctx.tensor_specs = {}
         ms = ctx.mesh_shape
-        for node in self.program._nodes:
+        for node in _flat(self.program._nodes):
             if self.pre_op_hook is not None:
                 self.pre_op_hook(self, node)
             for r in _refs((node.args, node.kwargs)):

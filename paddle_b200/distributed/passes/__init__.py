@@ -4,7 +4,9 @@ recorded static programs, a context that carries attributes between passes, and 
 Programs here are recorded call lists (``static.Program``), so a pass is a Python rewrite of that list.  The built-in
 passes cover what still has meaning on this runtime: ``fuse_elewise_add_act`` style fusions are done by the kernels
 themselves and are registered as no-ops so that strategy files naming them keep working; ``prune_side_effect_free``
-drops nodes nothing depends on."""
+drops nodes nothing depends on; ``auto_parallel_recompute`` turns the segments between checkpoints into nodes that
+are recomputed in the backward pass; ``auto_parallel_amp`` / ``auto_parallel_fp16`` run the forward under automatic
+mixed precision."""
 from __future__ import annotations
 
 
@@ -114,8 +116,7 @@ class _NoOp(PassBase):
 
 for _n in ("fuse_elewise_add_act", "fuse_bn_act", "fuse_bn_add_act", "fuse_relu_depthwise_conv", "fuse_optimizer",
            "fuse_all_reduce", "fuse_gemm_epilogue", "fused_attention", "fused_feedforward", "inplace_addto_op",
-           "auto_parallel_amp", "auto_parallel_fp16", "auto_parallel_recompute", "auto_parallel_sharding",
-           "auto_parallel_gradient_merge", "build_cinn"):
+           "auto_parallel_sharding", "auto_parallel_gradient_merge", "build_cinn"):
     register_pass(_n)(type(f"_{_n}", (_NoOp,), {}))
 
 
@@ -130,6 +131,127 @@ class PruneSideEffectFree(PassBase):
             return
         slots = [main_program._slot_of(t) for t in targets]
         main_program._nodes[:] = g.prune(main_program._nodes, slots)
+
+
+class SegmentNode:
+    """A run of recorded nodes executed as one node.  ``mode="recompute"``: under autograd the segment runs inside
+    ``fleet.recompute`` - only its inputs are kept, the nodes run again in the backward pass.
+    ``mode="autocast"``: the nodes run under ``torch.autocast`` with the given dtype."""
+
+    def __init__(self, nodes, in_slots, out_slots, mode, name, dtype=None):
+        self.nodes, self.in_slots, self.out_slots, self.mode, self.name = nodes, in_slots, out_slots, mode, name
+        self.dtype = dtype
+        self.args, self.kwargs, self.func = (), {}, None
+        self.runs = 0                                   # times the inner nodes ran (forward + recomputation)
+
+    type = property(lambda self: self.name)
+
+    def run(self, prog, env):
+        import torch
+
+        from ...static.graph import _Ref
+        ins = [prog._resolve(_Ref(s), env) for s in self.in_slots]
+
+        def body(*vals):
+            self.runs += 1
+            local = dict(zip(self.in_slots, vals))
+            for n in self.nodes:
+                n.run(prog, local)
+            return tuple(local[s] for s in self.out_slots)
+        if self.mode == "autocast":
+            dev = next((t.device.type for t in ins if isinstance(t, torch.Tensor)), "cpu")
+            with torch.autocast(dev, dtype=self.dtype):
+                outs = body(*ins)
+        elif torch.is_grad_enabled() and (prog._needs_grad or any(isinstance(t, torch.Tensor) and t.requires_grad for t in ins)):
+            from ..fleet.recompute import recompute
+            outs = recompute(body, *ins)
+            outs = outs if isinstance(outs, (tuple, list)) else (outs,)
+        else:
+            outs = body(*ins)
+        env.update(zip(self.out_slots, outs))
+
+    def __repr__(self):
+        return f"{self.out_slots} = {self.name}[{len(self.nodes)} nodes]({self.in_slots})"
+
+
+def _forward_range(program):
+    """Index of the first node that belongs to the backward pass / the optimizer (``len`` when there is none)."""
+    for i, n in enumerate(program._nodes):
+        if getattr(n.func, "_needs_grad", False) or n.name in ("backward", "gradients", "optimizer_step"):
+            return i
+    return len(program._nodes)
+
+
+def _wrap(program, lo, hi, mode, name, keep=(), dtype=None):
+    from ...static import graph as g
+    nodes = program._nodes[lo:hi]
+    produced, used_inside = [], []
+    for n in nodes:
+        used_inside.extend(s for s in g.node_inputs(n) if s not in produced)
+        produced.extend(n.out_slots)
+    # captured parameters are passed in too: the recomputation hands their gradients back as input gradients
+    in_slots = list(dict.fromkeys(used_inside))
+    later = set(g.block_inputs(program._nodes[hi:]))
+    named = {program._slot_of_id.get(id(t)) for t in program._names.values()}
+    out_slots = [s for s in dict.fromkeys(produced) if s in later or s in named or s in keep]
+    if not out_slots:
+        out_slots = [produced[-1]]
+    program._nodes[lo:hi] = [SegmentNode(nodes, in_slots, out_slots, mode, name, dtype)]
+
+
+@register_pass("auto_parallel_recompute")
+class RecomputePass(PassBase):
+    """Recompute instead of keeping activations (python/paddle/distributed/passes/auto_parallel_recompute.py): the
+    forward nodes are cut at the variables in attr ``checkpoints`` (variables of the program or their names); every
+    segment that ends at a checkpoint becomes one node that keeps only its inputs and runs again during backward.  The
+    nodes behind the last checkpoint are left alone.  Attr ``keep``: further variables that must stay fetchable."""
+
+    def _check_self(self):
+        return bool(self.get_attr("checkpoints"))
+
+    def _type(self):
+        return PassType.CALC_OPT
+
+    def _apply_single_impl(self, main_program, startup_program, context):
+        prog = main_program
+        cps = [prog._slot_of(v) for v in self.get_attr("checkpoints")]
+        keep = {prog._slot_of(v) for v in (self.get_attr("keep") or [])} | set(cps)
+        end = _forward_range(prog)
+        cuts, start = [], 0
+        for i, n in enumerate(prog._nodes[:end]):
+            if any(s in cps for s in n.out_slots):
+                cuts.append((start, i + 1))
+                start = i + 1
+        for k, (lo, hi) in enumerate(reversed(cuts)):           # from the back, so that indices stay valid
+            if hi - lo >= 2:
+                _wrap(prog, lo, hi, "recompute", f"recompute_segment_{len(cuts) - 1 - k}", keep)
+        prog._version += 1
+        if context is not None:
+            context.set_attr("recompute_segments", len(cuts))
+
+
+class _AutocastPass(PassBase):
+    """``auto_parallel_amp`` / ``auto_parallel_fp16`` (python/paddle/distributed/passes/auto_parallel_amp.py, _fp16.py):
+    the forward nodes run under automatic mixed precision with attr ``dtype`` (``"bfloat16"`` by default for amp on this
+    hardware, ``"float16"`` for the fp16 pass).  The cast lists are the runtime's own; ``custom_white_list`` /
+    ``custom_black_list`` are accepted and not applied."""
+    default_dtype = "bfloat16"
+
+    def _type(self):
+        return PassType.CALC_OPT
+
+    def _apply_single_impl(self, main_program, startup_program, context):
+        import torch
+        dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16}[str(self.get_attr("dtype", self.default_dtype))]
+        end = _forward_range(main_program)
+        if end:
+            keep = {main_program._slot_of(v) for v in (self.get_attr("keep") or [])}
+            _wrap(main_program, 0, end, "autocast", "amp_region", keep, dtype)
+            main_program._version += 1
+
+
+register_pass("auto_parallel_amp")(type("AMPPass", (_AutocastPass,), {}))
+register_pass("auto_parallel_fp16")(type("FP16Pass", (_AutocastPass,), {"default_dtype": "float16"}))
 
 
 class _PipelineSchedulerPass(PassBase):
