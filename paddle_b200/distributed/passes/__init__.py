@@ -116,7 +116,7 @@ class _NoOp(PassBase):
 
 for _n in ("fuse_elewise_add_act", "fuse_bn_act", "fuse_bn_add_act", "fuse_relu_depthwise_conv", "fuse_optimizer",
            "fuse_all_reduce", "fuse_gemm_epilogue", "fused_attention", "fused_feedforward", "inplace_addto_op",
-           "auto_parallel_sharding", "auto_parallel_gradient_merge", "build_cinn"):
+           "auto_parallel_sharding", "build_cinn"):
     register_pass(_n)(type(f"_{_n}", (_NoOp,), {}))
 
 
@@ -228,6 +228,47 @@ class RecomputePass(PassBase):
         prog._version += 1
         if context is not None:
             context.set_attr("recompute_segments", len(cuts))
+
+
+@register_pass("auto_parallel_gradient_merge")
+class GradientMergePass(PassBase):
+    """Accumulate gradients over ``k_steps`` runs of the program and update the parameters on the last of them
+    (python/paddle/distributed/passes/auto_parallel_gradient_merge.py).  ``avg`` (default true) divides the sum by
+    ``k_steps``.  The recorded ``minimize`` node is rebuilt: runs in between only add to the gradients."""
+
+    def _check_self(self):
+        return int(self.get_attr("k_steps", 1) or 1) >= 1
+
+    def _type(self):
+        return PassType.CALC_OPT
+
+    def _apply_single_impl(self, main_program, startup_program, context):
+        k, avg = int(self.get_attr("k_steps", 1) or 1), bool(self.get_attr("avg", True))
+        if k == 1:
+            return
+        from ...static import _plain
+        for node in main_program._nodes:
+            f = node.func
+            opt, params = getattr(f, "_optimizer", None), getattr(f, "_params", None)
+            if node.name != "minimize" or opt is None:
+                continue
+            state = {"i": 0}
+
+            def merged(loss_t, opt=opt, params=params, state=state):
+                lt = _plain(loss_t)
+                if not lt.requires_grad:
+                    return
+                if state["i"] % k == 0:
+                    for p in params:
+                        p.grad = None
+                state["i"] += 1
+                (lt / k if avg else lt).backward()
+                if state["i"] % k == 0:
+                    opt.step()
+            merged._needs_grad = merged._train_only = True
+            merged._optimizer, merged._params, merged._merge_state = opt, params, state
+            node.func = merged
+        main_program._version += 1
 
 
 class _AutocastPass(PassBase):

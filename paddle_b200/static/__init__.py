@@ -150,6 +150,7 @@ def _static_minimize(opt, loss, parameters=None, no_grad_set=None):
         opt.step()
     minimize._needs_grad = True
     minimize._train_only = True
+    minimize._optimizer, minimize._params = opt, params          # program passes rebuild the step from these
     prog._needs_grad = True
     # the example pass must not move the freshly initialised parameters: record without running
     prog.record(minimize, (loss,), {}, None, name="minimize", inplace=True)

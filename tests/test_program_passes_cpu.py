@@ -87,3 +87,34 @@ def test_planner_sees_through_segments():
     wrapped = Completer(main, [2, 2]).annotate("x", [0, -1]).complete_forward_annotation()
     assert [op.name for op in wrapped.dist_ops] == [op.name for op in plain.dist_ops]
     assert wrapped.get_tensor_dist_attr(h2).dims_mapping == [0, -1]
+
+
+def test_gradient_merge_pass_updates_every_k_runs_with_the_mean_gradient():
+    paddle.seed(4)
+    paddle.enable_static()
+    main, start = paddle.static.Program(), paddle.static.Program()
+    with paddle.static.program_guard(main, start):
+        x = paddle.static.data("x", [4, 8], "float32")
+        y = paddle.static.data("y", [4, 1], "float32")
+        lin = nn.Linear(8, 1)
+        loss = F.mse_loss(lin(x), y)
+        paddle.optimizer.SGD(learning_rate=0.1).minimize(loss)
+    paddle.disable_static()
+    new_pass("auto_parallel_gradient_merge", {"k_steps": 2, "avg": True}).apply([main], [start], PassContext())
+    g = torch.Generator().manual_seed(0)
+    batches = [(torch.randn(4, 8, generator=g), torch.randn(4, 1, generator=g)) for _ in range(2)]
+    w0, b0 = torch.from_numpy(lin.weight.numpy().copy()), torch.from_numpy(lin.bias.numpy().copy())
+    grads = []
+    for xb, yb in batches:                                       # the gradients both runs see, at the unchanged weights
+        w, b = w0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+        torch.nn.functional.mse_loss(xb @ w + b, yb).backward()
+        grads.append((w.grad, b.grad))
+    paddle.enable_static()
+    exe = paddle.static.Executor()
+    exe.run(main, feed={"x": batches[0][0].numpy(), "y": batches[0][1].numpy()}, fetch_list=[loss])
+    assert torch.equal(torch.as_tensor(lin.weight.numpy()), w0)                 # nothing moves on the first run
+    exe.run(main, feed={"x": batches[1][0].numpy(), "y": batches[1][1].numpy()}, fetch_list=[loss])
+    want_w = w0 - 0.1 * (grads[0][0] + grads[1][0]) / 2
+    want_b = b0 - 0.1 * (grads[0][1] + grads[1][1]) / 2
+    np.testing.assert_allclose(lin.weight.numpy(), want_w.numpy(), rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(lin.bias.numpy(), want_b.numpy(), rtol=1e-5, atol=1e-6)
